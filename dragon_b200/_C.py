@@ -1,0 +1,99 @@
+"""ctypes binding of the dgn C-ABI (include/dgn.h).
+
+The shared library is the only compute path: if it is missing this module
+raises, there is no fallback.
+"""
+
+import ctypes
+import os
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libdgn.so")
+
+HANDLE_BYTES = 256
+MAX_RANKS = 8
+
+OK, ERR_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_PEER, ERR_STATE, ERR_UNSUPPORTED = range(7)
+
+U8, I8, I32, I64, F16, BF16, F32, F64 = range(8)
+SUM, MEAN, PROD, MIN, MAX = range(5)
+VARIANT_AUTO, VARIANT_ONESHOT, VARIANT_TWOSHOT, VARIANT_NVLS = range(4)
+
+REDOPS = {"SUM": SUM, "MEAN": MEAN, "PROD": PROD, "MIN": MIN, "MAX": MAX}
+
+# Every symbol include/dgn.h declares: name -> (restype, argtypes).
+_c_void_pp = ctypes.POINTER(ctypes.c_void_p)
+_c_i64_p = ctypes.POINTER(ctypes.c_int64)
+_c_int_p = ctypes.POINTER(ctypes.c_int)
+SIGNATURES = {
+    "dgn_version": (ctypes.c_int, []),
+    "dgn_dtype_size": (ctypes.c_size_t, [ctypes.c_int]),
+    "dgn_last_error_string": (ctypes.c_char_p, []),
+    "dgn_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "dgn_comm_init_local": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, _c_void_pp]),
+    "dgn_comm_get_handle": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+    "dgn_comm_connect": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+    "dgn_comm_create": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_char_p,
+                                       ctypes.c_char_p, ctypes.c_int, _c_void_pp]),
+    "dgn_comm_create_emulated": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _c_void_pp]),
+    "dgn_comm_destroy": (ctypes.c_int, [ctypes.c_void_p]),
+    "dgn_comm_rank": (ctypes.c_int, [ctypes.c_void_p]),
+    "dgn_comm_size": (ctypes.c_int, [ctypes.c_void_p]),
+    "dgn_comm_device": (ctypes.c_int, [ctypes.c_void_p]),
+    "dgn_comm_status": (ctypes.c_int, [ctypes.c_void_p]),
+    "dgn_comm_set_wait_limit_ms": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
+    "dgn_comm_set_tuning": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                           ctypes.c_int64]),
+    "dgn_comm_has_nvls": (ctypes.c_int, [ctypes.c_void_p]),
+    "dgn_allreduce": (ctypes.c_int, [ctypes.c_void_p, _c_void_pp, _c_void_pp, _c_i64_p, ctypes.c_int,
+                                     ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "dgn_allgather": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                     ctypes.c_int, ctypes.c_void_p]),
+    "dgn_broadcast": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,
+                                     ctypes.c_int, ctypes.c_void_p]),
+    "dgn_reducescatter": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                         ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "dgn_launch_count": (ctypes.c_int64, []),
+    "dgn_comm_last_launch": (ctypes.c_int, [ctypes.c_void_p, _c_int_p, _c_int_p, _c_int_p, _c_i64_p,
+                                            _c_int_p]),
+}
+
+_lib = None
+
+
+class DgnError(RuntimeError):
+    """A dgn entry point returned a non-OK status."""
+
+    def __init__(self, status, message):
+        super().__init__("dgn status {} ({}): {}".format(status, _status_name(status), message))
+        self.status = status
+
+
+def _status_name(status):
+    names = ["OK", "ERR_ARG", "ERR_CUDA", "ERR_TIMEOUT", "ERR_PEER", "ERR_STATE", "ERR_UNSUPPORTED"]
+    return names[status] if 0 <= status < len(names) else "?"
+
+
+def lib_path():
+    return _LIB_PATH
+
+
+def lib():
+    """Load libdgn.so once; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError(
+                "{} is missing: build it with `python -m dragon_b200.build` "
+                "(there is no fallback path)".format(_LIB_PATH))
+        handle = ctypes.CDLL(_LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def check(status):
+    if status != OK:
+        raise DgnError(status, lib().dgn_last_error_string().decode("utf-8", "replace"))

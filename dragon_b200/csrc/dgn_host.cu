@@ -1,0 +1,980 @@
+// Host side of the dgn C-ABI: communicator bootstrap (symmetric workspace,
+// handle exchange, peer mapping), launch planning and the collective entry
+// points declared in include/dgn.h.
+//
+// The reference reaches its collectives through CollectiveOpImpl
+// (dragon/operators/distributed/collective_op_impl.h:22-158), which forwards
+// to MPI_* or nccl* library calls; here each entry point plans and launches
+// exactly one hand-written kernel (dgn_kernels.cuh) on the caller's stream.
+#include <cuda_runtime.h>
+
+#include <dirent.h>
+#include <errno.h>
+#include <fcntl.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/stat.h>
+#include <time.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <string>
+#include <vector>
+
+#include "../../include/dgn.h"
+#include "dgn_kernels.cuh"
+
+namespace dgn {
+// Defined in the per-dtype instantiation units.
+const void* reduce_kernel_fn_0(int, bool);
+const void* reduce_kernel_fn_1(int, bool);
+const void* reduce_kernel_fn_2(int, bool);
+const void* reduce_kernel_fn_3(int, bool);
+const void* reduce_kernel_fn_4(int, bool);
+const void* reduce_kernel_fn_5(int, bool);
+const void* reduce_kernel_fn_6(int, bool);
+const void* reduce_kernel_fn_7(int, bool);
+const void* allgather_kernel_fn();
+const void* broadcast_kernel_fn();
+const void* local_copy_kernel_fn(int es, bool table);
+}  // namespace dgn
+
+using namespace dgn;
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<long long> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define DGN_CUDA(expr)                                                              \
+  do {                                                                              \
+    cudaError_t e__ = (expr);                                                       \
+    if (e__ != cudaSuccess)                                                         \
+      return fail(DGN_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), \
+                  __FILE__, __LINE__);                                              \
+  } while (0)
+
+const size_t kElemSize[8] = {1, 1, 4, 8, 2, 2, 4, 8};
+
+long long env_ll(const char* name, long long dflt) {
+  const char* s = getenv(name);
+  if (!s || !*s) return dflt;
+  char* end = nullptr;
+  long long v = strtoll(s, &end, 10);
+  return (end && *end == '\0') ? v : dflt;
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) switched = cudaSetDevice(dev) == cudaSuccess;
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+constexpr uint32_t kMagic = 0x44474e31u;  // "DGN1"
+
+struct Handle {  // what one rank tells the others; padded to DGN_HANDLE_BYTES
+  uint32_t magic, version;
+  int32_t pid, device, rank, nranks, max_blocks, pad;
+  int64_t slot_bytes;
+  uint64_t total_bytes;
+  uint64_t base_ptr;
+  uint64_t host_id;
+  cudaIpcMemHandle_t ipc;
+};
+static_assert(sizeof(Handle) <= DGN_HANDLE_BYTES, "handle too large");
+
+uint64_t host_identity() {
+  uint64_t h = 1469598103934665603ull;
+  auto mix = [&](const char* s) {
+    for (; *s; ++s) h = (h ^ (unsigned char)*s) * 1099511628211ull;
+  };
+  char buf[256] = "";
+  gethostname(buf, sizeof(buf) - 1);
+  mix(buf);
+  FILE* f = fopen("/proc/sys/kernel/random/boot_id", "r");
+  if (f) {
+    if (fgets(buf, sizeof(buf), f)) mix(buf);
+    fclose(f);
+  }
+  return h;
+}
+
+struct Geometry {
+  int nranks = 1, max_blocks = 0;
+  long long slot_bytes = 0;
+  size_t flags_bytes = 0, last_off = 0, stage_off = 0, total = 0;
+};
+
+Geometry make_geometry(int nranks) {
+  Geometry g;
+  g.nranks = nranks;
+  g.max_blocks = (int)env_ll("DGN_MAX_BLOCKS", 128);
+  if (g.max_blocks < 1) g.max_blocks = 1;
+  if (g.max_blocks > 1024) g.max_blocks = 1024;
+  g.slot_bytes = env_ll("DGN_SLOT_BYTES", 64 * 1024);
+  if (g.slot_bytes < 4096) g.slot_bytes = 4096;
+  g.slot_bytes = (g.slot_bytes + 4095) & ~4095ll;
+  g.flags_bytes = (size_t)g.max_blocks * kMaxRanks * sizeof(u64);
+  g.last_off = g.flags_bytes;
+  size_t head = g.last_off + 2 * (size_t)g.max_blocks * sizeof(u64);
+  g.stage_off = (head + 4095) & ~(size_t)4095;
+  g.total = g.stage_off + 2 * (size_t)g.max_blocks * (size_t)(nranks + 1) * (size_t)g.slot_bytes;
+  return g;
+}
+
+struct TableEntry {
+  std::vector<const void*> in;
+  std::vector<void*> out;
+  std::vector<int64_t> counts;
+  int es = 0;
+  TensorEnt* d_table = nullptr;
+  TensorEnt* h_table = nullptr;  // pinned
+  int nt = 0;                    // non-empty tensors
+  long long nvec = 0;
+  uint64_t last_use = 0;
+};
+
+struct Plan {
+  int variant = 0, blocks = 1, threads = 512, cv = 1, rounds = 1;
+  u64 span = 2;
+};
+
+enum OpKind { kOpAllReduce = 0, kOpReduceScatter, kOpAllGather, kOpBroadcast };
+
+struct OpDesc {
+  int kind = 0, dtype = 0, redop = 0, root = 0, ntensors = 1;
+  long long count = 0;  // elements (AR single / RS per-rank block) or bytes (AG / BC)
+  long long nvec = 0;
+  const void* in = nullptr;
+  void* out = nullptr;
+  const TensorEnt* table = nullptr;
+  cudaStream_t stream = nullptr;
+};
+
+struct Team;
+
+}  // namespace
+
+struct dgn_comm {
+  int rank = 0, nranks = 1, device = 0, num_sms = 148;
+  Geometry geo;
+  void* base = nullptr;  // workspace
+  int* status_host = nullptr;
+  int* status_dev = nullptr;
+  void* peer_base[kMaxRanks] = {};
+  bool peer_ipc[kMaxRanks] = {};
+  PeerTable* d_peers = nullptr;
+  bool connected = false;
+  u64 epoch = 0, opcount = 0;
+  u64 wait_ns = 5000000000ull;
+  int tune_variant = 0, tune_blocks = 0, tune_threads = 0;
+  long long tune_chunk = 0;
+  long long oneshot_max_bytes = -1;
+  Team* team = nullptr;
+  std::vector<TableEntry> tables;
+  uint64_t table_clock = 0;
+  Plan last_plan;
+  std::string rdv_ok_file;
+};
+
+namespace {
+
+struct Team {
+  int n = 0, device = 0;
+  std::vector<dgn_comm*> members;
+  PeerTable* d_tables = nullptr;
+  u64 epoch = 0, opcount = 0;
+  OpDesc pending[kMaxRanks];
+  unsigned arrived = 0;
+  int alive = 0;
+};
+
+int alloc_workspace(dgn_comm* c) {
+  DeviceGuard g(c->device);
+  DGN_CUDA(cudaMalloc(&c->base, c->geo.total));
+  DGN_CUDA(cudaMemset(c->base, 0, c->geo.stage_off));
+  DGN_CUDA(cudaHostAlloc((void**)&c->status_host, 64, cudaHostAllocMapped | cudaHostAllocPortable));
+  *c->status_host = 0;
+  DGN_CUDA(cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0));
+  DGN_CUDA(cudaDeviceSynchronize());
+  cudaDeviceProp prop;
+  DGN_CUDA(cudaGetDeviceProperties(&prop, c->device));
+  c->num_sms = prop.multiProcessorCount;
+  return DGN_OK;
+}
+
+void fill_peer_table(const dgn_comm* c, PeerTable* t) {
+  memset(t, 0, sizeof(*t));
+  for (int j = 0; j < c->nranks; ++j) {
+    char* b = static_cast<char*>(c->peer_base[j]);
+    t->flags[j] = reinterpret_cast<u64*>(b);
+    t->stage[j] = b + c->geo.stage_off;
+  }
+  t->last_epoch = reinterpret_cast<u64*>(static_cast<char*>(c->base) + c->geo.last_off);
+  t->status = c->status_dev;
+  t->rank = c->rank;
+  t->nranks = c->nranks;
+  t->max_blocks = c->geo.max_blocks;
+  t->slot_bytes = c->geo.slot_bytes;
+}
+
+const void* reduce_fn(int dtype, int kind, bool table) {
+  switch (dtype) {
+    case DGN_U8: return reduce_kernel_fn_0(kind, table);
+    case DGN_I8: return reduce_kernel_fn_1(kind, table);
+    case DGN_I32: return reduce_kernel_fn_2(kind, table);
+    case DGN_I64: return reduce_kernel_fn_3(kind, table);
+    case DGN_F16: return reduce_kernel_fn_4(kind, table);
+    case DGN_BF16: return reduce_kernel_fn_5(kind, table);
+    case DGN_F32: return reduce_kernel_fn_6(kind, table);
+    case DGN_F64: return reduce_kernel_fn_7(kind, table);
+    default: return nullptr;
+  }
+}
+
+long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
+
+long long default_oneshot_max(int n) {
+  // Above these sizes the (n - 1)x link traffic of one-shot costs more than
+  // the second flag exchange of two-shot.
+  if (n <= 2) return 1ll << 20;
+  if (n <= 4) return 512ll << 10;
+  return 256ll << 10;
+}
+
+// Chooses variant and launch shape.  `block_cap` bounds the grid (cooperative
+// launches must be fully resident).
+Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
+  Plan p;
+  const int n = c->nranks;
+  const long long slot_vecs = c->geo.slot_bytes / 16;
+  int bmax = c->geo.max_blocks;
+  if (block_cap > 0 && block_cap < bmax) bmax = block_cap;
+  if (c->tune_blocks > 0 && c->tune_blocks < bmax) bmax = c->tune_blocks;
+  if (bmax < 1) bmax = 1;
+  p.threads = c->tune_threads > 0 ? c->tune_threads : 512;
+  if (p.threads > 512) p.threads = 512;
+  if (p.threads < 32) p.threads = 32;
+  p.threads = (p.threads / 32) * 32;
+  long long cv_cap = slot_vecs;
+  if (c->tune_chunk >= 16 && c->tune_chunk / 16 < cv_cap) cv_cap = c->tune_chunk / 16;
+
+  if (d.kind == kOpAllReduce) {
+    const long long bytes = d.nvec * 16;
+    const long long thr = c->oneshot_max_bytes >= 0 ? c->oneshot_max_bytes : default_oneshot_max(n);
+    bool oneshot = bytes <= thr;
+    if (c->tune_variant == DGN_VARIANT_ONESHOT) oneshot = true;
+    if (c->tune_variant == DGN_VARIANT_TWOSHOT) oneshot = false;
+    if (oneshot && ceil_div(d.nvec, bmax) > slot_vecs) oneshot = false;  // does not fit one round
+    if (oneshot) {
+      p.variant = DGN_VARIANT_ONESHOT;
+      long long b = ceil_div(d.nvec, 512);
+      if (c->tune_blocks > 0) b = c->tune_blocks;
+      if (b > bmax) b = bmax;
+      if (b < 1) b = 1;
+      if (ceil_div(d.nvec, b) > slot_vecs) b = ceil_div(d.nvec, slot_vecs);
+      p.blocks = (int)b;
+      p.cv = (int)ceil_div(d.nvec, b);
+      p.rounds = 1;
+      p.span = 2;
+      return p;
+    }
+  }
+  // Multi-round kernels: two-shot all-reduce, reduce-scatter, all-gather,
+  // broadcast.  `per` = vectors each block column has to cover.
+  long long per = d.nvec;
+  if (d.kind == kOpAllReduce) per = ceil_div(d.nvec, n);
+  p.variant = DGN_VARIANT_TWOSHOT;
+  int bdef = bmax < 64 ? bmax : 64;
+  if (c->tune_blocks > 0) bdef = bmax;
+  long long b = ceil_div(per, 512);
+  if (b > bdef) b = bdef;
+  if (b < 1) b = 1;
+  long long cv = ceil_div(per, b);
+  if (cv > cv_cap) cv = cv_cap;
+  if (cv < 1) cv = 1;
+  p.blocks = (int)b;
+  p.cv = (int)cv;
+  p.rounds = (int)ceil_div(per, b * cv);
+  if (p.rounds < 1) p.rounds = 1;
+  p.span = 2 * (u64)p.rounds + 1;
+  return p;
+}
+
+struct KernelChoice {
+  const void* fn = nullptr;
+  size_t smem = 0;
+};
+
+KernelChoice choose_kernel(const OpDesc& d, const Plan& p) {
+  KernelChoice k;
+  const bool table = d.ntensors > 1;
+  switch (d.kind) {
+    case kOpAllReduce:
+      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_ONESHOT ? 0 : 1, table);
+      k.smem = table ? table_smem_bytes(d.ntensors) : 0;
+      break;
+    case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
+    case kOpAllGather: k.fn = allgather_kernel_fn(); break;
+    case kOpBroadcast: k.fn = broadcast_kernel_fn(); break;
+  }
+  return k;
+}
+
+void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p, u64 epoch,
+                 u64 opcount) {
+  memset(P, 0, sizeof(*P));
+  P->count = d.count;
+  P->nvec = d.nvec;
+  P->epoch = epoch;
+  P->wait_ns = c->wait_ns;
+  P->scale = (double)(1.f / (float)c->nranks);
+  P->ntensors = d.ntensors;
+  P->parity = (int)(opcount & 1);
+  P->rounds = p.rounds;
+  P->cv = p.cv;
+  P->redop = d.redop;
+  P->root = d.root;
+}
+
+int launch(const void* fn, dim3 grid, int threads, size_t smem, cudaStream_t stream, OpParams* P,
+           bool cooperative) {
+  void* args[1] = {P};
+  cudaError_t e = cooperative
+                      ? cudaLaunchCooperativeKernel(fn, grid, dim3(threads), args, smem, stream)
+                      : cudaLaunchKernel(fn, grid, dim3(threads), args, smem, stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(DGN_ERR_CUDA, "kernel launch failed: %s (grid %u x %u, %d threads, %zu B smem)",
+                cudaGetErrorString(e), grid.x, grid.y, threads, smem);
+  }
+  g_launches.fetch_add(1);
+  return DGN_OK;
+}
+
+int check_ready(dgn_comm* c) {
+  if (!c) return fail(DGN_ERR_ARG, "null communicator");
+  if (!c->connected) return fail(DGN_ERR_STATE, "communicator is not connected");
+  if (c->status_host && *c->status_host != 0)
+    return fail(DGN_ERR_STATE, "communicator is unusable: an earlier collective reported status %d (%s)",
+                *c->status_host, dgn_status_string(*c->status_host));
+  return DGN_OK;
+}
+
+// Issues one multi-rank collective: directly for a real rank, or once every
+// virtual rank of an emulated team has arrived.
+int issue(dgn_comm* c, const OpDesc& d) {
+  DeviceGuard g(c->device);
+  if (!c->team) {
+    Plan p = make_plan(c, d, 0);
+    KernelChoice k = choose_kernel(d, p);
+    if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
+    OpParams P;
+    fill_params(&P, c, d, p, c->epoch, c->opcount);
+    P.peers = c->d_peers;
+    P.ra[0].in = d.in;
+    P.ra[0].out = d.out;
+    P.ra[0].table = d.table;
+    int rc = launch(k.fn, dim3(p.blocks, 1), p.threads, k.smem, d.stream, &P, false);
+    if (rc != DGN_OK) return rc;
+    c->epoch += p.span;
+    c->opcount += 1;
+    c->last_plan = p;
+    return DGN_OK;
+  }
+  Team* t = c->team;
+  if (t->arrived & (1u << c->rank)) {
+    t->arrived = 0;
+    return fail(DGN_ERR_STATE, "virtual rank %d issued a second collective before the others arrived", c->rank);
+  }
+  if (t->arrived) {
+    int first = 0;
+    while (!(t->arrived & (1u << first))) ++first;
+    const OpDesc& f = t->pending[first];
+    if (f.kind != d.kind || f.dtype != d.dtype || f.redop != d.redop || f.root != d.root ||
+        f.count != d.count || f.nvec != d.nvec || f.ntensors != d.ntensors || f.stream != d.stream) {
+      t->arrived = 0;
+      return fail(DGN_ERR_ARG, "virtual rank %d issued a collective that differs from rank %d's", c->rank, first);
+    }
+  }
+  t->pending[c->rank] = d;
+  t->arrived |= 1u << c->rank;
+  if (t->arrived != (1u << t->n) - 1u) return DGN_OK;
+  t->arrived = 0;
+
+  // Shape the launch so that every block of every virtual rank is resident.
+  Plan p = make_plan(c, d, 0);
+  KernelChoice k = choose_kernel(d, p);
+  if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
+  int per_sm = 0;
+  DGN_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k.fn, p.threads, k.smem));
+  int cap = per_sm * c->num_sms / t->n;
+  if (cap < 1) return fail(DGN_ERR_UNSUPPORTED, "emulated team does not fit on the device");
+  if (p.blocks > cap) {
+    p = make_plan(c, d, cap);
+    k = choose_kernel(d, p);
+  }
+  OpParams P;
+  fill_params(&P, c, d, p, t->epoch, t->opcount);
+  P.peers = t->d_tables;
+  for (int r = 0; r < t->n; ++r) {
+    P.ra[r].in = t->pending[r].in;
+    P.ra[r].out = t->pending[r].out;
+    P.ra[r].table = t->pending[r].table;
+  }
+  int rc = launch(k.fn, dim3(p.blocks, t->n), p.threads, k.smem, d.stream, &P, true);
+  if (rc != DGN_OK) return rc;
+  t->epoch += p.span;
+  t->opcount += 1;
+  for (dgn_comm* m : t->members) m->last_plan = p;
+  return DGN_OK;
+}
+
+int launch_local_copy(dgn_comm* c, const OpDesc& d, int es) {
+  DeviceGuard g(c->device);
+  const bool table = d.ntensors > 1;
+  const void* fn = local_copy_kernel_fn(es, table);
+  if (!fn) return fail(DGN_ERR_UNSUPPORTED, "no copy kernel for element size %d", es);
+  Plan p;
+  p.threads = c->tune_threads > 0 ? c->tune_threads : 512;
+  if (p.threads > 512) p.threads = 512;
+  long long b = ceil_div(d.nvec, (long long)p.threads * 4);
+  const long long cap = c->tune_blocks > 0 ? c->tune_blocks : (long long)c->num_sms * 4;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  p.blocks = (int)b;
+  p.variant = 0;
+  OpParams P;
+  fill_params(&P, c, d, p, 0, 0);
+  P.ra[0].in = d.in;
+  P.ra[0].out = d.out;
+  P.ra[0].table = d.table;
+  int rc = launch(fn, dim3(p.blocks, 1), p.threads, table ? table_smem_bytes(d.ntensors) : 0,
+                  d.stream, &P, false);
+  if (rc == DGN_OK) c->last_plan = p;
+  return rc;
+}
+
+// Device table for a bucket of tensors, cached on the tensor list (the same
+// gradients come back every step).
+int get_table(dgn_comm* c, const void* const* in, void* const* out, const int64_t* counts, int nt,
+              int es, cudaStream_t stream, const TableEntry** result) {
+  for (TableEntry& e : c->tables) {
+    if (e.es == es && (int)e.in.size() == nt && memcmp(e.in.data(), in, sizeof(void*) * nt) == 0 &&
+        memcmp(e.out.data(), out, sizeof(void*) * nt) == 0 &&
+        memcmp(e.counts.data(), counts, sizeof(int64_t) * nt) == 0) {
+      e.last_use = ++c->table_clock;
+      *result = &e;
+      return DGN_OK;
+    }
+  }
+  if (c->tables.size() >= 32) {  // evict the least recently used entry
+    size_t lru = 0;
+    for (size_t i = 1; i < c->tables.size(); ++i)
+      if (c->tables[i].last_use < c->tables[lru].last_use) lru = i;
+    cudaFree(c->tables[lru].d_table);  // synchronises with any kernel still reading it
+    cudaFreeHost(c->tables[lru].h_table);
+    c->tables.erase(c->tables.begin() + lru);
+  }
+  TableEntry e;
+  e.es = es;
+  e.in.assign(in, in + nt);
+  e.out.assign(out, out + nt);
+  e.counts.assign(counts, counts + nt);
+  DGN_CUDA(cudaHostAlloc((void**)&e.h_table, sizeof(TensorEnt) * (size_t)(nt + 1), cudaHostAllocDefault));
+  long long v = 0;
+  int k = 0;
+  for (int i = 0; i < nt; ++i) {
+    if (counts[i] == 0) continue;
+    e.h_table[k].in = static_cast<const char*>(in[i]);
+    e.h_table[k].out = static_cast<char*>(out[i]);
+    e.h_table[k].count = counts[i];
+    e.h_table[k].vbegin = v;
+    v += ceil_div(counts[i] * es, 16);
+    ++k;
+  }
+  e.nt = k;
+  e.nvec = v;
+  DGN_CUDA(cudaMalloc((void**)&e.d_table, sizeof(TensorEnt) * (size_t)(nt + 1)));
+  DGN_CUDA(cudaMemcpyAsync(e.d_table, e.h_table, sizeof(TensorEnt) * (size_t)k, cudaMemcpyHostToDevice, stream));
+  e.last_use = ++c->table_clock;
+  c->tables.push_back(std::move(e));
+  *result = &c->tables.back();
+  return DGN_OK;
+}
+
+void free_comm(dgn_comm* c) {
+  DeviceGuard g(c->device);
+  cudaDeviceSynchronize();
+  for (TableEntry& e : c->tables) {
+    cudaFree(e.d_table);
+    cudaFreeHost(e.h_table);
+  }
+  for (int j = 0; j < c->nranks; ++j)
+    if (j != c->rank && c->peer_ipc[j] && c->peer_base[j]) cudaIpcCloseMemHandle(c->peer_base[j]);
+  if (!c->team && c->d_peers) cudaFree(c->d_peers);
+  if (c->base) cudaFree(c->base);
+  if (c->status_host) cudaFreeHost(c->status_host);
+  if (!c->rdv_ok_file.empty()) unlink(c->rdv_ok_file.c_str());
+  delete c;
+}
+
+bool write_file_atomic(const std::string& path, const void* data, size_t n) {
+  std::string tmp = path + ".tmp";
+  FILE* f = fopen(tmp.c_str(), "wb");
+  if (!f) return false;
+  bool ok = fwrite(data, 1, n, f) == n;
+  ok = (fclose(f) == 0) && ok;
+  if (ok) ok = rename(tmp.c_str(), path.c_str()) == 0;
+  return ok;
+}
+
+bool read_file_exact(const std::string& path, void* data, size_t n) {
+  FILE* f = fopen(path.c_str(), "rb");
+  if (!f) return false;
+  bool ok = fread(data, 1, n, f) == n;
+  fclose(f);
+  return ok;
+}
+
+double now_s() {
+  struct timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return (double)ts.tv_sec + 1e-9 * (double)ts.tv_nsec;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// C-ABI
+
+extern "C" {
+
+int dgn_version(void) { return 100; }
+
+size_t dgn_dtype_size(int dtype) { return (dtype >= 0 && dtype < 8) ? kElemSize[dtype] : 0; }
+
+const char* dgn_last_error_string(void) { return g_err; }
+
+const char* dgn_status_string(int status) {
+  switch (status) {
+    case DGN_OK: return "ok";
+    case DGN_ERR_ARG: return "invalid argument";
+    case DGN_ERR_CUDA: return "CUDA error";
+    case DGN_ERR_TIMEOUT: return "timed out waiting for a peer";
+    case DGN_ERR_PEER: return "peer not reachable";
+    case DGN_ERR_STATE: return "invalid state";
+    case DGN_ERR_UNSUPPORTED: return "unsupported";
+    default: return "unknown status";
+  }
+}
+
+int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
+  if (!comm) return fail(DGN_ERR_ARG, "comm is null");
+  *comm = nullptr;
+  if (nranks < 1 || nranks > DGN_MAX_RANKS) return fail(DGN_ERR_ARG, "nranks %d outside 1..%d", nranks, DGN_MAX_RANKS);
+  if (rank < 0 || rank >= nranks) return fail(DGN_ERR_ARG, "rank %d outside 0..%d", rank, nranks - 1);
+  int ndev = 0;
+  DGN_CUDA(cudaGetDeviceCount(&ndev));
+  if (device < 0 || device >= ndev) return fail(DGN_ERR_ARG, "device %d outside 0..%d", device, ndev - 1);
+  dgn_comm* c = new dgn_comm();
+  c->rank = rank;
+  c->nranks = nranks;
+  c->device = device;
+  c->geo = make_geometry(nranks);
+  c->wait_ns = (u64)env_ll("DGN_WAIT_LIMIT_MS", 5000) * 1000000ull;
+  c->oneshot_max_bytes = env_ll("DGN_ONESHOT_MAX_BYTES", -1);
+  c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
+  int rc = alloc_workspace(c);
+  if (rc != DGN_OK) {
+    free_comm(c);
+    return rc;
+  }
+  if (nranks == 1) {
+    c->peer_base[0] = c->base;
+    c->connected = true;
+  }
+  *comm = c;
+  return DGN_OK;
+}
+
+int dgn_comm_get_handle(dgn_comm_t c, void* handle) {
+  if (!c || !handle) return fail(DGN_ERR_ARG, "null argument");
+  DeviceGuard g(c->device);
+  Handle h;
+  memset(&h, 0, sizeof(h));
+  h.magic = kMagic;
+  h.version = (uint32_t)dgn_version();
+  h.pid = (int32_t)getpid();
+  h.device = c->device;
+  h.rank = c->rank;
+  h.nranks = c->nranks;
+  h.max_blocks = c->geo.max_blocks;
+  h.slot_bytes = c->geo.slot_bytes;
+  h.total_bytes = c->geo.total;
+  h.base_ptr = (uint64_t)(uintptr_t)c->base;
+  h.host_id = host_identity();
+  DGN_CUDA(cudaIpcGetMemHandle(&h.ipc, c->base));
+  memset(handle, 0, DGN_HANDLE_BYTES);
+  memcpy(handle, &h, sizeof(h));
+  return DGN_OK;
+}
+
+int dgn_comm_connect(dgn_comm_t c, const void* all_handles) {
+  if (!c || !all_handles) return fail(DGN_ERR_ARG, "null argument");
+  if (c->team) return fail(DGN_ERR_STATE, "emulated communicators are connected at creation");
+  if (c->connected && c->nranks > 1) return fail(DGN_ERR_STATE, "already connected");
+  DeviceGuard g(c->device);
+  const uint64_t me_host = host_identity();
+  const int32_t me_pid = (int32_t)getpid();
+  for (int j = 0; j < c->nranks; ++j) {
+    Handle h;
+    memcpy(&h, static_cast<const char*>(all_handles) + (size_t)j * DGN_HANDLE_BYTES, sizeof(h));
+    if (h.magic != kMagic || h.version != (uint32_t)dgn_version())
+      return fail(DGN_ERR_ARG, "handle %d is not a dgn handle of this version", j);
+    if (h.rank != j || h.nranks != c->nranks)
+      return fail(DGN_ERR_ARG, "handle %d describes rank %d of %d", j, h.rank, h.nranks);
+    if (h.max_blocks != c->geo.max_blocks || h.slot_bytes != c->geo.slot_bytes || h.total_bytes != c->geo.total)
+      return fail(DGN_ERR_ARG, "rank %d uses a different workspace geometry", j);
+    if (h.host_id != me_host) return fail(DGN_ERR_PEER, "rank %d is on another host", j);
+    if (j == c->rank) {
+      c->peer_base[j] = c->base;
+      continue;
+    }
+    if (h.device != c->device) {
+      int can = 0;
+      DGN_CUDA(cudaDeviceCanAccessPeer(&can, c->device, h.device));
+      if (!can) return fail(DGN_ERR_PEER, "device %d cannot access device %d of rank %d", c->device, h.device, j);
+    }
+    if (h.pid == me_pid) {
+      if (h.device != c->device) {
+        cudaError_t e = cudaDeviceEnablePeerAccess(h.device, 0);
+        if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled)
+          return fail(DGN_ERR_PEER, "cudaDeviceEnablePeerAccess(%d): %s", h.device, cudaGetErrorString(e));
+        cudaGetLastError();
+      }
+      c->peer_base[j] = (void*)(uintptr_t)h.base_ptr;
+      c->peer_ipc[j] = false;
+    } else {
+      void* p = nullptr;
+      cudaError_t e = cudaIpcOpenMemHandle(&p, h.ipc, cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(DGN_ERR_PEER, "cudaIpcOpenMemHandle for rank %d: %s", j, cudaGetErrorString(e));
+      }
+      c->peer_base[j] = p;
+      c->peer_ipc[j] = true;
+    }
+  }
+  PeerTable t;
+  fill_peer_table(c, &t);
+  if (!c->d_peers) DGN_CUDA(cudaMalloc((void**)&c->d_peers, sizeof(PeerTable)));
+  DGN_CUDA(cudaMemcpy(c->d_peers, &t, sizeof(t), cudaMemcpyHostToDevice));
+  c->connected = true;
+  return DGN_OK;
+}
+
+int dgn_comm_create(int rank, int nranks, int device, const char* rendezvous_dir, const char* tag,
+                    int timeout_ms, dgn_comm_t* comm) {
+  if (!comm) return fail(DGN_ERR_ARG, "comm is null");
+  *comm = nullptr;
+  if (nranks > 1 && (!rendezvous_dir || !tag || !*tag)) return fail(DGN_ERR_ARG, "rendezvous_dir and tag are required");
+  dgn_comm* c = nullptr;
+  int rc = dgn_comm_init_local(rank, nranks, device, &c);
+  if (rc != DGN_OK) return rc;
+  if (nranks == 1) {
+    *comm = c;
+    return DGN_OK;
+  }
+  std::string dir(rendezvous_dir);
+  mkdir(dir.c_str(), 0777);
+  auto name = [&](int r, const char* suffix) {
+    return dir + "/" + tag + "." + std::to_string(r) + suffix;
+  };
+  char mine[DGN_HANDLE_BYTES];
+  rc = dgn_comm_get_handle(c, mine);
+  if (rc != DGN_OK) {
+    free_comm(c);
+    return rc;
+  }
+  if (!write_file_atomic(name(rank, ".h"), mine, sizeof(mine))) {
+    free_comm(c);
+    return fail(DGN_ERR_ARG, "cannot write rendezvous file in %s: %s", rendezvous_dir, strerror(errno));
+  }
+  std::vector<char> all((size_t)nranks * DGN_HANDLE_BYTES);
+  const double deadline = now_s() + 1e-3 * (timeout_ms > 0 ? timeout_ms : 60000);
+  for (int r = 0; r < nranks; ++r) {
+    while (!read_file_exact(name(r, ".h"), all.data() + (size_t)r * DGN_HANDLE_BYTES, DGN_HANDLE_BYTES)) {
+      if (now_s() > deadline) {
+        unlink(name(rank, ".h").c_str());
+        free_comm(c);
+        return fail(DGN_ERR_TIMEOUT, "rank %d never arrived at rendezvous '%s'", r, tag);
+      }
+      usleep(500);
+    }
+  }
+  rc = dgn_comm_connect(c, all.data());
+  if (rc != DGN_OK) {
+    unlink(name(rank, ".h").c_str());
+    free_comm(c);
+    return rc;
+  }
+  // Second phase: nobody removes its handle file before everyone has read it.
+  char one = 1;
+  write_file_atomic(name(rank, ".ok"), &one, 1);
+  for (int r = 0; r < nranks; ++r) {
+    char b;
+    while (!read_file_exact(name(r, ".ok"), &b, 1)) {
+      if (now_s() > deadline) {
+        free_comm(c);
+        return fail(DGN_ERR_TIMEOUT, "rank %d never finished rendezvous '%s'", r, tag);
+      }
+      usleep(500);
+    }
+  }
+  unlink(name(rank, ".h").c_str());
+  c->rdv_ok_file = name(rank, ".ok");
+  *comm = c;
+  return DGN_OK;
+}
+
+int dgn_comm_create_emulated(int nranks, int device, dgn_comm_t* comms) {
+  if (!comms) return fail(DGN_ERR_ARG, "comms is null");
+  if (nranks < 1 || nranks > DGN_MAX_RANKS) return fail(DGN_ERR_ARG, "nranks %d outside 1..%d", nranks, DGN_MAX_RANKS);
+  Team* t = new Team();
+  t->n = nranks;
+  t->device = device;
+  for (int r = 0; r < nranks; ++r) {
+    dgn_comm* c = nullptr;
+    int rc = dgn_comm_init_local(r, nranks, device, &c);
+    if (rc != DGN_OK) {
+      for (dgn_comm* m : t->members) free_comm(m);
+      delete t;
+      return rc;
+    }
+    c->team = t;
+    t->members.push_back(c);
+  }
+  DeviceGuard g(device);
+  std::vector<PeerTable> host(nranks);
+  for (int r = 0; r < nranks; ++r) {
+    dgn_comm* c = t->members[r];
+    for (int j = 0; j < nranks; ++j) c->peer_base[j] = t->members[j]->base;
+    fill_peer_table(c, &host[r]);
+  }
+  DGN_CUDA(cudaMalloc((void**)&t->d_tables, sizeof(PeerTable) * nranks));
+  DGN_CUDA(cudaMemcpy(t->d_tables, host.data(), sizeof(PeerTable) * nranks, cudaMemcpyHostToDevice));
+  t->alive = nranks;
+  for (int r = 0; r < nranks; ++r) {
+    t->members[r]->d_peers = t->d_tables;
+    t->members[r]->connected = true;
+    comms[r] = t->members[r];
+  }
+  return DGN_OK;
+}
+
+int dgn_comm_destroy(dgn_comm_t c) {
+  if (!c) return DGN_OK;
+  Team* t = c->team;
+  if (t) {
+    for (auto& m : t->members)
+      if (m == c) m = nullptr;
+    if (--t->alive == 0) {
+      DeviceGuard g(t->device);
+      cudaDeviceSynchronize();
+      cudaFree(t->d_tables);
+      delete t;
+    }
+  }
+  free_comm(c);
+  return DGN_OK;
+}
+
+int dgn_comm_rank(dgn_comm_t c) { return c ? c->rank : -1; }
+int dgn_comm_size(dgn_comm_t c) { return c ? c->nranks : 0; }
+int dgn_comm_device(dgn_comm_t c) { return c ? c->device : -1; }
+int dgn_comm_status(dgn_comm_t c) { return (c && c->status_host) ? *(volatile int*)c->status_host : DGN_ERR_ARG; }
+
+int dgn_comm_set_wait_limit_ms(dgn_comm_t c, int ms) {
+  if (!c || ms < 1) return fail(DGN_ERR_ARG, "bad wait limit");
+  c->wait_ns = (u64)ms * 1000000ull;
+  return DGN_OK;
+}
+
+int dgn_comm_set_tuning(dgn_comm_t c, int variant, int blocks, int threads, int64_t chunk_bytes) {
+  if (!c) return fail(DGN_ERR_ARG, "null communicator");
+  if (variant < 0 || variant > DGN_VARIANT_NVLS || blocks < 0 || threads < 0 || chunk_bytes < 0)
+    return fail(DGN_ERR_ARG, "bad tuning value");
+  if (variant == DGN_VARIANT_NVLS) return fail(DGN_ERR_UNSUPPORTED, "the NVLS variant is not set up on this communicator");
+  c->tune_variant = variant;
+  c->tune_blocks = blocks;
+  c->tune_threads = threads;
+  c->tune_chunk = chunk_bytes;
+  return DGN_OK;
+}
+
+int dgn_comm_has_nvls(dgn_comm_t) { return 0; }
+
+int dgn_allreduce(dgn_comm_t c, const void* const* in_ptrs, void* const* out_ptrs,
+                  const int64_t* counts, int ntensors, int dtype, int redop, void* stream) {
+  int rc = check_ready(c);
+  if (rc != DGN_OK) return rc;
+  if (ntensors < 0 || (ntensors > 0 && (!in_ptrs || !out_ptrs || !counts)))
+    return fail(DGN_ERR_ARG, "null tensor list");
+  const size_t es = dgn_dtype_size(dtype);
+  if (es == 0) return fail(DGN_ERR_ARG, "unknown dtype %d", dtype);
+  if (redop < DGN_SUM || redop > DGN_MAX) return fail(DGN_ERR_ARG, "unknown reduction %d", redop);
+  if (redop == DGN_MEAN && dtype <= DGN_I64)
+    return fail(DGN_ERR_UNSUPPORTED, "MEAN is defined for floating-point types only");
+  long long total = 0;
+  for (int i = 0; i < ntensors; ++i) {
+    if (counts[i] < 0) return fail(DGN_ERR_ARG, "negative count for tensor %d", i);
+    if (counts[i] > 0 && (!in_ptrs[i] || !out_ptrs[i])) return fail(DGN_ERR_ARG, "null pointer for tensor %d", i);
+    total += counts[i];
+  }
+  if (total == 0) return DGN_OK;
+  if (ntensors > kMaxTableTensors) {  // more entries than one launch takes
+    for (int i = 0; i < ntensors; i += kMaxTableTensors) {
+      const int m = ntensors - i < kMaxTableTensors ? ntensors - i : kMaxTableTensors;
+      rc = dgn_allreduce(c, in_ptrs + i, out_ptrs + i, counts + i, m, dtype, redop, stream);
+      if (rc != DGN_OK) return rc;
+    }
+    return DGN_OK;
+  }
+  OpDesc d;
+  d.kind = kOpAllReduce;
+  d.dtype = dtype;
+  d.redop = redop;
+  d.stream = static_cast<cudaStream_t>(stream);
+  // A list with a single non-empty tensor is the flat case.
+  int nonempty = 0, only = -1;
+  for (int i = 0; i < ntensors; ++i)
+    if (counts[i] > 0) { ++nonempty; only = i; }
+  if (nonempty == 1) {
+    d.ntensors = 1;
+    d.count = counts[only];
+    d.nvec = ceil_div(d.count * (long long)es, 16);
+    d.in = in_ptrs[only];
+    d.out = out_ptrs[only];
+  } else {
+    DeviceGuard g(c->device);
+    const TableEntry* te = nullptr;
+    rc = get_table(c, in_ptrs, out_ptrs, counts, ntensors, (int)es, d.stream, &te);
+    if (rc != DGN_OK) return rc;
+    d.ntensors = te->nt;
+    d.count = total;
+    d.nvec = te->nvec;
+    d.table = te->d_table;
+    if (d.nvec >= (1ll << 32)) return fail(DGN_ERR_UNSUPPORTED, "bucket larger than 64 GiB");
+  }
+  if (c->nranks == 1) {
+    bool inplace = true;
+    for (int i = 0; i < ntensors; ++i)
+      if (counts[i] > 0 && in_ptrs[i] != out_ptrs[i]) inplace = false;
+    if (inplace) return DGN_OK;  // nothing to move, as in collective_op.cc:89
+    return launch_local_copy(c, d, (int)es);
+  }
+  return issue(c, d);
+}
+
+int dgn_reducescatter(dgn_comm_t c, const void* in, void* out, int64_t count, int dtype, int redop,
+                      void* stream) {
+  int rc = check_ready(c);
+  if (rc != DGN_OK) return rc;
+  const size_t es = dgn_dtype_size(dtype);
+  if (es == 0) return fail(DGN_ERR_ARG, "unknown dtype %d", dtype);
+  if (redop < DGN_SUM || redop > DGN_MAX) return fail(DGN_ERR_ARG, "unknown reduction %d", redop);
+  if (redop == DGN_MEAN && dtype <= DGN_I64)
+    return fail(DGN_ERR_UNSUPPORTED, "MEAN is defined for floating-point types only");
+  if (count < 0) return fail(DGN_ERR_ARG, "negative count");
+  if (count == 0) return DGN_OK;
+  if (!in || !out) return fail(DGN_ERR_ARG, "null pointer");
+  OpDesc d;
+  d.kind = kOpReduceScatter;
+  d.dtype = dtype;
+  d.redop = redop;
+  d.count = count;
+  d.nvec = ceil_div(count * (long long)es, 16);
+  d.in = in;
+  d.out = out;
+  d.stream = static_cast<cudaStream_t>(stream);
+  if (c->nranks == 1) {
+    if (in == out) return DGN_OK;
+    return launch_local_copy(c, d, (int)es);
+  }
+  return issue(c, d);
+}
+
+int dgn_allgather(dgn_comm_t c, const void* in, void* out, int64_t count, int dtype, void* stream) {
+  int rc = check_ready(c);
+  if (rc != DGN_OK) return rc;
+  const size_t es = dgn_dtype_size(dtype);
+  if (es == 0) return fail(DGN_ERR_ARG, "unknown dtype %d", dtype);
+  if (count < 0) return fail(DGN_ERR_ARG, "negative count");
+  if (count == 0) return DGN_OK;
+  if (!in || !out) return fail(DGN_ERR_ARG, "null pointer");
+  OpDesc d;
+  d.kind = kOpAllGather;
+  d.dtype = DGN_U8;
+  d.count = count * (long long)es;  // bytes per rank
+  d.nvec = ceil_div(d.count, 16);
+  d.in = in;
+  d.out = out;
+  d.stream = static_cast<cudaStream_t>(stream);
+  if (c->nranks == 1) {
+    if (in == out) return DGN_OK;
+    return launch_local_copy(c, d, 1);
+  }
+  return issue(c, d);
+}
+
+int dgn_broadcast(dgn_comm_t c, void* buf, int64_t count, int dtype, int root, void* stream) {
+  int rc = check_ready(c);
+  if (rc != DGN_OK) return rc;
+  const size_t es = dgn_dtype_size(dtype);
+  if (es == 0) return fail(DGN_ERR_ARG, "unknown dtype %d", dtype);
+  if (count < 0) return fail(DGN_ERR_ARG, "negative count");
+  if (root < 0 || root >= c->nranks) return fail(DGN_ERR_ARG, "root %d outside 0..%d", root, c->nranks - 1);
+  if (count == 0 || c->nranks == 1) return DGN_OK;
+  if (!buf) return fail(DGN_ERR_ARG, "null pointer");
+  OpDesc d;
+  d.kind = kOpBroadcast;
+  d.dtype = DGN_U8;
+  d.root = root;
+  d.count = count * (long long)es;
+  d.nvec = ceil_div(d.count, 16);
+  d.in = buf;
+  d.out = buf;
+  d.stream = static_cast<cudaStream_t>(stream);
+  return issue(c, d);
+}
+
+int64_t dgn_launch_count(void) { return g_launches.load(); }
+
+int dgn_comm_last_launch(dgn_comm_t c, int* variant, int* blocks, int* threads, int64_t* chunk_bytes,
+                         int* rounds) {
+  if (!c) return fail(DGN_ERR_ARG, "null communicator");
+  if (variant) *variant = c->last_plan.variant;
+  if (blocks) *blocks = c->last_plan.blocks;
+  if (threads) *threads = c->last_plan.threads;
+  if (chunk_bytes) *chunk_bytes = (int64_t)c->last_plan.cv * 16;
+  if (rounds) *rounds = c->last_plan.rounds;
+  return DGN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,63 @@
+// One translation unit per element type (DGN_INST selects it) so the
+// template instantiations compile in parallel.  Each unit exports the host
+// stubs of its kernels as plain function pointers.
+#include "dgn_kernels.cuh"
+
+#ifndef DGN_INST
+#error "compile with -DDGN_INST=<dtype index 0..7, or 8 for the byte kernels>"
+#endif
+
+namespace dgn {
+
+#if DGN_INST == 0
+typedef uint8_t InstT;
+#elif DGN_INST == 1
+typedef int8_t InstT;
+#elif DGN_INST == 2
+typedef int32_t InstT;
+#elif DGN_INST == 3
+typedef int64_t InstT;
+#elif DGN_INST == 4
+typedef __half InstT;
+#elif DGN_INST == 5
+typedef __nv_bfloat16 InstT;
+#elif DGN_INST == 6
+typedef float InstT;
+#elif DGN_INST == 7
+typedef double InstT;
+#endif
+
+#define DGN_CAT2(a, b) a##b
+#define DGN_CAT(a, b) DGN_CAT2(a, b)
+
+#if DGN_INST < 8
+// kind: 0 one-shot, 1 two-shot, 2 reduce-scatter
+const void* DGN_CAT(reduce_kernel_fn_, DGN_INST)(int kind, bool table) {
+  switch (kind) {
+    case 0:
+      return table ? (const void*)ar_oneshot_kernel<InstT, true>
+                   : (const void*)ar_oneshot_kernel<InstT, false>;
+    case 1:
+      return table ? (const void*)ar_twoshot_kernel<InstT, true, false>
+                   : (const void*)ar_twoshot_kernel<InstT, false, false>;
+    case 2:
+      return (const void*)ar_twoshot_kernel<InstT, false, true>;
+    default:
+      return nullptr;
+  }
+}
+#else
+const void* allgather_kernel_fn() { return (const void*)allgather_kernel<0>; }
+const void* broadcast_kernel_fn() { return (const void*)broadcast_kernel<0>; }
+const void* local_copy_kernel_fn(int es, bool table) {
+  switch (es) {
+    case 1: return table ? (const void*)local_copy_kernel<1, true> : (const void*)local_copy_kernel<1, false>;
+    case 2: return table ? (const void*)local_copy_kernel<2, true> : (const void*)local_copy_kernel<2, false>;
+    case 4: return table ? (const void*)local_copy_kernel<4, true> : (const void*)local_copy_kernel<4, false>;
+    case 8: return table ? (const void*)local_copy_kernel<8, true> : (const void*)local_copy_kernel<8, false>;
+    default: return nullptr;
+  }
+}
+#endif
+
+}  // namespace dgn

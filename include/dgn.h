@@ -1,0 +1,182 @@
+/*
+ * dgn.h -- C-ABI of the B200-native `Collective` path (ALLREDUCE SUM/MEAN,
+ * ALLGATHER, BROADCAST, REDUCESCATTER over a process group).
+ *
+ * This is the boundary a Dragon build binds instead of its MPI / NCCL calls:
+ * plain pointers, sizes and integer handles only.  Every entry point returns a
+ * dgn_status; nothing aborts and nothing throws.  Device pointers are ordinary
+ * CUDA device pointers valid on the communicator's device, `stream` is a
+ * cudaStream_t passed as void*.  All collectives are asynchronous with respect
+ * to the host: they enqueue exactly one kernel on `stream` and return.
+ *
+ * Reference interfaces replaced (paths relative to the Dragon source tree):
+ *   dragon/operators/distributed/collective_op_impl_mpi.cc:50-85   (MPI_Bcast /
+ *       MPI_Allreduce / MPI_Reduce_scatter / MPI_Allgather call sites)
+ *   dragon/operators/distributed/collective_op_impl_nccl.cc:34-67  (the four
+ *       nccl* call sites) and :69-89 (unique-id broadcast + ncclCommInitRank)
+ *   dragon/operators/distributed/collective_op.cc:7-51             (bucket
+ *       concat/split copies and the per-tensor MEAN scale, both fused here)
+ */
+#ifndef DGN_H_
+#define DGN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DGN_MAX_RANKS 8
+#define DGN_HANDLE_BYTES 256
+
+typedef struct dgn_comm* dgn_comm_t;
+
+typedef enum {
+  DGN_OK = 0,
+  DGN_ERR_ARG = 1,      /* bad argument (null pointer, unknown dtype, ...) */
+  DGN_ERR_CUDA = 2,     /* a CUDA runtime call failed; see dgn_last_error_string */
+  DGN_ERR_TIMEOUT = 3,  /* a bounded device- or host-side wait ran out */
+  DGN_ERR_PEER = 4,     /* a peer GPU is not reachable by P2P / IPC */
+  DGN_ERR_STATE = 5,    /* call order violated (e.g. collective before connect) */
+  DGN_ERR_UNSUPPORTED = 6
+} dgn_status;
+
+/* Element types: the `dtypes::Numerical` list the reference dispatches on
+ * (dragon/core/types.h:69; dragon/operators/distributed/collective_op.cc:93). */
+typedef enum {
+  DGN_U8 = 0,
+  DGN_I8 = 1,
+  DGN_I32 = 2,
+  DGN_I64 = 3,
+  DGN_F16 = 4,
+  DGN_BF16 = 5,
+  DGN_F32 = 6,
+  DGN_F64 = 7
+} dgn_dtype;
+
+/* Reductions.  SUM/PROD/MIN/MAX are the reference's op map
+ * (collective_op_impl_mpi.cc:111-126).  MEAN is the operator-level
+ * "SUM, then scale by 1.f/float(comm_size)" of collective_op.cc:40-51, fused
+ * into the reduction epilogue; it is defined for floating-point types only. */
+typedef enum {
+  DGN_SUM = 0,
+  DGN_MEAN = 1,
+  DGN_PROD = 2,
+  DGN_MIN = 3,
+  DGN_MAX = 4
+} dgn_redop;
+
+/* Algorithm selector for dgn_comm_set_tuning / DGN_FORCE_VARIANT. */
+typedef enum {
+  DGN_VARIANT_AUTO = 0,
+  DGN_VARIANT_ONESHOT = 1, /* every rank pushes its whole message to every peer */
+  DGN_VARIANT_TWOSHOT = 2, /* reduce-scatter by peer stores + all-gather by peer loads */
+  DGN_VARIANT_NVLS = 3     /* NVSwitch multicast (multimem) where the box exposes it */
+} dgn_variant;
+
+/* ---- library ----------------------------------------------------------- */
+
+/* Version as major*10000 + minor*100 + patch. */
+int dgn_version(void);
+/* Size in bytes of one element of `dtype`, or 0 if unknown. */
+size_t dgn_dtype_size(int dtype);
+/* Text of the last error raised on the calling thread. */
+const char* dgn_last_error_string(void);
+const char* dgn_status_string(int status);
+
+/* ---- communicator bootstrap --------------------------------------------
+ * Replaces "root creates an ncclUniqueId, MPI_Bcast, ncclCommInitRank"
+ * (collective_op_impl_nccl.cc:69-89).  Three steps, so that the host
+ * framework can move the handles with whatever byte channel it already has
+ * (Dragon: MPI_Allgather on the group's MPI_Comm):
+ *   1. dgn_comm_init_local   allocates this rank's symmetric workspace,
+ *   2. dgn_comm_get_handle   fills DGN_HANDLE_BYTES describing it,
+ *   3. dgn_comm_connect      takes all ranks' handles (rank order) and maps
+ *                            every peer's workspace into this process.
+ * `nranks` <= DGN_MAX_RANKS; `nranks` == 1 gives the local-copy path. */
+int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm);
+int dgn_comm_get_handle(dgn_comm_t comm, void* handle /* DGN_HANDLE_BYTES */);
+int dgn_comm_connect(dgn_comm_t comm, const void* all_handles /* nranks * DGN_HANDLE_BYTES */);
+
+/* Convenience bootstrap without any external channel: ranks meet through
+ * files in `rendezvous_dir` (a directory all ranks of this node can write),
+ * under the unique name `tag`.  Waits at most `timeout_ms` for the peers. */
+int dgn_comm_create(int rank, int nranks, int device, const char* rendezvous_dir,
+                    const char* tag, int timeout_ms, dgn_comm_t* comm);
+
+/* `nranks` virtual ranks that all live on ONE device.  Each returned
+ * communicator behaves like one rank; a collective is launched (as a single
+ * cooperative kernel covering every virtual rank) when the last of the
+ * `nranks` communicators has issued its call, so a single host thread may
+ * call them one after another.  All calls of one collective must use the
+ * same stream.  Used to exercise the multi-rank kernels where fewer GPUs
+ * than ranks are available. */
+int dgn_comm_create_emulated(int nranks, int device, dgn_comm_t* comms /* [nranks] */);
+
+/* The caller must make sure no peer still runs a collective on this
+ * communicator (a host barrier after the last stream sync). */
+int dgn_comm_destroy(dgn_comm_t comm);
+
+int dgn_comm_rank(dgn_comm_t comm);
+int dgn_comm_size(dgn_comm_t comm);
+int dgn_comm_device(dgn_comm_t comm);
+
+/* Error word written by kernels of this communicator: DGN_OK, or
+ * DGN_ERR_TIMEOUT once a bounded device-side wait has run out.  Readable at
+ * any time without synchronising.  A communicator that timed out refuses
+ * further collectives with DGN_ERR_STATE. */
+int dgn_comm_status(dgn_comm_t comm);
+
+/* Upper bound, in milliseconds, on any single device-side wait for a peer
+ * (default 5000; environment DGN_WAIT_LIMIT_MS). */
+int dgn_comm_set_wait_limit_ms(dgn_comm_t comm, int ms);
+
+/* Kernel-shape overrides (0 keeps the automatic choice): variant, number of
+ * thread blocks, threads per block, bytes per block per round. */
+int dgn_comm_set_tuning(dgn_comm_t comm, int variant, int blocks, int threads,
+                        int64_t chunk_bytes);
+
+/* 1 if the NVSwitch-multicast variant was set up for this communicator. */
+int dgn_comm_has_nvls(dgn_comm_t comm);
+
+/* ---- collectives --------------------------------------------------------
+ * Every rank of the communicator must issue the same sequence of
+ * collectives with the same counts, dtype and reduction. */
+
+/* ALLREDUCE over a list of tensors (replaces MPI_Allreduce /
+ * ncclAllReduce at collective_op_impl_mpi.cc:60-66, _nccl.cc:43-50 together
+ * with the bucket concat/split of collective_op.cc:7-35 and the MEAN scale of
+ * collective_op.cc:40-51).  Tensor i has counts[i] elements; in_ptrs[i] may
+ * equal out_ptrs[i] (in place).  The list is reduced as one message. */
+int dgn_allreduce(dgn_comm_t comm, const void* const* in_ptrs, void* const* out_ptrs,
+                  const int64_t* counts, int ntensors, int dtype, int redop, void* stream);
+
+/* ALLGATHER: out holds nranks*count elements, rank r's block at r*count
+ * (replaces MPI_Allgather / ncclAllGather, collective_op_impl_mpi.cc:79-85). */
+int dgn_allgather(dgn_comm_t comm, const void* in, void* out, int64_t count, int dtype,
+                  void* stream);
+
+/* BROADCAST in place from group rank `root` (replaces MPI_Bcast /
+ * ncclBroadcast, collective_op_impl_mpi.cc:50-57). */
+int dgn_broadcast(dgn_comm_t comm, void* buf, int64_t count, int dtype, int root,
+                  void* stream);
+
+/* REDUCESCATTER: in holds nranks*count elements, out receives the reduced
+ * block `rank` (replaces MPI_Reduce_scatter / ncclReduceScatter,
+ * collective_op_impl_mpi.cc:69-76). */
+int dgn_reducescatter(dgn_comm_t comm, const void* in, void* out, int64_t count, int dtype,
+                      int redop, void* stream);
+
+/* ---- introspection for benchmarks and tests ------------------------------ */
+
+/* Number of kernels this library has launched from the calling process. */
+int64_t dgn_launch_count(void);
+/* Variant / grid the last collective of `comm` used (any pointer may be NULL). */
+int dgn_comm_last_launch(dgn_comm_t comm, int* variant, int* blocks, int* threads,
+                         int64_t* chunk_bytes, int* rounds);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DGN_H_ */

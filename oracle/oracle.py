@@ -1,0 +1,179 @@
+"""Python face of the CPU oracle (TEST INFRASTRUCTURE ONLY).
+
+Two checkers live here:
+
+* the C restatement of the `Collective` operator (collective_oracle.c, built
+  into liboracle.so by the Makefile beside it), bit-exact target for the CUDA
+  path -- ascending-rank order, fp32 accumulation for fp16/bf16, one rounding;
+* the fp64 host sum the tolerance contract is written against
+  (max relative error 1e-6 fp32 / 2e-3 fp16 / 1e-2 bf16).
+
+PARITY UNPINNED: the reference has no golden vectors for this path and cannot
+be built or imported on this machine (no MPI, no protoc); see the header of
+collective_oracle.c.  Only tests, the smoke check and the benchmark's CPU
+baseline may import this module.
+"""
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_DIR = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_DIR, "liboracle.so")
+
+U8, I8, I32, I64, F16, BF16, F32, F64 = range(8)
+SUM, MEAN, PROD, MIN, MAX = range(5)
+REDOPS = {"SUM": SUM, "MEAN": MEAN, "PROD": PROD, "MIN": MIN, "MAX": MAX}
+
+# numpy storage type per dtype code (bf16 travels as its uint16 bit pattern).
+NP_STORAGE = {U8: np.uint8, I8: np.int8, I32: np.int32, I64: np.int64, F16: np.float16,
+              BF16: np.uint16, F32: np.float32, F64: np.float64}
+TOLERANCE = {F32: 1e-6, F16: 2e-3, BF16: 1e-2, F64: 1e-12}
+
+_lib = None
+
+
+def build():
+    """Compile liboracle.so if it is missing or older than its source."""
+    src = os.path.join(_DIR, "collective_oracle.c")
+    if not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _DIR, "liboracle.so"], check=True, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT)
+    return _LIB
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        h = ctypes.CDLL(_LIB)
+        vpp = ctypes.POINTER(ctypes.c_void_p)
+        h.orc_allreduce.restype = ctypes.c_int
+        h.orc_allreduce.argtypes = [vpp, ctypes.c_int, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        h.orc_reducescatter.restype = ctypes.c_int
+        h.orc_reducescatter.argtypes = [vpp, ctypes.c_int, ctypes.c_int64, ctypes.c_int, ctypes.c_int, vpp]
+        h.orc_allgather.restype = ctypes.c_int
+        h.orc_allgather.argtypes = [vpp, ctypes.c_int, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p]
+        h.orc_broadcast.restype = ctypes.c_int
+        h.orc_broadcast.argtypes = [vpp, ctypes.c_int, ctypes.c_int64, ctypes.c_int, ctypes.c_int]
+        h.orc_mp_allreduce.restype = ctypes.c_int
+        h.orc_mp_allreduce.argtypes = [vpp, ctypes.c_int, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
+                                       ctypes.c_int, ctypes.POINTER(ctypes.c_double), ctypes.c_void_p]
+        h.orc_f32_to_f16.restype = ctypes.c_uint16
+        h.orc_f32_to_f16.argtypes = [ctypes.c_float]
+        h.orc_f16_to_f32.restype = ctypes.c_float
+        h.orc_f16_to_f32.argtypes = [ctypes.c_uint16]
+        h.orc_f32_to_bf16.restype = ctypes.c_uint16
+        h.orc_f32_to_bf16.argtypes = [ctypes.c_float]
+        h.orc_bf16_to_f32.restype = ctypes.c_float
+        h.orc_bf16_to_f32.argtypes = [ctypes.c_uint16]
+        _lib = h
+    return _lib
+
+
+def _ptrs(arrays):
+    return (ctypes.c_void_p * len(arrays))(*[a.ctypes.data for a in arrays])
+
+
+def _prep(bufs, dtype):
+    st = NP_STORAGE[dtype]
+    out = [np.ascontiguousarray(b).view(st).reshape(-1) for b in bufs]
+    n = out[0].size
+    assert all(b.size == n for b in out), "ragged rank buffers"
+    return out
+
+
+def allreduce(bufs, dtype, redop="SUM"):
+    """Result every rank must hold after ALLREDUCE of the per-rank arrays."""
+    op = REDOPS[redop.upper()] if isinstance(redop, str) else redop
+    bufs = _prep(bufs, dtype)
+    out = np.empty_like(bufs[0])
+    rc = lib().orc_allreduce(_ptrs(bufs), len(bufs), bufs[0].size, dtype, op, out.ctypes.data)
+    if rc != 0:
+        raise ValueError("oracle rejected allreduce(dtype={}, redop={})".format(dtype, redop))
+    return out
+
+
+def reducescatter(bufs, dtype, redop="SUM"):
+    """List of per-rank results of REDUCESCATTER (each input holds n equal blocks)."""
+    op = REDOPS[redop.upper()] if isinstance(redop, str) else redop
+    bufs = _prep(bufs, dtype)
+    n = len(bufs)
+    assert bufs[0].size % n == 0
+    count = bufs[0].size // n
+    outs = [np.empty(count, dtype=bufs[0].dtype) for _ in range(n)]
+    rc = lib().orc_reducescatter(_ptrs(bufs), n, count, dtype, op, _ptrs(outs))
+    if rc != 0:
+        raise ValueError("oracle rejected reducescatter")
+    return outs
+
+
+def allgather(bufs, dtype):
+    bufs = _prep(bufs, dtype)
+    out = np.empty(bufs[0].size * len(bufs), dtype=bufs[0].dtype)
+    rc = lib().orc_allgather(_ptrs(bufs), len(bufs), bufs[0].size, dtype, out.ctypes.data)
+    if rc != 0:
+        raise ValueError("oracle rejected allgather")
+    return out
+
+
+def broadcast(bufs, dtype, root=0):
+    """Per-rank buffers after an in-place BROADCAST from `root`."""
+    bufs = [b.copy() for b in _prep(bufs, dtype)]
+    rc = lib().orc_broadcast(_ptrs(bufs), len(bufs), bufs[0].size, dtype, root)
+    if rc != 0:
+        raise ValueError("oracle rejected broadcast")
+    return bufs
+
+
+def mp_allreduce(bufs, dtype, redop="SUM", iters=5):
+    """Runs the MPI-shaped multi-process all-reduce; returns (seconds per
+    iteration as a list, rank 0's result)."""
+    op = REDOPS[redop.upper()] if isinstance(redop, str) else redop
+    bufs = _prep(bufs, dtype)
+    secs = (ctypes.c_double * iters)()
+    out = np.empty_like(bufs[0])
+    rc = lib().orc_mp_allreduce(_ptrs(bufs), len(bufs), bufs[0].size, dtype, op, iters, secs, out.ctypes.data)
+    if rc != 0:
+        raise RuntimeError("orc_mp_allreduce failed with {}".format(rc))
+    return list(secs), out
+
+
+# ---- the fp64 side of the contract ---------------------------------------------
+
+def bf16_bits_to_f32(bits):
+    return (np.asarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(x):
+    """Round-to-nearest-even fp32 -> bf16 bit patterns (NaN -> 0x7fff)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    nan = (u & 0x7FFFFFFF) > 0x7F800000
+    r = ((u.astype(np.uint64) + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    r[nan] = 0x7FFF
+    return r
+
+
+def to_f64(buf, dtype):
+    st = NP_STORAGE[dtype]
+    a = np.ascontiguousarray(buf).view(st).reshape(-1)
+    if dtype == BF16:
+        return bf16_bits_to_f32(a).astype(np.float64)
+    return a.astype(np.float64)
+
+
+def fp64_sum(bufs, dtype, mean=False):
+    acc = np.zeros(np.ascontiguousarray(bufs[0]).view(NP_STORAGE[dtype]).size, dtype=np.float64)
+    for b in bufs:
+        acc += to_f64(b, dtype)
+    return acc / len(bufs) if mean else acc
+
+
+def max_rel_err(result, ref64, dtype):
+    """max |y - ref| / max(|ref|_inf, tiny): the contract's error measure,
+    relative to the largest reference magnitude of the message."""
+    y = to_f64(result, dtype)
+    scale = max(float(np.max(np.abs(ref64))) if ref64.size else 0.0, 1e-30)
+    return float(np.max(np.abs(y - ref64))) / scale if ref64.size else 0.0

@@ -1,0 +1,315 @@
+"""Parity of the CUDA collectives with the CPU oracle, through the C-ABI.
+
+All ranks are virtual ranks on one device (dgn_comm_create_emulated): one
+cooperative kernel runs every rank's blocks, so the flag protocol, the peer
+stores/loads and the reduction code are the ones a multi-GPU run executes.
+Integer and byte work must match bit for bit; floating point must match the
+oracle bit for bit too (same order, same single rounding) and stay within the
+contract's tolerance of an fp64 host sum: 1e-6 fp32, 2e-3 fp16, 1e-2 bf16.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+SIZES = [1, 7, 8, 9, 15, 16, 17, 1000, 4099, 65536 + 3]
+
+
+@pytest.fixture(scope="module")
+def teams(dgn_lib):
+    from dragon_b200.comm import Communicator
+    made = {}
+
+    def get(n):
+        if n not in made:
+            made[n] = Communicator.emulated(n, 0)
+        return made[n]
+
+    yield get
+    torch.cuda.synchronize()
+    for comms in made.values():
+        for c in comms:
+            c.destroy()
+
+
+def run_allreduce(comms, arrays, dtype, redop, inplace=False):
+    dev = "cuda:0"
+    ins = [H.to_torch(a, dtype, dev) for a in arrays]
+    outs = ins if inplace else [torch.empty_like(t) for t in ins]
+    for c, i, o in zip(comms, ins, outs):
+        c.all_reduce([i], [o], redop)
+    torch.cuda.synchronize()
+    assert all(c.status() == 0 for c in comms)
+    return [H.to_numpy(o, dtype) for o in outs]
+
+
+def check_allreduce(comms, count, dtype, redop, inplace=False):
+    n = len(comms)
+    arrays = [H.make_input(r, count, dtype) for r in range(n)]
+    want = oracle.allreduce(arrays, dtype, redop)
+    got = run_allreduce(comms, arrays, dtype, redop, inplace)
+    for r in range(n):
+        H.assert_bits_equal(got[r], want, "allreduce n={} count={} dtype={} {} rank {}".format(
+            n, count, H.NAMES[dtype], redop, r))
+    if dtype in oracle.TOLERANCE and redop in ("SUM", "MEAN"):
+        ref = oracle.fp64_sum(arrays, dtype, mean=(redop == "MEAN"))
+        err = oracle.max_rel_err(got[0], ref, dtype)
+        assert err <= oracle.TOLERANCE[dtype], "max rel err {} > {}".format(err, oracle.TOLERANCE[dtype])
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("dtype", H.ALL_DTYPES, ids=H.NAMES)
+def test_allreduce_sum_all_sizes(teams, n, dtype):
+    comms = teams(n)
+    for variant in (1, 2):
+        for c in comms:
+            c.set_tuning(variant=variant)
+        for count in SIZES:
+            check_allreduce(comms, count, dtype, "SUM")
+    for c in comms:
+        c.set_tuning()
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("dtype", H.FLOAT_DTYPES, ids=[H.NAMES[d] for d in H.FLOAT_DTYPES])
+def test_allreduce_mean_inplace(teams, n, dtype):
+    comms = teams(n)
+    for variant in (1, 2):
+        for c in comms:
+            c.set_tuning(variant=variant)
+        for count in (5, 4099, 1 << 18):
+            check_allreduce(comms, count, dtype, "MEAN", inplace=True)
+    for c in comms:
+        c.set_tuning()
+
+
+@pytest.mark.parametrize("redop", ["PROD", "MIN", "MAX"])
+@pytest.mark.parametrize("dtype", [oracle.I32, oracle.U8, oracle.F32, oracle.F16], ids=["i32", "u8", "f32", "f16"])
+def test_allreduce_other_reductions(teams, redop, dtype):
+    check_allreduce(teams(4), 4099, dtype, redop)
+
+
+def test_mean_rejected_for_integers(teams):
+    from dragon_b200 import _C
+    comms = teams(2)
+    t = torch.zeros(16, dtype=torch.int32, device="cuda:0")
+    with pytest.raises(_C.DgnError) as e:
+        comms[0].all_reduce([t], [t], "MEAN")
+    assert e.value.status == _C.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("n", [2, 8])
+def test_allreduce_multi_round_small_chunks(teams, n):
+    """Tiny chunks and few blocks force many rounds of the two-shot pipeline."""
+    comms = teams(n)
+    for c in comms:
+        c.set_tuning(variant=2, blocks=3, threads=64, chunk_bytes=256)
+    try:
+        for dtype in (oracle.F32, oracle.BF16, oracle.I64):
+            check_allreduce(comms, 20011, dtype, "SUM")
+        info = comms[0].last_launch()
+        assert info["rounds"] > 4 and info["blocks"] == 3
+    finally:
+        for c in comms:
+            c.set_tuning()
+
+
+def test_config1_fp32_16mib_two_ranks(teams):
+    """16 MiB fp32 SUM on 2 ranks (the reference's CPU-runnable case)."""
+    from dragon_b200 import workloads
+    comms = teams(2)
+    arrays = [workloads.uniform_message(r, 4194304) for r in range(2)]
+    got = run_allreduce(comms, arrays, oracle.F32, "SUM")
+    want = oracle.allreduce(arrays, oracle.F32, "SUM")
+    H.assert_bits_equal(got[0], want)
+    H.assert_bits_equal(got[1], want)
+    # n = 2 leaves no freedom in the order: a + b in fp32 is the fp64 sum rounded once.
+    ref = (arrays[0].astype(np.float64) + arrays[1].astype(np.float64)).astype(np.float32)
+    H.assert_bits_equal(got[0], ref)
+
+
+def test_back_to_back_collectives_reuse_staging(teams):
+    """Many collectives in a row without host syncs: staging reuse must be safe."""
+    comms = teams(4)
+    n = 4
+    dev = "cuda:0"
+    for variant in (1, 2):
+        for c in comms:
+            c.set_tuning(variant=variant)
+        steps = 24
+        ins = [[H.to_torch(H.make_input(r, 3001, oracle.F32, seed=50 * s), oracle.F32, dev) for r in range(n)]
+               for s in range(steps)]
+        outs = [[torch.empty_like(t) for t in row] for row in ins]
+        for s in range(steps):
+            for r in range(n):
+                comms[r].all_reduce([ins[s][r]], [outs[s][r]], "SUM")
+        torch.cuda.synchronize()
+        for s in range(steps):
+            want = oracle.allreduce([H.to_numpy(t, oracle.F32) for t in ins[s]], oracle.F32, "SUM")
+            for r in range(n):
+                H.assert_bits_equal(H.to_numpy(outs[s][r], oracle.F32), want, "step {}".format(s))
+    for c in comms:
+        c.set_tuning()
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_allreduce_bucket_of_tensors(teams, n):
+    """A tensor list travels as one message; results are per tensor."""
+    comms = teams(n)
+    dev = "cuda:0"
+    counts = [64, 1, 0, 4099, 7, 1 << 16, 33, 2048]
+    for dtype, redop in ((oracle.F32, "MEAN"), (oracle.F16, "MEAN"), (oracle.I32, "SUM")):
+        for variant in (1, 2):
+            for c in comms:
+                c.set_tuning(variant=variant)
+            arrays = [[H.make_input(r, k, dtype, seed=7 + 13 * i) for i, k in enumerate(counts)] for r in range(n)]
+            ins = [[H.to_torch(a, dtype, dev) for a in row] for row in arrays]
+            for r in range(n):
+                comms[r].all_reduce(ins[r], None, redop)
+            torch.cuda.synchronize()
+            for i, k in enumerate(counts):
+                want = oracle.allreduce([arrays[r][i] for r in range(n)], dtype, redop)
+                for r in range(n):
+                    H.assert_bits_equal(H.to_numpy(ins[r][i], dtype), want, "tensor {} rank {}".format(i, r))
+    for c in comms:
+        c.set_tuning()
+
+
+def test_allreduce_unaligned_views(teams):
+    """Tensors that start off a 16-byte boundary take the element path."""
+    comms = teams(2)
+    dev = "cuda:0"
+    for dtype in (oracle.F32, oracle.F16, oracle.U8):
+        arrays = [H.make_input(r, 5000, dtype) for r in range(2)]
+        full = [H.to_torch(a, dtype, dev) for a in arrays]
+        views = [t[1:4998] for t in full]
+        outs = [torch.zeros(5001, dtype=t.dtype, device=dev)[3:5000] for t in full]
+        for variant in (1, 2):
+            for c in comms:
+                c.set_tuning(variant=variant)
+            for r in range(2):
+                comms[r].all_reduce([views[r]], [outs[r]], "SUM")
+            torch.cuda.synchronize()
+            want = oracle.allreduce([a[1:4998] for a in arrays], dtype, "SUM")
+            for r in range(2):
+                H.assert_bits_equal(H.to_numpy(outs[r], dtype), want)
+    for c in comms:
+        c.set_tuning()
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_allgather_bit_exact(teams, n):
+    comms = teams(n)
+    dev = "cuda:0"
+    for dtype, count in ((oracle.I64, 65536), (oracle.BF16, 70001), (oracle.U8, 13), (oracle.F64, 1)):
+        arrays = [H.make_input(r, count, dtype) for r in range(n)]
+        if dtype == oracle.BF16:  # NaN payloads, infinities, signed zeros, subnormals travel untouched
+            arrays[0][:6] = np.array([0x7FC1, 0xFFFF, 0x7F80, 0x8000, 0x0001, 0xFF80], dtype=np.uint16)
+        ins = [H.to_torch(a, dtype, dev) for a in arrays]
+        outs = [torch.empty(n * count, dtype=t.dtype, device=dev) for t in ins]
+        for r in range(n):
+            comms[r].all_gather(ins[r], outs[r])
+        torch.cuda.synchronize()
+        want = oracle.allgather(arrays, dtype)
+        for r in range(n):
+            H.assert_bits_equal(H.to_numpy(outs[r], dtype), want, "allgather rank {}".format(r))
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_broadcast_bit_exact(teams, n):
+    comms = teams(n)
+    dev = "cuda:0"
+    for root in (0, n - 1):
+        for dtype, count in ((oracle.I64, 65536), (oracle.BF16, 100003), (oracle.U8, 1)):
+            arrays = [H.make_input(r, count, dtype) for r in range(n)]
+            bufs = [H.to_torch(a, dtype, dev) for a in arrays]
+            for r in range(n):
+                comms[r].broadcast(bufs[r], root)
+            torch.cuda.synchronize()
+            want = oracle.broadcast(arrays, dtype, root)
+            for r in range(n):
+                H.assert_bits_equal(H.to_numpy(bufs[r], dtype), want[r], "broadcast root {} rank {}".format(root, r))
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_reducescatter(teams, n):
+    comms = teams(n)
+    dev = "cuda:0"
+    for dtype, count, redop in ((oracle.F32, 4099, "SUM"), (oracle.F16, 1 << 15, "MEAN"), (oracle.I32, 5, "SUM")):
+        arrays = [H.make_input(r, n * count, dtype) for r in range(n)]
+        ins = [H.to_torch(a, dtype, dev) for a in arrays]
+        outs = [torch.empty(count, dtype=t.dtype, device=dev) for t in ins]
+        for r in range(n):
+            comms[r].reduce_scatter(ins[r], outs[r], redop)
+        torch.cuda.synchronize()
+        want = oracle.reducescatter(arrays, dtype, redop)
+        for r in range(n):
+            H.assert_bits_equal(H.to_numpy(outs[r], dtype), want[r], "reducescatter rank {}".format(r))
+
+
+def test_results_are_deterministic(teams):
+    comms = teams(8)
+    arrays = [H.make_input(r, 100003, oracle.F16) for r in range(8)]
+    a = run_allreduce(comms, arrays, oracle.F16, "MEAN")
+    b = run_allreduce(comms, arrays, oracle.F16, "MEAN")
+    for r in range(8):
+        H.assert_bits_equal(a[r], a[0])
+        H.assert_bits_equal(b[r], a[0])
+
+
+def test_single_rank_paths(dgn_lib):
+    """comm_size 1: in place is a no-op (collective_op.cc:89), out of place copies."""
+    from dragon_b200 import _C
+    from dragon_b200.comm import Communicator
+    c = Communicator.init_local(0, 1, 0)
+    try:
+        x = torch.randn(100003, device="cuda:0")
+        y = torch.zeros_like(x)
+        before = _C.lib().dgn_launch_count()
+        c.all_reduce([x], [x], "MEAN")
+        assert _C.lib().dgn_launch_count() == before
+        c.all_reduce([x], [y], "MEAN")
+        torch.cuda.synchronize()
+        assert _C.lib().dgn_launch_count() == before + 1
+        assert torch.equal(x, y)
+        parts = [torch.randn(k, device="cuda:0").half() for k in (5, 4096, 77)]
+        outs = [torch.zeros_like(p) for p in parts]
+        c.all_reduce(parts, outs, "SUM")
+        g = torch.zeros(100003, device="cuda:0")
+        c.all_gather(x, g)
+        c.broadcast(x, 0)
+        torch.cuda.synchronize()
+        assert all(torch.equal(a, b) for a, b in zip(parts, outs))
+        assert torch.equal(g, x)
+    finally:
+        c.destroy()
+
+
+def test_wait_limit_reports_timeout_without_hanging(dgn_lib):
+    """A peer that never launches: the kernel gives up after the limit, the
+    status word says so and the communicator refuses further work."""
+    from dragon_b200 import _C
+    from dragon_b200.comm import Communicator
+    a = Communicator.init_local(0, 2, 0)
+    b = Communicator.init_local(1, 2, 0)
+    try:
+        handles = [a.handle_bytes(), b.handle_bytes()]
+        a.connect(handles)
+        b.connect(handles)
+        a.set_wait_limit_ms(50)
+        x = torch.ones(1024, device="cuda:0")
+        a.all_reduce([x], [x], "SUM")  # rank 1 never joins
+        torch.cuda.synchronize()
+        assert a.status() == _C.ERR_TIMEOUT
+        with pytest.raises(_C.DgnError) as e:
+            a.all_reduce([x], [x], "SUM")
+        assert e.value.status == _C.ERR_STATE
+        assert b.status() == 0
+    finally:
+        a.destroy()
+        b.destroy()
