@@ -1,0 +1,533 @@
+#!/usr/bin/env python
+"""Benchmark of the `Collective` hot path: all-reduce bus bandwidth and latency.
+
+    python bench.py --gpus 1 --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference --gpus N ...      (CPU path, rank 0 only)
+
+One step = one ALLREDUCE (MEAN, fp32, 256 MiB per rank by default) through the
+dgn C-ABI.  At N = 1 the communicator has one rank and the step is the
+out-of-place local-copy path (HBM bound); at N >= 2 it is the peer-memory
+all-reduce over NVLink and `value` is the bus bandwidth
+S/t * 2(N-1)/N.  Rank 0 prints one JSON line.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+MiB = 1 << 20
+NVLINK_NOMINAL_GBS = 900.0      # per direction per GPU
+NVLINK_MEASURED_P2P_GBS = 770.0  # peer copy measured on this pool
+HBM_FALLBACK_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size-mib", type=float, default=256.0, help="message bytes per rank of the timed step")
+    ap.add_argument("--dtype", default="f32", choices=["f32", "f16", "bf16"])
+    ap.add_argument("--reduction", default="MEAN")
+    ap.add_argument("--sweep", default="auto", choices=["auto", "off", "full"],
+                    help="message-size sweep beside the headline (auto: up to 256 MiB)")
+    ap.add_argument("--no-nccl", action="store_true", help="skip the NCCL comparison in the sweep")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return HBM_FALLBACK_GBS, "fallback"
+
+
+class ClockSampler(object):
+    """Polls SM clock and throttle reasons of one GPU through NVML while a
+    timed region runs."""
+
+    def __init__(self, index, period_s=0.02):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # NVML missing: report nothing rather than guess
+            self.nv = None
+
+    _NAMES = {
+        0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+        0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting",
+    }
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self._NAMES.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def np_dtype_of(name):
+    import numpy as np
+    return {"f32": np.float32, "f16": np.float16}[name]
+
+
+def torch_dtype_of(name):
+    import torch
+    return {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[name]
+
+
+def make_message(rank, count, dtype_name, device):
+    """Seeded uniform[-1, 1) message of `count` elements on `device`."""
+    import torch
+    from dragon_b200 import workloads
+    x = torch.from_numpy(workloads.uniform_message(rank, count))
+    return x.to(device=device, dtype=torch_dtype_of(dtype_name))
+
+
+def time_steps(fn, steps, warmup, barrier=None):
+    """Runs fn() warmup + steps times on the current stream; returns the list of
+    per-step device durations in ms (CUDA events) and the whole-region ms."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record()
+    for i in range(steps):
+        fn()
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    return per, evs[0].elapsed_time(evs[steps])
+
+
+def cpu_config1_baseline():
+    """CPU restatement of the MPI path on the reference's own CPU case: 2 rank
+    processes, 16 MiB fp32 SUM, in place."""
+    from dragon_b200 import workloads
+    from oracle import oracle
+    bufs = [workloads.uniform_message(r, 4194304) for r in range(2)]
+    secs, _ = oracle.mp_allreduce(bufs, oracle.F32, "SUM", iters=20)
+    t = statistics.median(secs)
+    s = bufs[0].nbytes
+    return {"value": s / t / 1e9, "unit": "GB/s", "cores": 2, "kind": "port",
+            "sample": "20 in-place all-reduces of 16 MiB fp32 SUM over 2 rank processes on shared memory "
+                      "(median); bus GB/s = S/t * 2(n-1)/n", "ms_per_op": t * 1e3,
+            "host_cores": os.cpu_count()}
+
+
+# --------------------------------------------------------------------------
+# N = 1
+
+def bench_single(args):
+    import torch
+    from dragon_b200 import _C
+    from dragon_b200.comm import Communicator
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    esize = torch.tensor([], dtype=torch_dtype_of(args.dtype)).element_size()
+    count = int(args.size_mib * MiB) // esize
+    S = count * esize
+    comm = Communicator.init_local(0, 1, 0)
+    x = make_message(0, count, args.dtype, dev)
+    y = torch.empty_like(x)
+    op = comm.prepare_all_reduce([x], [y], args.reduction)
+    lib = _C.lib()
+
+    sampler = ClockSampler(0)
+    with sampler:
+        launches0 = lib.dgn_launch_count()
+        per, total_ms = time_steps(op, args.steps, args.warmup)
+        launches = lib.dgn_launch_count() - launches0 - args.warmup
+        # End to end: host buffers in, host result out, copies inside the timed region.
+        xh = x.cpu().pin_memory()
+        yh = torch.empty_like(xh).pin_memory()
+
+        def e2e_step():
+            x.copy_(xh, non_blocking=True)
+            op()
+            yh.copy_(y, non_blocking=True)
+
+        e2e_steps = max(3, min(args.steps, 10))
+        _, e2e_ms = time_steps(e2e_step, e2e_steps, 2)
+    assert torch.equal(yh, xh), "local-copy path returned different bytes"
+    ms = total_ms / args.steps
+    kernel_ms = statistics.mean(per)
+    peak, peak_kind = hbm_peak()
+    achieved = 2.0 * S / (kernel_ms * 1e-3) / 1e9
+    line = {
+        "metric": "allreduce bus GB/s & latency vs msg size (frac of 900 GB/s at 2/4/8 GPUs; "
+                  "at 1 GPU: local-copy path, algorithm GB/s = S/t)",
+        "value": S / (ms * 1e-3) / 1e9,
+        "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": args.dtype, "data": "synthetic",
+        "config": {
+            "workload": "Collective ALLREDUCE reduction={} {} {:g} MiB per rank, out of place, comm_size=1 "
+                        "(local-copy path)".format(args.reduction, args.dtype, args.size_mib),
+            "message_bytes": S, "world_size": 1,
+            "l2": "message ({:g} MiB) larger than the 126 MB L2; no flush between steps".format(args.size_mib),
+            "values": "uniform[-1,1) from numpy default_rng(1000+rank)",
+        },
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "algorithmic_bytes_per_launch": 2 * S, "kernel": "local_copy_kernel",
+                     "kernel_ms": kernel_ms},
+        "e2e": {"value": S / (e2e_ms / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": S, "d2h_bytes_per_step": S, "ms_per_step": e2e_ms / e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": sampler.summary(),
+    }
+    traffic_path = os.path.join(ROOT, "profiles", "local_copy_traffic.json")
+    if os.path.exists(traffic_path):
+        with open(traffic_path) as f:
+            t = json.load(f)
+        # ncu capture of a smaller message; DRAM traffic scales with the vectors copied.
+        line["roofline"]["traffic"] = t["dram_bytes_per_launch"] * (S / t["message_bytes"])
+    line["emulated_ranks_one_gpu"] = bench_emulated(args)
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_local_copy_baseline(args)
+        line["cpu_baseline_config1"] = cpu_config1_baseline()
+    comm.destroy()
+    return line
+
+
+def bench_emulated(args):
+    """The multi-rank kernels with 8 virtual ranks on this one GPU (all "peer"
+    traffic is local HBM traffic): times the two-shot and one-shot kernels the
+    multi-GPU runs use."""
+    import torch
+    from dragon_b200.comm import Communicator
+    out = {}
+    comms = Communicator.emulated(8, 0)
+    try:
+        for label, nbytes in (("oneshot_64KiB", 64 << 10), ("twoshot_64MiB", 64 << 20)):
+            count = nbytes // 4
+            xs = [make_message(r, count, "f32", "cuda:0") for r in range(8)]
+            ops = [c.prepare_all_reduce([x], [x], "MEAN") for c, x in zip(comms, xs)]
+
+            def step():
+                for op in ops:
+                    op()
+
+            per, total = time_steps(step, 10, 3)
+            out[label] = {"ms_per_allreduce": total / 10, "launch": comms[0].last_launch()}
+    finally:
+        torch.cuda.synchronize()
+        for c in comms:
+            c.destroy()
+    return out
+
+
+def cpu_local_copy_baseline(args):
+    """The oracle's comm_size-1 out-of-place path on one host core, on a
+    bounded sample of the message."""
+    import numpy as np
+    from dragon_b200 import workloads
+    from oracle import oracle
+    count = min(int(args.size_mib * MiB) // 4, 16 * MiB)  # 64 MiB fp32 sample
+    x = workloads.uniform_message(0, count)
+    y = np.zeros_like(x)
+    reps, t0 = 0, time.perf_counter()
+    while reps < 3 or time.perf_counter() - t0 < 3.0:
+        oracle.allreduce([x], oracle.F32, "MEAN", out=y)
+        reps += 1
+    t = (time.perf_counter() - t0) / reps
+    assert np.array_equal(x, y)
+    return {"value": x.nbytes / t / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": "{} passes of the oracle's comm_size=1 all-reduce over a {} MiB fp32 sample".format(
+                reps, x.nbytes // MiB), "host_cores": os.cpu_count()}
+
+
+# --------------------------------------------------------------------------
+# N >= 2 (one process per GPU under torch.distributed.run)
+
+def bench_multi(args):
+    import torch
+    import torch.distributed as dist
+    from dragon_b200 import _C
+    from dragon_b200.comm import Communicator
+
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group(backend="gloo")  # plumbing only: handle exchange, barriers, max over ranks
+
+    def barrier():
+        dist.barrier()
+
+    def max_over_ranks(v):
+        t = torch.tensor([float(v)], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    comm = Communicator.init_local(rank, world, local)
+    handles = [None] * world
+    dist.all_gather_object(handles, comm.handle_bytes())
+    comm.connect(handles)
+    barrier()
+    lib = _C.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    nccl = None
+    if not args.no_nccl:
+        from baseline.nccl_backend import NcclBackend
+
+        def exchange(payload):
+            box = [payload]
+            dist.broadcast_object_list(box, src=0)
+            return box[0]
+
+        nccl = NcclBackend(rank, world, exchange)
+
+    tdtype = torch_dtype_of(args.dtype)
+    esize = torch.tensor([], dtype=tdtype).element_size()
+    count = int(args.size_mib * MiB) // esize
+    S = count * esize
+    x = make_message(rank, count, args.dtype, dev)
+    x0 = x.clone()
+    op = comm.prepare_all_reduce([x], [x], args.reduction)
+    factor = 2.0 * (world - 1) / world
+
+    # Parity spot check of the headline message before timing (fp64 host sum of
+    # a slice; the full parity suite lives in tests/).
+    op()
+    torch.cuda.synchronize()
+    check = x[:4096].double().cpu()
+    parts = [None] * world
+    dist.all_gather_object(parts, x0[:4096].double().cpu())
+    ref = sum(parts) / (world if args.reduction.upper() == "MEAN" else 1)
+    tol = {"f32": 1e-6, "f16": 2e-3, "bf16": 1e-2}[args.dtype]
+    err = float((check - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+    assert err <= tol, "headline all-reduce off by {} (tolerance {})".format(err, tol)
+    x.copy_(x0)
+
+    sampler = ClockSampler(local)
+    with sampler:
+        launches0 = lib.dgn_launch_count()
+        per, total_ms = time_steps(op, args.steps, args.warmup, barrier)
+        launches = lib.dgn_launch_count() - launches0 - args.warmup
+        xh = x0.cpu().pin_memory()
+        yh = torch.empty_like(xh).pin_memory()
+
+        def e2e_step():
+            x.copy_(xh, non_blocking=True)
+            op()
+            yh.copy_(x, non_blocking=True)
+
+        e2e_steps = max(3, min(args.steps, 10))
+        _, e2e_ms = time_steps(e2e_step, e2e_steps, 2, barrier)
+    ms = max_over_ranks(total_ms) / args.steps
+    kernel_ms = max_over_ranks(statistics.mean(per))
+    e2e_ms = max_over_ranks(e2e_ms) / e2e_steps
+    launch = comm.last_launch()
+    busbw = S / (ms * 1e-3) / 1e9 * factor
+
+    sweep = run_sweep(args, comm, nccl, rank, world, dev, stream, barrier, max_over_ranks) if args.sweep != "off" else []
+
+    line = None
+    if rank == 0:
+        achieved = S / (kernel_ms * 1e-3) / 1e9 * factor
+        line = {
+            "metric": "allreduce bus GB/s & latency vs msg size at 2/4/8 B200 (frac of 900 GB/s)",
+            "value": busbw, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": args.dtype, "data": "synthetic",
+            "config": {
+                "workload": "Collective ALLREDUCE reduction={} {} {:g} MiB per rank, in place, comm_size={}".format(
+                    args.reduction, args.dtype, args.size_mib, world),
+                "message_bytes": S, "world_size": world,
+                "busbw": "S/t * 2(n-1)/n", "frac_of_900": busbw / NVLINK_NOMINAL_GBS,
+                "l2": "message ({:g} MiB) larger than the 126 MB L2; sweep points rotate over buffers "
+                      "totalling >= 256 MiB".format(args.size_mib),
+                "values": "uniform[-1,1) from numpy default_rng(1000+rank)",
+                "launch": launch,
+            },
+            "roofline": {"bound": "nvlink", "achieved": achieved, "peak": NVLINK_NOMINAL_GBS, "unit": "GB/s",
+                         "frac": achieved / NVLINK_NOMINAL_GBS, "traffic": None,
+                         "peak_kind": "nominal per direction per GPU; measured peer copy on this pool is "
+                                      "{:g} GB/s".format(NVLINK_MEASURED_P2P_GBS),
+                         "frac_of_measured_p2p": achieved / NVLINK_MEASURED_P2P_GBS,
+                         "algorithmic_bytes_per_launch": S * factor, "kernel_ms": kernel_ms},
+            "e2e": {"value": S / (e2e_ms * 1e-3) / 1e9 * factor, "unit": "GB/s",
+                    "h2d_bytes_per_step": S, "d2h_bytes_per_step": S, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches),
+            "clocks": sampler.summary(),
+            "sweep": sweep,
+        }
+    barrier()
+    torch.cuda.synchronize()
+    if nccl is not None:
+        nccl.destroy()
+    comm.destroy()
+    dist.destroy_process_group()
+    return line
+
+
+def run_sweep(args, comm, nccl, rank, world, dev, stream, barrier, max_over_ranks):
+    """Latency and bus bandwidth per message size, ours beside the NCCL
+    backend (operator to operator: MEAN includes the reference's scale launch)."""
+    import torch
+    from dragon_b200 import workloads
+    hi = (1 << 30) if args.sweep == "full" else (256 << 20)
+    factor = 2.0 * (world - 1) / world
+    rows = []
+    for dtype_name in ("f32", "f16"):
+        tdtype = torch_dtype_of(dtype_name)
+        esize = 4 if dtype_name == "f32" else 2
+        for nbytes in workloads.sweep_sizes(1 << 10, hi):
+            count = nbytes // esize
+            nbuf = max(1, min(32, (256 << 20) // nbytes))
+            base = make_message(rank, count, dtype_name, dev)
+            bufs = [base.clone() for _ in range(nbuf)]
+            iters = 200 if nbytes <= (1 << 20) else (40 if nbytes <= (64 << 20) else 10)
+            ops = [comm.prepare_all_reduce([b], [b], "MEAN") for b in bufs]
+            state = {"i": 0}
+
+            def ours():
+                ops[state["i"] % nbuf]()
+                state["i"] += 1
+
+            _, total = time_steps(ours, iters, 5, barrier)
+            t_ours = max_over_ranks(total) / iters
+            row = {"dtype": dtype_name, "bytes": nbytes, "ours_us": t_ours * 1e3,
+                   "ours_busbw": nbytes / (t_ours * 1e-3) / 1e9 * factor,
+                   "variant": comm.last_launch()["variant"]}
+            if nccl is not None:
+                def theirs():
+                    b = bufs[state["i"] % nbuf]
+                    nccl.operator_all_reduce([b], "MEAN", stream)
+                    state["i"] += 1
+
+                _, total = time_steps(theirs, iters, 5, barrier)
+                t_nccl = max_over_ranks(total) / iters
+                row["nccl_us"] = t_nccl * 1e3
+                row["nccl_busbw"] = nbytes / (t_nccl * 1e-3) / 1e9 * factor
+                row["speedup"] = t_nccl / t_ours
+            row["frac_of_900"] = row["ours_busbw"] / NVLINK_NOMINAL_GBS
+            rows.append(row)
+            del bufs, ops, base
+    return rows
+
+
+# --------------------------------------------------------------------------
+# reference arm: the CPU path on the host cores
+
+def bench_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    import numpy as np
+    from dragon_b200 import workloads
+    from oracle import oracle
+    n = max(1, args.gpus)
+    sample_bytes = min(int(args.size_mib * MiB), 64 * MiB)
+    count = sample_bytes // 4
+    cores = os.cpu_count() or 1
+    if n == 1:
+        x = workloads.uniform_message(0, count)
+        y = np.zeros_like(x)
+        for _ in range(min(args.warmup, 2)):
+            oracle.allreduce([x], oracle.F32, args.reduction, out=y)
+        times = []
+        for _ in range(min(args.steps, 10)):
+            t0 = time.perf_counter()
+            oracle.allreduce([x], oracle.F32, args.reduction, out=y)
+            times.append(time.perf_counter() - t0)
+        t = statistics.median(times)
+        value, used = x.nbytes / t / 1e9, 1
+        what = "comm_size=1 out-of-place all-reduce (copy) on one core"
+    else:
+        bufs = [workloads.uniform_message(r, count) for r in range(n)]
+        iters = max(2, min(args.steps, 10))
+        secs, out = oracle.mp_allreduce(bufs, oracle.F32, args.reduction, iters=iters + min(args.warmup, 2))
+        t = statistics.median(secs[min(args.warmup, 2):])
+        value, used = bufs[0].nbytes / t / 1e9 * 2.0 * (n - 1) / n, min(n, cores)
+        what = "{} rank processes over shared memory, reduce-scatter + all-gather".format(n)
+    sample = "{} MiB fp32 {} per rank ({}); Open MPI is not installed on this machine, so the CPU " \
+             "restatement of the MPI path is timed".format(sample_bytes // MiB, args.reduction, what)
+    return {
+        "impl": "reference",
+        "metric": "allreduce bus GB/s & latency vs msg size at 2/4/8 B200 (frac of 900 GB/s)"
+                  if n > 1 else "allreduce bus GB/s & latency vs msg size (frac of 900 GB/s at 2/4/8 GPUs; "
+                                "at 1 GPU: local-copy path, algorithm GB/s = S/t)",
+        "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "Collective ALLREDUCE reduction={} f32, CPU path, comm_size={}".format(args.reduction, n),
+                   "message_bytes": sample_bytes, "world_size": n},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": used, "kind": "port", "sample": sample,
+                         "host_cores": cores},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        line = bench_reference(args)
+    elif args.gpus <= 1 and int(os.environ.get("WORLD_SIZE", "1")) <= 1:
+        line = bench_single(args)
+    else:
+        line = bench_multi(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -131,7 +131,7 @@ Geometry make_geometry(int nranks) {
   g.slot_bytes = (g.slot_bytes + 4095) & ~4095ll;
   g.flags_bytes = (size_t)g.max_blocks * kMaxRanks * sizeof(u64);
   g.last_off = g.flags_bytes;
-  size_t head = g.last_off + 2 * (size_t)g.max_blocks * sizeof(u64);
+  size_t head = g.last_off + (size_t)g.max_blocks * sizeof(BlockState);
   g.stage_off = (head + 4095) & ~(size_t)4095;
   g.total = g.stage_off + 2 * (size_t)g.max_blocks * (size_t)(nranks + 1) * (size_t)g.slot_bytes;
   return g;
@@ -151,7 +151,6 @@ struct TableEntry {
 
 struct Plan {
   int variant = 0, blocks = 1, threads = 512, cv = 1, rounds = 1;
-  u64 span = 2;
 };
 
 enum OpKind { kOpAllReduce = 0, kOpReduceScatter, kOpAllGather, kOpBroadcast };
@@ -180,7 +179,6 @@ struct dgn_comm {
   bool peer_ipc[kMaxRanks] = {};
   PeerTable* d_peers = nullptr;
   bool connected = false;
-  u64 epoch = 0, opcount = 0;
   u64 wait_ns = 5000000000ull;
   int tune_variant = 0, tune_blocks = 0, tune_threads = 0;
   long long tune_chunk = 0;
@@ -198,7 +196,6 @@ struct Team {
   int n = 0, device = 0;
   std::vector<dgn_comm*> members;
   PeerTable* d_tables = nullptr;
-  u64 epoch = 0, opcount = 0;
   OpDesc pending[kMaxRanks];
   unsigned arrived = 0;
   int alive = 0;
@@ -225,7 +222,7 @@ void fill_peer_table(const dgn_comm* c, PeerTable* t) {
     t->flags[j] = reinterpret_cast<u64*>(b);
     t->stage[j] = b + c->geo.stage_off;
   }
-  t->last_epoch = reinterpret_cast<u64*>(static_cast<char*>(c->base) + c->geo.last_off);
+  t->blk = reinterpret_cast<BlockState*>(static_cast<char*>(c->base) + c->geo.last_off);
   t->status = c->status_dev;
   t->rank = c->rank;
   t->nranks = c->nranks;
@@ -291,7 +288,6 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
       p.blocks = (int)b;
       p.cv = (int)ceil_div(d.nvec, b);
       p.rounds = 1;
-      p.span = 2;
       return p;
     }
   }
@@ -312,7 +308,6 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
   p.cv = (int)cv;
   p.rounds = (int)ceil_div(per, b * cv);
   if (p.rounds < 1) p.rounds = 1;
-  p.span = 2 * (u64)p.rounds + 1;
   return p;
 }
 
@@ -336,16 +331,13 @@ KernelChoice choose_kernel(const OpDesc& d, const Plan& p) {
   return k;
 }
 
-void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p, u64 epoch,
-                 u64 opcount) {
+void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p) {
   memset(P, 0, sizeof(*P));
   P->count = d.count;
   P->nvec = d.nvec;
-  P->epoch = epoch;
   P->wait_ns = c->wait_ns;
   P->scale = (double)(1.f / (float)c->nranks);
   P->ntensors = d.ntensors;
-  P->parity = (int)(opcount & 1);
   P->rounds = p.rounds;
   P->cv = p.cv;
   P->redop = d.redop;
@@ -385,15 +377,13 @@ int issue(dgn_comm* c, const OpDesc& d) {
     KernelChoice k = choose_kernel(d, p);
     if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
     OpParams P;
-    fill_params(&P, c, d, p, c->epoch, c->opcount);
+    fill_params(&P, c, d, p);
     P.peers = c->d_peers;
     P.ra[0].in = d.in;
     P.ra[0].out = d.out;
     P.ra[0].table = d.table;
     int rc = launch(k.fn, dim3(p.blocks, 1), p.threads, k.smem, d.stream, &P, false);
     if (rc != DGN_OK) return rc;
-    c->epoch += p.span;
-    c->opcount += 1;
     c->last_plan = p;
     return DGN_OK;
   }
@@ -430,7 +420,7 @@ int issue(dgn_comm* c, const OpDesc& d) {
     k = choose_kernel(d, p);
   }
   OpParams P;
-  fill_params(&P, c, d, p, t->epoch, t->opcount);
+  fill_params(&P, c, d, p);
   P.peers = t->d_tables;
   for (int r = 0; r < t->n; ++r) {
     P.ra[r].in = t->pending[r].in;
@@ -439,8 +429,6 @@ int issue(dgn_comm* c, const OpDesc& d) {
   }
   int rc = launch(k.fn, dim3(p.blocks, t->n), p.threads, k.smem, d.stream, &P, true);
   if (rc != DGN_OK) return rc;
-  t->epoch += p.span;
-  t->opcount += 1;
   for (dgn_comm* m : t->members) m->last_plan = p;
   return DGN_OK;
 }
@@ -460,7 +448,7 @@ int launch_local_copy(dgn_comm* c, const OpDesc& d, int es) {
   p.blocks = (int)b;
   p.variant = 0;
   OpParams P;
-  fill_params(&P, c, d, p, 0, 0);
+  fill_params(&P, c, d, p);
   P.ra[0].in = d.in;
   P.ra[0].out = d.out;
   P.ra[0].table = d.table;

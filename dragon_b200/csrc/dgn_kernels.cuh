@@ -18,11 +18,17 @@
 // on its own slice of the message.  All waits are bounded: when the limit runs
 // out the block records DGN_ERR_TIMEOUT in the status word and leaves.
 //
-// Reuse safety.  Consecutive collectives alternate `parity`.  A block records
-// the last epoch it finished for each parity; before it touches any peer's
-// parity-p region again it waits until every peer's block b has signalled that
-// epoch ("done" signal), i.e. has stopped reading the data of the collective
-// that last used the region.
+// Protocol state is device-resident: block b keeps its next epoch number, its
+// collective count (whose low bit is the staging parity) and, per parity, the
+// epoch with which it last finished, in its own BlockState.  Every rank runs
+// the same sequence of collectives with the same launch shapes, so block b of
+// every rank holds the same numbers without any host bookkeeping, and a
+// captured launch can be replayed.
+//
+// Reuse safety.  Consecutive collectives of a block alternate parity.  Before
+// a block touches any peer's parity-p region again it waits until every
+// peer's block b has signalled the epoch with which the previous parity-p
+// collective finished ("done" signal), i.e. has stopped reading its data.
 //
 // Data always moves as 16-byte vectors with ld/st.global.cg (L2-coherent, no
 // L1 allocation), so data published by a peer before its release-store of a
@@ -45,11 +51,18 @@ enum : int { kErrTimeout = 3 };
 
 typedef unsigned long long u64;
 
+// Per-block protocol state (local device memory, touched by block b only).
+struct BlockState {
+  u64 epoch;         // last epoch number used by this block
+  u64 ops;           // collectives this block took part in; low bit = parity
+  u64 last_done[2];  // per parity: epoch of the last "done" signal
+};
+
 // One rank's view of the team.  Lives in that rank's device memory.
 struct PeerTable {
   char* stage[kMaxRanks];  // rank j's staging base, as mapped on this device
   u64* flags[kMaxRanks];   // rank j's flag array, as mapped on this device
-  u64* last_epoch;         // [2][max_blocks], local
+  struct BlockState* blk;  // [max_blocks], local
   int* status;             // error word (pinned host memory, device-visible)
   int rank, nranks, max_blocks, reserved;
   long long slot_bytes;    // bytes per slot
@@ -75,11 +88,9 @@ struct OpParams {
   RankArgs ra[kMaxRanks];  // indexed by blockIdx.y
   long long count;         // elements per rank (single tensor / per-rank block)
   long long nvec;          // flat 16-byte vectors of the message
-  u64 epoch;               // epochs epoch+1 .. epoch+span belong to this launch
   u64 wait_ns;
   double scale;            // MEAN factor, double(1.f / float(nranks))
   int ntensors;
-  int parity;
   int rounds;
   int cv;                  // vectors per block per round (<= slot_bytes / 16)
   int redop;
@@ -402,13 +413,25 @@ __device__ __forceinline__ long long clampll(long long x, long long lo, long lon
 }
 
 // Start-of-launch guard and end-of-launch bookkeeping shared by all kernels.
-__device__ __forceinline__ bool begin_collective(const PeerTable& pt, int b, const OpParams& P) {
-  const u64 prev = pt.last_epoch[(size_t)P.parity * pt.max_blocks + b];
-  return wait_peers(pt, b, prev, P.wait_ns);
+// Epochs base+1 .. base+span belong to the launch; `done` = base + span.
+struct Turn {
+  u64 base;
+  int parity;
+};
+__device__ __forceinline__ bool begin_collective(const PeerTable& pt, int b, const OpParams& P, Turn* turn) {
+  const BlockState st = pt.blk[b];
+  turn->base = st.epoch;
+  turn->parity = (int)(st.ops & 1ull);
+  return wait_peers(pt, b, st.last_done[turn->parity], P.wait_ns);
 }
-__device__ __forceinline__ void end_collective(const PeerTable& pt, int b, const OpParams& P, u64 done) {
+__device__ __forceinline__ void end_collective(const PeerTable& pt, int b, const Turn& turn, u64 done) {
   signal_peers(pt, b, done);
-  if (threadIdx.x == 0) pt.last_epoch[(size_t)P.parity * pt.max_blocks + b] = done;
+  if (threadIdx.x == 0) {
+    BlockState* st = pt.blk + b;
+    st->epoch = done;
+    st->ops += 1;
+    st->last_done[turn.parity] = done;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -423,23 +446,24 @@ __global__ void __launch_bounds__(512, 1) ar_oneshot_kernel(const OpParams P) {
   const RankArgs& ra = P.ra[blockIdx.y];
   const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
   const Message<(int)sizeof(T), TABLE> msg = make_message<(int)sizeof(T), TABLE>(P, ra, smem);
-  if (!begin_collective(pt, b, P)) return;
+  Turn turn;
+  if (!begin_collective(pt, b, P, &turn)) return;
 
   const long long v0 = (long long)b * P.cv;
   const long long len = clampll(P.nvec - v0, 0, P.cv);
   char* dst[kMaxRanks];  // dst[k]: my slot in the inbox of peer (r + k) % n
 #pragma unroll
-  for (int k = 1; k < kMaxRanks; ++k) dst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, P.parity, b, r) : nullptr;
+  for (int k = 1; k < kMaxRanks; ++k) dst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, turn.parity, b, r) : nullptr;
   for (long long v = threadIdx.x; v < len; v += blockDim.x) {
     const uint4 x = msg.load(v0 + v);
 #pragma unroll
     for (int k = 1; k < kMaxRanks; ++k)
       if (k < n) stv(dst[k] + v * 16, x);
   }
-  signal_peers(pt, b, P.epoch + 1);
-  if (!wait_peers(pt, b, P.epoch + 1, P.wait_ns)) return;
+  signal_peers(pt, b, turn.base + 1);
+  if (!wait_peers(pt, b, turn.base + 1, P.wait_ns)) return;
 
-  const char* const inbox0 = slot_ptr(pt, r, P.parity, b, 0);
+  const char* const inbox0 = slot_ptr(pt, r, turn.parity, b, 0);
   for (long long v = threadIdx.x; v < len; v += blockDim.x) {
     uint4 x[kMaxRanks];
 #pragma unroll
@@ -448,7 +472,7 @@ __global__ void __launch_bounds__(512, 1) ar_oneshot_kernel(const OpParams P) {
     }
     msg.store(v0 + v, reduce_dispatch<T>(x, n, P.redop, P.scale));
   }
-  end_collective(pt, b, P, P.epoch + 2);
+  end_collective(pt, b, turn, turn.base + 2);
 }
 
 // ---------------------------------------------------------------------------
@@ -474,7 +498,8 @@ __global__ void __launch_bounds__(512, 1) ar_twoshot_kernel(const OpParams P) {
   const RankArgs& ra = P.ra[blockIdx.y];
   const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
   const Message<ES, TABLE> msg = make_message<ES, TABLE>(P, ra, smem);
-  if (!begin_collective(pt, b, P)) return;
+  Turn turn;
+  if (!begin_collective(pt, b, P, &turn)) return;
 
   // Shard geometry.  AR: shards are consecutive runs of the flat message.
   // RS: shard s is the s-th block of `count` elements of the input.
@@ -494,8 +519,8 @@ __global__ void __launch_bounds__(512, 1) ar_twoshot_kernel(const OpParams P) {
     return msg.load((long long)s * vs + v);
   };
 
-  char* const my_outbox = slot_ptr(pt, r, P.parity, b, n);
-  const char* const inbox0 = slot_ptr(pt, r, P.parity, b, 0);
+  char* const my_outbox = slot_ptr(pt, r, turn.parity, b, n);
+  const char* const inbox0 = slot_ptr(pt, r, turn.parity, b, 0);
   int peer[kMaxRanks];           // peer[k] = (r + k) % n
   char* push_dst[kMaxRanks];     // my slot in peer[k]'s inbox
   const char* pull_src[kMaxRanks];  // peer[k]'s outbox
@@ -503,13 +528,13 @@ __global__ void __launch_bounds__(512, 1) ar_twoshot_kernel(const OpParams P) {
 #pragma unroll
   for (int k = 1; k < kMaxRanks; ++k) {
     peer[k] = (k < n) ? (r + k) % n : 0;
-    push_dst[k] = (k < n) ? slot_ptr(pt, peer[k], P.parity, b, r) : nullptr;
-    pull_src[k] = (k < n) ? slot_ptr(pt, peer[k], P.parity, b, n) : nullptr;
+    push_dst[k] = (k < n) ? slot_ptr(pt, peer[k], turn.parity, b, r) : nullptr;
+    pull_src[k] = (k < n) ? slot_ptr(pt, peer[k], turn.parity, b, n) : nullptr;
     plen[k] = (k < n) ? shard_len(peer[k]) : 0;
   }
   for (int round = 0; round < P.rounds; ++round) {
     const long long off = ((long long)round * gridDim.x + b) * P.cv;
-    const u64 e_push = P.epoch + 2 * (u64)round + 1, e_red = e_push + 1;
+    const u64 e_push = turn.base + 2 * (u64)round + 1, e_red = e_push + 1;
 
     // 1. push
     // All loads of an iteration are issued before the first store, so a
@@ -563,7 +588,7 @@ __global__ void __launch_bounds__(512, 1) ar_twoshot_kernel(const OpParams P) {
         if (k < n && off + v < plen[k]) msg.store((long long)peer[k] * vs + off + v, x[k]);
     }
   }
-  end_collective(pt, b, P, P.epoch + 2 * (u64)P.rounds + 1);
+  end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
 }
 
 // ---------------------------------------------------------------------------
@@ -577,23 +602,24 @@ __global__ void __launch_bounds__(512, 1) allgather_kernel(const OpParams P) {
   const PeerTable& pt = P.peers[blockIdx.y];
   const RankArgs& ra = P.ra[blockIdx.y];
   const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
-  if (!begin_collective(pt, b, P)) return;
+  Turn turn;
+  if (!begin_collective(pt, b, P, &turn)) return;
   const char* in = static_cast<const char*>(ra.in);
   char* out = static_cast<char*>(ra.out);
   const bool in_al = is_al16(in);
-  char* const my_outbox = slot_ptr(pt, r, P.parity, b, n);
+  char* const my_outbox = slot_ptr(pt, r, turn.parity, b, n);
   int peer[kMaxRanks];
   const char* pull_src[kMaxRanks];
 #pragma unroll
   for (int k = 1; k < kMaxRanks; ++k) {
     peer[k] = (k < n) ? (r + k) % n : 0;
-    pull_src[k] = (k < n) ? slot_ptr(pt, peer[k], P.parity, b, n) : nullptr;
+    pull_src[k] = (k < n) ? slot_ptr(pt, peer[k], turn.parity, b, n) : nullptr;
   }
 
   for (int round = 0; round < P.rounds; ++round) {
     const long long off = ((long long)round * gridDim.x + b) * P.cv;
     const long long len = clampll(P.nvec - off, 0, P.cv);
-    const u64 e_pub = P.epoch + 2 * (u64)round + 1, e_got = e_pub + 1;
+    const u64 e_pub = turn.base + 2 * (u64)round + 1, e_got = e_pub + 1;
     char* mine = out + (long long)r * P.count;
     const bool mine_al = is_al16(mine);
     for (long long v = threadIdx.x; v < len; v += blockDim.x) {
@@ -619,7 +645,7 @@ __global__ void __launch_bounds__(512, 1) allgather_kernel(const OpParams P) {
     signal_peers(pt, b, e_got);
     if (round + 1 < P.rounds && !wait_peers(pt, b, e_got, P.wait_ns)) return;
   }
-  end_collective(pt, b, P, P.epoch + 2 * (u64)P.rounds + 1);
+  end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
 }
 
 // ---------------------------------------------------------------------------
@@ -631,15 +657,16 @@ __global__ void __launch_bounds__(512, 1) broadcast_kernel(const OpParams P) {
   const PeerTable& pt = P.peers[blockIdx.y];
   const RankArgs& ra = P.ra[blockIdx.y];
   const int r = pt.rank, n = pt.nranks, b = blockIdx.x, root = P.root;
-  if (!begin_collective(pt, b, P)) return;
+  Turn turn;
+  if (!begin_collective(pt, b, P, &turn)) return;
   char* buf = static_cast<char*>(ra.out);
   const bool al = is_al16(buf);
-  char* const root_outbox = slot_ptr(pt, root, P.parity, b, n);
+  char* const root_outbox = slot_ptr(pt, root, turn.parity, b, n);
 
   for (int round = 0; round < P.rounds; ++round) {
     const long long off = ((long long)round * gridDim.x + b) * P.cv;
     const long long len = clampll(P.nvec - off, 0, P.cv);
-    const u64 e_pub = P.epoch + 2 * (u64)round + 1, e_got = e_pub + 1;
+    const u64 e_pub = turn.base + 2 * (u64)round + 1, e_got = e_pub + 1;
     if (r == root) {
       for (long long v = threadIdx.x; v < len; v += blockDim.x)
         stv(root_outbox + v * 16, load_vec<1>(buf, off + v, P.count, al));
@@ -652,7 +679,7 @@ __global__ void __launch_bounds__(512, 1) broadcast_kernel(const OpParams P) {
       signal_peers(pt, b, e_got, root);
     }
   }
-  end_collective(pt, b, P, P.epoch + 2 * (u64)P.rounds + 1);
+  end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
 }
 
 // ---------------------------------------------------------------------------

@@ -126,34 +126,37 @@ uint16_t orc_f32_to_bf16(float f) {
 
 /* ---- elementwise reduction over ranks ------------------------------------ */
 
-#define ORC_COMBINE(acc, v, op)                 \
-  do {                                          \
-    switch (op) {                               \
-      case ORC_PROD: acc = acc * (v); break;    \
-      case ORC_MIN: acc = (v) < acc ? (v) : acc; break; \
-      case ORC_MAX: acc = (v) > acc ? (v) : acc; break; \
-      default: acc = acc + (v); break;          \
-    }                                           \
-  } while (0)
+/* One loop per reduction so that the compiler can vectorise it; the order
+ * over ranks stays ascending in every loop. */
+#define ORC_LOOP(T, LOAD, COMBINE, FINISH)                 \
+  for (int64_t i = lo; i < hi; ++i) {                      \
+    T acc = LOAD(0, i);                                    \
+    for (int r = 1; r < n; ++r) {                          \
+      T v = LOAD(r, i);                                    \
+      COMBINE;                                             \
+    }                                                      \
+    FINISH;                                                \
+  }
+#define ORC_BY_OP(T, LOAD, SUMX, PRODX, STORE, STORE_MEAN)                \
+  switch (op) {                                                           \
+    case ORC_PROD: ORC_LOOP(T, LOAD, PRODX, STORE) break;                 \
+    case ORC_MIN: ORC_LOOP(T, LOAD, acc = v < acc ? v : acc, STORE) break; \
+    case ORC_MAX: ORC_LOOP(T, LOAD, acc = v > acc ? v : acc, STORE) break; \
+    case ORC_MEAN: ORC_LOOP(T, LOAD, SUMX, STORE_MEAN) break;             \
+    default: ORC_LOOP(T, LOAD, SUMX, STORE) break;                        \
+  }
 
 /* Unsigned arithmetic gives the two's-complement wraparound without UB. */
-#define ORC_INT_KERNEL(NAME, T, UT)                                                      \
+#define ORC_INT_KERNEL(NAME, T, UT)                                                            \
   static void NAME(const void* const* in, int n, int64_t lo, int64_t hi, int op, void* out) { \
-    T* y = (T*)out;                                                                      \
-    for (int64_t i = lo; i < hi; ++i) {                                                  \
-      T acc = ((const T*)in[0])[i];                                                      \
-      for (int r = 1; r < n; ++r) {                                                      \
-        T v = ((const T*)in[r])[i];                                                      \
-        switch (op) {                                                                    \
-          case ORC_PROD: acc = (T)((UT)acc * (UT)v); break;                              \
-          case ORC_MIN: acc = v < acc ? v : acc; break;                                  \
-          case ORC_MAX: acc = v > acc ? v : acc; break;                                  \
-          default: acc = (T)((UT)acc + (UT)v); break;                                    \
-        }                                                                                \
-      }                                                                                  \
-      y[i] = acc;                                                                        \
-    }                                                                                    \
+    T* y = (T*)out;                                                                            \
+    ORC_BY_OP(T, ORC_LOAD_##NAME, acc = (T)((UT)acc + (UT)v), acc = (T)((UT)acc * (UT)v),      \
+              y[i] = acc, y[i] = acc)                                                          \
   }
+#define ORC_LOAD_orc_red_u8(r, i) (((const uint8_t*)in[r])[i])
+#define ORC_LOAD_orc_red_i8(r, i) (((const int8_t*)in[r])[i])
+#define ORC_LOAD_orc_red_i32(r, i) (((const int32_t*)in[r])[i])
+#define ORC_LOAD_orc_red_i64(r, i) (((const int64_t*)in[r])[i])
 
 ORC_INT_KERNEL(orc_red_u8, uint8_t, uint8_t)
 ORC_INT_KERNEL(orc_red_i8, int8_t, uint8_t)
@@ -163,45 +166,30 @@ ORC_INT_KERNEL(orc_red_i64, int64_t, uint64_t)
 static void orc_red_f32(const void* const* in, int n, int64_t lo, int64_t hi, int op, void* out) {
   float* y = (float*)out;
   const float scale = 1.f / (float)n;
-  for (int64_t i = lo; i < hi; ++i) {
-    float acc = ((const float*)in[0])[i];
-    for (int r = 1; r < n; ++r) {
-      float v = ((const float*)in[r])[i];
-      ORC_COMBINE(acc, v, op);
-    }
-    y[i] = (op == ORC_MEAN) ? acc * scale : acc;
-  }
+#define ORC_LD(r, i) (((const float*)in[r])[i])
+  ORC_BY_OP(float, ORC_LD, acc = acc + v, acc = acc * v, y[i] = acc, y[i] = acc * scale)
+#undef ORC_LD
 }
 
 static void orc_red_f64(const void* const* in, int n, int64_t lo, int64_t hi, int op, void* out) {
   double* y = (double*)out;
   /* The reference passes the scale as a float (collective_op.cc:44-46). */
   const double scale = (double)(1.f / (float)n);
-  for (int64_t i = lo; i < hi; ++i) {
-    double acc = ((const double*)in[0])[i];
-    for (int r = 1; r < n; ++r) {
-      double v = ((const double*)in[r])[i];
-      ORC_COMBINE(acc, v, op);
-    }
-    y[i] = (op == ORC_MEAN) ? acc * scale : acc;
-  }
+#define ORC_LD(r, i) (((const double*)in[r])[i])
+  ORC_BY_OP(double, ORC_LD, acc = acc + v, acc = acc * v, y[i] = acc, y[i] = acc * scale)
+#undef ORC_LD
 }
 
 static void orc_red_h(const void* const* in, int n, int64_t lo, int64_t hi, int op, void* out,
                       int bf) {
   uint16_t* y = (uint16_t*)out;
   const float scale = 1.f / (float)n;
-  for (int64_t i = lo; i < hi; ++i) {
-    uint16_t h0 = ((const uint16_t*)in[0])[i];
-    float acc = bf ? orc_bf16_to_f32(h0) : orc_f16_to_f32(h0);
-    for (int r = 1; r < n; ++r) {
-      uint16_t h = ((const uint16_t*)in[r])[i];
-      float v = bf ? orc_bf16_to_f32(h) : orc_f16_to_f32(h);
-      ORC_COMBINE(acc, v, op);
-    }
-    if (op == ORC_MEAN) acc = acc * scale;
-    y[i] = bf ? orc_f32_to_bf16(acc) : orc_f32_to_f16(acc);
-  }
+#define ORC_LD(r, i) \
+  (bf ? orc_bf16_to_f32(((const uint16_t*)in[r])[i]) : orc_f16_to_f32(((const uint16_t*)in[r])[i]))
+#define ORC_ST(x) y[i] = bf ? orc_f32_to_bf16(x) : orc_f32_to_f16(x)
+  ORC_BY_OP(float, ORC_LD, acc = acc + v, acc = acc * v, ORC_ST(acc), ORC_ST(acc * scale))
+#undef ORC_LD
+#undef ORC_ST
 }
 
 /* Reduce elements [lo, hi) of n rank buffers into out[lo, hi). */

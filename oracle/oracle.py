@@ -85,11 +85,12 @@ def _prep(bufs, dtype):
     return out
 
 
-def allreduce(bufs, dtype, redop="SUM"):
+def allreduce(bufs, dtype, redop="SUM", out=None):
     """Result every rank must hold after ALLREDUCE of the per-rank arrays."""
     op = REDOPS[redop.upper()] if isinstance(redop, str) else redop
     bufs = _prep(bufs, dtype)
-    out = np.empty_like(bufs[0])
+    if out is None:
+        out = np.empty_like(bufs[0])
     rc = lib().orc_allreduce(_ptrs(bufs), len(bufs), bufs[0].size, dtype, op, out.ctypes.data)
     if rc != 0:
         raise ValueError("oracle rejected allreduce(dtype={}, redop={})".format(dtype, redop))
