@@ -418,16 +418,47 @@ def bench_multi(args):
     return line
 
 
+def time_graph(fn, ops_per_graph, replays, barrier):
+    """Device time per call of fn() with the host out of the way: `ops_per_graph`
+    calls are captured into one CUDA graph and the graph is replayed."""
+    import torch
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(ops_per_graph):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(replays):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    barrier()
+    return start.elapsed_time(stop) / (replays * ops_per_graph)
+
+
 def run_sweep(args, comm, nccl, rank, world, dev, stream, barrier, max_over_ranks):
     """Latency and bus bandwidth per message size, ours beside the NCCL
-    backend (operator to operator: MEAN includes the reference's scale launch)."""
+    backend (operator to operator: MEAN includes the reference's scale launch).
+    Every point is timed eagerly (one host call per op, CUDA events around the
+    loop); points up to 1 MiB are also timed as replayed CUDA graphs, which
+    takes the host launch path out of the latency."""
     import torch
     from dragon_b200 import workloads
     hi = (1 << 30) if args.sweep == "full" else (256 << 20)
     factor = 2.0 * (world - 1) / world
     rows = []
     for dtype_name in ("f32", "f16"):
-        tdtype = torch_dtype_of(dtype_name)
         esize = 4 if dtype_name == "f32" else 2
         for nbytes in workloads.sweep_sizes(1 << 10, hi):
             count = nbytes // esize
@@ -442,22 +473,27 @@ def run_sweep(args, comm, nccl, rank, world, dev, stream, barrier, max_over_rank
                 ops[state["i"] % nbuf]()
                 state["i"] += 1
 
+            def theirs():
+                b = bufs[state["i"] % nbuf]
+                nccl.operator_all_reduce([b], "MEAN", torch.cuda.current_stream().cuda_stream)
+                state["i"] += 1
+
             _, total = time_steps(ours, iters, 5, barrier)
             t_ours = max_over_ranks(total) / iters
             row = {"dtype": dtype_name, "bytes": nbytes, "ours_us": t_ours * 1e3,
                    "ours_busbw": nbytes / (t_ours * 1e-3) / 1e9 * factor,
                    "variant": comm.last_launch()["variant"]}
             if nccl is not None:
-                def theirs():
-                    b = bufs[state["i"] % nbuf]
-                    nccl.operator_all_reduce([b], "MEAN", stream)
-                    state["i"] += 1
-
                 _, total = time_steps(theirs, iters, 5, barrier)
                 t_nccl = max_over_ranks(total) / iters
                 row["nccl_us"] = t_nccl * 1e3
                 row["nccl_busbw"] = nbytes / (t_nccl * 1e-3) / 1e9 * factor
                 row["speedup"] = t_nccl / t_ours
+            if nbytes <= (1 << 20):
+                row["ours_graph_us"] = max_over_ranks(time_graph(ours, 20, 10, barrier)) * 1e3
+                if nccl is not None:
+                    row["nccl_graph_us"] = max_over_ranks(time_graph(theirs, 20, 10, barrier)) * 1e3
+                    row["graph_speedup"] = row["nccl_graph_us"] / row["ours_graph_us"]
             row["frac_of_900"] = row["ours_busbw"] / NVLINK_NOMINAL_GBS
             rows.append(row)
             del bufs, ops, base

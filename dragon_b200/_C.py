@@ -7,7 +7,8 @@ raises, there is no fallback.
 import ctypes
 import os
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libdgn.so")
+_LIB_PATH = os.environ.get("DGN_LIBRARY") or os.path.join(
+    os.path.dirname(os.path.abspath(__file__)), "lib", "libdgn.so")
 
 HANDLE_BYTES = 256
 MAX_RANKS = 8
@@ -16,7 +17,7 @@ OK, ERR_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_PEER, ERR_STATE, ERR_UNSUPPORTED = range
 
 U8, I8, I32, I64, F16, BF16, F32, F64 = range(8)
 SUM, MEAN, PROD, MIN, MAX = range(5)
-VARIANT_AUTO, VARIANT_ONESHOT, VARIANT_TWOSHOT, VARIANT_NVLS = range(4)
+VARIANT_AUTO, VARIANT_ONESHOT, VARIANT_TWOSHOT, VARIANT_NVLS, VARIANT_LL = range(5)
 
 REDOPS = {"SUM": SUM, "MEAN": MEAN, "PROD": PROD, "MIN": MIN, "MAX": MAX}
 

@@ -115,25 +115,33 @@ uint64_t host_identity() {
 }
 
 struct Geometry {
-  int nranks = 1, max_blocks = 0;
-  long long slot_bytes = 0;
-  size_t flags_bytes = 0, last_off = 0, stage_off = 0, total = 0;
+  int nranks = 1, max_blocks = 0, ll_max_blocks = 0;
+  long long slot_bytes = 0, ll_slot_bytes = 0;
+  size_t flags_bytes = 0, blk_off = 0, stage_off = 0, ll_off = 0, total = 0;
 };
 
+// Workspace layout: [flags][block states] | [staging] | [low-latency region].
 Geometry make_geometry(int nranks) {
   Geometry g;
   g.nranks = nranks;
-  g.max_blocks = (int)env_ll("DGN_MAX_BLOCKS", 128);
+  g.max_blocks = (int)env_ll("DGN_MAX_BLOCKS", 160);
   if (g.max_blocks < 1) g.max_blocks = 1;
   if (g.max_blocks > 1024) g.max_blocks = 1024;
-  g.slot_bytes = env_ll("DGN_SLOT_BYTES", 64 * 1024);
+  g.slot_bytes = env_ll("DGN_SLOT_BYTES", 128 * 1024);
   if (g.slot_bytes < 4096) g.slot_bytes = 4096;
   g.slot_bytes = (g.slot_bytes + 4095) & ~4095ll;
-  g.flags_bytes = (size_t)g.max_blocks * kMaxRanks * sizeof(u64);
-  g.last_off = g.flags_bytes;
-  size_t head = g.last_off + (size_t)g.max_blocks * sizeof(BlockState);
+  g.ll_max_blocks = (int)env_ll("DGN_LL_MAX_BLOCKS", 32);
+  if (g.ll_max_blocks < 1) g.ll_max_blocks = 1;
+  if (g.ll_max_blocks > g.max_blocks) g.ll_max_blocks = g.max_blocks;
+  g.ll_slot_bytes = env_ll("DGN_LL_SLOT_BYTES", 32 * 1024);
+  if (g.ll_slot_bytes < 4096) g.ll_slot_bytes = 4096;
+  g.ll_slot_bytes = (g.ll_slot_bytes + 4095) & ~4095ll;
+  g.flags_bytes = (size_t)g.max_blocks * 3 * kMaxRanks * sizeof(u64);
+  g.blk_off = g.flags_bytes;
+  size_t head = g.blk_off + (size_t)g.max_blocks * sizeof(BlockState);
   g.stage_off = (head + 4095) & ~(size_t)4095;
-  g.total = g.stage_off + 2 * (size_t)g.max_blocks * (size_t)(nranks + 1) * (size_t)g.slot_bytes;
+  g.ll_off = g.stage_off + 2 * (size_t)g.max_blocks * 2 * (size_t)(2 * nranks) * (size_t)g.slot_bytes;
+  g.total = g.ll_off + 2 * (size_t)g.ll_max_blocks * (size_t)nranks * (size_t)g.ll_slot_bytes;
   return g;
 }
 
@@ -177,12 +185,13 @@ struct dgn_comm {
   int* status_dev = nullptr;
   void* peer_base[kMaxRanks] = {};
   bool peer_ipc[kMaxRanks] = {};
-  PeerTable* d_peers = nullptr;
+  PeerTable table;  // this rank's view of the team, copied into every launch
   bool connected = false;
   u64 wait_ns = 5000000000ull;
   int tune_variant = 0, tune_blocks = 0, tune_threads = 0;
   long long tune_chunk = 0;
-  long long oneshot_max_bytes = -1;
+  long long oneshot_max_bytes = -1, ll_max_bytes = -1;
+  bool fused_twoshot = false;  // DGN_TWOSHOT_FUSED=1: lock-step two-shot kernel instead of the warp-specialised one
   Team* team = nullptr;
   std::vector<TableEntry> tables;
   uint64_t table_clock = 0;
@@ -195,7 +204,6 @@ namespace {
 struct Team {
   int n = 0, device = 0;
   std::vector<dgn_comm*> members;
-  PeerTable* d_tables = nullptr;
   OpDesc pending[kMaxRanks];
   unsigned arrived = 0;
   int alive = 0;
@@ -205,6 +213,7 @@ int alloc_workspace(dgn_comm* c) {
   DeviceGuard g(c->device);
   DGN_CUDA(cudaMalloc(&c->base, c->geo.total));
   DGN_CUDA(cudaMemset(c->base, 0, c->geo.stage_off));
+  DGN_CUDA(cudaMemset(static_cast<char*>(c->base) + c->geo.ll_off, 0, c->geo.total - c->geo.ll_off));
   DGN_CUDA(cudaHostAlloc((void**)&c->status_host, 64, cudaHostAllocMapped | cudaHostAllocPortable));
   *c->status_host = 0;
   DGN_CUDA(cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0));
@@ -221,13 +230,16 @@ void fill_peer_table(const dgn_comm* c, PeerTable* t) {
     char* b = static_cast<char*>(c->peer_base[j]);
     t->flags[j] = reinterpret_cast<u64*>(b);
     t->stage[j] = b + c->geo.stage_off;
+    t->ll[j] = b + c->geo.ll_off;
   }
-  t->blk = reinterpret_cast<BlockState*>(static_cast<char*>(c->base) + c->geo.last_off);
+  t->blk = reinterpret_cast<BlockState*>(static_cast<char*>(c->base) + c->geo.blk_off);
   t->status = c->status_dev;
   t->rank = c->rank;
   t->nranks = c->nranks;
   t->max_blocks = c->geo.max_blocks;
+  t->ll_max_blocks = c->geo.ll_max_blocks;
   t->slot_bytes = c->geo.slot_bytes;
+  t->ll_slot_bytes = c->geo.ll_slot_bytes;
 }
 
 const void* reduce_fn(int dtype, int kind, bool table) {
@@ -245,6 +257,12 @@ const void* reduce_fn(int dtype, int kind, bool table) {
 }
 
 long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
+
+long long default_ll_max(int n) {
+  if (n <= 2) return 256ll << 10;
+  if (n <= 4) return 128ll << 10;
+  return 64ll << 10;
+}
 
 long long default_oneshot_max(int n) {
   // Above these sizes the (n - 1)x link traffic of one-shot costs more than
@@ -265,7 +283,7 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
   if (c->tune_blocks > 0 && c->tune_blocks < bmax) bmax = c->tune_blocks;
   if (bmax < 1) bmax = 1;
   p.threads = c->tune_threads > 0 ? c->tune_threads : 512;
-  if (p.threads > 512) p.threads = 512;
+  if (p.threads > kMaxThreads) p.threads = kMaxThreads;
   if (p.threads < 32) p.threads = 32;
   p.threads = (p.threads / 32) * 32;
   long long cv_cap = slot_vecs;
@@ -273,6 +291,31 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
 
   if (d.kind == kOpAllReduce) {
     const long long bytes = d.nvec * 16;
+    // Low-latency one-shot: flag-in-data lines, no barrier at all.
+    const long long ll_vecs = c->geo.ll_slot_bytes / 32;  // data vectors per LL slot
+    int ll_bmax = c->geo.ll_max_blocks;
+    if (block_cap > 0 && block_cap < ll_bmax) ll_bmax = block_cap;
+    const bool ll_fits = ceil_div(d.nvec, ll_bmax) <= ll_vecs;
+    const long long ll_thr = c->ll_max_bytes >= 0 ? c->ll_max_bytes : default_ll_max(n);
+    bool ll = ll_fits && bytes <= ll_thr;
+    if (c->tune_variant == DGN_VARIANT_LL) ll = ll_fits;
+    else if (c->tune_variant != DGN_VARIANT_AUTO) ll = false;
+    if (ll) {
+      p.variant = DGN_VARIANT_LL;
+      long long b = ceil_div(d.nvec, 256);
+      if (c->tune_blocks > 0) b = c->tune_blocks;
+      if (b > ll_bmax) b = ll_bmax;
+      if (b < 1) b = 1;
+      if (ceil_div(d.nvec, b) > ll_vecs) b = ceil_div(d.nvec, ll_vecs);
+      p.blocks = (int)b;
+      p.cv = (int)ceil_div(d.nvec, b);
+      p.rounds = 1;
+      if (c->tune_threads <= 0) {
+        long long t = ((long long)p.cv + 31) / 32 * 32;
+        p.threads = (int)(t < 64 ? 64 : (t > 512 ? 512 : t));
+      }
+      return p;
+    }
     const long long thr = c->oneshot_max_bytes >= 0 ? c->oneshot_max_bytes : default_oneshot_max(n);
     bool oneshot = bytes <= thr;
     if (c->tune_variant == DGN_VARIANT_ONESHOT) oneshot = true;
@@ -296,7 +339,7 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
   long long per = d.nvec;
   if (d.kind == kOpAllReduce) per = ceil_div(d.nvec, n);
   p.variant = DGN_VARIANT_TWOSHOT;
-  int bdef = bmax < 64 ? bmax : 64;
+  int bdef = bmax < c->num_sms ? bmax : c->num_sms;  // one block per SM
   if (c->tune_blocks > 0) bdef = bmax;
   long long b = ceil_div(per, 512);
   if (b > bdef) b = bdef;
@@ -316,12 +359,12 @@ struct KernelChoice {
   size_t smem = 0;
 };
 
-KernelChoice choose_kernel(const OpDesc& d, const Plan& p) {
+KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
   KernelChoice k;
   const bool table = d.ntensors > 1;
   switch (d.kind) {
     case kOpAllReduce:
-      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_ONESHOT ? 0 : 1, table);
+      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_LL ? 3 : (p.variant == DGN_VARIANT_ONESHOT ? 0 : (p.threads >= 96 && p.rounds >= 3 && !c->fused_twoshot ? 4 : 1)), table);
       k.smem = table ? table_smem_bytes(d.ntensors) : 0;
       break;
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
@@ -374,11 +417,11 @@ int issue(dgn_comm* c, const OpDesc& d) {
   DeviceGuard g(c->device);
   if (!c->team) {
     Plan p = make_plan(c, d, 0);
-    KernelChoice k = choose_kernel(d, p);
+    KernelChoice k = choose_kernel(c, d, p);
     if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
     OpParams P;
     fill_params(&P, c, d, p);
-    P.peers = c->d_peers;
+    P.peers[0] = c->table;
     P.ra[0].in = d.in;
     P.ra[0].out = d.out;
     P.ra[0].table = d.table;
@@ -409,7 +452,7 @@ int issue(dgn_comm* c, const OpDesc& d) {
 
   // Shape the launch so that every block of every virtual rank is resident.
   Plan p = make_plan(c, d, 0);
-  KernelChoice k = choose_kernel(d, p);
+  KernelChoice k = choose_kernel(c, d, p);
   if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
   int per_sm = 0;
   DGN_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k.fn, p.threads, k.smem));
@@ -417,12 +460,12 @@ int issue(dgn_comm* c, const OpDesc& d) {
   if (cap < 1) return fail(DGN_ERR_UNSUPPORTED, "emulated team does not fit on the device");
   if (p.blocks > cap) {
     p = make_plan(c, d, cap);
-    k = choose_kernel(d, p);
+    k = choose_kernel(c, d, p);
   }
   OpParams P;
   fill_params(&P, c, d, p);
-  P.peers = t->d_tables;
   for (int r = 0; r < t->n; ++r) {
+    P.peers[r] = t->members[r]->table;
     P.ra[r].in = t->pending[r].in;
     P.ra[r].out = t->pending[r].out;
     P.ra[r].table = t->pending[r].table;
@@ -515,7 +558,6 @@ void free_comm(dgn_comm* c) {
   }
   for (int j = 0; j < c->nranks; ++j)
     if (j != c->rank && c->peer_ipc[j] && c->peer_base[j]) cudaIpcCloseMemHandle(c->peer_base[j]);
-  if (!c->team && c->d_peers) cudaFree(c->d_peers);
   if (c->base) cudaFree(c->base);
   if (c->status_host) cudaFreeHost(c->status_host);
   if (!c->rdv_ok_file.empty()) unlink(c->rdv_ok_file.c_str());
@@ -587,6 +629,8 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
   c->geo = make_geometry(nranks);
   c->wait_ns = (u64)env_ll("DGN_WAIT_LIMIT_MS", 5000) * 1000000ull;
   c->oneshot_max_bytes = env_ll("DGN_ONESHOT_MAX_BYTES", -1);
+  c->ll_max_bytes = env_ll("DGN_LL_MAX_BYTES", -1);
+  c->fused_twoshot = env_ll("DGN_TWOSHOT_FUSED", 0) != 0;
   c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
   int rc = alloc_workspace(c);
   if (rc != DGN_OK) {
@@ -595,6 +639,7 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
   }
   if (nranks == 1) {
     c->peer_base[0] = c->base;
+    fill_peer_table(c, &c->table);
     c->connected = true;
   }
   *comm = c;
@@ -669,10 +714,7 @@ int dgn_comm_connect(dgn_comm_t c, const void* all_handles) {
       c->peer_ipc[j] = true;
     }
   }
-  PeerTable t;
-  fill_peer_table(c, &t);
-  if (!c->d_peers) DGN_CUDA(cudaMalloc((void**)&c->d_peers, sizeof(PeerTable)));
-  DGN_CUDA(cudaMemcpy(c->d_peers, &t, sizeof(t), cudaMemcpyHostToDevice));
+  fill_peer_table(c, &c->table);
   c->connected = true;
   return DGN_OK;
 }
@@ -758,18 +800,13 @@ int dgn_comm_create_emulated(int nranks, int device, dgn_comm_t* comms) {
     c->team = t;
     t->members.push_back(c);
   }
-  DeviceGuard g(device);
-  std::vector<PeerTable> host(nranks);
   for (int r = 0; r < nranks; ++r) {
     dgn_comm* c = t->members[r];
     for (int j = 0; j < nranks; ++j) c->peer_base[j] = t->members[j]->base;
-    fill_peer_table(c, &host[r]);
+    fill_peer_table(c, &c->table);
   }
-  DGN_CUDA(cudaMalloc((void**)&t->d_tables, sizeof(PeerTable) * nranks));
-  DGN_CUDA(cudaMemcpy(t->d_tables, host.data(), sizeof(PeerTable) * nranks, cudaMemcpyHostToDevice));
   t->alive = nranks;
   for (int r = 0; r < nranks; ++r) {
-    t->members[r]->d_peers = t->d_tables;
     t->members[r]->connected = true;
     comms[r] = t->members[r];
   }
@@ -782,12 +819,7 @@ int dgn_comm_destroy(dgn_comm_t c) {
   if (t) {
     for (auto& m : t->members)
       if (m == c) m = nullptr;
-    if (--t->alive == 0) {
-      DeviceGuard g(t->device);
-      cudaDeviceSynchronize();
-      cudaFree(t->d_tables);
-      delete t;
-    }
+    if (--t->alive == 0) delete t;
   }
   free_comm(c);
   return DGN_OK;
@@ -806,7 +838,7 @@ int dgn_comm_set_wait_limit_ms(dgn_comm_t c, int ms) {
 
 int dgn_comm_set_tuning(dgn_comm_t c, int variant, int blocks, int threads, int64_t chunk_bytes) {
   if (!c) return fail(DGN_ERR_ARG, "null communicator");
-  if (variant < 0 || variant > DGN_VARIANT_NVLS || blocks < 0 || threads < 0 || chunk_bytes < 0)
+  if (variant < 0 || variant > DGN_VARIANT_LL || blocks < 0 || threads < 0 || chunk_bytes < 0)
     return fail(DGN_ERR_ARG, "bad tuning value");
   if (variant == DGN_VARIANT_NVLS) return fail(DGN_ERR_UNSUPPORTED, "the NVLS variant is not set up on this communicator");
   c->tune_variant = variant;

@@ -1,24 +1,30 @@
 // Device side of the B200-native `Collective` path: peer-memory kernels for
-// ALLREDUCE (one-shot and two-shot), REDUCESCATTER, ALLGATHER, BROADCAST and
-// the single-rank copy path.
+// ALLREDUCE (low-latency one-shot, one-shot, pipelined two-shot),
+// REDUCESCATTER, ALLGATHER, BROADCAST and the single-rank copy path.
 //
 // Memory model.  Every rank owns one "symmetric workspace" that all peers map
 // (CUDA IPC across processes, peer access inside one process):
 //
-//   flags   u64[max_blocks][kMaxRanks]   slot [b][s] is written only by block b
-//                                        of rank s, with strictly increasing
-//                                        epoch numbers (never reset)
-//   stage   for parity p in {0,1}, block b: (nranks + 1) slots of slot_bytes
-//           slot s < nranks : "inbox" written by rank s (peer stores)
-//           slot nranks     : "outbox" written by the owner, read by peers
+//   flags   u64[max_blocks][3][kMaxRanks]  slot [b][ch][s] is written only by
+//                                        block b of rank s, with strictly
+//                                        increasing epoch numbers (never reset);
+//                                        channel A = "data published",
+//                                        channel B = "data consumed / done",
+//                                        channel C = "gather box emptied"
+//   stage   for parity p in {0,1}, block b, half h in {0,1}:
+//           2 * nranks slots of slot_bytes
+//           slot s < nranks   : "inbox" written by rank s (peer stores)
+//           slot nranks + s   : "gather box" written by rank s (reduced data);
+//                               slot nranks doubles as the owner's "outbox"
+//                               that peers read in all-gather and broadcast
+//   ll      for parity p, block b, source s: ll_slot_bytes of flag-in-data lines
 //
 // Block b of one rank only ever talks to block b of the other ranks, so a
-// collective needs no grid-wide barrier: each block runs
-//   pre-wait -> (push | publish) -> signal -> wait -> reduce/pull -> ... -> done
-// on its own slice of the message.  All waits are bounded: when the limit runs
-// out the block records DGN_ERR_TIMEOUT in the status word and leaves.
+// collective needs no grid-wide barrier.  All waits are bounded: when the
+// limit runs out the block records DGN_ERR_TIMEOUT in the status word and
+// leaves.
 //
-// Protocol state is device-resident: block b keeps its next epoch number, its
+// Protocol state is device-resident: block b keeps its last epoch number, its
 // collective count (whose low bit is the staging parity) and, per parity, the
 // epoch with which it last finished, in its own BlockState.  Every rank runs
 // the same sequence of collectives with the same launch shapes, so block b of
@@ -27,12 +33,12 @@
 //
 // Reuse safety.  Consecutive collectives of a block alternate parity.  Before
 // a block touches any peer's parity-p region again it waits until every
-// peer's block b has signalled the epoch with which the previous parity-p
-// collective finished ("done" signal), i.e. has stopped reading its data.
+// peer's block b has signalled (channel B) the epoch with which the previous
+// parity-p collective finished, i.e. has stopped reading its data.
 //
-// Data always moves as 16-byte vectors with ld/st.global.cg (L2-coherent, no
-// L1 allocation), so data published by a peer before its release-store of a
-// flag is seen after the acquire-load of that flag.
+// Data moves as 16-byte vectors with ld/st.global.cg (L2-coherent, no L1
+// allocation), so data published by a peer before its release-store of a flag
+// is seen after the acquire-load of that flag.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -44,6 +50,15 @@ namespace dgn {
 
 constexpr int kMaxRanks = 8;
 constexpr int kMaxTableTensors = 1024;  // bucket entries one launch can take
+constexpr int kChanA = 0, kChanB = 1;
+#ifndef DGN_UNROLL
+#define DGN_UNROLL 4
+#endif
+#ifndef DGN_MAX_THREADS
+#define DGN_MAX_THREADS 512
+#endif
+constexpr int kUnroll = DGN_UNROLL;     // independent 16-byte accesses per thread
+constexpr int kMaxThreads = DGN_MAX_THREADS;
 
 enum : int { kU8 = 0, kI8, kI32, kI64, kF16, kBF16, kF32, kF64 };
 enum : int { kSum = 0, kMean, kProd, kMin, kMax };
@@ -56,16 +71,20 @@ struct BlockState {
   u64 epoch;         // last epoch number used by this block
   u64 ops;           // collectives this block took part in; low bit = parity
   u64 last_done[2];  // per parity: epoch of the last "done" signal
+  u64 ll_ops;        // low-latency collectives this block took part in
+  u64 reserved[3];
 };
 
-// One rank's view of the team.  Lives in that rank's device memory.
+// One rank's view of the team; passed by value in the kernel parameters.
 struct PeerTable {
   char* stage[kMaxRanks];  // rank j's staging base, as mapped on this device
-  u64* flags[kMaxRanks];   // rank j's flag array, as mapped on this device
-  struct BlockState* blk;  // [max_blocks], local
+  char* ll[kMaxRanks];     // rank j's low-latency region
+  u64* flags[kMaxRanks];   // rank j's flag array
+  BlockState* blk;         // [max_blocks], local
   int* status;             // error word (pinned host memory, device-visible)
-  int rank, nranks, max_blocks, reserved;
-  long long slot_bytes;    // bytes per slot
+  int rank, nranks, max_blocks, ll_max_blocks;
+  long long slot_bytes;    // bytes per staging slot
+  long long ll_slot_bytes; // bytes per low-latency slot (holds half as much data)
 };
 
 // One tensor of a bucket; `vbegin` is its first 16-byte vector in the flat
@@ -80,19 +99,19 @@ struct TensorEnt {
 struct RankArgs {
   const void* in;
   void* out;
-  const TensorEnt* table;  // device memory, ntensors (+1 sentinel) entries
+  const TensorEnt* table;  // device memory, ntensors entries
 };
 
 struct OpParams {
-  const PeerTable* peers;  // [gridDim.y]
-  RankArgs ra[kMaxRanks];  // indexed by blockIdx.y
-  long long count;         // elements per rank (single tensor / per-rank block)
-  long long nvec;          // flat 16-byte vectors of the message
+  PeerTable peers[kMaxRanks];  // indexed by blockIdx.y (one entry unless emulated)
+  RankArgs ra[kMaxRanks];      // indexed by blockIdx.y
+  long long count;             // elements per rank (single tensor / per-rank block)
+  long long nvec;              // flat 16-byte vectors of the message
   u64 wait_ns;
-  double scale;            // MEAN factor, double(1.f / float(nranks))
+  double scale;                // MEAN factor, double(1.f / float(nranks))
   int ntensors;
   int rounds;
-  int cv;                  // vectors per block per round (<= slot_bytes / 16)
+  int cv;                      // vectors per block per round (<= slot_bytes / 16)
   int redop;
   int root;
 };
@@ -115,22 +134,22 @@ __device__ __forceinline__ u64 global_timer_ns() {
 }
 
 // Publishes everything this block has stored so far, then tells block `b` of
-// the peers (all, or only `only`) that epoch `val` is reached.
-__device__ __forceinline__ void signal_peers(const PeerTable& pt, int b, u64 val, int only = -1) {
+// the peers (all, or only `only`), on channel `chan`, that epoch `val` is reached.
+__device__ __forceinline__ void signal_peers(const PeerTable& pt, int b, int chan, u64 val, int only = -1) {
   __syncthreads();
   const int t = threadIdx.x;
   if (t < pt.nranks && t != pt.rank && (only < 0 || t == only))
-    st_release_sys(pt.flags[t] + (size_t)b * kMaxRanks + pt.rank, val);
+    st_release_sys(pt.flags[t] + ((size_t)b * 3 + chan) * kMaxRanks + pt.rank, val);
 }
 
 // Waits until block `b` of the peers (all, or only `only`) has reached epoch
 // `target`.  Returns false, for the whole block, if the limit ran out.
-__device__ __forceinline__ bool wait_peers(const PeerTable& pt, int b, u64 target, u64 wait_ns,
+__device__ __forceinline__ bool wait_peers(const PeerTable& pt, int b, int chan, u64 target, u64 wait_ns,
                                            int only = -1) {
   bool ok = true;
   const int t = threadIdx.x;
   if (t < pt.nranks && t != pt.rank && (only < 0 || t == only)) {
-    const u64* f = pt.flags[pt.rank] + (size_t)b * kMaxRanks + t;
+    const u64* f = pt.flags[pt.rank] + ((size_t)b * 3 + chan) * kMaxRanks + t;
     if (ld_acquire_sys(f) < target) {
       const u64 t0 = global_timer_ns();
       unsigned spins = 0;
@@ -369,13 +388,13 @@ template <> __device__ __forceinline__ float apply_scale<float>(float a, double 
 template <> __device__ __forceinline__ double apply_scale<double>(double a, double s) { return a * s; }
 
 // Combines x[0..n) in ascending order (x[0] first), optionally scales, packs.
-template <typename T, int OP>
+template <typename T, int OP, int CAP = kMaxRanks>
 __device__ __forceinline__ uint4 reduce_vectors(const uint4* x, int n, bool mean, double scale) {
   typedef Elem<T> EL;
   typename EL::Acc acc[EL::E], v[EL::E];
   EL::unpack(x[0], acc);
 #pragma unroll
-  for (int s = 1; s < kMaxRanks; ++s) {
+  for (int s = 1; s < CAP; ++s) {
     if (s < n) {
       EL::unpack(x[s], v);
 #pragma unroll
@@ -389,22 +408,24 @@ __device__ __forceinline__ uint4 reduce_vectors(const uint4* x, int n, bool mean
   return EL::pack(acc);
 }
 
-template <typename T>
+template <typename T, int CAP = kMaxRanks>
 __device__ __forceinline__ uint4 reduce_dispatch(const uint4* x, int n, int redop, double scale) {
   switch (redop) {
-    case kProd: return reduce_vectors<T, kProd>(x, n, false, scale);
-    case kMin: return reduce_vectors<T, kMin>(x, n, false, scale);
-    case kMax: return reduce_vectors<T, kMax>(x, n, false, scale);
-    case kMean: return reduce_vectors<T, kSum>(x, n, true, scale);
-    default: return reduce_vectors<T, kSum>(x, n, false, scale);
+    case kProd: return reduce_vectors<T, kProd, CAP>(x, n, false, scale);
+    case kMin: return reduce_vectors<T, kMin, CAP>(x, n, false, scale);
+    case kMax: return reduce_vectors<T, kMax, CAP>(x, n, false, scale);
+    case kMean: return reduce_vectors<T, kSum, CAP>(x, n, true, scale);
+    default: return reduce_vectors<T, kSum, CAP>(x, n, false, scale);
   }
 }
 
 // ---------------------------------------------------------------------------
 // geometry helpers
 
-__device__ __forceinline__ char* slot_ptr(const PeerTable& pt, int owner, int parity, int b, int slot) {
-  const long long idx = ((long long)parity * pt.max_blocks + b) * (pt.nranks + 1) + slot;
+// Staging slot `slot` of (parity, block b, half) in rank `owner`'s workspace.
+__device__ __forceinline__ char* slot_ptr(const PeerTable& pt, int owner, int parity, int b, int half,
+                                          int slot) {
+  const long long idx = (((long long)parity * pt.max_blocks + b) * 2 + half) * (2 * pt.nranks) + slot;
   return pt.stage[owner] + idx * pt.slot_bytes;
 }
 
@@ -412,8 +433,8 @@ __device__ __forceinline__ long long clampll(long long x, long long lo, long lon
   return x < lo ? lo : (x > hi ? hi : x);
 }
 
-// Start-of-launch guard and end-of-launch bookkeeping shared by all kernels.
-// Epochs base+1 .. base+span belong to the launch; `done` = base + span.
+// Start-of-launch guard and end-of-launch bookkeeping shared by the
+// flag-based kernels.  Epochs base+1 .. done belong to the launch.
 struct Turn {
   u64 base;
   int parity;
@@ -422,10 +443,10 @@ __device__ __forceinline__ bool begin_collective(const PeerTable& pt, int b, con
   const BlockState st = pt.blk[b];
   turn->base = st.epoch;
   turn->parity = (int)(st.ops & 1ull);
-  return wait_peers(pt, b, st.last_done[turn->parity], P.wait_ns);
+  return wait_peers(pt, b, kChanB, st.last_done[turn->parity], P.wait_ns);
 }
 __device__ __forceinline__ void end_collective(const PeerTable& pt, int b, const Turn& turn, u64 done) {
-  signal_peers(pt, b, done);
+  signal_peers(pt, b, kChanB, done);
   if (threadIdx.x == 0) {
     BlockState* st = pt.blk + b;
     st->epoch = done;
@@ -434,13 +455,121 @@ __device__ __forceinline__ void end_collective(const PeerTable& pt, int b, const
   }
 }
 
+// Copy loops.  Each thread keeps kUnroll independent 16-byte accesses in
+// flight: all loads of a batch are issued before the first store.
+// src(v) -> uint4, dst(v, x); v runs over [0, len).
+template <typename Src, typename Dst>
+__device__ __forceinline__ void copy_vectors(long long len, Src src, Dst dst) {
+  const long long T = blockDim.x;
+  long long v = threadIdx.x;
+  for (; v + (kUnroll - 1) * T < len; v += kUnroll * T) {
+    uint4 x[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) x[u] = src(v + u * T);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) dst(v + u * T, x[u]);
+  }
+  for (; v < len; v += T) dst(v, src(v));
+}
+
+// ---------------------------------------------------------------------------
+// ALLREDUCE, low-latency one-shot ("LL"): data travels in 16-byte lines
+// {lo32, flag, hi32, flag}; the receiver polls the line itself, so there is no
+// separate flag store, no release fence and no barrier.  Every rank stores its
+// slice into every peer's LL inbox, then reduces all n copies itself in
+// ascending rank order.  The flag is the block's LL collective count + 1;
+// two parities suffice because a peer cannot start collective k + 2 before
+// this rank has sent collective k + 1, i.e. has finished reading k.
+
+__device__ __forceinline__ void st_ll(void* p, unsigned lo, unsigned hi, unsigned flag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(lo), "r"(flag),
+               "r"(hi), "r"(flag)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_ll(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ char* ll_ptr(const PeerTable& pt, int owner, int parity, int b, int src) {
+  const long long idx = ((long long)parity * pt.ll_max_blocks + b) * pt.nranks + src;
+  return pt.ll[owner] + idx * pt.ll_slot_bytes;
+}
+
+template <typename T, bool TABLE>
+__global__ void __launch_bounds__(kMaxThreads, 1) ar_oneshot_ll_kernel(const __grid_constant__ OpParams P) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const PeerTable& pt = P.peers[blockIdx.y];
+  const RankArgs& ra = P.ra[blockIdx.y];
+  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
+  const Message<(int)sizeof(T), TABLE> msg = make_message<(int)sizeof(T), TABLE>(P, ra, smem);
+  const u64 ops = pt.blk[b].ll_ops;
+  const unsigned flag = (unsigned)(ops % 0xfffffffeull) + 1u;  // never 0, the value of untouched memory
+  const int parity = (int)(ops & 1ull);
+  __syncthreads();  // everyone has read ll_ops before it is bumped
+  if (threadIdx.x == 0) pt.blk[b].ll_ops = ops + 1;
+
+  const long long v0 = (long long)b * P.cv;
+  const long long len = clampll(P.nvec - v0, 0, P.cv);
+  char* dst[kMaxRanks];
+#pragma unroll
+  for (int k = 1; k < kMaxRanks; ++k) dst[k] = (k < n) ? ll_ptr(pt, (r + k) % n, parity, b, r) : nullptr;
+  const char* const inbox0 = ll_ptr(pt, r, parity, b, 0);
+
+  for (long long v = threadIdx.x; v < len; v += blockDim.x) {
+    const uint4 mine = msg.load(v0 + v);
+#pragma unroll
+    for (int k = 1; k < kMaxRanks; ++k) {
+      if (k < n) {
+        st_ll(dst[k] + v * 32, mine.x, mine.y, flag);
+        st_ll(dst[k] + v * 32 + 16, mine.z, mine.w, flag);
+      }
+    }
+    uint4 x[kMaxRanks];
+    bool ok = true;
+#pragma unroll
+    for (int s = 0; s < kMaxRanks; ++s) {
+      if (s < n) {
+        if (s == r) {
+          x[s] = mine;
+        } else {
+          const char* line = inbox0 + s * pt.ll_slot_bytes + v * 32;
+          uint4 a = ld_ll(line), c = ld_ll(line + 16);
+          if (a.y != flag || a.w != flag || c.y != flag || c.w != flag) {
+            const u64 t0 = global_timer_ns();
+            unsigned spins = 0;
+            for (;;) {
+              a = ld_ll(line);
+              c = ld_ll(line + 16);
+              if (a.y == flag && a.w == flag && c.y == flag && c.w == flag) break;
+              if ((++spins & 31u) == 0u && global_timer_ns() - t0 > P.wait_ns) {
+                *(volatile int*)pt.status = kErrTimeout;
+                ok = false;
+                break;
+              }
+            }
+          }
+          x[s] = make_uint4(a.x, a.z, c.x, c.z);
+        }
+      }
+    }
+    if (!ok) return;
+    msg.store(v0 + v, reduce_dispatch<T>(x, n, P.redop, P.scale));
+  }
+}
+
 // ---------------------------------------------------------------------------
 // ALLREDUCE, one-shot: every rank stores its slice into every peer's inbox,
 // one flag exchange, then every rank reduces all n copies itself (ascending
-// rank order, so all ranks produce identical bits).  Epochs: +1 data, +2 done.
+// rank order, so all ranks produce identical bits).
+// Epochs: base+1 data (channel A), base+2 done (channel B).
 
 template <typename T, bool TABLE>
-__global__ void __launch_bounds__(512, 1) ar_oneshot_kernel(const OpParams P) {
+__global__ void __launch_bounds__(kMaxThreads, 1) ar_oneshot_kernel(const __grid_constant__ OpParams P) {
   extern __shared__ __align__(16) unsigned char smem[];
   const PeerTable& pt = P.peers[blockIdx.y];
   const RankArgs& ra = P.ra[blockIdx.y];
@@ -453,17 +582,18 @@ __global__ void __launch_bounds__(512, 1) ar_oneshot_kernel(const OpParams P) {
   const long long len = clampll(P.nvec - v0, 0, P.cv);
   char* dst[kMaxRanks];  // dst[k]: my slot in the inbox of peer (r + k) % n
 #pragma unroll
-  for (int k = 1; k < kMaxRanks; ++k) dst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, turn.parity, b, r) : nullptr;
+  for (int k = 1; k < kMaxRanks; ++k)
+    dst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, turn.parity, b, 0, r) : nullptr;
   for (long long v = threadIdx.x; v < len; v += blockDim.x) {
     const uint4 x = msg.load(v0 + v);
 #pragma unroll
     for (int k = 1; k < kMaxRanks; ++k)
       if (k < n) stv(dst[k] + v * 16, x);
   }
-  signal_peers(pt, b, turn.base + 1);
-  if (!wait_peers(pt, b, turn.base + 1, P.wait_ns)) return;
+  signal_peers(pt, b, kChanA, turn.base + 1);
+  if (!wait_peers(pt, b, kChanA, turn.base + 1, P.wait_ns)) return;
 
-  const char* const inbox0 = slot_ptr(pt, r, turn.parity, b, 0);
+  const char* const inbox0 = slot_ptr(pt, r, turn.parity, b, 0, 0);
   for (long long v = threadIdx.x; v < len; v += blockDim.x) {
     uint4 x[kMaxRanks];
 #pragma unroll
@@ -476,22 +606,32 @@ __global__ void __launch_bounds__(512, 1) ar_oneshot_kernel(const OpParams P) {
 }
 
 // ---------------------------------------------------------------------------
-// ALLREDUCE two-shot / REDUCESCATTER.
+// ALLREDUCE two-shot / REDUCESCATTER, software-pipelined, stores only.
+// Peer traffic is remote stores exclusively: on NVLink, two GPUs storing to
+// each other sustain more per direction than any mix with remote loads.
 // The flat message is cut into n shards of vs = ceil(nvec / n) vectors; rank r
-// owns shard r.  Per round, block b works on vectors [off, off + cv) of every
-// shard, off = (round * gridDim.x + b) * cv:
-//   1. push   : store my copy of peer j's shard slice into j's inbox[r]
-//   2. reduce : sum my shard slice over all ranks (own copy from the input,
+// owns shard r.  In round i, block b works on vectors [off, off + cv) of every
+// shard, off = (i * gridDim.x + b) * cv, in three stages:
+//   push(i)   : store my copy of peer j's shard slice into j's inbox[r]
+//   reduce(i) : sum my shard slice over all ranks (own copy from the input,
 //               the others from my inbox), scale, write to my output and to
-//               my outbox
-//   3. pull   : load every peer's outbox into my output
-// Epochs per round i: epoch + 2i + 1 (pushed), epoch + 2i + 2 (reduced);
-// done = epoch + 2 * rounds + 1.
-// REDUCESCATTER (RS = true) is steps 1-2 with shard s = block s of the input
-// and the result written to `out` only.
+//               gather box [r] of every peer
+//   gather(i) : copy the peers' reduced slices from my gather box to my output
+// Iteration i of the loop runs gather(i-2), push(i) and reduce(i-1) fused, on
+// staging halves (i-2)%2, i%2, (i-1)%2, so the link and local HBM are busy at
+// the same time.
+// Signals: pushed(i) = base+2i+1 on channel A, reduced(i) = base+2i+2 on
+// channel B; done = base+2*rounds+1 on channel B.
+// Why two halves suffice: push(i) overwrites the inbox half read by the
+// peers' reduce(i-2), whose completion (reduced(i-2)) is awaited at the top of
+// iteration i; reduce(i-1) overwrites the gather-box half the peers emptied in
+// their gather(i-3), which they finished before signalling pushed(i-1), also
+// awaited at the top of iteration i.
+// REDUCESCATTER (RS = true) has no gather stage: shard s is block s of the
+// input and the result goes to `out` only.
 
 template <typename T, bool TABLE, bool RS>
-__global__ void __launch_bounds__(512, 1) ar_twoshot_kernel(const OpParams P) {
+__global__ void __launch_bounds__(kMaxThreads, 1) ar_twoshot_kernel(const __grid_constant__ OpParams P) {
   extern __shared__ __align__(16) unsigned char smem[];
   constexpr int ES = (int)sizeof(T);
   const PeerTable& pt = P.peers[blockIdx.y];
@@ -501,15 +641,13 @@ __global__ void __launch_bounds__(512, 1) ar_twoshot_kernel(const OpParams P) {
   Turn turn;
   if (!begin_collective(pt, b, P, &turn)) return;
 
-  // Shard geometry.  AR: shards are consecutive runs of the flat message.
-  // RS: shard s is the s-th block of `count` elements of the input.
   const long long vs = RS ? P.nvec : (P.nvec + n - 1) / n;
-  const long long total = RS ? P.nvec * n : P.nvec;
   const char* in = static_cast<const char*>(ra.in);
   char* out = static_cast<char*>(ra.out);
+  const bool out_al = is_al16(out);
 
   auto shard_len = [&](int s) -> long long {
-    return RS ? vs : clampll(total - (long long)s * vs, 0, vs);
+    return RS ? vs : clampll(P.nvec - (long long)s * vs, 0, vs);
   };
   auto load_shard = [&](int s, long long v) -> uint4 {
     if (RS) {
@@ -518,87 +656,322 @@ __global__ void __launch_bounds__(512, 1) ar_twoshot_kernel(const OpParams P) {
     }
     return msg.load((long long)s * vs + v);
   };
+  const long long mylen_total = shard_len(r);
+  const int rounds = P.rounds;
+  const long long cv = P.cv;
+  const long long stride = (long long)gridDim.x * cv;
 
-  char* const my_outbox = slot_ptr(pt, r, turn.parity, b, n);
-  const char* const inbox0 = slot_ptr(pt, r, turn.parity, b, 0);
-  int peer[kMaxRanks];           // peer[k] = (r + k) % n
-  char* push_dst[kMaxRanks];     // my slot in peer[k]'s inbox
-  const char* pull_src[kMaxRanks];  // peer[k]'s outbox
-  long long plen[kMaxRanks];     // vectors in peer[k]'s shard
-#pragma unroll
-  for (int k = 1; k < kMaxRanks; ++k) {
-    peer[k] = (k < n) ? (r + k) % n : 0;
-    push_dst[k] = (k < n) ? slot_ptr(pt, peer[k], turn.parity, b, r) : nullptr;
-    pull_src[k] = (k < n) ? slot_ptr(pt, peer[k], turn.parity, b, n) : nullptr;
-    plen[k] = (k < n) ? shard_len(peer[k]) : 0;
-  }
-  for (int round = 0; round < P.rounds; ++round) {
-    const long long off = ((long long)round * gridDim.x + b) * P.cv;
-    const u64 e_push = turn.base + 2 * (u64)round + 1, e_red = e_push + 1;
+  for (int i = 0; i < rounds + 2; ++i) {
+    const bool do_pull = !RS && i >= 2;
+    const bool do_push = i < rounds;
+    const bool do_reduce = i >= 1 && i <= rounds;
+    // Both waits are for signals the peers sent at the end of their previous
+    // iteration: reduced(i-2) frees the inbox half push(i) refills and
+    // publishes the gather-box half gather(i-2) reads; pushed(i-1) publishes
+    // the inbox half reduce(i-1) reads and frees the gather-box half it refills.
+    if (i >= 2 && !wait_peers(pt, b, kChanB, turn.base + 2 * (u64)(i - 2) + 2, P.wait_ns)) return;
+    if (do_reduce && !wait_peers(pt, b, kChanA, turn.base + 2 * (u64)(i - 1) + 1, P.wait_ns)) return;
 
-    // 1. push
-    // All loads of an iteration are issued before the first store, so a
-    // thread keeps n - 1 vectors in flight.
-    for (long long v = threadIdx.x; v < P.cv; v += blockDim.x) {
-      uint4 x[kMaxRanks];
+    // The three stages run fused, vector by vector and without a barrier in
+    // between, so that at any time some warps feed the link (push, reduce)
+    // and some move data inside local HBM (gather).
+    const long long off_push = (long long)i * stride + (long long)b * cv;
+    const long long off_red = (long long)(i - 1) * stride + (long long)b * cv;
+    const long long off_pull = (long long)(i - 2) * stride + (long long)b * cv;
+    const long long red_len = do_reduce ? clampll(mylen_total - off_red, 0, cv) : 0;
+    const char* inbox0 = slot_ptr(pt, r, turn.parity, b, (i - 1) & 1, 0);
+    char* gdst[kMaxRanks];  // gather box [r] of peer (r + k) % n
 #pragma unroll
-      for (int k = 1; k < kMaxRanks; ++k)
-        if (k < n && off + v < plen[k]) x[k] = load_shard(peer[k], off + v);
+    for (int k = 1; k < kMaxRanks; ++k)
+      gdst[k] = (k < n && !RS) ? slot_ptr(pt, (r + k) % n, turn.parity, b, (i - 1) & 1, n + r) : nullptr;
+    for (long long v0 = (long long)threadIdx.x; v0 < cv; v0 += (long long)kUnroll * blockDim.x) {
+      if (do_pull) {  // gather(i-2): local copy out of my gather box
+        for (int k = 1; k < n; ++k) {
+          const int peer = (r + 1 + (k - 1 + b) % (n - 1)) % n;
+          const long long len = clampll(shard_len(peer) - off_pull, 0, cv);
+          const char* src = slot_ptr(pt, r, turn.parity, b, i & 1, n + peer);
+          const long long obase = (long long)peer * vs + off_pull;
+          uint4 x[kUnroll];
 #pragma unroll
-      for (int k = 1; k < kMaxRanks; ++k)
-        if (k < n && off + v < plen[k]) stv(push_dst[k] + v * 16, x[k]);
-    }
-    signal_peers(pt, b, e_push);
-    if (!wait_peers(pt, b, e_push, P.wait_ns)) return;
-
-    // 2. reduce my shard slice
-    const long long mylen = clampll(shard_len(r) - off, 0, P.cv);
-    for (long long v = threadIdx.x; v < mylen; v += blockDim.x) {
-      uint4 x[kMaxRanks];
+          for (int u = 0; u < kUnroll; ++u) {
+            const long long v = v0 + (long long)u * blockDim.x;
+            if (v < len) x[u] = ldv(src + v * 16);
+          }
 #pragma unroll
-      for (int s = 0; s < kMaxRanks; ++s) {
-        if (s < n) x[s] = (s == r) ? load_shard(r, off + v) : ldv(inbox0 + s * pt.slot_bytes + v * 16);
+          for (int u = 0; u < kUnroll; ++u) {
+            const long long v = v0 + (long long)u * blockDim.x;
+            if (v < len) msg.store(obase + v, x[u]);
+          }
+        }
       }
-      const uint4 y = reduce_dispatch<T>(x, n, P.redop, P.scale);
-      if (RS) {
-        store_vec<ES>(out, off + v, P.count, is_al16(out), y);
-      } else {
-        msg.store((long long)r * vs + off + v, y);
-        stv(my_outbox + v * 16, y);
+      if (do_push) {
+        for (int k = 1; k < n; ++k) {
+          const int peer = (r + 1 + (k - 1 + b) % (n - 1)) % n;
+          const long long len = clampll(shard_len(peer) - off_push, 0, cv);
+          char* dst = slot_ptr(pt, peer, turn.parity, b, i & 1, r);
+          uint4 x[kUnroll];
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            const long long v = v0 + (long long)u * blockDim.x;
+            if (v < len) x[u] = load_shard(peer, off_push + v);
+          }
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            const long long v = v0 + (long long)u * blockDim.x;
+            if (v < len) stv(dst + v * 16, x[u]);
+          }
+        }
+      }
+      if (do_reduce) {
+#pragma unroll 1
+        for (int u = 0; u < kUnroll; ++u) {
+          const long long v = v0 + (long long)u * blockDim.x;
+          if (v < red_len) {
+            uint4 x[kMaxRanks];
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s) {
+              if (s < n)
+                x[s] = (s == r) ? load_shard(r, off_red + v) : ldv(inbox0 + s * pt.slot_bytes + v * 16);
+            }
+            const uint4 y = reduce_dispatch<T>(x, n, P.redop, P.scale);
+            if (RS) {
+              store_vec<ES>(out, off_red + v, P.count, out_al, y);
+            } else {
+              msg.store((long long)r * vs + off_red + v, y);
+#pragma unroll
+              for (int k = 1; k < kMaxRanks; ++k)
+                if (k < n) stv(gdst[k] + v * 16, y);
+            }
+          }
+        }
       }
     }
-    if (RS) {
-      // Peers may refill my inbox only after this read; the next round's
-      // e_push wait on their side is ordered after this signal.
-      signal_peers(pt, b, e_red);
-      if (!wait_peers(pt, b, e_red, P.wait_ns)) return;
-      continue;
-    }
-    signal_peers(pt, b, e_red);
-    if (!wait_peers(pt, b, e_red, P.wait_ns)) return;
+    // One barrier publishes both kinds of stores.
+    if (do_push) signal_peers(pt, b, kChanA, turn.base + 2 * (u64)i + 1);
+    if (do_reduce) signal_peers(pt, b, kChanB, turn.base + 2 * (u64)(i - 1) + 2);
+  }
+  end_collective(pt, b, turn, turn.base + 2 * (u64)rounds + 1);
+}
 
-    // 3. pull
-    for (long long v = threadIdx.x; v < P.cv; v += blockDim.x) {
-      uint4 x[kMaxRanks];
-#pragma unroll
-      for (int k = 1; k < kMaxRanks; ++k)
-        if (k < n && off + v < plen[k]) x[k] = ldv(pull_src[k] + v * 16);
-#pragma unroll
-      for (int k = 1; k < kMaxRanks; ++k)
-        if (k < n && off + v < plen[k]) msg.store((long long)peer[k] * vs + off + v, x[k]);
+// ---------------------------------------------------------------------------
+// ALLREDUCE two-shot, warp-specialised dataflow version (the large-message
+// path).  Same data movement as above (stores only; push, reduce, gather),
+// but the three stages are run by three groups of warps of one block, each in
+// its own loop over the rounds with its own named barrier and its own flag
+// channel, so a stage that waits for a peer's flag or for its release fence
+// does not stop the other two.  kDepth staging halves let the pusher run up
+// to kDepth rounds ahead of the peers' reducers, and the reducer up to kDepth
+// rounds ahead of the peers' gatherers.
+//   pusher  : [wait reduced(i-kDepth) on B]  push(i)    signal pushed(i)   on A
+//   reducer : wait pushed(j) on A, [gathered(j-kDepth) on C]
+//                                           reduce(j)  signal reduced(j)  on B
+//   gatherer: wait reduced(j) on B          gather(j)  signal gathered(j) on C
+// Epoch of round j on every channel: base + j + 1; done = base + rounds + 1 (B).
+
+constexpr int kDepth = 2;
+constexpr int kChanC = 2;
+
+struct Role {
+  int id;  // named barrier
+  int t;   // thread index inside the role
+  int n;   // threads in the role (multiple of 32)
+};
+
+__device__ __forceinline__ void role_sync(const Role& g) {
+  asm volatile("bar.sync %0, %1;" ::"r"(g.id), "r"(g.n) : "memory");
+}
+// AND-reduction over the role's threads; every thread gets the same answer.
+__device__ __forceinline__ bool role_all(const Role& g, bool pred) {
+  unsigned out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %3, 0;\n\tbar.red.and.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(g.id), "r"(g.n), "r"((unsigned)pred)
+      : "memory");
+  return out != 0;
+}
+
+__device__ __forceinline__ void role_signal(const PeerTable& pt, const Role& g, int b, int chan, u64 val) {
+  role_sync(g);
+  if (g.t < pt.nranks && g.t != pt.rank)
+    st_release_sys(pt.flags[g.t] + ((size_t)b * 3 + chan) * kMaxRanks + pt.rank, val);
+}
+
+__device__ __forceinline__ bool role_wait(const PeerTable& pt, const Role& g, int b, int chan, u64 target,
+                                          u64 wait_ns, volatile int* abort_flag) {
+  bool ok = true;
+  if (g.t < pt.nranks && g.t != pt.rank) {
+    const u64* f = pt.flags[pt.rank] + ((size_t)b * 3 + chan) * kMaxRanks + g.t;
+    if (ld_acquire_sys(f) < target) {
+      const u64 t0 = global_timer_ns();
+      unsigned spins = 0;
+      for (;;) {
+        if (ld_acquire_sys(f) >= target) break;
+        if ((++spins & 31u) == 0u) {
+          if (*abort_flag) { ok = false; break; }
+          if (global_timer_ns() - t0 > wait_ns) {
+            *(volatile int*)pt.status = kErrTimeout;
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+        }
+      }
     }
   }
-  end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
+  return role_all(g, ok && *abort_flag == 0);
+}
+
+// Copy loop of one role: kUnroll loads in flight per thread.
+template <typename Src, typename Dst>
+__device__ __forceinline__ void role_copy(const Role& g, long long len, Src src, Dst dst) {
+  const long long T = g.n;
+  long long v = g.t;
+  for (; v + (kUnroll - 1) * T < len; v += kUnroll * T) {
+    uint4 x[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) x[u] = src(v + u * T);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) dst(v + u * T, x[u]);
+  }
+  for (; v < len; v += T) dst(v, src(v));
+}
+
+// Reduce stage of one role: per step a thread loads VEC vectors from each of
+// up to CAP ranks (own copy through `mine`, the others from the inbox slots),
+// so CAP * VEC loads are in flight before the first store; results go to the
+// local output (`put`) and to the gather boxes gdst[1..n).
+template <typename T, int CAP, int VEC, typename Mine, typename Put>
+__device__ __forceinline__ void reduce_stage(const Role& g, long long len, int n, int r, Mine mine, Put put,
+                                             const char* inbox0, long long slot_bytes, char* const* gdst,
+                                             int redop, double scale) {
+  for (long long v0 = g.t; v0 < len; v0 += (long long)VEC * g.n) {
+    uint4 x[VEC][CAP];
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) {
+      const long long v = v0 + (long long)u * g.n;
+      if (v < len) {
+#pragma unroll
+        for (int s = 0; s < CAP; ++s)
+          if (s < n) x[u][s] = (s == r) ? mine(v) : ldv(inbox0 + s * slot_bytes + v * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) {
+      const long long v = v0 + (long long)u * g.n;
+      if (v < len) {
+        const uint4 y = reduce_dispatch<T, CAP>(x[u], n, redop, scale);
+        put(v, y);
+#pragma unroll
+        for (int k = 1; k < CAP; ++k)
+          if (k < n) stv(gdst[k] + v * 16, y);
+      }
+    }
+  }
+}
+
+template <typename T, bool TABLE>
+__global__ void __launch_bounds__(kMaxThreads, 1) ar_twoshot_ws_kernel(const __grid_constant__ OpParams P) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ int s_abort;
+  constexpr int ES = (int)sizeof(T);
+  const PeerTable& pt = P.peers[blockIdx.y];
+  const RankArgs& ra = P.ra[blockIdx.y];
+  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
+  const Message<ES, TABLE> msg = make_message<ES, TABLE>(P, ra, smem);
+  if (threadIdx.x == 0) s_abort = 0;
+  Turn turn;
+  if (!begin_collective(pt, b, P, &turn)) return;  // block-wide barrier inside: s_abort is visible
+
+  const long long vs = (P.nvec + n - 1) / n;
+  auto shard_len = [&](int s) -> long long { return clampll(P.nvec - (long long)s * vs, 0, vs); };
+  const int rounds = P.rounds;
+  const long long cv = P.cv;
+  const long long stride = (long long)gridDim.x * cv;
+  const u64 base = turn.base;
+
+  // Warp split: 3/8 push, 3/8 reduce, the rest gather (at least one warp each).
+  const int nwarps = blockDim.x >> 5;
+  int w_push = (nwarps * 3) >> 3, w_red = (nwarps * 3) >> 3;
+  if (w_push < 1) w_push = 1;
+  if (w_red < 1) w_red = 1;
+  const int warp = threadIdx.x >> 5;
+  Role g;
+  int role;
+  if (warp < w_push) { role = 0; g.id = 1; g.t = threadIdx.x; g.n = w_push * 32; }
+  else if (warp < w_push + w_red) { role = 1; g.id = 2; g.t = threadIdx.x - w_push * 32; g.n = w_red * 32; }
+  else { role = 2; g.id = 3; g.t = threadIdx.x - (w_push + w_red) * 32; g.n = (nwarps - w_push - w_red) * 32; }
+  volatile int* abort_flag = &s_abort;
+  bool alive = true;
+
+  if (role == 0) {
+    for (int i = 0; i < rounds && alive; ++i) {
+      if (i >= kDepth && !role_wait(pt, g, b, kChanB, base + (u64)(i - kDepth) + 1, P.wait_ns, abort_flag)) { alive = false; break; }
+      const long long off = (long long)i * stride + (long long)b * cv;
+      for (int k = 1; k < n; ++k) {
+        const int peer = (r + 1 + (k - 1 + b) % (n - 1)) % n;  // blocks start at different peers
+        const long long len = clampll(shard_len(peer) - off, 0, cv);
+        char* dst = slot_ptr(pt, peer, turn.parity, b, i % kDepth, r);
+        const long long ibase = (long long)peer * vs + off;
+        role_copy(g, len, [&](long long v) { return msg.load(ibase + v); },
+                  [&](long long v, uint4 x) { stv(dst + v * 16, x); });
+      }
+      role_signal(pt, g, b, kChanA, base + (u64)i + 1);
+    }
+  } else if (role == 1) {
+    const long long mylen_total = shard_len(r);
+    for (int j = 0; j < rounds && alive; ++j) {
+      if (!role_wait(pt, g, b, kChanA, base + (u64)j + 1, P.wait_ns, abort_flag)) { alive = false; break; }
+      if (j >= kDepth && !role_wait(pt, g, b, kChanC, base + (u64)(j - kDepth) + 1, P.wait_ns, abort_flag)) { alive = false; break; }
+      const long long off = (long long)j * stride + (long long)b * cv;
+      const long long len = clampll(mylen_total - off, 0, cv);
+      const char* inbox0 = slot_ptr(pt, r, turn.parity, b, j % kDepth, 0);
+      char* gdst[kMaxRanks];  // gather box [r] of peer (r + k) % n
+#pragma unroll
+      for (int k = 1; k < kMaxRanks; ++k)
+        gdst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, turn.parity, b, j % kDepth, n + r) : nullptr;
+      const long long obase = (long long)r * vs + off;
+      if (n <= 2) reduce_stage<T, 2, 4>(g, len, n, r, [&](long long v) { return msg.load(obase + v); },
+                                        [&](long long v, uint4 y) { msg.store(obase + v, y); }, inbox0,
+                                        pt.slot_bytes, gdst, P.redop, P.scale);
+      else if (n <= 4) reduce_stage<T, 4, 2>(g, len, n, r, [&](long long v) { return msg.load(obase + v); },
+                                             [&](long long v, uint4 y) { msg.store(obase + v, y); }, inbox0,
+                                             pt.slot_bytes, gdst, P.redop, P.scale);
+      else reduce_stage<T, 8, 1>(g, len, n, r, [&](long long v) { return msg.load(obase + v); },
+                                 [&](long long v, uint4 y) { msg.store(obase + v, y); }, inbox0,
+                                 pt.slot_bytes, gdst, P.redop, P.scale);
+      role_signal(pt, g, b, kChanB, base + (u64)j + 1);
+    }
+  } else {
+    for (int j = 0; j < rounds && alive; ++j) {
+      if (!role_wait(pt, g, b, kChanB, base + (u64)j + 1, P.wait_ns, abort_flag)) { alive = false; break; }
+      const long long off = (long long)j * stride + (long long)b * cv;
+      for (int k = 1; k < n; ++k) {
+        const int peer = (r + 1 + (k - 1 + b) % (n - 1)) % n;
+        const long long len = clampll(shard_len(peer) - off, 0, cv);
+        const char* src = slot_ptr(pt, r, turn.parity, b, j % kDepth, n + peer);
+        const long long obase = (long long)peer * vs + off;
+        role_copy(g, len, [&](long long v) { return ldv(src + v * 16); },
+                  [&](long long v, uint4 x) { msg.store(obase + v, x); });
+      }
+      role_signal(pt, g, b, kChanC, base + (u64)j + 1);
+    }
+  }
+  // All three roles meet; a role that gave up takes the whole block out.
+  if (__syncthreads_or(!alive)) return;
+  end_collective(pt, b, turn, base + (u64)rounds + 1);
 }
 
 // ---------------------------------------------------------------------------
 // ALLGATHER (bytes).  Per round: copy my slice to my outbox and to my own
-// block of the output, signal, then pull every peer's outbox into its block
-// of my output.  A second signal per round tells peers the outbox may be
-// overwritten.  `count` is bytes per rank here; vectors are of bytes.
+// block of the output, signal (A), then pull every peer's outbox into its
+// block of my output and signal (B) that the outbox may be overwritten.
+// Outbox halves alternate per round, so the wait for B lags one round.
+// `count` is bytes per rank here.
 
 template <int kUnused>
-__global__ void __launch_bounds__(512, 1) allgather_kernel(const OpParams P) {
+__global__ void __launch_bounds__(kMaxThreads, 1) allgather_kernel(const __grid_constant__ OpParams P) {
   const PeerTable& pt = P.peers[blockIdx.y];
   const RankArgs& ra = P.ra[blockIdx.y];
   const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
@@ -607,53 +980,44 @@ __global__ void __launch_bounds__(512, 1) allgather_kernel(const OpParams P) {
   const char* in = static_cast<const char*>(ra.in);
   char* out = static_cast<char*>(ra.out);
   const bool in_al = is_al16(in);
-  char* const my_outbox = slot_ptr(pt, r, turn.parity, b, n);
-  int peer[kMaxRanks];
-  const char* pull_src[kMaxRanks];
-#pragma unroll
-  for (int k = 1; k < kMaxRanks; ++k) {
-    peer[k] = (k < n) ? (r + k) % n : 0;
-    pull_src[k] = (k < n) ? slot_ptr(pt, peer[k], turn.parity, b, n) : nullptr;
-  }
+  char* mine = out + (long long)r * P.count;
+  const bool mine_al = is_al16(mine);
+  const long long cv = P.cv;
 
   for (int round = 0; round < P.rounds; ++round) {
-    const long long off = ((long long)round * gridDim.x + b) * P.cv;
-    const long long len = clampll(P.nvec - off, 0, P.cv);
+    const long long off = ((long long)round * gridDim.x + b) * cv;
+    const long long len = clampll(P.nvec - off, 0, cv);
     const u64 e_pub = turn.base + 2 * (u64)round + 1, e_got = e_pub + 1;
-    char* mine = out + (long long)r * P.count;
-    const bool mine_al = is_al16(mine);
-    for (long long v = threadIdx.x; v < len; v += blockDim.x) {
-      const uint4 x = load_vec<1>(in, off + v, P.count, in_al);
-      stv(my_outbox + v * 16, x);
-      if (mine != in) store_vec<1>(mine, off + v, P.count, mine_al, x);
+    // The half written now was pulled by the peers two rounds ago.
+    if (round >= 2 && !wait_peers(pt, b, kChanB, turn.base + 2 * (u64)(round - 2) + 2, P.wait_ns)) return;
+    char* outbox = slot_ptr(pt, r, turn.parity, b, round & 1, n);
+    copy_vectors(len, [&](long long v) { return load_vec<1>(in, off + v, P.count, in_al); },
+                 [&](long long v, uint4 x) {
+                   stv(outbox + v * 16, x);
+                   if (mine != in) store_vec<1>(mine, off + v, P.count, mine_al, x);
+                 });
+    signal_peers(pt, b, kChanA, e_pub);
+    if (!wait_peers(pt, b, kChanA, e_pub, P.wait_ns)) return;
+    for (int k = 1; k < n; ++k) {
+      const int peer = (r + 1 + (k - 1 + b) % (n - 1)) % n;
+      const char* src = slot_ptr(pt, peer, turn.parity, b, round & 1, n);
+      char* dst = out + (long long)peer * P.count;
+      const bool dst_al = is_al16(dst);
+      copy_vectors(len, [&](long long v) { return ldv(src + v * 16); },
+                   [&](long long v, uint4 x) { store_vec<1>(dst, off + v, P.count, dst_al, x); });
     }
-    signal_peers(pt, b, e_pub);
-    if (!wait_peers(pt, b, e_pub, P.wait_ns)) return;
-    for (long long v = threadIdx.x; v < len; v += blockDim.x) {
-      uint4 x[kMaxRanks];
-#pragma unroll
-      for (int k = 1; k < kMaxRanks; ++k)
-        if (k < n) x[k] = ldv(pull_src[k] + v * 16);
-#pragma unroll
-      for (int k = 1; k < kMaxRanks; ++k) {
-        if (k < n) {
-          char* dst = out + (long long)peer[k] * P.count;
-          store_vec<1>(dst, off + v, P.count, is_al16(dst), x[k]);
-        }
-      }
-    }
-    signal_peers(pt, b, e_got);
-    if (round + 1 < P.rounds && !wait_peers(pt, b, e_got, P.wait_ns)) return;
+    signal_peers(pt, b, kChanB, e_got);
   }
   end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
 }
 
 // ---------------------------------------------------------------------------
-// BROADCAST in place (bytes).  The root publishes a slice in its outbox, the
-// others pull it and acknowledge; the root refills only after all acks.
+// BROADCAST in place (bytes).  The root publishes a slice in an outbox half
+// (A), the others pull it and acknowledge (B); the root refills a half only
+// after all acknowledgements of the round that used it.
 
 template <int kUnused>
-__global__ void __launch_bounds__(512, 1) broadcast_kernel(const OpParams P) {
+__global__ void __launch_bounds__(kMaxThreads, 1) broadcast_kernel(const __grid_constant__ OpParams P) {
   const PeerTable& pt = P.peers[blockIdx.y];
   const RankArgs& ra = P.ra[blockIdx.y];
   const int r = pt.rank, n = pt.nranks, b = blockIdx.x, root = P.root;
@@ -661,33 +1025,34 @@ __global__ void __launch_bounds__(512, 1) broadcast_kernel(const OpParams P) {
   if (!begin_collective(pt, b, P, &turn)) return;
   char* buf = static_cast<char*>(ra.out);
   const bool al = is_al16(buf);
-  char* const root_outbox = slot_ptr(pt, root, turn.parity, b, n);
+  const long long cv = P.cv;
 
   for (int round = 0; round < P.rounds; ++round) {
-    const long long off = ((long long)round * gridDim.x + b) * P.cv;
-    const long long len = clampll(P.nvec - off, 0, P.cv);
+    const long long off = ((long long)round * gridDim.x + b) * cv;
+    const long long len = clampll(P.nvec - off, 0, cv);
     const u64 e_pub = turn.base + 2 * (u64)round + 1, e_got = e_pub + 1;
+    char* root_outbox = slot_ptr(pt, root, turn.parity, b, round & 1, n);
     if (r == root) {
-      for (long long v = threadIdx.x; v < len; v += blockDim.x)
-        stv(root_outbox + v * 16, load_vec<1>(buf, off + v, P.count, al));
-      signal_peers(pt, b, e_pub);
-      if (round + 1 < P.rounds && !wait_peers(pt, b, e_got, P.wait_ns)) return;
+      if (round >= 2 && !wait_peers(pt, b, kChanB, turn.base + 2 * (u64)(round - 2) + 2, P.wait_ns)) return;
+      copy_vectors(len, [&](long long v) { return load_vec<1>(buf, off + v, P.count, al); },
+                   [&](long long v, uint4 x) { stv(root_outbox + v * 16, x); });
+      signal_peers(pt, b, kChanA, e_pub);
     } else {
-      if (!wait_peers(pt, b, e_pub, P.wait_ns, root)) return;
-      for (long long v = threadIdx.x; v < len; v += blockDim.x)
-        store_vec<1>(buf, off + v, P.count, al, ldv(root_outbox + v * 16));
-      signal_peers(pt, b, e_got, root);
+      if (!wait_peers(pt, b, kChanA, e_pub, P.wait_ns, root)) return;
+      copy_vectors(len, [&](long long v) { return ldv(root_outbox + v * 16); },
+                   [&](long long v, uint4 x) { store_vec<1>(buf, off + v, P.count, al, x); });
+      signal_peers(pt, b, kChanB, e_got, root);
     }
   }
   end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
 }
 
 // ---------------------------------------------------------------------------
-// Single-rank path: out = in (* scale for MEAN, which is 1 at n = 1), one pass
-// over HBM.  Also serves the table form (bucket -> per-tensor copies).
+// Single-rank path: out = in (the MEAN factor is 1 at n = 1), one pass over
+// HBM.  Also serves the table form (bucket -> per-tensor copies).
 
 template <int ES, bool TABLE>
-__global__ void __launch_bounds__(512, 1) local_copy_kernel(const OpParams P) {
+__global__ void __launch_bounds__(kMaxThreads, 1) local_copy_kernel(const __grid_constant__ OpParams P) {
   extern __shared__ __align__(16) unsigned char smem[];
   const Message<ES, TABLE> msg = make_message<ES, TABLE>(P, P.ra[0], smem);
   const long long stride = (long long)gridDim.x * blockDim.x;

@@ -31,7 +31,8 @@ typedef double InstT;
 #define DGN_CAT(a, b) DGN_CAT2(a, b)
 
 #if DGN_INST < 8
-// kind: 0 one-shot, 1 two-shot, 2 reduce-scatter
+// kind: 0 one-shot, 1 two-shot (lock-step), 2 reduce-scatter, 3 low-latency one-shot,
+//       4 two-shot (warp-specialised)
 const void* DGN_CAT(reduce_kernel_fn_, DGN_INST)(int kind, bool table) {
   switch (kind) {
     case 0:
@@ -42,6 +43,12 @@ const void* DGN_CAT(reduce_kernel_fn_, DGN_INST)(int kind, bool table) {
                    : (const void*)ar_twoshot_kernel<InstT, false, false>;
     case 2:
       return (const void*)ar_twoshot_kernel<InstT, false, true>;
+    case 4:
+      return table ? (const void*)ar_twoshot_ws_kernel<InstT, true>
+                   : (const void*)ar_twoshot_ws_kernel<InstT, false>;
+    case 3:
+      return table ? (const void*)ar_oneshot_ll_kernel<InstT, true>
+                   : (const void*)ar_oneshot_ll_kernel<InstT, false>;
     default:
       return nullptr;
   }

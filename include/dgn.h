@@ -72,7 +72,8 @@ typedef enum {
   DGN_VARIANT_AUTO = 0,
   DGN_VARIANT_ONESHOT = 1, /* every rank pushes its whole message to every peer */
   DGN_VARIANT_TWOSHOT = 2, /* reduce-scatter by peer stores + all-gather by peer loads */
-  DGN_VARIANT_NVLS = 3     /* NVSwitch multicast (multimem) where the box exposes it */
+  DGN_VARIANT_NVLS = 3,    /* NVSwitch multicast (multimem) where the box exposes it */
+  DGN_VARIANT_LL = 4       /* one-shot with flag-in-data lines, no barrier (small messages) */
 } dgn_variant;
 
 /* ---- library ----------------------------------------------------------- */
