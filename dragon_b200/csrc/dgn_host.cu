@@ -130,10 +130,10 @@ Geometry make_geometry(int nranks) {
   g.slot_bytes = env_ll("DGN_SLOT_BYTES", 128 * 1024);
   if (g.slot_bytes < 4096) g.slot_bytes = 4096;
   g.slot_bytes = (g.slot_bytes + 4095) & ~4095ll;
-  g.ll_max_blocks = (int)env_ll("DGN_LL_MAX_BLOCKS", 32);
+  g.ll_max_blocks = (int)env_ll("DGN_LL_MAX_BLOCKS", 64);
   if (g.ll_max_blocks < 1) g.ll_max_blocks = 1;
   if (g.ll_max_blocks > g.max_blocks) g.ll_max_blocks = g.max_blocks;
-  g.ll_slot_bytes = env_ll("DGN_LL_SLOT_BYTES", 32 * 1024);
+  g.ll_slot_bytes = env_ll("DGN_LL_SLOT_BYTES", 64 * 1024);
   if (g.ll_slot_bytes < 4096) g.ll_slot_bytes = 4096;
   g.ll_slot_bytes = (g.ll_slot_bytes + 4095) & ~4095ll;
   g.flags_bytes = (size_t)g.max_blocks * 3 * kMaxRanks * sizeof(u64);
@@ -259,9 +259,11 @@ const void* reduce_fn(int dtype, int kind, bool table) {
 long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 
 long long default_ll_max(int n) {
-  if (n <= 2) return 256ll << 10;
-  if (n <= 4) return 128ll << 10;
-  return 64ll << 10;
+  // Flag-in-data lines carry 8 bytes of data per 16 sent and every rank sends
+  // its whole message to every peer: (n - 1) * 2 * S bytes per rank.
+  if (n <= 2) return 1ll << 20;
+  if (n <= 4) return 256ll << 10;
+  return 128ll << 10;
 }
 
 long long default_oneshot_max(int n) {
