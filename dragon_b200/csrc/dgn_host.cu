@@ -592,6 +592,12 @@ double now_s() {
 
 }  // namespace
 
+namespace dgn {
+// For the other translation units of the library: record an error message for
+// dgn_last_error_string and hand back `code`.
+int report_error(int code, const char* message) { return fail(code, "%s", message); }
+}  // namespace dgn
+
 // ---------------------------------------------------------------------------
 // C-ABI
 

@@ -169,6 +169,32 @@ int dgn_broadcast(dgn_comm_t comm, void* buf, int64_t count, int dtype, int root
 int dgn_reducescatter(dgn_comm_t comm, const void* in, void* out, int64_t count, int dtype,
                       int redop, void* stream);
 
+/* ALLREDUCE of `nranks` buffers that all live on the CURRENT device, without
+ * allocating anything.  (No counterpart in the reference: Dragon's collectives
+ * always go through a communicator that owns library-allocated buffers.)
+ *
+ * For callers that must not call cudaMalloc -- a framework whose memory
+ * planner already owns the whole device pool, a serving loop that cannot take
+ * the allocator's device-wide synchronisation, a plug-in invoked where its
+ * host forbids allocation.  Such callers cannot create a dgn communicator,
+ * whose workspace is allocated; here the kernel's scratch memory is a fixed
+ * 4,198,400-byte array inside the library image (each GPU that loads the
+ * library holds it until the process exits).
+ *
+ * in_ptrs[r] / out_ptrs[r] (r < nranks <= 8) are device buffers of `count`
+ * elements on the current device; every out buffer receives the reduction of
+ * all in buffers (same order and rounding as dgn_allreduce); in_ptrs[r] may
+ * equal out_ptrs[r].  Limit: count * element size <= 16384 bytes; larger
+ * messages are rejected with DGN_ERR_ARG and a message.
+ * The first call on a device looks up the array's device address; make that
+ * call before any stream capture begins on that device.  The call enqueues a
+ * memset of the scratch it uses and one kernel on `stream` and returns; it
+ * calls no allocating routine.  All calls share the one array per device:
+ * two calls whose work overlaps on the GPU (different streams, no ordering
+ * between them) race and give undefined results -- order them. */
+int dgn_allreduce_static(int nranks, const void* const* in_ptrs, void* const* out_ptrs,
+                         int64_t count, int dtype, int redop, void* stream);
+
 /* ---- introspection for benchmarks and tests ------------------------------ */
 
 /* Number of kernels this library has launched from the calling process. */
