@@ -85,17 +85,17 @@ def build(verbose=False, extra_flags=()):
     if _newer(lib, objs):
         _run([nvcc] + ARCH + ["-shared", "-o", lib] + objs + ["-Xlinker", "--no-undefined"])
 
-    # The C++ operator layer (host code only) links against libdgn.
+    # The C++ operator layer (host code; nvcc drives g++ and links the CUDA
+    # runtime) links against libdgn.
     op_dir = os.path.join(ROOT, "operators")
     if os.path.isdir(op_dir):
-        cxx = shutil.which("g++") or "g++"
         srcs = [os.path.join(op_dir, f) for f in sorted(os.listdir(op_dir)) if f.endswith(".cc")]
         op_hdrs = [os.path.join(op_dir, f) for f in sorted(os.listdir(op_dir)) if f.endswith(".h")]
         op_lib = os.path.join(LIB, "libdragon_collective.so")
         if srcs and _newer(op_lib, srcs + op_hdrs + [lib] + hdrs):
-            _run([cxx, "-O2", "-std=c++17", "-fPIC", "-Wall", "-shared", "-o", op_lib] + srcs
-                 + ["-I", os.path.join(REPO, "include"), "-I", ROOT, "-L", LIB, "-ldgn",
-                    "-Wl,-rpath,$ORIGIN", "-Wl,--no-undefined"])
+            _run([nvcc, "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared", "-o", op_lib]
+                 + srcs + ["-I", os.path.join(REPO, "include"), "-I", op_dir, "-L", LIB, "-ldgn",
+                           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-Xlinker", "--no-undefined"])
     return lib
 
 
