@@ -20,6 +20,7 @@
 #include <unistd.h>
 
 #include <atomic>
+#include <deque>
 #include <string>
 #include <vector>
 
@@ -204,8 +205,7 @@ namespace {
 struct Team {
   int n = 0, device = 0;
   std::vector<dgn_comm*> members;
-  OpDesc pending[kMaxRanks];
-  unsigned arrived = 0;
+  std::deque<OpDesc> pending[kMaxRanks];
   int alive = 0;
 };
 
@@ -432,50 +432,49 @@ int issue(dgn_comm* c, const OpDesc& d) {
     c->last_plan = p;
     return DGN_OK;
   }
+  // Emulated team: a virtual rank may run several collectives ahead of the
+  // others (one operator call can issue one per bucket), so calls queue per
+  // rank; whenever every rank has one waiting, the heads are launched together.
   Team* t = c->team;
-  if (t->arrived & (1u << c->rank)) {
-    t->arrived = 0;
-    return fail(DGN_ERR_STATE, "virtual rank %d issued a second collective before the others arrived", c->rank);
-  }
-  if (t->arrived) {
-    int first = 0;
-    while (!(t->arrived & (1u << first))) ++first;
-    const OpDesc& f = t->pending[first];
-    if (f.kind != d.kind || f.dtype != d.dtype || f.redop != d.redop || f.root != d.root ||
-        f.count != d.count || f.nvec != d.nvec || f.ntensors != d.ntensors || f.stream != d.stream) {
-      t->arrived = 0;
-      return fail(DGN_ERR_ARG, "virtual rank %d issued a collective that differs from rank %d's", c->rank, first);
+  t->pending[c->rank].push_back(d);
+  for (;;) {
+    for (int r = 0; r < t->n; ++r)
+      if (t->pending[r].empty()) return DGN_OK;
+    const OpDesc f = t->pending[0].front();
+    for (int r = 1; r < t->n; ++r) {
+      const OpDesc& o = t->pending[r].front();
+      if (f.kind != o.kind || f.dtype != o.dtype || f.redop != o.redop || f.root != o.root ||
+          f.count != o.count || f.nvec != o.nvec || f.ntensors != o.ntensors || f.stream != o.stream) {
+        for (int q = 0; q < t->n; ++q) t->pending[q].clear();
+        return fail(DGN_ERR_ARG, "virtual rank %d issued a collective that differs from rank 0's", r);
+      }
     }
+    // Shape the launch so that every block of every virtual rank is resident.
+    Plan p = make_plan(c, f, 0);
+    KernelChoice k = choose_kernel(c, f, p);
+    if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", f.dtype);
+    int per_sm = 0;
+    DGN_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k.fn, p.threads, k.smem));
+    int cap = per_sm * c->num_sms / t->n;
+    if (cap < 1) return fail(DGN_ERR_UNSUPPORTED, "emulated team does not fit on the device");
+    if (p.blocks > cap) {
+      p = make_plan(c, f, cap);
+      k = choose_kernel(c, f, p);
+    }
+    OpParams P;
+    fill_params(&P, c, f, p);
+    for (int r = 0; r < t->n; ++r) {
+      const OpDesc& o = t->pending[r].front();
+      P.peers[r] = t->members[r]->table;
+      P.ra[r].in = o.in;
+      P.ra[r].out = o.out;
+      P.ra[r].table = o.table;
+    }
+    for (int r = 0; r < t->n; ++r) t->pending[r].pop_front();
+    int rc = launch(k.fn, dim3(p.blocks, t->n), p.threads, k.smem, f.stream, &P, true);
+    if (rc != DGN_OK) return rc;
+    for (dgn_comm* m : t->members) m->last_plan = p;
   }
-  t->pending[c->rank] = d;
-  t->arrived |= 1u << c->rank;
-  if (t->arrived != (1u << t->n) - 1u) return DGN_OK;
-  t->arrived = 0;
-
-  // Shape the launch so that every block of every virtual rank is resident.
-  Plan p = make_plan(c, d, 0);
-  KernelChoice k = choose_kernel(c, d, p);
-  if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
-  int per_sm = 0;
-  DGN_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k.fn, p.threads, k.smem));
-  int cap = per_sm * c->num_sms / t->n;
-  if (cap < 1) return fail(DGN_ERR_UNSUPPORTED, "emulated team does not fit on the device");
-  if (p.blocks > cap) {
-    p = make_plan(c, d, cap);
-    k = choose_kernel(c, d, p);
-  }
-  OpParams P;
-  fill_params(&P, c, d, p);
-  for (int r = 0; r < t->n; ++r) {
-    P.peers[r] = t->members[r]->table;
-    P.ra[r].in = t->pending[r].in;
-    P.ra[r].out = t->pending[r].out;
-    P.ra[r].table = t->pending[r].table;
-  }
-  int rc = launch(k.fn, dim3(p.blocks, t->n), p.threads, k.smem, d.stream, &P, true);
-  if (rc != DGN_OK) return rc;
-  for (dgn_comm* m : t->members) m->last_plan = p;
-  return DGN_OK;
 }
 
 int launch_local_copy(dgn_comm* c, const OpDesc& d, int es) {

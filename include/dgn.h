@@ -110,8 +110,9 @@ int dgn_comm_create(int rank, int nranks, int device, const char* rendezvous_dir
  * communicator behaves like one rank; a collective is launched (as a single
  * cooperative kernel covering every virtual rank) when the last of the
  * `nranks` communicators has issued its call, so a single host thread may
- * call them one after another.  All calls of one collective must use the
- * same stream.  Used to exercise the multi-rank kernels where fewer GPUs
+ * call them one after another; calls queue per rank, so one rank may issue
+ * several collectives before the others follow.  All calls of one collective
+ * must use the same stream.  Used to exercise the multi-rank kernels where fewer GPUs
  * than ranks are available. */
 int dgn_comm_create_emulated(int nranks, int device, dgn_comm_t* comms /* [nranks] */);
 

@@ -50,8 +50,8 @@ def to_numpy(t, dtype):
 
 
 def assert_bits_equal(got, want, what=""):
-    got = np.ascontiguousarray(got).view(np.uint8)
-    want = np.ascontiguousarray(want).view(np.uint8)
+    got = np.ascontiguousarray(got).reshape(-1).view(np.uint8)
+    want = np.ascontiguousarray(want).reshape(-1).view(np.uint8)
     assert got.size == want.size, "{}: size {} != {}".format(what, got.size, want.size)
     if not np.array_equal(got, want):
         bad = np.flatnonzero(got != want)

@@ -1,0 +1,51 @@
+"""Child process of tests/test_multigpu.py: one rank on its own GPU, joined to
+the other through the library's file rendezvous and CUDA IPC."""
+
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world, rdv = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+    import numpy as np
+    import torch
+
+    from dragon_b200.comm import Communicator
+    from oracle import oracle
+    from tests import helpers as H
+
+    torch.cuda.set_device(rank)
+    dev = "cuda:{}".format(rank)
+    comm = Communicator.create(rank, world, rank, rdv, "ipc-test", timeout_ms=120000)
+    comm.set_wait_limit_ms(20000)
+    for variant in (4, 1, 2):
+        comm.set_tuning(variant=variant)
+        for dtype, count, redop in ((oracle.F16, 300001, "MEAN"), (oracle.F32, 1 << 22, "SUM")):
+            arrays = [H.make_input(r, count, dtype) for r in range(world)]
+            x = H.to_torch(arrays[rank], dtype, dev)
+            comm.all_reduce([x], None, redop)
+            torch.cuda.synchronize()
+            assert comm.status() == 0
+            H.assert_bits_equal(H.to_numpy(x, dtype), oracle.allreduce(arrays, dtype, redop))
+    comm.set_tuning()
+    idx = [np.arange(1000, dtype=np.int64) * (r + 1) for r in range(world)]
+    out = torch.empty(world * 1000, dtype=torch.int64, device=dev)
+    comm.all_gather(torch.from_numpy(idx[rank]).to(dev), out)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), np.concatenate(idx))
+    # Leave only after the peer has finished too: a last all-reduce is the barrier.
+    done = torch.ones(1, device=dev)
+    comm.all_reduce([done], None, "SUM")
+    torch.cuda.synchronize()
+    assert float(done.item()) == world
+    import time
+    time.sleep(0.5)
+    comm.destroy()
+    print("WORKER_OK", rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,149 @@
+"""Real peer traffic: one rank per GPU.  Skipped where fewer than two GPUs are
+visible.  Ranks of one process use peer access; the two-process case goes
+through CUDA IPC and the file rendezvous (dgn_comm_create)."""
+
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def gpu_count():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+needs_two = pytest.mark.skipif(gpu_count() < 2, reason="needs at least two GPUs")
+
+
+@pytest.fixture(scope="module")
+def comms(dgn_lib):
+    from dragon_b200.comm import Communicator
+    n = min(gpu_count(), 8)
+    made = [Communicator.init_local(r, n, r) for r in range(n)]
+    handles = [c.handle_bytes() for c in made]
+    for c in made:
+        c.connect(handles)
+    yield made
+    for r in range(n):
+        torch.cuda.synchronize(r)
+    for c in made:
+        c.destroy()
+
+
+def sync_all(n):
+    for r in range(n):
+        torch.cuda.synchronize(r)
+
+
+@needs_two
+@pytest.mark.parametrize("variant", [4, 1, 2])
+def test_allreduce_across_gpus(comms, variant):
+    n = len(comms)
+    for c in comms:
+        c.set_tuning(variant=variant)
+    try:
+        for dtype, redop, count in ((oracle.F32, "MEAN", 100003), (oracle.F16, "MEAN", 1 << 20),
+                                    (oracle.BF16, "SUM", 4099), (oracle.I64, "SUM", 70001),
+                                    (oracle.F32, "SUM", 4194304)):
+            arrays = [H.make_input(r, count, dtype) for r in range(n)]
+            xs = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
+            for r in range(n):
+                with torch.cuda.device(r):
+                    comms[r].all_reduce([xs[r]], None, redop)
+            sync_all(n)
+            want = oracle.allreduce(arrays, dtype, redop)
+            for r in range(n):
+                assert comms[r].status() == 0
+                H.assert_bits_equal(H.to_numpy(xs[r], dtype), want, "variant {} rank {}".format(variant, r))
+    finally:
+        for c in comms:
+            c.set_tuning()
+
+
+@needs_two
+def test_back_to_back_mixed_collectives_across_gpus(comms):
+    n = len(comms)
+    steps = 12
+    sizes = [257, 70000, 3, 1 << 19, 5000, 1 << 21]
+    arrays = [[H.make_input(r, sizes[s % len(sizes)], oracle.F32, seed=31 * s) for r in range(n)] for s in range(steps)]
+    xs = [[H.to_torch(a, oracle.F32, "cuda:{}".format(r)) for r, a in enumerate(row)] for row in arrays]
+    gathered = [torch.empty(n * 257, device="cuda:{}".format(r)) for r in range(n)]
+    for s in range(steps):
+        for r in range(n):
+            with torch.cuda.device(r):
+                comms[r].all_reduce([xs[s][r]], None, "SUM")
+                if s == 6:
+                    comms[r].all_gather(xs[0][r], gathered[r])
+                    comms[r].broadcast(xs[2][r], n - 1)
+    sync_all(n)
+    for s in range(steps):
+        if s in (0, 2):
+            continue
+        want = oracle.allreduce(arrays[s], oracle.F32, "SUM")
+        for r in range(n):
+            H.assert_bits_equal(H.to_numpy(xs[s][r], oracle.F32), want, "step {} rank {}".format(s, r))
+    first = oracle.allreduce(arrays[0], oracle.F32, "SUM")
+    for r in range(n):
+        H.assert_bits_equal(H.to_numpy(gathered[r], oracle.F32), np.tile(first, n))
+
+
+@needs_two
+def test_gather_broadcast_reducescatter_across_gpus(comms):
+    n = len(comms)
+    arrays = [H.make_input(r, n * 65536, oracle.I64) for r in range(n)]
+    xs = [H.to_torch(a, oracle.I64, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
+    outs = [torch.empty(n * n * 65536, dtype=torch.int64, device="cuda:{}".format(r)) for r in range(n)]
+    rs = [torch.empty(65536, dtype=torch.int64, device="cuda:{}".format(r)) for r in range(n)]
+    for r in range(n):
+        with torch.cuda.device(r):
+            comms[r].all_gather(xs[r], outs[r])
+            comms[r].reduce_scatter(xs[r], rs[r], "SUM")
+    sync_all(n)
+    want = oracle.allgather(arrays, oracle.I64)
+    parts = oracle.reducescatter(arrays, oracle.I64, "SUM")
+    for r in range(n):
+        assert np.array_equal(outs[r].cpu().numpy(), want)
+        assert np.array_equal(rs[r].cpu().numpy(), parts[r])
+    for r in range(n):
+        with torch.cuda.device(r):
+            comms[r].broadcast(xs[r], 1)
+    sync_all(n)
+    for r in range(n):
+        assert np.array_equal(xs[r].cpu().numpy(), arrays[1])
+
+
+@needs_two
+def test_two_processes_over_ipc_and_file_rendezvous():
+    with tempfile.TemporaryDirectory() as rdv:
+        procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "mp_gpu_worker.py"), str(r), "2", rdv],
+                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+        for r, p in enumerate(procs):
+            try:
+                out, _ = p.communicate(timeout=300)
+            except subprocess.TimeoutExpired:
+                for q in procs:
+                    q.kill()
+                raise
+            assert p.returncode == 0 and "WORKER_OK {}".format(r) in out, out[-3000:]
+
+
+def test_rendezvous_gives_up_on_a_rank_that_never_arrives(dgn_lib):
+    """Failure made on the host: the second rank never shows up; creation
+    returns DGN_ERR_TIMEOUT after the limit and no GPU work was started."""
+    from dragon_b200 import _C
+    from dragon_b200.comm import Communicator
+    with tempfile.TemporaryDirectory() as rdv:
+        with pytest.raises(_C.DgnError) as e:
+            Communicator.create(0, 2, 0, rdv, "lonely", timeout_ms=300)
+        assert e.value.status == _C.ERR_TIMEOUT and "never arrived" in str(e.value)
+        assert os.listdir(rdv) == []
