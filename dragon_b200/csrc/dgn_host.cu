@@ -209,8 +209,37 @@ struct Team {
   int alive = 0;
 };
 
+const void* reduce_fn(int dtype, int kind, bool table);
+
+// Loads every kernel of the library on the current device.  With lazy module
+// loading the first launch of a kernel has to load its module, which can wait
+// for the device to go idle; a device that is already spinning in a
+// collective, waiting for this very launch on a peer, would never go idle.
+// Touching each kernel once, before any collective, takes loading out of the
+// launch path.
+int preload_kernels() {
+  cudaFuncAttributes attr;
+  for (int dtype = 0; dtype < 8; ++dtype) {
+    for (int kind = 0; kind <= 4; ++kind) {
+      for (int table = 0; table < 2; ++table) {
+        const void* fn = reduce_fn(dtype, kind, table != 0);
+        if (fn) DGN_CUDA(cudaFuncGetAttributes(&attr, fn));
+      }
+    }
+  }
+  DGN_CUDA(cudaFuncGetAttributes(&attr, allgather_kernel_fn()));
+  DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_kernel_fn()));
+  const int sizes[4] = {1, 2, 4, 8};
+  for (int es : sizes)
+    for (int table = 0; table < 2; ++table)
+      DGN_CUDA(cudaFuncGetAttributes(&attr, local_copy_kernel_fn(es, table != 0)));
+  return DGN_OK;
+}
+
 int alloc_workspace(dgn_comm* c) {
   DeviceGuard g(c->device);
+  int rc = preload_kernels();
+  if (rc != DGN_OK) return rc;
   DGN_CUDA(cudaMalloc(&c->base, c->geo.total));
   DGN_CUDA(cudaMemset(c->base, 0, c->geo.stage_off));
   DGN_CUDA(cudaMemset(static_cast<char*>(c->base) + c->geo.ll_off, 0, c->geo.total - c->geo.ll_off));
