@@ -43,6 +43,9 @@ def parse_args():
                     help="message-size sweep beside the headline (auto: up to 256 MiB)")
     ap.add_argument("--no-nccl", action="store_true", help="skip the NCCL comparison in the sweep")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-emulated", action="store_true", help="N=1: skip the emulated 8-rank timings")
+    ap.add_argument("--emulated-only", action="store_true",
+                    help="N=1: run only the emulated multi-rank kernels (profiling target)")
     return ap.parse_args()
 
 
@@ -229,13 +232,13 @@ def bench_single(args):
         "gpu_launches": int(launches),
         "clocks": sampler.summary(),
     }
-    traffic_path = os.path.join(ROOT, "profiles", "local_copy_traffic.json")
-    if os.path.exists(traffic_path):
-        with open(traffic_path) as f:
-            t = json.load(f)
-        # ncu capture of a smaller message; DRAM traffic scales with the vectors copied.
-        line["roofline"]["traffic"] = t["dram_bytes_per_launch"] * (S / t["message_bytes"])
-    line["emulated_ranks_one_gpu"] = bench_emulated(args)
+    # DRAM traffic of the copy kernel from its ncu capture (profiles/local_copy_kernel_256MiB.md):
+    # 268.5 MB read + 221.3 MB written per 256 MiB message; the rest of the
+    # written lines is still in the 126 MB L2 when the kernel ends.  Traffic
+    # grows with the vectors copied, so it is scaled by the message size.
+    line["roofline"]["traffic"] = (268.47e6 + 221.29e6) * (S / float(256 * MiB))
+    if not args.no_emulated:
+        line["emulated_ranks_one_gpu"] = bench_emulated(args)
     if not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_local_copy_baseline(args)
         line["cpu_baseline_config1"] = cpu_config1_baseline()
@@ -252,7 +255,7 @@ def bench_emulated(args):
     out = {}
     comms = Communicator.emulated(8, 0)
     try:
-        for label, nbytes in (("oneshot_64KiB", 64 << 10), ("twoshot_64MiB", 64 << 20)):
+        for label, nbytes in (("lowlatency_64KiB", 64 << 10), ("twoshot_64MiB", 64 << 20)):
             count = nbytes // 4
             xs = [make_message(r, count, "f32", "cuda:0") for r in range(8)]
             ops = [c.prepare_all_reduce([x], [x], "MEAN") for c, x in zip(comms, xs)]
@@ -557,6 +560,8 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         line = bench_reference(args)
+    elif args.emulated_only:
+        line = {"emulated_ranks_one_gpu": bench_emulated(args)}
     elif args.gpus <= 1 and int(os.environ.get("WORLD_SIZE", "1")) <= 1:
         line = bench_single(args)
     else:
