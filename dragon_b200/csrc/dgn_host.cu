@@ -118,10 +118,11 @@ uint64_t host_identity() {
 struct Geometry {
   int nranks = 1, max_blocks = 0, ll_max_blocks = 0;
   long long slot_bytes = 0, ll_slot_bytes = 0;
-  size_t flags_bytes = 0, blk_off = 0, stage_off = 0, ll_off = 0, total = 0;
+  size_t flags_bytes = 0, blk_off = 0, stage_off = 0, ll_off = 0, ll2_off = 0, total = 0;
 };
 
-// Workspace layout: [flags][block states] | [staging] | [low-latency region].
+// Workspace layout: [flags][block states] | [staging] | [low-latency region] |
+// [two-shot low-latency region].
 Geometry make_geometry(int nranks) {
   Geometry g;
   g.nranks = nranks;
@@ -142,7 +143,8 @@ Geometry make_geometry(int nranks) {
   size_t head = g.blk_off + (size_t)g.max_blocks * sizeof(BlockState);
   g.stage_off = (head + 4095) & ~(size_t)4095;
   g.ll_off = g.stage_off + 2 * (size_t)g.max_blocks * 2 * (size_t)(2 * nranks) * (size_t)g.slot_bytes;
-  g.total = g.ll_off + 2 * (size_t)g.ll_max_blocks * (size_t)nranks * (size_t)g.ll_slot_bytes;
+  g.ll2_off = g.ll_off + 2 * (size_t)g.ll_max_blocks * (size_t)nranks * (size_t)g.ll_slot_bytes;
+  g.total = g.ll2_off + 2 * (size_t)g.ll_max_blocks * 2 * (size_t)nranks * (size_t)g.ll_slot_bytes;
   return g;
 }
 
@@ -191,7 +193,7 @@ struct dgn_comm {
   u64 wait_ns = 5000000000ull;
   int tune_variant = 0, tune_blocks = 0, tune_threads = 0;
   long long tune_chunk = 0;
-  long long oneshot_max_bytes = -1, ll_max_bytes = -1;
+  long long oneshot_max_bytes = -1, ll_max_bytes = -1, ll2_max_bytes = -1;
   bool fused_twoshot = false;  // DGN_TWOSHOT_FUSED=1: lock-step two-shot kernel instead of the warp-specialised one
   Team* team = nullptr;
   std::vector<TableEntry> tables;
@@ -220,7 +222,7 @@ const void* reduce_fn(int dtype, int kind, bool table);
 int preload_kernels() {
   cudaFuncAttributes attr;
   for (int dtype = 0; dtype < 8; ++dtype) {
-    for (int kind = 0; kind <= 4; ++kind) {
+    for (int kind = 0; kind <= 5; ++kind) {
       for (int table = 0; table < 2; ++table) {
         const void* fn = reduce_fn(dtype, kind, table != 0);
         if (fn) DGN_CUDA(cudaFuncGetAttributes(&attr, fn));
@@ -260,6 +262,7 @@ void fill_peer_table(const dgn_comm* c, PeerTable* t) {
     t->flags[j] = reinterpret_cast<u64*>(b);
     t->stage[j] = b + c->geo.stage_off;
     t->ll[j] = b + c->geo.ll_off;
+    t->ll2[j] = b + c->geo.ll2_off;
   }
   t->blk = reinterpret_cast<BlockState*>(static_cast<char*>(c->base) + c->geo.blk_off);
   t->status = c->status_dev;
@@ -290,16 +293,23 @@ long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 long long default_ll_max(int n) {
   // Flag-in-data lines carry 8 bytes of data per 16 sent and every rank sends
   // its whole message to every peer: (n - 1) * 2 * S bytes per rank.
+  // Measured: n = 2 up to 1 MiB, n = 4 up to 512 KiB.
   if (n <= 2) return 1ll << 20;
-  if (n <= 4) return 256ll << 10;
+  if (n <= 4) return 512ll << 10;
   return 128ll << 10;
+}
+
+long long default_ll2_max(int n) {
+  // Two ranks gain nothing from sharding (one-shot moves the same bytes).
+  if (n <= 2) return 0;
+  return 4ll << 20;
 }
 
 long long default_oneshot_max(int n) {
   // Above these sizes the (n - 1)x link traffic of one-shot costs more than
   // the second flag exchange of two-shot.
   if (n <= 2) return 1ll << 20;
-  if (n <= 4) return 512ll << 10;
+  if (n <= 4) return 1ll << 20;
   return 256ll << 10;
 }
 
@@ -346,6 +356,31 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
         p.threads = (int)(t < 64 ? 64 : (t > 512 ? 512 : t));
       }
       return p;
+    }
+    // Low-latency two-shot: shard slices as flag-in-data lines.
+    {
+      const long long vs = ceil_div(d.nvec, n);
+      const bool ll2_fits = ceil_div(vs, ll_bmax) <= ll_vecs;
+      const long long ll2_thr = c->ll2_max_bytes >= 0 ? c->ll2_max_bytes : default_ll2_max(n);
+      bool ll2 = ll2_fits && bytes <= ll2_thr;
+      if (c->tune_variant == DGN_VARIANT_LL2) ll2 = ll2_fits;
+      else if (c->tune_variant != DGN_VARIANT_AUTO) ll2 = false;
+      if (ll2) {
+        p.variant = DGN_VARIANT_LL2;
+        long long b = ceil_div(vs, 256);
+        if (c->tune_blocks > 0) b = c->tune_blocks;
+        if (b > ll_bmax) b = ll_bmax;
+        if (b < 1) b = 1;
+        if (ceil_div(vs, b) > ll_vecs) b = ceil_div(vs, ll_vecs);
+        p.blocks = (int)b;
+        p.cv = (int)ceil_div(vs, b);
+        p.rounds = 1;
+        if (c->tune_threads <= 0) {
+          long long t = ((long long)p.cv + 31) / 32 * 32;
+          p.threads = (int)(t < 64 ? 64 : (t > 512 ? 512 : t));
+        }
+        return p;
+      }
     }
     const long long thr = c->oneshot_max_bytes >= 0 ? c->oneshot_max_bytes : default_oneshot_max(n);
     bool oneshot = bytes <= thr;
@@ -395,7 +430,7 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
   const bool table = d.ntensors > 1;
   switch (d.kind) {
     case kOpAllReduce:
-      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_LL ? 3 : (p.variant == DGN_VARIANT_ONESHOT ? 0 : (p.threads >= 96 && p.rounds >= 3 && !c->fused_twoshot ? 4 : 1)), table);
+      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_LL2 ? 5 : p.variant == DGN_VARIANT_LL ? 3 : (p.variant == DGN_VARIANT_ONESHOT ? 0 : (p.threads >= 96 && p.rounds >= 3 && !c->fused_twoshot ? 4 : 1)), table);
       k.smem = table ? table_smem_bytes(d.ntensors) : 0;
       break;
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
@@ -479,17 +514,25 @@ int issue(dgn_comm* c, const OpDesc& d) {
       }
     }
     // Shape the launch so that every block of every virtual rank is resident.
+    // A smaller grid can mean another block size, hence another occupancy:
+    // iterate until the plan fits its own cap.
     Plan p = make_plan(c, f, 0);
     KernelChoice k = choose_kernel(c, f, p);
-    if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", f.dtype);
-    int per_sm = 0;
-    DGN_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k.fn, p.threads, k.smem));
-    int cap = per_sm * c->num_sms / t->n;
-    if (cap < 1) return fail(DGN_ERR_UNSUPPORTED, "emulated team does not fit on the device");
-    if (p.blocks > cap) {
-      p = make_plan(c, f, cap);
-      k = choose_kernel(c, f, p);
+    bool fits = false;
+    for (int iter = 0; iter < 6 && !fits; ++iter) {
+      if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", f.dtype);
+      int per_sm = 0;
+      DGN_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k.fn, p.threads, k.smem));
+      const int cap = per_sm * c->num_sms / t->n;
+      if (cap < 1) return fail(DGN_ERR_UNSUPPORTED, "emulated team does not fit on the device");
+      if (p.blocks <= cap) {
+        fits = true;
+      } else {
+        p = make_plan(c, f, cap);
+        k = choose_kernel(c, f, p);
+      }
     }
+    if (!fits) return fail(DGN_ERR_UNSUPPORTED, "no resident launch shape for the emulated team");
     OpParams P;
     fill_params(&P, c, f, p);
     for (int r = 0; r < t->n; ++r) {
@@ -669,6 +712,7 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
   c->wait_ns = (u64)env_ll("DGN_WAIT_LIMIT_MS", 5000) * 1000000ull;
   c->oneshot_max_bytes = env_ll("DGN_ONESHOT_MAX_BYTES", -1);
   c->ll_max_bytes = env_ll("DGN_LL_MAX_BYTES", -1);
+  c->ll2_max_bytes = env_ll("DGN_LL2_MAX_BYTES", -1);
   c->fused_twoshot = env_ll("DGN_TWOSHOT_FUSED", 0) != 0;
   c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
   int rc = alloc_workspace(c);
@@ -877,7 +921,7 @@ int dgn_comm_set_wait_limit_ms(dgn_comm_t c, int ms) {
 
 int dgn_comm_set_tuning(dgn_comm_t c, int variant, int blocks, int threads, int64_t chunk_bytes) {
   if (!c) return fail(DGN_ERR_ARG, "null communicator");
-  if (variant < 0 || variant > DGN_VARIANT_LL || blocks < 0 || threads < 0 || chunk_bytes < 0)
+  if (variant < 0 || variant > DGN_VARIANT_LL2 || blocks < 0 || threads < 0 || chunk_bytes < 0)
     return fail(DGN_ERR_ARG, "bad tuning value");
   if (variant == DGN_VARIANT_NVLS) return fail(DGN_ERR_UNSUPPORTED, "the NVLS variant is not set up on this communicator");
   c->tune_variant = variant;

@@ -79,6 +79,7 @@ struct BlockState {
 struct PeerTable {
   char* stage[kMaxRanks];  // rank j's staging base, as mapped on this device
   char* ll[kMaxRanks];     // rank j's low-latency region
+  char* ll2[kMaxRanks];    // rank j's region of the two-shot low-latency kernel
   u64* flags[kMaxRanks];   // rank j's flag array
   BlockState* blk;         // [max_blocks], local
   int* status;             // error word (pinned host memory, device-visible)
@@ -559,6 +560,120 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_oneshot_ll_kernel(const __g
     }
     if (!ok) return;
     msg.store(v0 + v, reduce_dispatch<T>(x, n, P.redop, P.scale));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// ALLREDUCE, low-latency two-shot: the same flag-in-data lines, but each rank
+// sends only shard slices.  Block b covers vectors [b*cv, (b+1)*cv) of every
+// shard:
+//   1. store my copy of peer j's slice, as lines, into j's inbox [kind 0][r]
+//   2. poll my inbox, reduce my slice in ascending rank order, scale, write my
+//      output and store the result, as lines, into every peer's gather area
+//      [kind 1][r]
+//   3. poll my gather area and write the peers' slices to my output
+// No fence and no separate flag anywhere: two link hops in total.  The link
+// carries 4(n-1)/n * S bytes per rank (lines are half flags), against
+// 2(n-1) * S for the one-shot kernel, so this one wins from a few hundred KiB.
+// Parity reuse is safe for the same reason as in the one-shot kernel: a peer
+// reaches collective k + 2 only after this rank has sent its part of k + 1.
+
+__device__ __forceinline__ char* ll2_ptr(const PeerTable& pt, int owner, int parity, int b, int kind, int src) {
+  const long long idx = (((long long)parity * pt.ll_max_blocks + b) * 2 + kind) * pt.nranks + src;
+  return pt.ll2[owner] + idx * pt.ll_slot_bytes;
+}
+
+// Polls one 32-byte pair of lines until both carry `flag`; false on timeout.
+__device__ __forceinline__ bool poll_ll(const char* line, unsigned flag, u64 wait_ns, int* status, uint4* out) {
+  uint4 a = ld_ll(line), c = ld_ll(line + 16);
+  if (a.y != flag || a.w != flag || c.y != flag || c.w != flag) {
+    const u64 t0 = global_timer_ns();
+    unsigned spins = 0;
+    for (;;) {
+      a = ld_ll(line);
+      c = ld_ll(line + 16);
+      if (a.y == flag && a.w == flag && c.y == flag && c.w == flag) break;
+      if ((++spins & 31u) == 0u && global_timer_ns() - t0 > wait_ns) {
+        *(volatile int*)status = kErrTimeout;
+        return false;
+      }
+    }
+  }
+  *out = make_uint4(a.x, a.z, c.x, c.z);
+  return true;
+}
+
+template <typename T, bool TABLE>
+__global__ void __launch_bounds__(kMaxThreads, 1) ar_twoshot_ll_kernel(const __grid_constant__ OpParams P) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const PeerTable& pt = P.peers[blockIdx.y];
+  const RankArgs& ra = P.ra[blockIdx.y];
+  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
+  const Message<(int)sizeof(T), TABLE> msg = make_message<(int)sizeof(T), TABLE>(P, ra, smem);
+  // The two low-latency kernels share one counter per block but use separate regions.
+  const u64 ops = pt.blk[b].ll_ops;
+  const unsigned flag = (unsigned)(ops % 0xfffffffeull) + 1u;
+  const int parity = (int)(ops & 1ull);
+  __syncthreads();
+  if (threadIdx.x == 0) pt.blk[b].ll_ops = ops + 1;
+
+  const long long vs = (P.nvec + n - 1) / n;
+  const long long off = (long long)b * P.cv;
+  auto shard_len = [&](int s) -> long long { return clampll(clampll(P.nvec - (long long)s * vs, 0, vs) - off, 0, P.cv); };
+
+  // 1. push
+  for (int k = 1; k < n; ++k) {
+    const int peer = (r + k) % n;
+    const long long len = shard_len(peer);
+    char* dst = ll2_ptr(pt, peer, parity, b, 0, r);
+    const long long ibase = (long long)peer * vs + off;
+    for (long long v = threadIdx.x; v < len; v += blockDim.x) {
+      const uint4 x = msg.load(ibase + v);
+      st_ll(dst + v * 32, x.x, x.y, flag);
+      st_ll(dst + v * 32 + 16, x.z, x.w, flag);
+    }
+  }
+  // 2. reduce my slice and publish it
+  {
+    const long long len = shard_len(r);
+    const long long obase = (long long)r * vs + off;
+    const char* inbox0 = ll2_ptr(pt, r, parity, b, 0, 0);
+    char* gdst[kMaxRanks];
+#pragma unroll
+    for (int k = 1; k < kMaxRanks; ++k) gdst[k] = (k < n) ? ll2_ptr(pt, (r + k) % n, parity, b, 1, r) : nullptr;
+    for (long long v = threadIdx.x; v < len; v += blockDim.x) {
+      uint4 x[kMaxRanks];
+      bool ok = true;
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s) {
+        if (s < n) {
+          if (s == r) x[s] = msg.load(obase + v);
+          else ok = poll_ll(inbox0 + s * pt.ll_slot_bytes + v * 32, flag, P.wait_ns, pt.status, &x[s]) && ok;
+        }
+      }
+      if (!ok) return;
+      const uint4 y = reduce_dispatch<T>(x, n, P.redop, P.scale);
+      msg.store(obase + v, y);
+#pragma unroll
+      for (int k = 1; k < kMaxRanks; ++k) {
+        if (k < n) {
+          st_ll(gdst[k] + v * 32, y.x, y.y, flag);
+          st_ll(gdst[k] + v * 32 + 16, y.z, y.w, flag);
+        }
+      }
+    }
+  }
+  // 3. gather
+  for (int k = 1; k < n; ++k) {
+    const int peer = (r + k) % n;
+    const long long len = shard_len(peer);
+    const char* src = ll2_ptr(pt, r, parity, b, 1, peer);
+    const long long obase = (long long)peer * vs + off;
+    for (long long v = threadIdx.x; v < len; v += blockDim.x) {
+      uint4 y;
+      if (!poll_ll(src + v * 32, flag, P.wait_ns, pt.status, &y)) return;
+      msg.store(obase + v, y);
+    }
   }
 }
 

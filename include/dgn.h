@@ -73,7 +73,8 @@ typedef enum {
   DGN_VARIANT_ONESHOT = 1, /* every rank pushes its whole message to every peer */
   DGN_VARIANT_TWOSHOT = 2, /* reduce-scatter by peer stores + all-gather by peer loads */
   DGN_VARIANT_NVLS = 3,    /* NVSwitch multicast (multimem) where the box exposes it */
-  DGN_VARIANT_LL = 4       /* one-shot with flag-in-data lines, no barrier (small messages) */
+  DGN_VARIANT_LL = 4,      /* one-shot with flag-in-data lines, no barrier (small messages) */
+  DGN_VARIANT_LL2 = 5      /* two-shot with flag-in-data lines (medium messages) */
 } dgn_variant;
 
 /* ---- library ----------------------------------------------------------- */

@@ -21,7 +21,7 @@ def main():
     dev = "cuda:{}".format(rank)
     comm = Communicator.create(rank, world, rank, rdv, "ipc-test", timeout_ms=120000)
     comm.set_wait_limit_ms(20000)
-    for variant in (4, 1, 2):
+    for variant in (4, 5, 1, 2):
         comm.set_tuning(variant=variant)
         for dtype, count, redop in ((oracle.F16, 300001, "MEAN"), (oracle.F32, 1 << 22, "SUM")):
             arrays = [H.make_input(r, count, dtype) for r in range(world)]

@@ -66,7 +66,7 @@ def check_allreduce(comms, count, dtype, redop, inplace=False):
 @pytest.mark.parametrize("dtype", H.ALL_DTYPES, ids=H.NAMES)
 def test_allreduce_sum_all_sizes(teams, n, dtype):
     comms = teams(n)
-    for variant in (1, 2, 4):
+    for variant in (1, 2, 4, 5):
         for c in comms:
             c.set_tuning(variant=variant)
         for count in SIZES:
@@ -79,7 +79,7 @@ def test_allreduce_sum_all_sizes(teams, n, dtype):
 @pytest.mark.parametrize("dtype", H.FLOAT_DTYPES, ids=[H.NAMES[d] for d in H.FLOAT_DTYPES])
 def test_allreduce_mean_inplace(teams, n, dtype):
     comms = teams(n)
-    for variant in (1, 2, 4):
+    for variant in (1, 2, 4, 5):
         for c in comms:
             c.set_tuning(variant=variant)
         for count in (5, 4099, 1 << 18):
@@ -138,7 +138,7 @@ def test_back_to_back_collectives_reuse_staging(teams):
     comms = teams(4)
     n = 4
     dev = "cuda:0"
-    for variant in (1, 2, 4):
+    for variant in (1, 2, 4, 5):
         for c in comms:
             c.set_tuning(variant=variant)
         steps = 24
@@ -164,7 +164,7 @@ def test_allreduce_bucket_of_tensors(teams, n):
     dev = "cuda:0"
     counts = [64, 1, 0, 4099, 7, 1 << 16, 33, 2048]
     for dtype, redop in ((oracle.F32, "MEAN"), (oracle.F16, "MEAN"), (oracle.I32, "SUM")):
-        for variant in (1, 2, 4):
+        for variant in (1, 2, 4, 5):
             for c in comms:
                 c.set_tuning(variant=variant)
             arrays = [[H.make_input(r, k, dtype, seed=7 + 13 * i) for i, k in enumerate(counts)] for r in range(n)]
@@ -189,7 +189,7 @@ def test_allreduce_unaligned_views(teams):
         full = [H.to_torch(a, dtype, dev) for a in arrays]
         views = [t[1:4998] for t in full]
         outs = [torch.zeros(5001, dtype=t.dtype, device=dev)[3:5000] for t in full]
-        for variant in (1, 2, 4):
+        for variant in (1, 2, 4, 5):
             for c in comms:
                 c.set_tuning(variant=variant)
             for r in range(2):

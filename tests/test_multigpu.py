@@ -46,7 +46,7 @@ def sync_all(n):
 
 
 @needs_two
-@pytest.mark.parametrize("variant", [4, 1, 2])
+@pytest.mark.parametrize("variant", [4, 5, 1, 2])
 def test_allreduce_across_gpus(comms, variant):
     n = len(comms)
     for c in comms:
