@@ -141,6 +141,10 @@ class Communicator(object):
     def status(self):
         return _C.lib().dgn_comm_status(self._h)
 
+    def has_nvls(self):
+        """True if the NVSwitch multicast variant was set up for this communicator."""
+        return bool(_C.lib().dgn_comm_has_nvls(self._h))
+
     def set_wait_limit_ms(self, ms):
         _C.check(_C.lib().dgn_comm_set_wait_limit_ms(self._h, int(ms)))
 

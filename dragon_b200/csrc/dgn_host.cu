@@ -20,12 +20,15 @@
 #include <unistd.h>
 
 #include <atomic>
+#include <map>
+#include <mutex>
 #include <deque>
 #include <string>
 #include <vector>
 
 #include "../../include/dgn.h"
 #include "dgn_kernels.cuh"
+#include "dgn_nvls.h"
 
 namespace dgn {
 // Defined in the per-dtype instantiation units.
@@ -96,6 +99,8 @@ struct Handle {  // what one rank tells the others; padded to DGN_HANDLE_BYTES
   uint64_t base_ptr;
   uint64_t host_id;
   cudaIpcMemHandle_t ipc;
+  int32_t nvls_capable;
+  char nvls_sock[64];  // rank 0: name of the multicast rendezvous socket
 };
 static_assert(sizeof(Handle) <= DGN_HANDLE_BYTES, "handle too large");
 
@@ -200,6 +205,13 @@ struct dgn_comm {
   uint64_t table_clock = 0;
   Plan last_plan;
   std::string rdv_ok_file;
+  // NVSwitch multicast staging (optional)
+  NvlsBuffer* nvls = nullptr;
+  bool nvls_capable = false;
+  char nvls_sock[64] = {};
+  int nvls_max_blocks = 0;
+  long long nvls_slot_bytes = 0, nvls_min_bytes = 0;
+  size_t nvls_bytes = 0;
 };
 
 namespace {
@@ -222,7 +234,7 @@ const void* reduce_fn(int dtype, int kind, bool table);
 int preload_kernels() {
   cudaFuncAttributes attr;
   for (int dtype = 0; dtype < 8; ++dtype) {
-    for (int kind = 0; kind <= 5; ++kind) {
+    for (int kind = 0; kind <= 6; ++kind) {
       for (int table = 0; table < 2; ++table) {
         const void* fn = reduce_fn(dtype, kind, table != 0);
         if (fn) DGN_CUDA(cudaFuncGetAttributes(&attr, fn));
@@ -236,6 +248,13 @@ int preload_kernels() {
     for (int table = 0; table < 2; ++table)
       DGN_CUDA(cudaFuncGetAttributes(&attr, local_copy_kernel_fn(es, table != 0)));
   return DGN_OK;
+}
+
+thread_local bool g_skip_nvls = false;  // set while emulated ranks are created
+std::mutex g_registry_mutex;
+std::map<uint64_t, dgn_comm*>& registry() {  // workspace base -> communicator, this process
+  static std::map<uint64_t, dgn_comm*> r;
+  return r;
 }
 
 int alloc_workspace(dgn_comm* c) {
@@ -272,6 +291,10 @@ void fill_peer_table(const dgn_comm* c, PeerTable* t) {
   t->ll_max_blocks = c->geo.ll_max_blocks;
   t->slot_bytes = c->geo.slot_bytes;
   t->ll_slot_bytes = c->geo.ll_slot_bytes;
+  t->nvls_uc = t->nvls_mc = nullptr;
+  if (c->nvls) nvls_pointers(c->nvls, &t->nvls_uc, &t->nvls_mc);
+  t->nvls_slot_bytes = c->nvls_slot_bytes;
+  t->nvls_max_blocks = c->nvls_max_blocks;
 }
 
 const void* reduce_fn(int dtype, int kind, bool table) {
@@ -301,8 +324,9 @@ long long default_ll_max(int n) {
 
 long long default_ll2_max(int n) {
   // Two ranks gain nothing from sharding (one-shot moves the same bytes).
+  // Measured at n = 8 (replayed graphs): best from 256 KiB to 2 MiB.
   if (n <= 2) return 0;
-  return 4ll << 20;
+  return 2ll << 20;
 }
 
 long long default_oneshot_max(int n) {
@@ -330,6 +354,32 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
   long long cv_cap = slot_vecs;
   if (c->tune_chunk >= 16 && c->tune_chunk / 16 < cv_cap) cv_cap = c->tune_chunk / 16;
 
+  if (d.kind == kOpAllReduce && c->nvls && !c->team &&
+      (d.dtype == DGN_F32 || d.dtype == DGN_F16 || d.dtype == DGN_BF16) &&
+      (d.redop == DGN_SUM || d.redop == DGN_MEAN)) {
+    // NVSwitch multicast: in-switch reduction, about half the link traffic.
+    const long long bytes = d.nvec * 16;
+    bool nvls = bytes >= c->nvls_min_bytes && c->tune_variant == DGN_VARIANT_AUTO;
+    if (c->tune_variant == DGN_VARIANT_NVLS) nvls = true;
+    if (nvls) {
+      const long long vs = ceil_div(d.nvec, n);
+      long long cap_v = c->nvls_slot_bytes / 16;
+      if (c->tune_chunk >= 16 && c->tune_chunk / 16 < cap_v) cap_v = c->tune_chunk / 16;
+      int nb = c->nvls_max_blocks < c->num_sms ? c->nvls_max_blocks : c->num_sms;
+      if (c->tune_blocks > 0 && c->tune_blocks < c->nvls_max_blocks) nb = c->tune_blocks;
+      long long b = ceil_div(vs, 512);
+      if (b > nb) b = nb;
+      if (b < 1) b = 1;
+      long long cv = ceil_div(vs, b);
+      if (cv > cap_v) cv = cap_v;
+      p.variant = DGN_VARIANT_NVLS;
+      p.blocks = (int)b;
+      p.cv = (int)cv;
+      p.rounds = (int)ceil_div(vs, b * cv);
+      if (p.threads < 96) p.threads = 96;
+      return p;
+    }
+  }
   if (d.kind == kOpAllReduce) {
     const long long bytes = d.nvec * 16;
     // Low-latency one-shot: flag-in-data lines, no barrier at all.
@@ -430,7 +480,7 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
   const bool table = d.ntensors > 1;
   switch (d.kind) {
     case kOpAllReduce:
-      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_LL2 ? 5 : p.variant == DGN_VARIANT_LL ? 3 : (p.variant == DGN_VARIANT_ONESHOT ? 0 : (p.threads >= 96 && p.rounds >= 3 && !c->fused_twoshot ? 4 : 1)), table);
+      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_NVLS ? 6 : p.variant == DGN_VARIANT_LL2 ? 5 : p.variant == DGN_VARIANT_LL ? 3 : (p.variant == DGN_VARIANT_ONESHOT ? 0 : (p.threads >= 96 && p.rounds >= 3 && !c->fused_twoshot ? 4 : 1)), table);
       k.smem = table ? table_smem_bytes(d.ntensors) : 0;
       break;
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
@@ -634,6 +684,11 @@ void free_comm(dgn_comm* c) {
   }
   for (int j = 0; j < c->nranks; ++j)
     if (j != c->rank && c->peer_ipc[j] && c->peer_base[j]) cudaIpcCloseMemHandle(c->peer_base[j]);
+  if (c->nvls) nvls_destroy(c->nvls);
+  {
+    std::lock_guard<std::mutex> lock(g_registry_mutex);
+    registry().erase((uint64_t)(uintptr_t)c->base);
+  }
   if (c->base) cudaFree(c->base);
   if (c->status_host) cudaFreeHost(c->status_host);
   if (!c->rdv_ok_file.empty()) unlink(c->rdv_ok_file.c_str());
@@ -671,6 +726,66 @@ namespace dgn {
 // dgn_last_error_string and hand back `code`.
 int report_error(int code, const char* message) { return fail(code, "%s", message); }
 }  // namespace dgn
+
+// Sets up the NVSwitch multicast staging if every rank can take part: all
+// ranks in this process (the last one to connect does the work for all), or
+// every rank in a process of its own (rank 0 coordinates over a socket).
+// Every rank takes the same decisions from the same handle table, and the
+// socket protocol makes all ranks succeed or fail together, so the variant is
+// either available on all ranks or on none.  Failure is not an error: the
+// communicator simply has no multicast variant.
+namespace {
+void drop_nvls(dgn_comm* c) {
+  if (c->nvls) nvls_destroy(c->nvls);
+  c->nvls = nullptr;
+}
+
+void setup_nvls(dgn_comm* c, const void* all_handles) {
+  std::vector<Handle> hs(c->nranks);
+  bool all_capable = true, same_pid = true, distinct_pid = true;
+  for (int j = 0; j < c->nranks; ++j) {
+    memcpy(&hs[j], static_cast<const char*>(all_handles) + (size_t)j * DGN_HANDLE_BYTES, sizeof(Handle));
+    all_capable = all_capable && hs[j].nvls_capable != 0;
+    same_pid = same_pid && hs[j].pid == hs[0].pid;
+    for (int q = 0; q < j; ++q) distinct_pid = distinct_pid && hs[q].pid != hs[j].pid;
+  }
+  if (!all_capable || (!same_pid && !distinct_pid)) {
+    drop_nvls(c);
+    return;
+  }
+  std::string why;
+  if (distinct_pid) {
+    DeviceGuard g(c->device);
+    int rc;
+    if (c->rank == 0) {
+      rc = c->nvls ? nvls_root_finish(c->nvls, 20000, &why) : 1;
+      if (rc != 0) drop_nvls(c);
+    } else {
+      rc = nvls_peer_join(c->device, c->nranks, c->nvls_bytes, hs[0].nvls_sock, 20000, &c->nvls, &why);
+      if (rc != 0) c->nvls = nullptr;
+    }
+    return;
+  }
+  // One process: wait until every member has connected, then set all up at once.
+  std::lock_guard<std::mutex> lock(g_registry_mutex);
+  std::vector<dgn_comm*> members(c->nranks, nullptr);
+  for (int j = 0; j < c->nranks; ++j) {
+    auto it = registry().find(hs[j].base_ptr);
+    if (it == registry().end()) return;
+    members[j] = it->second;
+    if (members[j] != c && !members[j]->connected) return;  // not the last one yet
+  }
+  drop_nvls(members[0]);  // the socket-mode preparation of rank 0 is not needed here
+  std::vector<int> devices(c->nranks);
+  for (int j = 0; j < c->nranks; ++j) devices[j] = members[j]->device;
+  std::vector<NvlsBuffer*> bufs(c->nranks, nullptr);
+  if (nvls_setup_inprocess(c->nranks, devices.data(), c->nvls_bytes, bufs.data(), &why) != 0) return;
+  for (int j = 0; j < c->nranks; ++j) {
+    members[j]->nvls = bufs[j];
+    if (members[j] != c) fill_peer_table(members[j], &members[j]->table);
+  }
+}
+}  // namespace
 
 // ---------------------------------------------------------------------------
 // C-ABI
@@ -720,6 +835,28 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
     free_comm(c);
     return rc;
   }
+  {
+    std::lock_guard<std::mutex> lock(g_registry_mutex);
+    registry()[(uint64_t)(uintptr_t)c->base] = c;
+  }
+  if (nranks > 1 && !g_skip_nvls && env_ll("DGN_NVLS", 1) != 0) {
+    DeviceGuard g(device);
+    c->nvls_max_blocks = c->geo.max_blocks;
+    c->nvls_slot_bytes = env_ll("DGN_NVLS_SLOT_BYTES", 32 * 1024);
+    if (c->nvls_slot_bytes < 4096) c->nvls_slot_bytes = 4096;
+    c->nvls_slot_bytes = (c->nvls_slot_bytes + 4095) & ~4095ll;
+    c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", 8ll << 20);
+    c->nvls_bytes = 2 * (size_t)c->nvls_max_blocks * 2 * 2 * (size_t)nranks * (size_t)c->nvls_slot_bytes;
+    c->nvls_capable = nvls_device_supported(device);
+    if (c->nvls_capable && rank == 0) {
+      // Rank 0 owns the multicast object and the rendezvous socket.
+      std::string why;
+      if (nvls_root_prepare(device, nranks, c->nvls_bytes, &c->nvls, c->nvls_sock, &why) != 0) {
+        c->nvls = nullptr;
+        c->nvls_capable = false;
+      }
+    }
+  }
   if (nranks == 1) {
     c->peer_base[0] = c->base;
     fill_peer_table(c, &c->table);
@@ -746,6 +883,8 @@ int dgn_comm_get_handle(dgn_comm_t c, void* handle) {
   h.base_ptr = (uint64_t)(uintptr_t)c->base;
   h.host_id = host_identity();
   DGN_CUDA(cudaIpcGetMemHandle(&h.ipc, c->base));
+  h.nvls_capable = c->nvls_capable ? 1 : 0;
+  memcpy(h.nvls_sock, c->nvls_sock, sizeof(h.nvls_sock));
   memset(handle, 0, DGN_HANDLE_BYTES);
   memcpy(handle, &h, sizeof(h));
   return DGN_OK;
@@ -797,6 +936,7 @@ int dgn_comm_connect(dgn_comm_t c, const void* all_handles) {
       c->peer_ipc[j] = true;
     }
   }
+  setup_nvls(c, all_handles);
   fill_peer_table(c, &c->table);
   c->connected = true;
   return DGN_OK;
@@ -874,7 +1014,9 @@ int dgn_comm_create_emulated(int nranks, int device, dgn_comm_t* comms) {
   t->device = device;
   for (int r = 0; r < nranks; ++r) {
     dgn_comm* c = nullptr;
+    g_skip_nvls = true;
     int rc = dgn_comm_init_local(r, nranks, device, &c);
+    g_skip_nvls = false;
     if (rc != DGN_OK) {
       for (dgn_comm* m : t->members) free_comm(m);
       delete t;
@@ -923,7 +1065,8 @@ int dgn_comm_set_tuning(dgn_comm_t c, int variant, int blocks, int threads, int6
   if (!c) return fail(DGN_ERR_ARG, "null communicator");
   if (variant < 0 || variant > DGN_VARIANT_LL2 || blocks < 0 || threads < 0 || chunk_bytes < 0)
     return fail(DGN_ERR_ARG, "bad tuning value");
-  if (variant == DGN_VARIANT_NVLS) return fail(DGN_ERR_UNSUPPORTED, "the NVLS variant is not set up on this communicator");
+  if (variant == DGN_VARIANT_NVLS && !c->nvls)
+    return fail(DGN_ERR_UNSUPPORTED, "the NVLS variant is not set up on this communicator");
   c->tune_variant = variant;
   c->tune_blocks = blocks;
   c->tune_threads = threads;
@@ -931,7 +1074,7 @@ int dgn_comm_set_tuning(dgn_comm_t c, int variant, int blocks, int threads, int6
   return DGN_OK;
 }
 
-int dgn_comm_has_nvls(dgn_comm_t) { return 0; }
+int dgn_comm_has_nvls(dgn_comm_t c) { return (c && c->nvls) ? 1 : 0; }
 
 int dgn_allreduce(dgn_comm_t c, const void* const* in_ptrs, void* const* out_ptrs,
                   const int64_t* counts, int ntensors, int dtype, int redop, void* stream) {

@@ -86,6 +86,13 @@ struct PeerTable {
   int rank, nranks, max_blocks, ll_max_blocks;
   long long slot_bytes;    // bytes per staging slot
   long long ll_slot_bytes; // bytes per low-latency slot (holds half as much data)
+  // NVSwitch multicast staging (null when the variant is not set up): the same
+  // physical buffers seen through this rank's own mapping and through the
+  // multicast mapping, which addresses all ranks' buffers at once.
+  char* nvls_uc;
+  char* nvls_mc;
+  long long nvls_slot_bytes;
+  int nvls_max_blocks, reserved2;
 };
 
 // One tensor of a bucket; `vbegin` is its first 16-byte vector in the flat
@@ -1074,6 +1081,191 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_twoshot_ws_kernel(const __g
     }
   }
   // All three roles meet; a role that gave up takes the whole block out.
+  if (__syncthreads_or(!alive)) return;
+  end_collective(pt, b, turn, base + (u64)rounds + 1);
+}
+
+// ---------------------------------------------------------------------------
+// ALLREDUCE through NVSwitch multicast ("NVLS"): the switch adds the ranks'
+// copies on a multimem.ld_reduce and replicates a multimem.st to all ranks,
+// so a rank sends and receives about S(1 + 1/n) bytes instead of 2S(n-1)/n.
+// Each rank owns a staging buffer that is bound to one multicast object;
+// for parity p, block b, half h it holds an "in" area and an "out" area of
+// n slots (slot s = the slice rank s owns).  Three warp roles per block:
+//   stage-in : copy my input slices into my "in" area          signal A
+//   reducer  : wait A from all; for my own slice: ld_reduce over all ranks'
+//              "in" slots, scale, multimem.st into everyone's "out" slot
+//                                                              signal B
+//   stage-out: wait B from all; copy my "out" area to my output signal C
+// Flags and epochs are those of the warp-specialised two-shot kernel.  The
+// dependencies between this rank's own roles (my reducer reads my "in" area
+// through the switch, my stage-out reads my "out" area) go through three
+// counters in shared memory.  No TMA and no cluster multicast is involved: multimem
+// instructions address an NVSwitch multicast mapping.
+// The order in which the switch adds is not specified: results satisfy the
+// tolerance contract, are identical on all ranks, but need not match the
+// ascending-rank order of the other kernels bit for bit.
+
+template <typename T> struct Multimem;
+template <> struct Multimem<float> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct Multimem<__half> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};"
+                 :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct Multimem<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                 :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+
+// Byte offset of slot `slot` of area `area` (0 in, 1 out) of (parity, block, half).
+__device__ __forceinline__ long long nvls_offset(const PeerTable& pt, int parity, int b, int half, int area, int slot) {
+  const long long idx = ((((long long)parity * pt.nvls_max_blocks + b) * 2 + half) * 2 + area) * pt.nranks + slot;
+  return idx * pt.nvls_slot_bytes;
+}
+
+// Spins on a shared-memory counter written by another role of this block.
+__device__ __forceinline__ bool wait_local(const Role& g, volatile int* counter, int target, u64 wait_ns,
+                                           volatile int* abort_flag) {
+  bool ok = true;
+  if (g.t == 0 && *counter < target) {
+    const u64 t0 = global_timer_ns();
+    unsigned spins = 0;
+    while (*counter < target) {
+      if ((++spins & 63u) == 0u && (*abort_flag || global_timer_ns() - t0 > wait_ns)) { ok = false; break; }
+    }
+  }
+  return role_all(g, ok && *abort_flag == 0);
+}
+
+template <typename T, bool TABLE>
+__global__ void __launch_bounds__(kMaxThreads, 1) ar_nvls_kernel(const __grid_constant__ OpParams P) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ int s_abort, s_staged, s_reduced, s_emptied;
+  constexpr int ES = (int)sizeof(T);
+  const PeerTable& pt = P.peers[blockIdx.y];
+  const RankArgs& ra = P.ra[blockIdx.y];
+  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
+  const Message<ES, TABLE> msg = make_message<ES, TABLE>(P, ra, smem);
+  if (threadIdx.x == 0) { s_abort = 0; s_staged = 0; s_reduced = 0; s_emptied = 0; }
+  Turn turn;
+  if (!begin_collective(pt, b, P, &turn)) return;
+
+  const long long vs = (P.nvec + n - 1) / n;
+  auto shard_len = [&](int s) -> long long { return clampll(P.nvec - (long long)s * vs, 0, vs); };
+  const int rounds = P.rounds;
+  const long long cv = P.cv;
+  const long long stride = (long long)gridDim.x * cv;
+  const u64 base = turn.base;
+
+  const int nwarps = blockDim.x >> 5;
+  int w_in = (nwarps * 3) >> 3, w_red = nwarps >> 2;
+  if (w_in < 1) w_in = 1;
+  if (w_red < 1) w_red = 1;
+  const int warp = threadIdx.x >> 5;
+  Role g;
+  int role;
+  if (warp < w_in) { role = 0; g.id = 1; g.t = threadIdx.x; g.n = w_in * 32; }
+  else if (warp < w_in + w_red) { role = 1; g.id = 2; g.t = threadIdx.x - w_in * 32; g.n = w_red * 32; }
+  else { role = 2; g.id = 3; g.t = threadIdx.x - (w_in + w_red) * 32; g.n = (nwarps - w_in - w_red) * 32; }
+  volatile int* abort_flag = &s_abort;
+  bool alive = true;
+
+  if (role == 0) {  // stage-in
+    for (int i = 0; i < rounds; ++i) {
+      if (i >= kDepth) {
+        if (!role_wait(pt, g, b, kChanB, base + (u64)(i - kDepth) + 1, P.wait_ns, abort_flag) ||
+            !wait_local(g, &s_reduced, i - kDepth + 1, P.wait_ns, abort_flag)) { alive = false; break; }
+      }
+      const long long off = (long long)i * stride + (long long)b * cv;
+      for (int s = 0; s < n; ++s) {
+        const long long len = clampll(shard_len(s) - off, 0, cv);
+        char* dst = pt.nvls_uc + nvls_offset(pt, turn.parity, b, i % kDepth, 0, s);
+        const long long ibase = (long long)s * vs + off;
+        role_copy(g, len, [&](long long v) { return msg.load(ibase + v); },
+                  [&](long long v, uint4 x) { stv(dst + v * 16, x); });
+      }
+      role_signal(pt, g, b, kChanA, base + (u64)i + 1);
+      // The switch also reads this rank's own copy: tell my reducer it is complete.
+      if (g.t == 0) { __threadfence_system(); s_staged = i + 1; }
+    }
+  } else if (role == 1) {  // reducer
+    const long long mylen_total = shard_len(r);
+    const bool mean = P.redop == kMean;
+    for (int j = 0; j < rounds; ++j) {
+      if (!role_wait(pt, g, b, kChanA, base + (u64)j + 1, P.wait_ns, abort_flag) ||
+          !wait_local(g, &s_staged, j + 1, P.wait_ns, abort_flag)) { alive = false; break; }
+      if (j >= kDepth) {
+        if (!role_wait(pt, g, b, kChanC, base + (u64)(j - kDepth) + 1, P.wait_ns, abort_flag) ||
+            !wait_local(g, &s_emptied, j - kDepth + 1, P.wait_ns, abort_flag)) { alive = false; break; }
+      }
+      const long long off = (long long)j * stride + (long long)b * cv;
+      const long long len = clampll(mylen_total - off, 0, cv);
+      const char* src = pt.nvls_mc + nvls_offset(pt, turn.parity, b, j % kDepth, 0, r);
+      char* dst = pt.nvls_mc + nvls_offset(pt, turn.parity, b, j % kDepth, 1, r);
+      for (long long v0 = g.t; v0 < len; v0 += (long long)kUnroll * g.n) {
+        uint4 x[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const long long v = v0 + (long long)u * g.n;
+          if (v < len) x[u] = Multimem<T>::ld_reduce(src + v * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const long long v = v0 + (long long)u * g.n;
+          if (v < len) {
+            uint4 y = x[u];
+            if (mean) y = reduce_vectors<T, kSum, 1>(&y, 1, true, P.scale);
+            Multimem<T>::st(dst + v * 16, y);
+          }
+        }
+      }
+      role_signal(pt, g, b, kChanB, base + (u64)j + 1);  // barrier inside: the whole role is done
+      // My own stage-out reads what my multimem stores left in my memory.
+      if (g.t == 0) { __threadfence_system(); s_reduced = j + 1; }
+    }
+  } else {  // stage-out
+    for (int j = 0; j < rounds; ++j) {
+      if (!role_wait(pt, g, b, kChanB, base + (u64)j + 1, P.wait_ns, abort_flag) ||
+          !wait_local(g, &s_reduced, j + 1, P.wait_ns, abort_flag)) { alive = false; break; }
+      const long long off = (long long)j * stride + (long long)b * cv;
+      for (int s = 0; s < n; ++s) {
+        const long long len = clampll(shard_len(s) - off, 0, cv);
+        const char* src = pt.nvls_uc + nvls_offset(pt, turn.parity, b, j % kDepth, 1, s);
+        const long long obase = (long long)s * vs + off;
+        role_copy(g, len, [&](long long v) { return ldv(src + v * 16); },
+                  [&](long long v, uint4 x) { msg.store(obase + v, x); });
+      }
+      role_signal(pt, g, b, kChanC, base + (u64)j + 1);
+      if (g.t == 0) { __threadfence_block(); s_emptied = j + 1; }
+    }
+  }
   if (__syncthreads_or(!alive)) return;
   end_collective(pt, b, turn, base + (u64)rounds + 1);
 }

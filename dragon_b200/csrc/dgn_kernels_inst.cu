@@ -32,7 +32,8 @@ typedef double InstT;
 
 #if DGN_INST < 8
 // kind: 0 one-shot, 1 two-shot (lock-step), 2 reduce-scatter, 3 low-latency one-shot,
-//       4 two-shot (warp-specialised), 5 low-latency two-shot
+//       4 two-shot (warp-specialised), 5 low-latency two-shot,
+//       6 NVSwitch multicast (float, half and bfloat16 only)
 const void* DGN_CAT(reduce_kernel_fn_, DGN_INST)(int kind, bool table) {
   switch (kind) {
     case 0:
@@ -46,6 +47,11 @@ const void* DGN_CAT(reduce_kernel_fn_, DGN_INST)(int kind, bool table) {
     case 4:
       return table ? (const void*)ar_twoshot_ws_kernel<InstT, true>
                    : (const void*)ar_twoshot_ws_kernel<InstT, false>;
+#if DGN_INST >= 4 && DGN_INST <= 6
+    case 6:
+      return table ? (const void*)ar_nvls_kernel<InstT, true>
+                   : (const void*)ar_nvls_kernel<InstT, false>;
+#endif
     case 5:
       return table ? (const void*)ar_twoshot_ll_kernel<InstT, true>
                    : (const void*)ar_twoshot_ll_kernel<InstT, false>;

@@ -30,6 +30,17 @@ def main():
             torch.cuda.synchronize()
             assert comm.status() == 0
             H.assert_bits_equal(H.to_numpy(x, dtype), oracle.allreduce(arrays, dtype, redop))
+    if comm.has_nvls():  # the multicast handle travelled over the unix socket
+        comm.set_tuning(variant=3)
+        for dtype, count, redop in ((oracle.F16, 300001, "MEAN"), (oracle.F32, 1 << 22, "SUM")):
+            arrays = [H.make_input(r, count, dtype) for r in range(world)]
+            x = H.to_torch(arrays[rank], dtype, dev)
+            comm.all_reduce([x], None, redop)
+            torch.cuda.synchronize()
+            assert comm.status() == 0 and comm.last_launch()["variant"] == 3
+            ref = oracle.fp64_sum(arrays, dtype, mean=(redop == "MEAN"))
+            assert oracle.max_rel_err(H.to_numpy(x, dtype), ref, dtype) <= oracle.TOLERANCE[dtype]
+        print("NVLS_OK", rank)
     comm.set_tuning()
     idx = [np.arange(1000, dtype=np.int64) * (r + 1) for r in range(world)]
     out = torch.empty(world * 1000, dtype=torch.int64, device=dev)

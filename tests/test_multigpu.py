@@ -71,6 +71,39 @@ def test_allreduce_across_gpus(comms, variant):
 
 
 @needs_two
+def test_nvls_allreduce_across_gpus(comms):
+    """The NVSwitch multicast variant, where the box exposes it: the switch
+    chooses the order of the additions, so the check is the tolerance contract
+    against an fp64 host sum plus identical bits on every rank."""
+    n = len(comms)
+    if not comms[0].has_nvls():
+        pytest.skip("NVSwitch multicast is not available on this box")
+    assert all(c.has_nvls() for c in comms)
+    for c in comms:
+        c.set_tuning(variant=3)
+    try:
+        for dtype, redop, count in ((oracle.F32, "MEAN", 100003), (oracle.F16, "MEAN", (1 << 22) + 5),
+                                    (oracle.BF16, "SUM", 70001), (oracle.F32, "SUM", 1 << 24), (oracle.F32, "SUM", 7)):
+            arrays = [H.make_input(r, count, dtype) for r in range(n)]
+            for rep in range(2):
+                xs = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
+                for r in range(n):
+                    with torch.cuda.device(r):
+                        comms[r].all_reduce([xs[r]], None, redop)
+                sync_all(n)
+                assert comms[0].last_launch()["variant"] == 3
+                ref = oracle.fp64_sum(arrays, dtype, mean=(redop == "MEAN"))
+                got0 = H.to_numpy(xs[0], dtype)
+                assert oracle.max_rel_err(got0, ref, dtype) <= oracle.TOLERANCE[dtype]
+                for r in range(n):
+                    assert comms[r].status() == 0
+                    H.assert_bits_equal(H.to_numpy(xs[r], dtype), got0, "rank {} differs from rank 0".format(r))
+    finally:
+        for c in comms:
+            c.set_tuning()
+
+
+@needs_two
 def test_back_to_back_mixed_collectives_across_gpus(comms):
     n = len(comms)
     steps = 12
