@@ -380,6 +380,7 @@ def bench_multi(args):
     busbw = S / (ms * 1e-3) / 1e9 * factor
 
     sweep = run_sweep(args, comm, nccl, rank, world, dev, stream, barrier, max_over_ranks) if args.sweep != "off" else []
+    extras = run_operator_configs(comm, nccl, rank, world, dev, barrier, max_over_ranks) if args.sweep != "off" else {}
 
     line = None
     if rank == 0:
@@ -411,6 +412,8 @@ def bench_multi(args):
             "gpu_launches": int(launches),
             "clocks": sampler.summary(),
             "sweep": sweep,
+            "operator_configs": extras,
+            "nvls": comm.has_nvls(),
         }
     barrier()
     torch.cuda.synchronize()
@@ -419,6 +422,86 @@ def bench_multi(args):
     comm.destroy()
     dist.destroy_process_group()
     return line
+
+
+def run_operator_configs(comm, nccl, rank, world, dev, barrier, max_over_ranks):
+    """The gradient-bucket and gather/broadcast configurations, operator to
+    operator: ours is one fused launch per bucket; the NCCL backend restated as
+    the reference runs it (concat copies, ncclAllReduce, split copies, one
+    scale launch per tensor for MEAN)."""
+    import torch
+    from dragon_b200 import workloads
+    out = {}
+    stream_of = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+
+    def timed(fn, iters=10, warm=3):
+        _, total = time_steps(fn, iters, warm, barrier)
+        return max_over_ranks(total) / iters
+
+    def gen(shapes, std, dtype):
+        g = torch.Generator(device=dev).manual_seed(1000 + rank)
+        return [(torch.randn(workloads.numel(s), generator=g, device=dev) * std).to(dtype) for s in shapes]
+
+    # ResNet-50: 161 fp32 tensors, one bucket, MEAN.
+    shapes = workloads.resnet50_shapes()
+    grads = gen(shapes, 1e-3, torch.float32)
+    nbytes = sum(g.numel() * 4 for g in grads)
+    op = comm.prepare_all_reduce(grads, grads, "MEAN")
+    row = {"tensors": len(grads), "bytes": nbytes, "ours_us": timed(op) * 1e3}
+    if nccl is not None:
+        scratch = torch.empty(nbytes // 4, device=dev)
+        row["nccl_us"] = timed(lambda: nccl.operator_all_reduce(grads, "MEAN", stream_of(), bucket=scratch)) * 1e3
+        row["nccl_unbucketed_us"] = timed(lambda: nccl.operator_all_reduce(grads, "MEAN", stream_of())) * 1e3
+        row["speedup"] = row["nccl_us"] / row["ours_us"]
+        del scratch
+    row["ours_busbw"] = nbytes / (row["ours_us"] * 1e-6) / 1e9 * 2.0 * (world - 1) / world
+    out["resnet50_fp32_one_bucket_mean"] = row
+    del grads, op
+
+    # BERT-base: 199 fp16 tensors in 25 MiB buckets, MEAN with fp32 accumulation.
+    shapes = workloads.bert_base_shapes()
+    grads = gen(shapes, 1e-2, torch.float16)
+    buckets = workloads.greedy_buckets(shapes, 2, 25 * MiB)
+    ops = [comm.prepare_all_reduce([grads[i] for i in b], [grads[i] for i in b], "MEAN") for b in buckets]
+    nbytes = sum(g.numel() * 2 for g in grads)
+
+    def ours_all():
+        for o in ops:
+            o()
+
+    row = {"tensors": len(grads), "buckets": len(buckets), "bytes": nbytes, "ours_us": timed(ours_all, 5, 2) * 1e3}
+    if nccl is not None:
+        scratch = torch.empty(max(sum(grads[i].numel() for i in b) for b in buckets), dtype=torch.float16, device=dev)
+
+        def theirs_all():
+            for b in buckets:
+                nccl.operator_all_reduce([grads[i] for i in b], "MEAN", stream_of(), bucket=scratch if len(b) > 1 else None)
+
+        row["nccl_us"] = timed(theirs_all, 5, 2) * 1e3
+        row["speedup"] = row["nccl_us"] / row["ours_us"]
+        del scratch
+    row["ours_busbw"] = nbytes / (row["ours_us"] * 1e-6) / 1e9 * 2.0 * (world - 1) / world
+    out["bert_base_fp16_25MiB_buckets_mean"] = row
+    del grads, ops
+
+    # ALLGATHER / BROADCAST(root 0): int64 [65536] and bf16 [8192, 4096].
+    for label, make in (("int64_65536", lambda: torch.randint(0, 1 << 40, (65536,), device=dev, dtype=torch.int64)),
+                        ("bf16_8192x4096", lambda: torch.randn(8192, 4096, device=dev).to(torch.bfloat16))):
+        x = make()
+        y = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=dev)
+        sbytes = x.numel() * x.element_size()
+        iters = 50 if sbytes < MiB else 10
+        t_ag = timed(lambda: comm.all_gather(x, y), iters)
+        t_bc = timed(lambda: comm.broadcast(x, 0), iters)
+        row = {"shard_bytes": sbytes, "allgather_us": t_ag * 1e3,
+               "allgather_busbw": world * sbytes / t_ag / 1e6 * (world - 1) / world,
+               "broadcast_us": t_bc * 1e3, "broadcast_busbw": sbytes / t_bc / 1e6}
+        if nccl is not None:
+            row["nccl_allgather_us"] = timed(lambda: nccl.all_gather(x, y, stream_of()), iters) * 1e3
+            row["nccl_broadcast_us"] = timed(lambda: nccl.broadcast(x, 0, stream_of()), iters) * 1e3
+        out[label] = row
+        del x, y
+    return out
 
 
 def time_graph(fn, ops_per_graph, replays, barrier):

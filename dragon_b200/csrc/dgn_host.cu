@@ -370,7 +370,11 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
       long long b = ceil_div(vs, 512);
       if (b > nb) b = nb;
       if (b < 1) b = 1;
-      long long cv = ceil_div(vs, b);
+      // About four rounds let the three roles overlap without paying the
+      // per-round flag exchange too often; chunks stay within 16 .. 64 KiB.
+      long long cv = ceil_div(vs, b * 4);
+      if (cv < 1024) cv = 1024;
+      if (cv > ceil_div(vs, b)) cv = ceil_div(vs, b);
       if (cv > cap_v) cv = cap_v;
       p.variant = DGN_VARIANT_NVLS;
       p.blocks = (int)b;
@@ -501,6 +505,8 @@ void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p)
   P->cv = p.cv;
   P->redop = d.redop;
   P->root = d.root;
+  P->warps_a = (int)env_ll("DGN_NVLS_WARPS_IN", 0);
+  P->warps_b = (int)env_ll("DGN_NVLS_WARPS_REDUCE", 0);
 }
 
 int launch(const void* fn, dim3 grid, int threads, size_t smem, cudaStream_t stream, OpParams* P,
@@ -842,10 +848,14 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
   if (nranks > 1 && !g_skip_nvls && env_ll("DGN_NVLS", 1) != 0) {
     DeviceGuard g(device);
     c->nvls_max_blocks = c->geo.max_blocks;
-    c->nvls_slot_bytes = env_ll("DGN_NVLS_SLOT_BYTES", 32 * 1024);
+    c->nvls_slot_bytes = env_ll("DGN_NVLS_SLOT_BYTES", 64 * 1024);
     if (c->nvls_slot_bytes < 4096) c->nvls_slot_bytes = 4096;
     c->nvls_slot_bytes = (c->nvls_slot_bytes + 4095) & ~4095ll;
-    c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", 8ll << 20);
+    // Measured at n = 8: ahead of the store-only two-shot kernel from 256 MiB
+    // (674 against 603 GB/s; 763 against 621 at 1 GiB), behind at 64 MiB.  With
+    // fewer ranks the switch saves too little traffic (1.5 S per direction at
+    // n = 2 against 1.0 S), so the variant is opt-in there.
+    c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", nranks >= 8 ? (128ll << 20) : (1ll << 62));
     c->nvls_bytes = 2 * (size_t)c->nvls_max_blocks * 2 * 2 * (size_t)nranks * (size_t)c->nvls_slot_bytes;
     c->nvls_capable = nvls_device_supported(device);
     if (c->nvls_capable && rank == 0) {
