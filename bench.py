@@ -112,11 +112,6 @@ class ClockSampler(object):
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def np_dtype_of(name):
-    import numpy as np
-    return {"f32": np.float32, "f16": np.float16}[name]
-
-
 def torch_dtype_of(name):
     import torch
     return {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[name]

@@ -42,6 +42,7 @@ const void* reduce_kernel_fn_6(int, bool);
 const void* reduce_kernel_fn_7(int, bool);
 const void* allgather_kernel_fn();
 const void* broadcast_kernel_fn();
+const void* broadcast_scatter_kernel_fn();
 const void* local_copy_kernel_fn(int es, bool table);
 }  // namespace dgn
 
@@ -199,6 +200,7 @@ struct dgn_comm {
   int tune_variant = 0, tune_blocks = 0, tune_threads = 0;
   long long tune_chunk = 0;
   long long oneshot_max_bytes = -1, ll_max_bytes = -1, ll2_max_bytes = -1;
+  long long bcast_scatter_min_bytes = 1ll << 20;
   bool fused_twoshot = false;  // DGN_TWOSHOT_FUSED=1: lock-step two-shot kernel instead of the warp-specialised one
   Team* team = nullptr;
   std::vector<TableEntry> tables;
@@ -243,6 +245,7 @@ int preload_kernels() {
   }
   DGN_CUDA(cudaFuncGetAttributes(&attr, allgather_kernel_fn()));
   DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_kernel_fn()));
+  DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_scatter_kernel_fn()));
   const int sizes[4] = {1, 2, 4, 8};
   for (int es : sizes)
     for (int table = 0; table < 2; ++table)
@@ -459,6 +462,17 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
   long long per = d.nvec;
   if (d.kind == kOpAllReduce) per = ceil_div(d.nvec, n);
   p.variant = DGN_VARIANT_TWOSHOT;
+  if (d.kind == kOpBroadcast) {
+    // Small messages: peers pull from the root (one flag exchange).  Large
+    // ones: scatter + all-gather, so the root sends about 2 S instead of
+    // (n - 1) S.  With two ranks both send S and pulling is one step shorter.
+    const long long thr = c->bcast_scatter_min_bytes;
+    bool scatter = n > 2 && d.nvec * 16 >= thr;
+    if (c->tune_variant == DGN_VARIANT_ONESHOT) scatter = false;
+    if (c->tune_variant == DGN_VARIANT_TWOSHOT && n > 2) scatter = true;
+    if (scatter) per = ceil_div(d.nvec, n);
+    else p.variant = DGN_VARIANT_ONESHOT;
+  }
   int bdef = bmax < c->num_sms ? bmax : c->num_sms;  // one block per SM
   if (c->tune_blocks > 0) bdef = bmax;
   long long b = ceil_div(per, 512);
@@ -489,7 +503,9 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
       break;
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
     case kOpAllGather: k.fn = allgather_kernel_fn(); break;
-    case kOpBroadcast: k.fn = broadcast_kernel_fn(); break;
+    case kOpBroadcast:
+      k.fn = p.variant == DGN_VARIANT_TWOSHOT ? broadcast_scatter_kernel_fn() : broadcast_kernel_fn();
+      break;
   }
   return k;
 }
@@ -835,6 +851,7 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
   c->ll_max_bytes = env_ll("DGN_LL_MAX_BYTES", -1);
   c->ll2_max_bytes = env_ll("DGN_LL2_MAX_BYTES", -1);
   c->fused_twoshot = env_ll("DGN_TWOSHOT_FUSED", 0) != 0;
+  c->bcast_scatter_min_bytes = env_ll("DGN_BCAST_SCATTER_MIN_BYTES", 1ll << 20);
   c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
   int rc = alloc_workspace(c);
   if (rc != DGN_OK) {

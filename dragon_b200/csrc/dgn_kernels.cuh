@@ -151,13 +151,13 @@ __device__ __forceinline__ void signal_peers(const PeerTable& pt, int b, int cha
     st_release_sys(pt.flags[t] + ((size_t)b * 3 + chan) * kMaxRanks + pt.rank, val);
 }
 
-// Waits until block `b` of the peers (all, or only `only`) has reached epoch
-// `target`.  Returns false, for the whole block, if the limit ran out.
+// Waits until block `b` of the peers (all, only `only`, or all but `except`)
+// has reached epoch `target`.  Returns false, for the whole block, if the limit ran out.
 __device__ __forceinline__ bool wait_peers(const PeerTable& pt, int b, int chan, u64 target, u64 wait_ns,
-                                           int only = -1) {
+                                           int only = -1, int except = -1) {
   bool ok = true;
   const int t = threadIdx.x;
-  if (t < pt.nranks && t != pt.rank && (only < 0 || t == only)) {
+  if (t < pt.nranks && t != pt.rank && (only < 0 || t == only) && t != except) {
     const u64* f = pt.flags[pt.rank] + ((size_t)b * 3 + chan) * kMaxRanks + t;
     if (ld_acquire_sys(f) < target) {
       const u64 t0 = global_timer_ns();
@@ -1361,6 +1361,90 @@ __global__ void __launch_bounds__(kMaxThreads, 1) broadcast_kernel(const __grid_
     }
   }
   end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
+}
+
+// ---------------------------------------------------------------------------
+// BROADCAST in place for large messages: scatter + all-gather, stores only.
+// Pulling from the root makes the root send (n-1) S bytes; here the message is
+// cut into n shards and, per round and block,
+//   root        : stores slice j into peer j's inbox and its own slice into
+//                 every peer's gather box                      signal A
+//   peer j      : after A from the root, copies its slice from the inbox to its
+//                 buffer and stores it into the gather box of every other
+//                 peer                                         signal B
+//   every peer  : after B from the other peers, copies the gather boxes to its
+//                 buffer                                       signal C
+// so the root sends about 2 S (n-1)/n bytes and every other rank (n-2)/n S.
+// Staging halves alternate per round; a half is refilled only after C of the
+// round that used it came from every rank.  Epochs of round i: A = base+3i+1,
+// B = base+3i+2, C = base+3i+3; done = base+3*rounds+1 (channel B).
+
+template <int kUnused>
+__global__ void __launch_bounds__(kMaxThreads, 1) broadcast_scatter_kernel(const __grid_constant__ OpParams P) {
+  const PeerTable& pt = P.peers[blockIdx.y];
+  const RankArgs& ra = P.ra[blockIdx.y];
+  const int r = pt.rank, n = pt.nranks, b = blockIdx.x, root = P.root;
+  Turn turn;
+  if (!begin_collective(pt, b, P, &turn)) return;
+  char* buf = static_cast<char*>(ra.out);
+  const bool al = is_al16(buf);
+  const long long cv = P.cv;
+  const long long vs = (P.nvec + n - 1) / n;
+  auto shard_len = [&](int s) -> long long { return clampll(P.nvec - (long long)s * vs, 0, vs); };
+
+  for (int i = 0; i < P.rounds; ++i) {
+    const long long off = ((long long)i * gridDim.x + b) * cv;
+    const int half = i & 1;
+    const u64 e_a = turn.base + 3 * (u64)i + 1, e_b = e_a + 1, e_c = e_a + 2;
+    if (i >= 2 && !wait_peers(pt, b, kChanC, turn.base + 3 * (u64)(i - 2) + 3, P.wait_ns)) return;
+    if (r == root) {
+      const long long own_len = clampll(shard_len(root) - off, 0, cv);
+      for (int k = 1; k < n; ++k) {
+        const int peer = (r + 1 + (k - 1 + b) % (n - 1)) % n;
+        const long long len = clampll(shard_len(peer) - off, 0, cv);
+        char* inbox = slot_ptr(pt, peer, turn.parity, b, half, root);
+        const long long base_v = (long long)peer * vs + off;
+        copy_vectors(len, [&](long long v) { return load_vec<1>(buf, base_v + v, P.count, al); },
+                     [&](long long v, uint4 x) { stv(inbox + v * 16, x); });
+        char* gbox = slot_ptr(pt, peer, turn.parity, b, half, n + root);
+        const long long own_v = (long long)root * vs + off;
+        copy_vectors(own_len, [&](long long v) { return load_vec<1>(buf, own_v + v, P.count, al); },
+                     [&](long long v, uint4 x) { stv(gbox + v * 16, x); });
+      }
+      signal_peers(pt, b, kChanA, e_a);
+      signal_peers(pt, b, kChanC, e_c);  // the root holds no staged data of its own
+    } else {
+      if (!wait_peers(pt, b, kChanA, e_a, P.wait_ns, root)) return;
+      {  // my slice: inbox -> my buffer and every other peer's gather box
+        const long long len = clampll(shard_len(r) - off, 0, cv);
+        const char* inbox = slot_ptr(pt, r, turn.parity, b, half, root);
+        const long long base_v = (long long)r * vs + off;
+        char* gdst[kMaxRanks];
+        int ng = 0;
+        for (int k = 1; k < n; ++k) {
+          const int peer = (r + k) % n;
+          if (peer != root) gdst[ng++] = slot_ptr(pt, peer, turn.parity, b, half, n + r);
+        }
+        copy_vectors(len, [&](long long v) { return ldv(inbox + v * 16); },
+                     [&](long long v, uint4 x) {
+                       store_vec<1>(buf, base_v + v, P.count, al, x);
+                       for (int q = 0; q < ng; ++q) stv(gdst[q] + v * 16, x);
+                     });
+      }
+      signal_peers(pt, b, kChanB, e_b);
+      if (!wait_peers(pt, b, kChanB, e_b, P.wait_ns, -1, root)) return;
+      for (int k = 1; k < n; ++k) {
+        const int src_rank = (r + 1 + (k - 1 + b) % (n - 1)) % n;
+        const long long len = clampll(shard_len(src_rank) - off, 0, cv);
+        const char* gbox = slot_ptr(pt, r, turn.parity, b, half, n + src_rank);
+        const long long base_v = (long long)src_rank * vs + off;
+        copy_vectors(len, [&](long long v) { return ldv(gbox + v * 16); },
+                     [&](long long v, uint4 x) { store_vec<1>(buf, base_v + v, P.count, al, x); });
+      }
+      signal_peers(pt, b, kChanC, e_c);
+    }
+  }
+  end_collective(pt, b, turn, turn.base + 3 * (u64)P.rounds + 1);
 }
 
 // ---------------------------------------------------------------------------

@@ -224,16 +224,31 @@ def test_allgather_bit_exact(teams, n):
 def test_broadcast_bit_exact(teams, n):
     comms = teams(n)
     dev = "cuda:0"
-    for root in (0, n - 1):
-        for dtype, count in ((oracle.I64, 65536), (oracle.BF16, 100003), (oracle.U8, 1)):
-            arrays = [H.make_input(r, count, dtype) for r in range(n)]
-            bufs = [H.to_torch(a, dtype, dev) for a in arrays]
-            for r in range(n):
-                comms[r].broadcast(bufs[r], root)
-            torch.cuda.synchronize()
-            want = oracle.broadcast(arrays, dtype, root)
-            for r in range(n):
-                H.assert_bits_equal(H.to_numpy(bufs[r], dtype), want[r], "broadcast root {} rank {}".format(root, r))
+    # variant 1: peers pull from the root; variant 2: scatter + all-gather
+    # (large messages); the third shape forces many rounds of the latter.
+    shapes = [dict(variant=1), dict(variant=2), dict(variant=2, blocks=3, threads=64, chunk_bytes=512)]
+    most_rounds = 0
+    try:
+        for shape in shapes:
+            for c in comms:
+                c.set_tuning(**shape)
+            for root in (0, n - 1):
+                for dtype, count in ((oracle.I64, 65536), (oracle.BF16, 100003), (oracle.U8, 1), (oracle.F32, 7)):
+                    arrays = [H.make_input(r, count, dtype) for r in range(n)]
+                    bufs = [H.to_torch(a, dtype, dev) for a in arrays]
+                    for r in range(n):
+                        comms[r].broadcast(bufs[r], root)
+                    torch.cuda.synchronize()
+                    assert all(c.status() == 0 for c in comms)
+                    most_rounds = max(most_rounds, comms[0].last_launch()["rounds"])
+                    want = oracle.broadcast(arrays, dtype, root)
+                    for r in range(n):
+                        H.assert_bits_equal(H.to_numpy(bufs[r], dtype), want[r],
+                                            "broadcast {} root {} rank {}".format(shape, root, r))
+        assert most_rounds > 4
+    finally:
+        for c in comms:
+            c.set_tuning()
 
 
 @pytest.mark.parametrize("n", [2, 4, 8])

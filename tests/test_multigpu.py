@@ -153,6 +153,17 @@ def test_gather_broadcast_reducescatter_across_gpus(comms):
     sync_all(n)
     for r in range(n):
         assert np.array_equal(xs[r].cpu().numpy(), arrays[1])
+    # Large broadcast (scatter + all-gather from three ranks up), odd size, last rank as root.
+    big = [H.make_input(r, (1 << 22) + 3, oracle.F32) for r in range(n)]
+    bs = [H.to_torch(a, oracle.F32, "cuda:{}".format(r)) for r, a in enumerate(big)]
+    for rep in range(2):
+        for r in range(n):
+            with torch.cuda.device(r):
+                comms[r].broadcast(bs[r], n - 1)
+    sync_all(n)
+    for r in range(n):
+        assert comms[r].status() == 0
+        H.assert_bits_equal(H.to_numpy(bs[r], oracle.F32), big[n - 1], "large broadcast rank {}".format(r))
 
 
 @needs_two
