@@ -868,11 +868,11 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
     c->nvls_slot_bytes = env_ll("DGN_NVLS_SLOT_BYTES", 64 * 1024);
     if (c->nvls_slot_bytes < 4096) c->nvls_slot_bytes = 4096;
     c->nvls_slot_bytes = (c->nvls_slot_bytes + 4095) & ~4095ll;
-    // Measured at n = 8: ahead of the store-only two-shot kernel from 256 MiB
-    // (674 against 603 GB/s; 763 against 621 at 1 GiB), behind at 64 MiB.  With
-    // fewer ranks the switch saves too little traffic (1.5 S per direction at
-    // n = 2 against 1.0 S), so the variant is opt-in there.
-    c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", nranks >= 8 ? (128ll << 20) : (1ll << 62));
+    // Measured at n = 8 against the store-only two-shot kernel: 507 vs 561 GB/s
+    // at 128 MiB, 630 vs 605 at 256 MiB, 725 vs 635 at 512 MiB, 764 vs 621 at
+    // 1 GiB.  With fewer ranks the switch saves too little traffic (1.5 S per
+    // direction at n = 2 against 1.0 S), so the variant is opt-in there.
+    c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", nranks >= 8 ? (256ll << 20) : (1ll << 62));
     c->nvls_bytes = 2 * (size_t)c->nvls_max_blocks * 2 * 2 * (size_t)nranks * (size_t)c->nvls_slot_bytes;
     c->nvls_capable = nvls_device_supported(device);
     if (c->nvls_capable && rank == 0) {
