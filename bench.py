@@ -329,7 +329,16 @@ def bench_multi(args):
             dist.broadcast_object_list(box, src=0)
             return box[0]
 
-        nccl = NcclBackend(rank, world, exchange)
+        # All ranks must agree before anyone enters ncclCommInitRank.
+        try:
+            from baseline.nccl_backend import _find_library
+            _find_library()
+            have = 1.0
+        except Exception:
+            have = 0.0
+        flag = torch.tensor([have], dtype=torch.float64)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        nccl = NcclBackend(rank, world, exchange) if flag.item() > 0 else None
 
     tdtype = torch_dtype_of(args.dtype)
     esize = torch.tensor([], dtype=tdtype).element_size()
