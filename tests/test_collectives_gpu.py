@@ -267,6 +267,42 @@ def test_reducescatter(teams, n):
             H.assert_bits_equal(H.to_numpy(outs[r], dtype), want[r], "reducescatter rank {}".format(r))
 
 
+def test_captured_launches_can_be_replayed(teams):
+    """Protocol state (epochs, parity, low-latency counters) lives in device
+    memory, so a CUDA graph that holds collectives can be replayed: every
+    replay must give the all-reduce of whatever the buffers hold at that time."""
+    n = 4
+    comms = teams(n)
+    dev = "cuda:0"
+    small = [torch.zeros(3001, device=dev) for _ in range(n)]        # low-latency kernel
+    large = [torch.zeros(1 << 20, device=dev) for _ in range(n)]     # two-shot kernel
+    ops = [c.prepare_all_reduce([a], [a], "SUM") for c, a in zip(comms, small)]
+    ops += [c.prepare_all_reduce([a], [a], "MEAN") for c, a in zip(comms, large)]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for op in ops:  # first launches outside the capture (table / module set-up)
+            op()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for op in ops:
+            op()
+    for rep in range(3):
+        for r in range(n):
+            small[r].fill_(float(rep + r + 1))
+            large[r].copy_(torch.arange(1 << 20, device=dev, dtype=torch.float32) % 7 + r * rep)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert all(c.status() == 0 for c in comms)
+        want_small = float(sum(rep + r + 1 for r in range(n)))
+        want_large = torch.arange(1 << 20, device=dev, dtype=torch.float32) % 7 + rep * (n - 1) / 2.0
+        for r in range(n):
+            assert torch.equal(small[r], torch.full((3001,), want_small, device=dev)), "replay {}".format(rep)
+            assert torch.equal(large[r], want_large), "replay {}".format(rep)
+
+
 def test_results_are_deterministic(teams):
     comms = teams(8)
     arrays = [H.make_input(r, 100003, oracle.F16) for r in range(8)]
