@@ -41,6 +41,8 @@ def parse_args():
     ap.add_argument("--reduction", default="MEAN")
     ap.add_argument("--sweep", default="auto", choices=["auto", "off", "full"],
                     help="message-size sweep beside the headline (auto: up to 256 MiB)")
+    ap.add_argument("--configs", default="auto", choices=["auto", "off"],
+                    help="operator configurations (gradient buckets, gather/broadcast shapes) beside the headline")
     ap.add_argument("--no-nccl", action="store_true", help="skip the NCCL comparison in the sweep")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-emulated", action="store_true", help="N=1: skip the emulated 8-rank timings")
@@ -384,7 +386,7 @@ def bench_multi(args):
     busbw = S / (ms * 1e-3) / 1e9 * factor
 
     sweep = run_sweep(args, comm, nccl, rank, world, dev, stream, barrier, max_over_ranks) if args.sweep != "off" else []
-    extras = run_operator_configs(comm, nccl, rank, world, dev, barrier, max_over_ranks) if args.sweep != "off" else {}
+    extras = run_operator_configs(comm, nccl, rank, world, dev, barrier, max_over_ranks) if args.configs != "off" else {}
 
     line = None
     if rank == 0:

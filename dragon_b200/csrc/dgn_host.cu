@@ -41,6 +41,7 @@ const void* reduce_kernel_fn_5(int, bool);
 const void* reduce_kernel_fn_6(int, bool);
 const void* reduce_kernel_fn_7(int, bool);
 const void* allgather_kernel_fn();
+const void* allgather_ll_kernel_fn();
 const void* broadcast_kernel_fn();
 const void* broadcast_scatter_kernel_fn();
 const void* local_copy_kernel_fn(int es, bool table);
@@ -201,6 +202,7 @@ struct dgn_comm {
   long long tune_chunk = 0;
   long long oneshot_max_bytes = -1, ll_max_bytes = -1, ll2_max_bytes = -1;
   long long bcast_scatter_min_bytes = 1ll << 20;
+  long long ll_allgather_max_bytes = 512ll << 10;  // per-rank block of the low-latency all-gather
   bool fused_twoshot = false;  // DGN_TWOSHOT_FUSED=1: lock-step two-shot kernel instead of the warp-specialised one
   Team* team = nullptr;
   std::vector<TableEntry> tables;
@@ -244,6 +246,7 @@ int preload_kernels() {
     }
   }
   DGN_CUDA(cudaFuncGetAttributes(&attr, allgather_kernel_fn()));
+  DGN_CUDA(cudaFuncGetAttributes(&attr, allgather_ll_kernel_fn()));
   DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_kernel_fn()));
   DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_scatter_kernel_fn()));
   const int sizes[4] = {1, 2, 4, 8};
@@ -457,6 +460,32 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
       return p;
     }
   }
+  if (d.kind == kOpAllGather) {
+    // Small blocks: flag-in-data lines, one hop.
+    const long long ll_vecs = c->geo.ll_slot_bytes / 32;
+    int ll_bmax = c->geo.ll_max_blocks;
+    if (block_cap > 0 && block_cap < ll_bmax) ll_bmax = block_cap;
+    const bool fits = ceil_div(d.nvec, ll_bmax) <= ll_vecs;
+    bool ll = fits && d.nvec * 16 <= c->ll_allgather_max_bytes;
+    if (c->tune_variant == DGN_VARIANT_LL) ll = fits;
+    else if (c->tune_variant != DGN_VARIANT_AUTO) ll = false;
+    if (ll) {
+      p.variant = DGN_VARIANT_LL;
+      long long b = ceil_div(d.nvec, 256);
+      if (c->tune_blocks > 0) b = c->tune_blocks;
+      if (b > ll_bmax) b = ll_bmax;
+      if (b < 1) b = 1;
+      if (ceil_div(d.nvec, b) > ll_vecs) b = ceil_div(d.nvec, ll_vecs);
+      p.blocks = (int)b;
+      p.cv = (int)ceil_div(d.nvec, b);
+      p.rounds = 1;
+      if (c->tune_threads <= 0) {
+        long long t = ((long long)p.cv + 31) / 32 * 32;
+        p.threads = (int)(t < 64 ? 64 : (t > 512 ? 512 : t));
+      }
+      return p;
+    }
+  }
   // Multi-round kernels: two-shot all-reduce, reduce-scatter, all-gather,
   // broadcast.  `per` = vectors each block column has to cover.
   long long per = d.nvec;
@@ -502,7 +531,7 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
       k.smem = table ? table_smem_bytes(d.ntensors) : 0;
       break;
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
-    case kOpAllGather: k.fn = allgather_kernel_fn(); break;
+    case kOpAllGather: k.fn = p.variant == DGN_VARIANT_LL ? allgather_ll_kernel_fn() : allgather_kernel_fn(); break;
     case kOpBroadcast:
       k.fn = p.variant == DGN_VARIANT_TWOSHOT ? broadcast_scatter_kernel_fn() : broadcast_kernel_fn();
       break;
@@ -852,6 +881,7 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
   c->ll2_max_bytes = env_ll("DGN_LL2_MAX_BYTES", -1);
   c->fused_twoshot = env_ll("DGN_TWOSHOT_FUSED", 0) != 0;
   c->bcast_scatter_min_bytes = env_ll("DGN_BCAST_SCATTER_MIN_BYTES", 1ll << 20);
+  c->ll_allgather_max_bytes = env_ll("DGN_LL_ALLGATHER_MAX_BYTES", 512ll << 10);
   c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
   int rc = alloc_workspace(c);
   if (rc != DGN_OK) {

@@ -1328,6 +1328,58 @@ __global__ void __launch_bounds__(kMaxThreads, 1) allgather_kernel(const __grid_
 }
 
 // ---------------------------------------------------------------------------
+// ALLGATHER for small blocks (bytes), low-latency: every rank stores its block
+// as flag-in-data lines into every peer's low-latency inbox and polls its own
+// inbox; one link hop, no fence, no barrier.  Uses the region and the counter
+// of the low-latency all-reduce kernels (every rank needs every other rank's
+// lines to finish, so the same two-parity argument holds).
+
+template <int kUnused>
+__global__ void __launch_bounds__(kMaxThreads, 1) allgather_ll_kernel(const __grid_constant__ OpParams P) {
+  const PeerTable& pt = P.peers[blockIdx.y];
+  const RankArgs& ra = P.ra[blockIdx.y];
+  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
+  const u64 ops = pt.blk[b].ll_ops;
+  const unsigned flag = (unsigned)(ops % 0xfffffffeull) + 1u;
+  const int parity = (int)(ops & 1ull);
+  __syncthreads();
+  if (threadIdx.x == 0) pt.blk[b].ll_ops = ops + 1;
+
+  const char* in = static_cast<const char*>(ra.in);
+  char* out = static_cast<char*>(ra.out);
+  const bool in_al = is_al16(in);
+  char* mine = out + (long long)r * P.count;
+  const bool mine_al = is_al16(mine);
+  const long long off = (long long)b * P.cv;
+  const long long len = clampll(P.nvec - off, 0, P.cv);
+  char* dst[kMaxRanks];
+#pragma unroll
+  for (int k = 1; k < kMaxRanks; ++k) dst[k] = (k < n) ? ll_ptr(pt, (r + k) % n, parity, b, r) : nullptr;
+  for (long long v = threadIdx.x; v < len; v += blockDim.x) {
+    const uint4 x = load_vec<1>(in, off + v, P.count, in_al);
+    if (mine != in) store_vec<1>(mine, off + v, P.count, mine_al, x);
+#pragma unroll
+    for (int k = 1; k < kMaxRanks; ++k) {
+      if (k < n) {
+        st_ll(dst[k] + v * 32, x.x, x.y, flag);
+        st_ll(dst[k] + v * 32 + 16, x.z, x.w, flag);
+      }
+    }
+  }
+  for (int k = 1; k < n; ++k) {
+    const int src = (r + k) % n;
+    const char* lines = ll_ptr(pt, r, parity, b, src);
+    char* block = out + (long long)src * P.count;
+    const bool al = is_al16(block);
+    for (long long v = threadIdx.x; v < len; v += blockDim.x) {
+      uint4 x;
+      if (!poll_ll(lines + v * 32, flag, P.wait_ns, pt.status, &x)) return;
+      store_vec<1>(block, off + v, P.count, al, x);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // BROADCAST in place (bytes).  The root publishes a slice in an outbox half
 // (A), the others pull it and acknowledge (B); the root refills a half only
 // after all acknowledgements of the round that used it.

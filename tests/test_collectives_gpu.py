@@ -206,7 +206,13 @@ def test_allreduce_unaligned_views(teams):
 def test_allgather_bit_exact(teams, n):
     comms = teams(n)
     dev = "cuda:0"
-    for dtype, count in ((oracle.I64, 65536), (oracle.BF16, 70001), (oracle.U8, 13), (oracle.F64, 1)):
+    # variant 0: automatic (low-latency lines for small blocks, pull above);
+    # variant 2: always publish-and-pull.
+    for variant, dtype, count in ((0, oracle.I64, 65536), (0, oracle.BF16, 70001), (0, oracle.U8, 13), (0, oracle.F64, 1),
+                                  (0, oracle.F32, (1 << 20) + 3), (2, oracle.I64, 65536), (2, oracle.BF16, 70001),
+                                  (2, oracle.U8, 13), (4, oracle.F32, 100003)):
+        for c in comms:
+            c.set_tuning(variant=variant)
         arrays = [H.make_input(r, count, dtype) for r in range(n)]
         if dtype == oracle.BF16:  # NaN payloads, infinities, signed zeros, subnormals travel untouched
             arrays[0][:6] = np.array([0x7FC1, 0xFFFF, 0x7F80, 0x8000, 0x0001, 0xFF80], dtype=np.uint16)
@@ -217,7 +223,9 @@ def test_allgather_bit_exact(teams, n):
         torch.cuda.synchronize()
         want = oracle.allgather(arrays, dtype)
         for r in range(n):
-            H.assert_bits_equal(H.to_numpy(outs[r], dtype), want, "allgather rank {}".format(r))
+            H.assert_bits_equal(H.to_numpy(outs[r], dtype), want, "allgather variant {} rank {}".format(variant, r))
+    for c in comms:
+        c.set_tuning()
 
 
 @pytest.mark.parametrize("n", [2, 4, 8])
