@@ -869,7 +869,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_twoshot_kernel(const __grid
         }
       }
     }
-    // One barrier publishes both kinds of stores.
+    // Publish the pushed slices (A) and the reduced slice (B).
     if (do_push) signal_peers(pt, b, kChanA, turn.base + 2 * (u64)i + 1);
     if (do_reduce) signal_peers(pt, b, kChanB, turn.base + 2 * (u64)(i - 1) + 2);
   }
