@@ -149,6 +149,55 @@ def time_steps(fn, steps, warmup, barrier=None):
     return per, evs[0].elapsed_time(evs[steps])
 
 
+def time_e2e(comm, xh, yh, bufs_in, bufs_out, reduction, steps, warmup, barrier=None):
+    """End to end through the public call with HOST buffers: every step copies
+    the input from pinned host memory to the device, runs the all-reduce and
+    copies the result back to pinned host memory.  Three streams and two
+    device buffers let the H2D copy of step i+1, the collective of step i and
+    the D2H copy of step i-1 overlap, as a training loop with pinned staging
+    buffers would.  Returns milliseconds for `steps` steps (first H2D issued to
+    last D2H finished)."""
+    import torch
+    s_in, s_op, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ops = [comm.prepare_all_reduce([a], [b], reduction) for a, b in zip(bufs_in, bufs_out)]
+    nb = len(bufs_in)
+    free = [None] * nb  # D2H of the step that last used buffer k has finished
+
+    def step(i):
+        k = i % nb
+        with torch.cuda.stream(s_in):
+            if free[k] is not None:
+                s_in.wait_event(free[k])
+            bufs_in[k].copy_(xh, non_blocking=True)
+            e_in = torch.cuda.Event()
+            e_in.record(s_in)
+        with torch.cuda.stream(s_op):
+            s_op.wait_event(e_in)
+            ops[k](s_op)
+            e_op = torch.cuda.Event()
+            e_op.record(s_op)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(e_op)
+            yh.copy_(bufs_out[k], non_blocking=True)
+            free[k] = torch.cuda.Event()
+            free[k].record(s_out)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(s_in)
+    for i in range(warmup, warmup + steps):
+        step(i)
+    stop.record(s_out)
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    return start.elapsed_time(stop)
+
+
 def cpu_config1_baseline():
     """CPU restatement of the MPI path on the reference's own CPU case: 2 rank
     processes, 16 MiB fp32 SUM, in place."""
@@ -191,14 +240,9 @@ def bench_single(args):
         # End to end: host buffers in, host result out, copies inside the timed region.
         xh = x.cpu().pin_memory()
         yh = torch.empty_like(xh).pin_memory()
-
-        def e2e_step():
-            x.copy_(xh, non_blocking=True)
-            op()
-            yh.copy_(y, non_blocking=True)
-
         e2e_steps = max(3, min(args.steps, 10))
-        _, e2e_ms = time_steps(e2e_step, e2e_steps, 2)
+        e2e_ms = time_e2e(comm, xh, yh, [x, torch.empty_like(x)], [y, torch.empty_like(y)], args.reduction,
+                          e2e_steps, 2)
     assert torch.equal(yh, xh), "local-copy path returned different bytes"
     ms = total_ms / args.steps
     kernel_ms = statistics.mean(per)
@@ -225,7 +269,8 @@ def bench_single(args):
                      "algorithmic_bytes_per_launch": 2 * S, "kernel": "local_copy_kernel",
                      "kernel_ms": kernel_ms},
         "e2e": {"value": S / (e2e_ms / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
-                "h2d_bytes_per_step": S, "d2h_bytes_per_step": S, "ms_per_step": e2e_ms / e2e_steps},
+                "h2d_bytes_per_step": S, "d2h_bytes_per_step": S, "ms_per_step": e2e_ms / e2e_steps,
+                "pipeline": "H2D, all-reduce and D2H on three streams, two device buffers"},
         "gpu_launches": int(launches),
         "clocks": sampler.summary(),
     }
@@ -371,14 +416,10 @@ def bench_multi(args):
         launches = lib.dgn_launch_count() - launches0 - args.warmup
         xh = x0.cpu().pin_memory()
         yh = torch.empty_like(xh).pin_memory()
-
-        def e2e_step():
-            x.copy_(xh, non_blocking=True)
-            op()
-            yh.copy_(x, non_blocking=True)
-
         e2e_steps = max(3, min(args.steps, 10))
-        _, e2e_ms = time_steps(e2e_step, e2e_steps, 2, barrier)
+        x2 = torch.empty_like(x)
+        e2e_ms = time_e2e(comm, xh, yh, [x, x2], [x, x2], args.reduction, e2e_steps, 2, barrier)
+        del x2
     ms = max_over_ranks(total_ms) / args.steps
     kernel_ms = max_over_ranks(statistics.mean(per))
     e2e_ms = max_over_ranks(e2e_ms) / e2e_steps
@@ -414,7 +455,8 @@ def bench_multi(args):
                          "frac_of_measured_p2p": achieved / NVLINK_MEASURED_P2P_GBS,
                          "algorithmic_bytes_per_launch": S * factor, "kernel_ms": kernel_ms},
             "e2e": {"value": S / (e2e_ms * 1e-3) / 1e9 * factor, "unit": "GB/s",
-                    "h2d_bytes_per_step": S, "d2h_bytes_per_step": S, "ms_per_step": e2e_ms},
+                    "h2d_bytes_per_step": S, "d2h_bytes_per_step": S, "ms_per_step": e2e_ms,
+                    "pipeline": "H2D, all-reduce and D2H on three streams, two device buffers"},
             "gpu_launches": int(launches),
             "clocks": sampler.summary(),
             "sweep": sweep,
