@@ -372,3 +372,87 @@ def test_wait_limit_reports_timeout_without_hanging(dgn_lib):
     finally:
         a.destroy()
         b.destroy()
+
+
+def test_empty_messages_launch_nothing(teams):
+    """count == 0 is legal everywhere and enqueues no kernel."""
+    from dragon_b200 import _C
+    comms = teams(2)
+    lib = _C.lib()
+    before = lib.dgn_launch_count()
+    e32 = [torch.empty(0, device="cuda:0") for _ in range(2)]
+    for r in range(2):
+        comms[r].all_reduce([e32[r]], None, "MEAN")
+        comms[r].all_reduce([], None, "SUM")
+        comms[r].all_gather(e32[r], torch.empty(0, device="cuda:0"))
+        comms[r].broadcast(e32[r], 1)
+        comms[r].reduce_scatter(e32[r], torch.empty(0, device="cuda:0"), "SUM")
+    torch.cuda.synchronize()
+    assert lib.dgn_launch_count() == before
+    # A list whose only non-empty tensor is in the middle is the flat case.
+    xs = [[torch.empty(0, device="cuda:0"), torch.full((33,), float(r + 1), device="cuda:0"),
+           torch.empty(0, device="cuda:0")] for r in range(2)]
+    for r in range(2):
+        comms[r].all_reduce(xs[r], None, "SUM")
+    torch.cuda.synchronize()
+    assert torch.equal(xs[0][1], torch.full((33,), 3.0, device="cuda:0"))
+    assert lib.dgn_launch_count() == before + 1
+
+
+def test_more_tensors_than_one_launch_takes(teams):
+    """A list longer than the per-launch table (1024 entries) is split into several launches."""
+    from dragon_b200 import _C
+    comms = teams(2)
+    nt = 1500
+    rng = np.random.default_rng(5)
+    counts = rng.integers(1, 40, nt)
+    host = [[rng.integers(-1000, 1000, int(k)).astype(np.int32) for k in counts] for _ in range(2)]
+    dev = [[torch.from_numpy(a).to("cuda:0") for a in row] for row in host]
+    before = _C.lib().dgn_launch_count()
+    for r in range(2):
+        comms[r].all_reduce(dev[r], None, "SUM")
+    torch.cuda.synchronize()
+    assert _C.lib().dgn_launch_count() == before + 2
+    for i in (0, 1, 777, 1023, 1024, 1499):
+        want = host[0][i] + host[1][i]
+        assert np.array_equal(dev[0][i].cpu().numpy(), want) and np.array_equal(dev[1][i].cpu().numpy(), want)
+
+
+def test_argument_errors(dgn_lib):
+    """Bad arguments come back as status codes with a message; nothing is launched."""
+    import ctypes
+    from dragon_b200 import _C
+    from dragon_b200.comm import Communicator
+    a = Communicator.init_local(0, 2, 0)
+    b = Communicator.init_local(1, 2, 0)
+    try:
+        x = torch.zeros(8, device="cuda:0")
+        with pytest.raises(_C.DgnError) as e:  # not connected yet
+            a.all_reduce([x], None, "SUM")
+        assert e.value.status == _C.ERR_STATE
+        ha, hb = a.handle_bytes(), b.handle_bytes()
+        with pytest.raises(_C.DgnError) as e:  # handles in the wrong order
+            a.connect([hb, ha])
+        assert e.value.status == _C.ERR_ARG
+        with pytest.raises(_C.DgnError) as e:  # not a handle
+            a.connect([ha, b"\0" * _C.HANDLE_BYTES])
+        assert e.value.status == _C.ERR_ARG
+        a.connect([ha, hb])
+        b.connect([ha, hb])
+        with pytest.raises(_C.DgnError) as e:
+            a.set_tuning(variant=99)
+        assert e.value.status == _C.ERR_ARG
+        with pytest.raises(_C.DgnError) as e:
+            a.broadcast(x, root=2)
+        assert e.value.status == _C.ERR_ARG and "root" in str(e.value)
+        assert dgn_lib.dgn_allreduce(a._h, None, None, None, 1, _C.F32, _C.SUM, None) == _C.ERR_ARG
+        one = (ctypes.c_void_p * 1)(x.data_ptr())
+        cnt = (ctypes.c_int64 * 1)(8)
+        assert dgn_lib.dgn_allreduce(a._h, one, one, cnt, 1, 42, _C.SUM, None) == _C.ERR_ARG
+        assert dgn_lib.dgn_allreduce(a._h, one, one, cnt, 1, _C.F32, 9, None) == _C.ERR_ARG
+        neg = (ctypes.c_int64 * 1)(-1)
+        assert dgn_lib.dgn_allreduce(a._h, one, one, neg, 1, _C.F32, _C.SUM, None) == _C.ERR_ARG
+        assert a.status() == 0 and b.status() == 0
+    finally:
+        a.destroy()
+        b.destroy()
