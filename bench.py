@@ -275,10 +275,10 @@ def bench_single(args):
         "clocks": sampler.summary(),
     }
     # DRAM traffic of the copy kernel from its ncu capture (profiles/local_copy_kernel_256MiB.md):
-    # 268.5 MB read + 221.3 MB written per 256 MiB message; the rest of the
+    # 268.5 MB read + 221.7 MB written per 256 MiB message; the rest of the
     # written lines is still in the 126 MB L2 when the kernel ends.  Traffic
     # grows with the vectors copied, so it is scaled by the message size.
-    line["roofline"]["traffic"] = (268.47e6 + 221.29e6) * (S / float(256 * MiB))
+    line["roofline"]["traffic"] = (268.46e6 + 221.73e6) * (S / float(256 * MiB))
     if not args.no_emulated:
         line["emulated_ranks_one_gpu"] = bench_emulated(args)
     if not args.no_cpu_baseline:
