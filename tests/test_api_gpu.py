@@ -210,3 +210,35 @@ def test_single_rank_group_is_a_no_op(dgn_lib):
         assert torch.equal(x, torch.arange(8.0, device=DEV))
     finally:
         distributed.finalize()
+
+
+def test_optimizer_call_sites(dgn_lib):
+    """The two gradient-sync call sites of the reference's optimizers: SUM per
+    dtype with buckets and a 1/n grad scale (torch frontend), MEAN unbucketed
+    (native); mixed dtypes and a missing gradient."""
+    from dragon_b200 import distributed, gradient_sync
+    distributed.init_emulated_world(N, 0)
+    try:
+        group = distributed.new_group(list(range(N)))
+        spec = [(oracle.F32, 1000), (oracle.F16, 4099), (oracle.F32, 7), (oracle.F16, 33), (oracle.F32, 70001)]
+        host = [[H.make_input(r, k, dt, seed=11 + i) for i, (dt, k) in enumerate(spec)] for r in range(N)]
+        grads = [[H.to_torch(a, dt, DEV) for a, (dt, _) in zip(row, spec)] for row in host]
+        with group.as_default():
+            scales = per_rank(lambda r: gradient_sync.sync_gradients_torch_style(
+                grads[r][:2] + [None] + grads[r][2:], bucket_size=64 * 1024))
+        assert scales == [1.0 / N] * N
+        for i, (dt, _) in enumerate(spec):
+            want = oracle.allreduce([host[r][i] for r in range(N)], dt, "SUM")
+            for r in range(N):
+                H.assert_bits_equal(H.to_numpy(grads[r][i], dt), want, "torch style tensor {}".format(i))
+        f32 = [i for i, (dt, _) in enumerate(spec) if dt == oracle.F32]
+        grads = [[H.to_torch(host[r][i], oracle.F32, DEV) for i in f32] for r in range(N)]
+        per_rank(lambda r: gradient_sync.sync_gradients_native_style(grads[r], group))
+        for j, i in enumerate(f32):
+            want = oracle.allreduce([host[r][i] for r in range(N)], oracle.F32, "MEAN")
+            for r in range(N):
+                H.assert_bits_equal(H.to_numpy(grads[r][j], oracle.F32), want, "native style tensor {}".format(i))
+        assert gradient_sync.sync_gradients_torch_style([torch.ones(3, device=DEV)]) == 1.0  # no group: untouched
+    finally:
+        torch.cuda.synchronize()
+        distributed.finalize()
