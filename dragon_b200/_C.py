@@ -53,6 +53,8 @@ SIGNATURES = {
                                      ctypes.c_int, ctypes.c_void_p]),
     "dgn_reducescatter": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                          ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "dgn_allreduce_host": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                          ctypes.c_int, ctypes.c_int]),
     "dgn_allreduce_static": (ctypes.c_int, [ctypes.c_int, _c_void_pp, _c_void_pp, ctypes.c_int64, ctypes.c_int,
                                             ctypes.c_int, ctypes.c_void_p]),
     "dgn_launch_count": (ctypes.c_int64, []),

@@ -173,6 +173,20 @@ class Communicator(object):
             outputs = [outputs]
         self.prepare_all_reduce(inputs, outputs, reduction)(stream)
 
+    def all_reduce_host(self, values, reduction="SUM"):
+        """Synchronous all-reduce of a small numpy array that lives in host memory."""
+        import numpy as np
+        codes = {np.dtype(np.uint8): _C.U8, np.dtype(np.int8): _C.I8, np.dtype(np.int32): _C.I32,
+                 np.dtype(np.int64): _C.I64, np.dtype(np.float16): _C.F16, np.dtype(np.float32): _C.F32,
+                 np.dtype(np.float64): _C.F64}
+        arr = np.ascontiguousarray(values)
+        if arr.dtype not in codes:
+            raise TypeError("Unsupported data type: {}".format(arr.dtype))
+        out = np.empty_like(arr)
+        _C.check(_C.lib().dgn_allreduce_host(self._h, arr.ctypes.data, out.ctypes.data, arr.size,
+                                             codes[arr.dtype], redop_code(reduction)))
+        return out
+
     def all_gather(self, tensor, output, stream=None):
         """output[r] = rank r's tensor; output holds size * tensor.numel() elements."""
         _check_tensor(tensor, self.device)

@@ -209,6 +209,12 @@ struct dgn_comm {
   uint64_t table_clock = 0;
   Plan last_plan;
   std::string rdv_ok_file;
+  // host-memory all-reduce: its own stream and two 4 KiB staging buffers
+  cudaStream_t host_stream = nullptr;
+  void* host_dev = nullptr;
+  void* host_pin = nullptr;
+  cudaStream_t last_stream = nullptr;  // stream of the latest collective
+  bool has_last_stream = false;
   // NVSwitch multicast staging (optional)
   NvlsBuffer* nvls = nullptr;
   bool nvls_capable = false;
@@ -273,6 +279,9 @@ int alloc_workspace(dgn_comm* c) {
   DGN_CUDA(cudaHostAlloc((void**)&c->status_host, 64, cudaHostAllocMapped | cudaHostAllocPortable));
   *c->status_host = 0;
   DGN_CUDA(cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0));
+  DGN_CUDA(cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking));
+  DGN_CUDA(cudaMalloc(&c->host_dev, 4096));
+  DGN_CUDA(cudaHostAlloc(&c->host_pin, 4096, cudaHostAllocDefault));
   DGN_CUDA(cudaDeviceSynchronize());
   cudaDeviceProp prop;
   DGN_CUDA(cudaGetDeviceProperties(&prop, c->device));
@@ -585,6 +594,8 @@ int check_ready(dgn_comm* c) {
 // virtual rank of an emulated team has arrived.
 int issue(dgn_comm* c, const OpDesc& d) {
   DeviceGuard g(c->device);
+  c->last_stream = d.stream;
+  c->has_last_stream = true;
   if (!c->team) {
     Plan p = make_plan(c, d, 0);
     KernelChoice k = choose_kernel(c, d, p);
@@ -745,6 +756,9 @@ void free_comm(dgn_comm* c) {
   }
   if (c->base) cudaFree(c->base);
   if (c->status_host) cudaFreeHost(c->status_host);
+  if (c->host_pin) cudaFreeHost(c->host_pin);
+  if (c->host_dev) cudaFree(c->host_dev);
+  if (c->host_stream) cudaStreamDestroy(c->host_stream);
   if (!c->rdv_ok_file.empty()) unlink(c->rdv_ok_file.c_str());
   delete c;
 }
@@ -1199,6 +1213,38 @@ int dgn_allreduce(dgn_comm_t c, const void* const* in_ptrs, void* const* out_ptr
     return launch_local_copy(c, d, (int)es);
   }
   return issue(c, d);
+}
+
+int dgn_allreduce_host(dgn_comm_t c, const void* in, void* out, int64_t count, int dtype, int redop) {
+  int rc = check_ready(c);
+  if (rc != DGN_OK) return rc;
+  if (c->team) return fail(DGN_ERR_UNSUPPORTED, "the host all-reduce blocks and cannot run on an emulated communicator");
+  const size_t es = dgn_dtype_size(dtype);
+  if (es == 0) return fail(DGN_ERR_ARG, "unknown dtype %d", dtype);
+  if (count < 0) return fail(DGN_ERR_ARG, "negative count");
+  if (count == 0) return DGN_OK;
+  if (!in || !out) return fail(DGN_ERR_ARG, "null pointer");
+  const size_t bytes = (size_t)count * es;
+  if (bytes > 4096) return fail(DGN_ERR_ARG, "the host all-reduce takes at most 4096 bytes, got %zu", bytes);
+  if (c->nranks == 1) {
+    if (in != out) memmove(out, in, bytes);
+    return DGN_OK;
+  }
+  DeviceGuard g(c->device);
+  // Kernels of one communicator must not overlap: wait for the latest one.
+  if (c->has_last_stream) DGN_CUDA(cudaStreamSynchronize(c->last_stream));
+  memcpy(c->host_pin, in, bytes);
+  DGN_CUDA(cudaMemcpyAsync(c->host_dev, c->host_pin, bytes, cudaMemcpyHostToDevice, c->host_stream));
+  const void* ins[1] = {c->host_dev};
+  void* outs[1] = {c->host_dev};
+  int64_t counts[1] = {count};
+  rc = dgn_allreduce(c, ins, outs, counts, 1, dtype, redop, c->host_stream);
+  if (rc != DGN_OK) return rc;
+  DGN_CUDA(cudaMemcpyAsync(c->host_pin, c->host_dev, bytes, cudaMemcpyDeviceToHost, c->host_stream));
+  DGN_CUDA(cudaStreamSynchronize(c->host_stream));
+  if (dgn_comm_status(c) != DGN_OK) return fail(DGN_ERR_TIMEOUT, "a peer did not join the host all-reduce in time");
+  memcpy(out, c->host_pin, bytes);
+  return DGN_OK;
 }
 
 int dgn_reducescatter(dgn_comm_t c, const void* in, void* out, int64_t count, int dtype, int redop,

@@ -70,6 +70,13 @@ class CollectiveOpImpl {
     DGN_CHECK(dgn_broadcast(comm_, y, N, DgnTypeOf<T>::value, comm_root_, stream));
   }
 
+  // Host pointers, synchronous: the overload SyncBatchNorm and the ZeRO update
+  // call for a count or a flag (collective_op_impl.h:91-94 in the reference).
+  template <typename T>
+  void AllReduce(const T* x, T* y, int64_t N) {
+    DGN_CHECK(dgn_allreduce_host(comm_, x, y, N, DgnTypeOf<T>::value, redop_));
+  }
+
   template <typename T>
   void AllReduce(const T* x, T* y, int64_t N, void* stream) {
     const void* in[1] = {x};

@@ -171,6 +171,16 @@ int dgn_broadcast(dgn_comm_t comm, void* buf, int64_t count, int dtype, int root
 int dgn_reducescatter(dgn_comm_t comm, const void* in, void* out, int64_t count, int dtype,
                       int redop, void* stream);
 
+/* ALLREDUCE of a few values that live in HOST memory, synchronous: returns
+ * when `out` holds the result (replaces the host overload
+ * CollectiveOpImpl::AllReduce(x, y, N) -> MPI_Allreduce on host pointers,
+ * collective_op_impl.h:91-94, which SyncBatchNorm uses for its batch count
+ * and the ZeRO update for its overflow flag).  At most 4096 bytes.  The values
+ * travel through the low-latency device kernel on a stream of the
+ * communicator; collectives issued earlier on this communicator are waited
+ * for first.  Not available on emulated communicators. */
+int dgn_allreduce_host(dgn_comm_t comm, const void* in, void* out, int64_t count, int dtype, int redop);
+
 /* ALLREDUCE of `nranks` buffers that all live on the CURRENT device, without
  * allocating anything.  (No counterpart in the reference: Dragon's collectives
  * always go through a communicator that owns library-allocated buffers.)

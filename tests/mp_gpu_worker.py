@@ -47,6 +47,16 @@ def main():
     comm.all_gather(torch.from_numpy(idx[rank]).to(dev), out)
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), np.concatenate(idx))
+    # Host-memory all-reduce (synchronous), right after device collectives.
+    counts = comm.all_reduce_host(np.array([rank + 1, 10 * (rank + 1)], dtype=np.int64), "SUM")
+    assert counts.tolist() == [3, 30]
+    flag = comm.all_reduce_host(np.array([0.25 * (rank + 1)], dtype=np.float32), "MAX")
+    assert flag.tolist() == [0.5]
+    try:
+        comm.all_reduce_host(np.zeros(2000, dtype=np.float32))
+        raise AssertionError("an oversize host all-reduce must be refused")
+    except Exception as e:  # noqa: BLE001
+        assert "4096" in str(e)
     # Leave only after the peer has finished too: a last all-reduce is the barrier.
     done = torch.ones(1, device=dev)
     comm.all_reduce([done], None, "SUM")

@@ -456,3 +456,18 @@ def test_argument_errors(dgn_lib):
     finally:
         a.destroy()
         b.destroy()
+
+
+def test_host_allreduce_where_no_peer_is_needed(teams, dgn_lib):
+    """The host-memory all-reduce: identity at comm_size 1, refused on emulated
+    ranks (it blocks, and virtual ranks share one host thread)."""
+    from dragon_b200 import _C
+    from dragon_b200.comm import Communicator
+    c = Communicator.init_local(0, 1, 0)
+    try:
+        assert c.all_reduce_host(np.array([3, 4], dtype=np.int64)).tolist() == [3, 4]
+    finally:
+        c.destroy()
+    with pytest.raises(_C.DgnError) as e:
+        teams(2)[0].all_reduce_host(np.array([1.0], dtype=np.float32))
+    assert e.value.status == _C.ERR_UNSUPPORTED
