@@ -62,6 +62,27 @@ SIGNATURES = {
                                             _c_int_p]),
 }
 
+
+
+class AdamWArgs(ctypes.Structure):
+    """dgn_adamw_args of include/dgn.h."""
+    _fields_ = [("lr", ctypes.c_float), ("beta1", ctypes.c_float), ("beta2", ctypes.c_float),
+                ("eps", ctypes.c_float), ("weight_decay", ctypes.c_float), ("grad_scale", ctypes.c_float),
+                ("clip_norm", ctypes.c_float), ("clip_value", ctypes.c_float)]
+
+
+SIGNATURES.update({
+    "dgn_zero_shard_count": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64]),
+    "dgn_zero_state_count": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int]),
+    "dgn_zero_state_offset": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int]),
+    "dgn_zero_init_master": (ctypes.c_int, [ctypes.c_void_p, _c_void_pp, _c_i64_p, ctypes.c_int, ctypes.c_int,
+                                            ctypes.c_void_p, ctypes.c_void_p]),
+    "dgn_zero_adamw": (ctypes.c_int, [ctypes.c_void_p, _c_void_pp, _c_void_pp, _c_i64_p, ctypes.c_int,
+                                      ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                      ctypes.c_void_p, ctypes.POINTER(ctypes.c_float),
+                                      ctypes.POINTER(AdamWArgs), ctypes.c_void_p, ctypes.c_void_p]),
+})
+
 _lib = None
 
 

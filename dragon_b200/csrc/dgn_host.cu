@@ -29,6 +29,7 @@
 #include "../../include/dgn.h"
 #include "dgn_kernels.cuh"
 #include "dgn_nvls.h"
+#include "dgn_zero.cuh"
 
 namespace dgn {
 // Defined in the per-dtype instantiation units.
@@ -45,6 +46,7 @@ const void* allgather_ll_kernel_fn();
 const void* broadcast_kernel_fn();
 const void* broadcast_scatter_kernel_fn();
 const void* local_copy_kernel_fn(int es, bool table);
+const void* zero_kernel_fn(int dtype, int which);  // dgn_zero_inst.cu
 }  // namespace dgn
 
 using namespace dgn;
@@ -145,7 +147,7 @@ Geometry make_geometry(int nranks) {
   g.ll_slot_bytes = env_ll("DGN_LL_SLOT_BYTES", 64 * 1024);
   if (g.ll_slot_bytes < 4096) g.ll_slot_bytes = 4096;
   g.ll_slot_bytes = (g.ll_slot_bytes + 4095) & ~4095ll;
-  g.flags_bytes = (size_t)g.max_blocks * 3 * kMaxRanks * sizeof(u64);
+  g.flags_bytes = (size_t)g.max_blocks * kChannels * kMaxRanks * sizeof(u64);
   g.blk_off = g.flags_bytes;
   size_t head = g.blk_off + (size_t)g.max_blocks * sizeof(BlockState);
   g.stage_off = (head + 4095) & ~(size_t)4095;
@@ -171,16 +173,40 @@ struct Plan {
   int variant = 0, blocks = 1, threads = 512, cv = 1, rounds = 1;
 };
 
-enum OpKind { kOpAllReduce = 0, kOpReduceScatter, kOpAllGather, kOpBroadcast };
+enum OpKind { kOpAllReduce = 0, kOpReduceScatter, kOpAllGather, kOpBroadcast, kOpZeroReduce, kOpZeroUpdate };
+
+inline bool is_zero_kind(int kind) { return kind == kOpZeroReduce || kind == kOpZeroUpdate; }
+
+// Hyper-parameters of one sharded optimizer step; identical on every rank.
+struct ZeroHyper {
+  float lr = 0, beta1 = 0, beta2 = 0, eps = 0, wd = 0, grad_scale = 1, clip_norm = 0, clip_value = 0;
+  int check_finite = 0, use_lr_scales = 0;
+};
 
 struct OpDesc {
   int kind = 0, dtype = 0, redop = 0, root = 0, ntensors = 1;
-  long long count = 0;  // elements (AR single / RS per-rank block) or bytes (AG / BC)
+  long long count = 0;  // elements (AR single / RS per-rank block / bucket of a sharded step) or bytes (AG / BC)
   long long nvec = 0;
   const void* in = nullptr;
   void* out = nullptr;
   const TensorEnt* table = nullptr;
   cudaStream_t stream = nullptr;
+  ZeroRank zr = {};  // sharded optimizer step only
+  ZeroHyper zh;
+};
+
+// Device table of a sharded optimizer step, cached on the tensor list.
+struct ZeroTableEntry {
+  std::vector<const void*> grads;
+  std::vector<void*> params;
+  std::vector<int64_t> counts;
+  std::vector<float> lrs;
+  int es = 0;
+  ZeroEnt* d_table = nullptr;
+  ZeroEnt* h_table = nullptr;  // pinned
+  int nt = 0;                  // non-empty tensors
+  long long total = 0;
+  uint64_t last_use = 0;
 };
 
 struct Team;
@@ -206,6 +232,7 @@ struct dgn_comm {
   bool fused_twoshot = false;  // DGN_TWOSHOT_FUSED=1: lock-step two-shot kernel instead of the warp-specialised one
   Team* team = nullptr;
   std::vector<TableEntry> tables;
+  std::vector<ZeroTableEntry> zero_tables;
   uint64_t table_clock = 0;
   Plan last_plan;
   std::string rdv_ok_file;
@@ -259,6 +286,10 @@ int preload_kernels() {
   for (int es : sizes)
     for (int table = 0; table < 2; ++table)
       DGN_CUDA(cudaFuncGetAttributes(&attr, local_copy_kernel_fn(es, table != 0)));
+  const int zero_types[3] = {DGN_F16, DGN_BF16, DGN_F32};
+  for (int dtype : zero_types)
+    for (int which = 0; which < 3; ++which)
+      DGN_CUDA(cudaFuncGetAttributes(&attr, zero_kernel_fn(dtype, which)));
   return DGN_OK;
 }
 
@@ -502,6 +533,9 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
   // broadcast.  `per` = vectors each block column has to cover.
   long long per = d.nvec;
   if (d.kind == kOpAllReduce) per = ceil_div(d.nvec, n);
+  // Sharded optimizer step: the longest shard, ceil(total / n) elements, may
+  // begin and end inside a vector.
+  if (is_zero_kind(d.kind)) per = ceil_div(ceil_div(d.count, n), 16 / (long long)kElemSize[d.dtype]) + 1;
   p.variant = DGN_VARIANT_TWOSHOT;
   if (d.kind == kOpBroadcast) {
     // Small messages: peers pull from the root (one flag exchange).  Large
@@ -547,6 +581,11 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
     case kOpBroadcast:
       k.fn = p.variant == DGN_VARIANT_TWOSHOT ? broadcast_scatter_kernel_fn() : broadcast_kernel_fn();
       break;
+    case kOpZeroReduce:
+    case kOpZeroUpdate:
+      k.fn = zero_kernel_fn(d.dtype, d.kind == kOpZeroReduce ? 0 : 1);
+      k.smem = zero_smem_bytes(d.ntensors);
+      break;
   }
   return k;
 }
@@ -566,7 +605,24 @@ void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p)
   P->warps_b = (int)env_ll("DGN_NVLS_WARPS_REDUCE", 0);
 }
 
-int launch(const void* fn, dim3 grid, int threads, size_t smem, cudaStream_t stream, OpParams* P,
+void fill_zero_params(ZeroParams* Z, const dgn_comm* c, const OpDesc& d, const Plan& p) {
+  memset(Z, 0, sizeof(*Z));
+  fill_params(&Z->base, c, d, p);
+  Z->total = d.count;
+  Z->rc = ceil_div(d.count, c->nranks);
+  Z->lr = d.zh.lr;
+  Z->beta1 = d.zh.beta1;
+  Z->beta2 = d.zh.beta2;
+  Z->eps = d.zh.eps;
+  Z->wd = d.zh.wd;
+  Z->grad_scale = d.zh.grad_scale;
+  Z->clip_norm = d.zh.clip_norm;
+  Z->clip_value = d.zh.clip_value;
+  Z->check_finite = d.zh.check_finite;
+  Z->use_lr_scales = d.zh.use_lr_scales;
+}
+
+int launch(const void* fn, dim3 grid, int threads, size_t smem, cudaStream_t stream, void* P,
            bool cooperative) {
   void* args[1] = {P};
   cudaError_t e = cooperative
@@ -600,13 +656,22 @@ int issue(dgn_comm* c, const OpDesc& d) {
     Plan p = make_plan(c, d, 0);
     KernelChoice k = choose_kernel(c, d, p);
     if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
-    OpParams P;
-    fill_params(&P, c, d, p);
-    P.peers[0] = c->table;
-    P.ra[0].in = d.in;
-    P.ra[0].out = d.out;
-    P.ra[0].table = d.table;
-    int rc = launch(k.fn, dim3(p.blocks, 1), p.threads, k.smem, d.stream, &P, false);
+    int rc;
+    if (is_zero_kind(d.kind)) {
+      ZeroParams Z;
+      fill_zero_params(&Z, c, d, p);
+      Z.base.peers[0] = c->table;
+      Z.zr[0] = d.zr;
+      rc = launch(k.fn, dim3(p.blocks, 1), p.threads, k.smem, d.stream, &Z, false);
+    } else {
+      OpParams P;
+      fill_params(&P, c, d, p);
+      P.peers[0] = c->table;
+      P.ra[0].in = d.in;
+      P.ra[0].out = d.out;
+      P.ra[0].table = d.table;
+      rc = launch(k.fn, dim3(p.blocks, 1), p.threads, k.smem, d.stream, &P, false);
+    }
     if (rc != DGN_OK) return rc;
     c->last_plan = p;
     return DGN_OK;
@@ -623,7 +688,8 @@ int issue(dgn_comm* c, const OpDesc& d) {
     for (int r = 1; r < t->n; ++r) {
       const OpDesc& o = t->pending[r].front();
       if (f.kind != o.kind || f.dtype != o.dtype || f.redop != o.redop || f.root != o.root ||
-          f.count != o.count || f.nvec != o.nvec || f.ntensors != o.ntensors || f.stream != o.stream) {
+          f.count != o.count || f.nvec != o.nvec || f.ntensors != o.ntensors || f.stream != o.stream ||
+          memcmp(&f.zh, &o.zh, sizeof(ZeroHyper)) != 0) {
         for (int q = 0; q < t->n; ++q) t->pending[q].clear();
         return fail(DGN_ERR_ARG, "virtual rank %d issued a collective that differs from rank 0's", r);
       }
@@ -649,16 +715,24 @@ int issue(dgn_comm* c, const OpDesc& d) {
     }
     if (!fits) return fail(DGN_ERR_UNSUPPORTED, "no resident launch shape for the emulated team");
     OpParams P;
-    fill_params(&P, c, f, p);
+    ZeroParams Z;
+    const bool zero = is_zero_kind(f.kind);
+    if (zero) fill_zero_params(&Z, c, f, p);
+    else fill_params(&P, c, f, p);
     for (int r = 0; r < t->n; ++r) {
       const OpDesc& o = t->pending[r].front();
-      P.peers[r] = t->members[r]->table;
-      P.ra[r].in = o.in;
-      P.ra[r].out = o.out;
-      P.ra[r].table = o.table;
+      if (zero) {
+        Z.base.peers[r] = t->members[r]->table;
+        Z.zr[r] = o.zr;
+      } else {
+        P.peers[r] = t->members[r]->table;
+        P.ra[r].in = o.in;
+        P.ra[r].out = o.out;
+        P.ra[r].table = o.table;
+      }
     }
     for (int r = 0; r < t->n; ++r) t->pending[r].pop_front();
-    int rc = launch(k.fn, dim3(p.blocks, t->n), p.threads, k.smem, f.stream, &P, true);
+    int rc = launch(k.fn, dim3(p.blocks, t->n), p.threads, k.smem, f.stream, zero ? (void*)&Z : (void*)&P, true);
     if (rc != DGN_OK) return rc;
     for (dgn_comm* m : t->members) m->last_plan = p;
   }
@@ -740,10 +814,94 @@ int get_table(dgn_comm* c, const void* const* in, void* const* out, const int64_
   return DGN_OK;
 }
 
+// Device table of a sharded optimizer step (gradients, parameters, flat
+// element offsets, learning-rate scales), cached like the bucket tables.
+int get_zero_table(dgn_comm* c, const void* const* grads, void* const* params, const int64_t* counts, int nt,
+                   const float* lrs, int es, cudaStream_t stream, const ZeroTableEntry** result) {
+  for (ZeroTableEntry& e : c->zero_tables) {
+    if (e.es == es && (int)e.grads.size() == nt && memcmp(e.grads.data(), grads, sizeof(void*) * nt) == 0 &&
+        memcmp(e.params.data(), params, sizeof(void*) * nt) == 0 &&
+        memcmp(e.counts.data(), counts, sizeof(int64_t) * nt) == 0 &&
+        (lrs ? (e.lrs.size() == (size_t)nt && memcmp(e.lrs.data(), lrs, sizeof(float) * nt) == 0) : e.lrs.empty())) {
+      e.last_use = ++c->table_clock;
+      *result = &e;
+      return DGN_OK;
+    }
+  }
+  if (c->zero_tables.size() >= 16) {  // evict the least recently used entry
+    size_t lru = 0;
+    for (size_t i = 1; i < c->zero_tables.size(); ++i)
+      if (c->zero_tables[i].last_use < c->zero_tables[lru].last_use) lru = i;
+    cudaFree(c->zero_tables[lru].d_table);  // synchronises with any kernel still reading it
+    cudaFreeHost(c->zero_tables[lru].h_table);
+    c->zero_tables.erase(c->zero_tables.begin() + lru);
+  }
+  ZeroTableEntry e;
+  e.es = es;
+  e.grads.assign(grads, grads + nt);
+  e.params.assign(params, params + nt);
+  e.counts.assign(counts, counts + nt);
+  if (lrs) e.lrs.assign(lrs, lrs + nt);
+  DGN_CUDA(cudaHostAlloc((void**)&e.h_table, sizeof(ZeroEnt) * (size_t)(nt + 1), cudaHostAllocDefault));
+  long long total = 0;
+  int k = 0;
+  for (int i = 0; i < nt; ++i) {
+    if (counts[i] == 0) continue;
+    e.h_table[k].grad = static_cast<const char*>(grads[i]);
+    e.h_table[k].param = static_cast<char*>(params[i]);
+    e.h_table[k].ebegin = total;
+    e.h_table[k].lr_scale = lrs ? lrs[i] : 1.f;
+    e.h_table[k].reserved = 0;
+    total += counts[i];
+    ++k;
+  }
+  e.nt = k;
+  e.total = total;
+  cudaError_t err = cudaMalloc((void**)&e.d_table, sizeof(ZeroEnt) * (size_t)(nt + 1));
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(e.d_table, e.h_table, sizeof(ZeroEnt) * (size_t)k, cudaMemcpyHostToDevice, stream);
+  if (err != cudaSuccess) {
+    cudaFree(e.d_table);
+    cudaFreeHost(e.h_table);
+    return fail(DGN_ERR_CUDA, "bucket table of the sharded optimizer step: %s", cudaGetErrorString(err));
+  }
+  e.last_use = ++c->table_clock;
+  c->zero_tables.push_back(std::move(e));
+  *result = &c->zero_tables.back();
+  return DGN_OK;
+}
+
+// Argument checks shared by the entry points of the sharded optimizer step.
+int check_zero_bucket(const void* const* a, const void* const* b, const int64_t* counts, int ntensors, int dtype,
+                      long long* total, int* nonempty) {
+  if (dtype != DGN_F16 && dtype != DGN_BF16 && dtype != DGN_F32)
+    return fail(DGN_ERR_UNSUPPORTED, "the sharded optimizer step takes float16, bfloat16 or float32, got dtype %d", dtype);
+  if (ntensors < 1 || !a || !b || !counts) return fail(DGN_ERR_ARG, "null or empty tensor list");
+  const size_t es = kElemSize[dtype];
+  *total = 0;
+  *nonempty = 0;
+  for (int i = 0; i < ntensors; ++i) {
+    if (counts[i] < 0) return fail(DGN_ERR_ARG, "negative count for tensor %d", i);
+    if (counts[i] == 0) continue;
+    if (!a[i] || !b[i]) return fail(DGN_ERR_ARG, "null pointer for tensor %d", i);
+    if (((uintptr_t)a[i] | (uintptr_t)b[i]) & (es - 1))
+      return fail(DGN_ERR_ARG, "tensor %d is not aligned to its element size", i);
+    *total += counts[i];
+    ++*nonempty;
+  }
+  if (*nonempty > kMaxTableTensors)
+    return fail(DGN_ERR_UNSUPPORTED, "a bucket takes at most %d tensors, got %d", kMaxTableTensors, *nonempty);
+  return DGN_OK;
+}
+
 void free_comm(dgn_comm* c) {
   DeviceGuard g(c->device);
   cudaDeviceSynchronize();
   for (TableEntry& e : c->tables) {
+    cudaFree(e.d_table);
+    cudaFreeHost(e.h_table);
+  }
+  for (ZeroTableEntry& e : c->zero_tables) {
     cudaFree(e.d_table);
     cudaFreeHost(e.h_table);
   }
@@ -1316,6 +1474,116 @@ int dgn_broadcast(dgn_comm_t c, void* buf, int64_t count, int dtype, int root, v
   d.in = buf;
   d.out = buf;
   d.stream = static_cast<cudaStream_t>(stream);
+  return issue(c, d);
+}
+
+int64_t dgn_zero_shard_count(int nranks, int64_t total) {
+  if (nranks < 1 || total < 0) return -1;
+  return ceil_div(total, nranks);
+}
+
+int64_t dgn_zero_state_count(int nranks, int64_t total, int dtype) {
+  const size_t es = dgn_dtype_size(dtype);
+  if (nranks < 1 || total < 0 || es == 0) return -1;
+  const long long E = 16 / (long long)es;
+  return (ceil_div(ceil_div(total, nranks), E) + 1) * E;
+}
+
+int64_t dgn_zero_state_offset(int rank, int nranks, int64_t total, int dtype) {
+  const size_t es = dgn_dtype_size(dtype);
+  if (nranks < 1 || rank < 0 || rank >= nranks || total < 0 || es == 0) return -1;
+  const ShardGeom sg = shard_geom(total, ceil_div(total, nranks), rank, (int)(16 / es));
+  return sg.e_lo - sg.g_lo * (long long)(16 / es);
+}
+
+int dgn_zero_init_master(dgn_comm_t c, const void* const* param_ptrs, const int64_t* counts, int ntensors,
+                         int dtype, float* master, void* stream) {
+  int rc = check_ready(c);
+  if (rc != DGN_OK) return rc;
+  long long total = 0;
+  int nonempty = 0;
+  rc = check_zero_bucket(param_ptrs, param_ptrs, counts, ntensors, dtype, &total, &nonempty);
+  if (rc != DGN_OK) return rc;
+  if (total == 0) return DGN_OK;
+  if (!master || ((uintptr_t)master & 15u)) return fail(DGN_ERR_ARG, "master must be a 16-byte aligned device pointer");
+  if (c->team && !c->team->pending[c->rank].empty())
+    return fail(DGN_ERR_STATE, "virtual rank %d still has collectives waiting for the other ranks", c->rank);
+  DeviceGuard g(c->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const ZeroTableEntry* te = nullptr;
+  rc = get_zero_table(c, param_ptrs, const_cast<void* const*>(param_ptrs), counts, ntensors, nullptr,
+                      (int)kElemSize[dtype], s, &te);
+  if (rc != DGN_OK) return rc;
+  OpDesc d;
+  d.kind = kOpZeroReduce;
+  d.dtype = dtype;
+  d.count = total;
+  d.ntensors = te->nt;
+  d.stream = s;
+  Plan p;
+  ZeroParams Z;
+  fill_zero_params(&Z, c, d, p);
+  Z.base.peers[0] = c->table;
+  Z.zr[0].table = te->d_table;
+  Z.zr[0].master = master;
+  const long long E = 16 / (long long)kElemSize[dtype];
+  const long long nv = ceil_div(ceil_div(total, c->nranks), E) + 1;
+  long long blocks = ceil_div(nv, 256);
+  if (blocks > (long long)c->num_sms * 8) blocks = (long long)c->num_sms * 8;
+  return launch(zero_kernel_fn(dtype, 2), dim3((unsigned)blocks, 1), 256, zero_smem_bytes(te->nt), s, &Z, false);
+}
+
+int dgn_zero_adamw(dgn_comm_t c, const void* const* grad_ptrs, void* const* param_ptrs, const int64_t* counts,
+                   int ntensors, int dtype, float* master, float* m, float* v, float* grad_shard,
+                   const float* lr_scales, const dgn_adamw_args* args, float* found_inf, void* stream) {
+  int rc = check_ready(c);
+  if (rc != DGN_OK) return rc;
+  if (!args) return fail(DGN_ERR_ARG, "null hyper-parameters");
+  long long total = 0;
+  int nonempty = 0;
+  rc = check_zero_bucket(grad_ptrs, const_cast<const void* const*>(param_ptrs), counts, ntensors, dtype, &total,
+                         &nonempty);
+  if (rc != DGN_OK) return rc;
+  if (total == 0) return DGN_OK;
+  if (!master || !m || !v || !grad_shard)
+    return fail(DGN_ERR_ARG, "master, m, v and grad_shard are required");
+  if (((uintptr_t)master | (uintptr_t)m | (uintptr_t)v | (uintptr_t)grad_shard) & 15u)
+    return fail(DGN_ERR_ARG, "master, m, v and grad_shard must be 16-byte aligned");
+  DeviceGuard g(c->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  bool scaled = false;
+  if (lr_scales)
+    for (int i = 0; i < ntensors; ++i) scaled = scaled || lr_scales[i] != 1.f;
+  const ZeroTableEntry* te = nullptr;
+  rc = get_zero_table(c, grad_ptrs, param_ptrs, counts, ntensors, scaled ? lr_scales : nullptr,
+                      (int)kElemSize[dtype], s, &te);
+  if (rc != DGN_OK) return rc;
+  OpDesc d;
+  d.kind = kOpZeroReduce;
+  d.dtype = dtype;
+  d.count = total;
+  d.nvec = ceil_div(total * (long long)kElemSize[dtype], 16);
+  d.ntensors = te->nt;
+  d.stream = s;
+  d.zr.table = te->d_table;
+  d.zr.master = master;
+  d.zr.m = m;
+  d.zr.v = v;
+  d.zr.gshard = grad_shard;
+  d.zr.found_inf = found_inf;
+  d.zh.lr = args->lr;
+  d.zh.beta1 = args->beta1;
+  d.zh.beta2 = args->beta2;
+  d.zh.eps = args->eps;
+  d.zh.wd = args->weight_decay;
+  d.zh.grad_scale = args->grad_scale;
+  d.zh.clip_norm = args->clip_norm;
+  d.zh.clip_value = args->clip_value;
+  d.zh.check_finite = found_inf ? 1 : 0;
+  d.zh.use_lr_scales = scaled ? 1 : 0;
+  rc = issue(c, d);
+  if (rc != DGN_OK) return rc;
+  d.kind = kOpZeroUpdate;
   return issue(c, d);
 }
 

@@ -5,12 +5,14 @@
 // Memory model.  Every rank owns one "symmetric workspace" that all peers map
 // (CUDA IPC across processes, peer access inside one process):
 //
-//   flags   u64[max_blocks][3][kMaxRanks]  slot [b][ch][s] is written only by
+//   flags   u64[max_blocks][4][kMaxRanks]  slot [b][ch][s] is written only by
 //                                        block b of rank s, with strictly
 //                                        increasing epoch numbers (never reset);
 //                                        channel A = "data published",
 //                                        channel B = "data consumed / done",
-//                                        channel C = "gather box emptied"
+//                                        channel C = "gather box emptied",
+//                                        channel D = one-word messages of the
+//                                        sharded optimizer step (dgn_zero.cuh)
 //   stage   for parity p in {0,1}, block b, half h in {0,1}:
 //           2 * nranks slots of slot_bytes
 //           slot s < nranks   : "inbox" written by rank s (peer stores)
@@ -50,6 +52,7 @@ namespace dgn {
 
 constexpr int kMaxRanks = 8;
 constexpr int kMaxTableTensors = 1024;  // bucket entries one launch can take
+constexpr int kChannels = 4;  // flag words per (block, source rank)
 constexpr int kChanA = 0, kChanB = 1;
 #ifndef DGN_UNROLL
 #define DGN_UNROLL 4
@@ -72,7 +75,9 @@ struct BlockState {
   u64 ops;           // collectives this block took part in; low bit = parity
   u64 last_done[2];  // per parity: epoch of the last "done" signal
   u64 ll_ops;        // low-latency collectives this block took part in
-  u64 reserved[3];
+  u64 zero_part;     // sharded optimizer step: {sum of squares (fp32 bits), non-finite count} of this block
+  u64 zero_blocks;   // block 0 only: grid size of the launch that wrote zero_part
+  u64 zero_ops;      // sharded optimizer steps whose verdict this block exchanged
 };
 
 // One rank's view of the team; passed by value in the kernel parameters.
@@ -148,7 +153,7 @@ __device__ __forceinline__ void signal_peers(const PeerTable& pt, int b, int cha
   __syncthreads();
   const int t = threadIdx.x;
   if (t < pt.nranks && t != pt.rank && (only < 0 || t == only))
-    st_release_sys(pt.flags[t] + ((size_t)b * 3 + chan) * kMaxRanks + pt.rank, val);
+    st_release_sys(pt.flags[t] + ((size_t)b * kChannels + chan) * kMaxRanks + pt.rank, val);
 }
 
 // Waits until block `b` of the peers (all, only `only`, or all but `except`)
@@ -158,7 +163,7 @@ __device__ __forceinline__ bool wait_peers(const PeerTable& pt, int b, int chan,
   bool ok = true;
   const int t = threadIdx.x;
   if (t < pt.nranks && t != pt.rank && (only < 0 || t == only) && t != except) {
-    const u64* f = pt.flags[pt.rank] + ((size_t)b * 3 + chan) * kMaxRanks + t;
+    const u64* f = pt.flags[pt.rank] + ((size_t)b * kChannels + chan) * kMaxRanks + t;
     if (ld_acquire_sys(f) < target) {
       const u64 t0 = global_timer_ns();
       unsigned spins = 0;
@@ -918,14 +923,14 @@ __device__ __forceinline__ bool role_all(const Role& g, bool pred) {
 __device__ __forceinline__ void role_signal(const PeerTable& pt, const Role& g, int b, int chan, u64 val) {
   role_sync(g);
   if (g.t < pt.nranks && g.t != pt.rank)
-    st_release_sys(pt.flags[g.t] + ((size_t)b * 3 + chan) * kMaxRanks + pt.rank, val);
+    st_release_sys(pt.flags[g.t] + ((size_t)b * kChannels + chan) * kMaxRanks + pt.rank, val);
 }
 
 __device__ __forceinline__ bool role_wait(const PeerTable& pt, const Role& g, int b, int chan, u64 target,
                                           u64 wait_ns, volatile int* abort_flag) {
   bool ok = true;
   if (g.t < pt.nranks && g.t != pt.rank) {
-    const u64* f = pt.flags[pt.rank] + ((size_t)b * 3 + chan) * kMaxRanks + g.t;
+    const u64* f = pt.flags[pt.rank] + ((size_t)b * kChannels + chan) * kMaxRanks + g.t;
     if (ld_acquire_sys(f) < target) {
       const u64 t0 = global_timer_ns();
       unsigned spins = 0;

@@ -181,6 +181,57 @@ int dgn_reducescatter(dgn_comm_t comm, const void* in, void* out, int64_t count,
  * for first.  Not available on emulated communicators. */
 int dgn_allreduce_host(dgn_comm_t comm, const void* in, void* out, int64_t count, int dtype, int redop);
 
+/* ---- sharded (ZeRO-style) AdamW step --------------------------------------
+ * One call replaces the body of the reference's ZeroAdamW operator for one
+ * bucket (dragon/operators/training/zero_update_op_base.cc:103-143 with
+ * adam_op.cc:48-81): concat copies, reduce-scatter, CheckFinite + host
+ * all-reduce of the overflow flag, Cast, Scale, clip, AdamW on the fp32 master
+ * shard, all-gather, split copies.  Here it is two kernels on `stream` and no
+ * host synchronisation; gradients are read from, and parameters written to,
+ * the tensors themselves.
+ *
+ * The bucket is the element-wise concatenation of its tensors, `total`
+ * elements; rank r owns elements [r*rc, (r+1)*rc), rc = dgn_zero_shard_count
+ * = ceil(total / nranks), the reference's partition
+ * (zero_update_op_base.cc:24-31).  The fp32 state arrays of a rank (master, m,
+ * v and the gradient scratch) hold dgn_zero_state_count floats each; element i
+ * of the reference's state tensors lives at index dgn_zero_state_offset + i
+ * (the arrays are aligned with the 16-byte vectors of the flat bucket, so up
+ * to 16 / element size - 1 leading entries are padding).  All four must be
+ * 16-byte aligned device pointers; m and v start as zeros. */
+typedef struct {
+  float lr;           /* step size the kernel applies: lr * sqrt(1 - beta2^t) / (1 - beta1^t) (adam_op.cc:52) */
+  float beta1, beta2, eps;
+  float weight_decay; /* decoupled decay the kernel applies: lr * weight_decay (adam_op.cc:56); <= 0: none */
+  float grad_scale;   /* multiplies the reduced gradient (zero_update_op_base.cc:86-89); callers fold 1/nranks in */
+  float clip_norm;    /* > 0: scale this rank's gradient shard down to that L2 norm (:90-95) */
+  float clip_value;   /* > 0 and clip_norm <= 0: clamp gradients to [-clip_value, clip_value] (:96-99) */
+} dgn_adamw_args;
+
+int64_t dgn_zero_shard_count(int nranks, int64_t total);
+int64_t dgn_zero_state_count(int nranks, int64_t total, int dtype);
+int64_t dgn_zero_state_offset(int rank, int nranks, int64_t total, int dtype);
+
+/* master <- fp32 copies of this rank's shard of the parameters (InitMaster,
+ * zero_update_op_base.cc:21-44); padding entries become zero.  Local work. */
+int dgn_zero_init_master(dgn_comm_t comm, const void* const* param_ptrs, const int64_t* counts,
+                         int ntensors, int dtype, float* master, void* stream);
+
+/* One AdamW step on the bucket.  dtype is DGN_F16, DGN_BF16 or DGN_F32; at
+ * most 1024 non-empty tensors.  grad_shard is scratch of state_count floats.
+ * lr_scales (host array, one per tensor, or NULL) are the per-parameter
+ * learning-rate multipliers of the reference's `lr_scales` argument.
+ * found_inf (device-visible float, or NULL) enables the overflow check: when
+ * any rank's reduced shard holds a non-finite value, every rank adds 1 to
+ * *found_inf and leaves master, m, v and the parameters untouched
+ * (zero_update_op_base.cc:121-134); NULL skips the check, like an operator
+ * without the extra output.  Every rank must pass the same hyper-parameters
+ * and the same choice of found_inf / lr_scales. */
+int dgn_zero_adamw(dgn_comm_t comm, const void* const* grad_ptrs, void* const* param_ptrs,
+                   const int64_t* counts, int ntensors, int dtype, float* master, float* m, float* v,
+                   float* grad_shard, const float* lr_scales, const dgn_adamw_args* args,
+                   float* found_inf, void* stream);
+
 /* ALLREDUCE of `nranks` buffers that all live on the CURRENT device, without
  * allocating anything.  (No counterpart in the reference: Dragon's collectives
  * always go through a communicator that owns library-allocated buffers.)

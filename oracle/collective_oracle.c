@@ -353,3 +353,28 @@ int orc_mp_allreduce(const void* const* in, int n, int64_t count, int dtype, int
   munmap(shm, total);
   return bad ? 4 : 0;
 }
+
+/* ---- AdamW on an fp32 shard (the update of the sharded optimizer step) -------
+ * Restates the reference's CPU kernel _AdamW
+ * (dragon/kernels/training/cpu/adam_kernel.cc:36-57) and, when `lrs` is given,
+ * its variant with per-element learning-rate scales
+ * (dragon/kernels/training/cuda/adam_kernel.cu:58-80; that variant has no CPU
+ * twin in the reference).  x and y are the same array there (the fp32 master
+ * copy, zero_update_op_base.cc:139 with adam_op.cc:58-62), so one pointer is
+ * taken here.  `lr` and `wd` are what the operator passes: lr * correction and
+ * lr * weight_decay (adam_op.cc:52,56).  Built with -ffp-contract=off: every
+ * operation below rounds exactly once, fmaf is the only fused one. */
+void orc_adamw(int64_t n, float lr, float beta1, float beta2, float eps, float wd, const float* lrs,
+               const float* g, float* m, float* v, float* y) {
+  for (int64_t i = 0; i < n; ++i) {
+    const float gi = g[i];
+    const float mi = m[i] = fmaf(beta1, m[i], (1.f - beta1) * gi);
+    const float vi = v[i] = fmaf(beta2, v[i], (1.f - beta2) * gi * gi);
+    if (lrs) {
+      y[i] -= wd > 0.f ? fmaf(wd * lrs[i], y[i], lr * lrs[i] * mi / (sqrtf(vi) + eps))
+                       : lr * lrs[i] * mi / (sqrtf(vi) + eps);
+    } else {
+      y[i] -= wd > 0.f ? fmaf(wd, y[i], lr * mi / (sqrtf(vi) + eps)) : lr * mi / (sqrtf(vi) + eps);
+    }
+  }
+}

@@ -69,6 +69,8 @@ def lib():
         h.orc_f32_to_bf16.argtypes = [ctypes.c_float]
         h.orc_bf16_to_f32.restype = ctypes.c_float
         h.orc_bf16_to_f32.argtypes = [ctypes.c_uint16]
+        h.orc_adamw.restype = None
+        h.orc_adamw.argtypes = [ctypes.c_int64] + [ctypes.c_float] * 5 + [ctypes.c_void_p] * 5
         _lib = h
     return _lib
 
@@ -178,3 +180,103 @@ def max_rel_err(result, ref64, dtype):
     y = to_f64(result, dtype)
     scale = max(float(np.max(np.abs(ref64))) if ref64.size else 0.0, 1e-30)
     return float(np.max(np.abs(y - ref64))) / scale if ref64.size else 0.0
+
+
+# ---- sharded (ZeRO-style) AdamW step -----------------------------------------
+
+def from_f32(x, dtype):
+    """fp32 -> storage of `dtype`, round to nearest even (convert::To of the reference)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    if dtype == F16:
+        with np.errstate(over="ignore"):
+            return x.astype(np.float16)
+    if dtype == BF16:
+        return f32_to_bf16_bits(x)
+    return x.copy()
+
+
+def to_f32(buf, dtype):
+    a = np.ascontiguousarray(buf).view(NP_STORAGE[dtype]).reshape(-1)
+    return bf16_bits_to_f32(a) if dtype == BF16 else a.astype(np.float32)
+
+
+def adamw(g, m, v, y, lr, beta1, beta2, eps, wd, lrs=None):
+    """In-place AdamW on fp32 arrays through the C restatement (orc_adamw)."""
+    for a in (g, m, v, y):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    if lrs is not None:
+        lrs = np.ascontiguousarray(lrs, dtype=np.float32)
+    lib().orc_adamw(g.size, lr, beta1, beta2, eps, wd, lrs.ctypes.data if lrs is not None else None,
+                    g.ctypes.data, m.ctypes.data, v.ctypes.data, y.ctypes.data)
+
+
+def zero_shard_count(total, n):
+    return (total + n - 1) // n
+
+
+def zero_init_master(params_flat, n, dtype):
+    """Per-rank fp32 master shards of the flat parameters (InitMaster,
+    dragon/operators/training/zero_update_op_base.cc:21-44); entries past the
+    end of the bucket are zero."""
+    total = params_flat.size
+    rc = zero_shard_count(total, n)
+    full = np.zeros(n * rc, dtype=np.float32)
+    full[:total] = to_f32(params_flat, dtype)
+    return [full[r * rc:(r + 1) * rc].copy() for r in range(n)]
+
+
+def zero_adamw_step(grads, params, states, counts, dtype, hyper, lr_scales=None, check_finite=False):
+    """One step of the reference's ZeroAdamW operator for one bucket
+    (zero_update_op_base.cc:103-143, adam_op.cc:48-81), all ranks at once.
+
+    grads   per rank: flat gradient bucket (storage of `dtype`)
+    params  per rank: flat parameter bucket, updated in place
+    states  per rank: dict(master=, m=, v=) of rc fp32 values, updated in place
+    counts  element counts of the tensors in the bucket (for lr_scales)
+    hyper   dict(lr, beta1, beta2, eps, weight_decay, grad_scale, clip_norm, clip_value)
+            with lr / weight_decay as the kernel receives them
+    Returns 1.0 if the step was skipped because of an overflow, else 0.0.
+    The reduce-scatter sums in ascending rank order in fp32 and rounds once to
+    `dtype`, like the all-reduce of this oracle."""
+    n = len(grads)
+    total = int(sum(counts))
+    rc = zero_shard_count(total, n)
+    st = NP_STORAGE[dtype]
+    padded = []
+    for gr in grads:  # the send buffer, zero beyond the bucket (:118)
+        buf = np.zeros(n * rc, dtype=st)
+        buf[:total] = np.ascontiguousarray(gr).view(st).reshape(-1)
+        padded.append(buf)
+    recv = reducescatter(padded, dtype, "SUM")
+    if check_finite:  # CheckFinite per rank, then the host all-reduce and min(., 1) (:121-131)
+        if any(not np.all(np.isfinite(to_f32(x, dtype))) for x in recv):
+            return 1.0
+    f32 = np.float32
+    new_shards = []
+    for r in range(n):
+        lo = min(r * rc, total)
+        valid = min((r + 1) * rc, total) - lo
+        dx = to_f32(recv[r], dtype)[:valid].copy()
+        if hyper["grad_scale"] != 1.0:  # TransformGrad (:85-101)
+            dx *= f32(hyper["grad_scale"])
+        if hyper["clip_norm"] > 0:
+            norm = f32(np.sqrt(f32(np.dot(dx.astype(np.float64), dx.astype(np.float64)))))
+            if norm > f32(hyper["clip_norm"]):
+                dx *= f32(hyper["clip_norm"]) / norm
+        elif hyper["clip_value"] > 0:
+            cv = f32(hyper["clip_value"])
+            dx = np.maximum(-cv, np.minimum(dx, cv))
+        lrs = None
+        if lr_scales is not None and any(x != 1 for x in lr_scales):  # SetDenseHyper (:47-60)
+            dense = np.repeat(np.asarray(lr_scales, dtype=np.float32), np.asarray(counts, dtype=np.int64))
+            lrs = np.ascontiguousarray(dense[lo:lo + valid])
+        s = states[r]
+        m, v, y = (np.ascontiguousarray(s[k][:valid]) for k in ("m", "v", "master"))
+        adamw(np.ascontiguousarray(dx), m, v, y, hyper["lr"], hyper["beta1"], hyper["beta2"], hyper["eps"],
+              hyper["weight_decay"], lrs)
+        s["m"][:valid], s["v"][:valid], s["master"][:valid] = m, v, y
+        new_shards.append(from_f32(y, dtype))
+    flat = np.concatenate(new_shards)  # the all-gather (:141) and the split copies (:142)
+    for p in params:
+        np.ascontiguousarray(p).view(st).reshape(-1)[:total] = flat[:total]
+    return 0.0
