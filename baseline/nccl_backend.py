@@ -67,6 +67,8 @@ class NcclBackend(object):
                                            ctypes.c_void_p, ctypes.c_void_p]
         self.lib.ncclBroadcast.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int,
                                            ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+        self.lib.ncclReduceScatter.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int,
+                                               ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
         self.lib.ncclCommDestroy.argtypes = [ctypes.c_void_p]
 
     def _check(self, rc):
@@ -114,6 +116,44 @@ class NcclBackend(object):
             alpha = 1.0 / float(self.nranks)
             for t in tensors:
                 t.mul_(alpha)
+
+    def reduce_scatter_sum(self, src, dst, stream):
+        self._check(self.lib.ncclReduceScatter(src.data_ptr(), dst.data_ptr(), dst.numel(), _NCCL_DTYPE[src.dtype],
+                                               NCCL_SUM, self.comm, ctypes.c_void_p(stream)))
+
+    def operator_zero_adamw(self, grads, params, state, hyper, stream, check_finite=True):
+        """What the reference's ZeroAdamW operator enqueues for one bucket
+        (zero_update_op_base.cc:103-143): concat copies into the send half of a
+        flat buffer, ncclReduceScatter, CheckFinite with a device-to-host read
+        of the flag (the host all-reduce of the flag that follows is left out,
+        in the baseline's favour), Cast, Scale, one fused AdamW kernel on the
+        fp32 master shard, a cast of the new values, ncclAllGather, split
+        copies.  `state` holds flat (n*rc + rc elements), master, m, v, step
+        (fp32 shard tensors; step is a 1-element fp32 tensor)."""
+        rc = state["master"].numel()
+        flat = state["flat"]
+        recv, send = flat[:rc], flat[rc:]
+        if check_finite:
+            send.zero_()
+        off = 0
+        for g in grads:
+            send[off:off + g.numel()].copy_(g.view(-1), non_blocking=True)
+            off += g.numel()
+        self.reduce_scatter_sum(send, recv, stream)
+        if check_finite and not bool(torch.isfinite(recv).all().item()):
+            return False
+        dx = recv.float()
+        dx.mul_(hyper["grad_scale"])
+        torch._fused_adamw_([state["master"]], [dx], [state["m"]], [state["v"]], [], [state["step"]],
+                            lr=hyper["lr"], beta1=hyper["beta1"], beta2=hyper["beta2"],
+                            weight_decay=hyper["weight_decay"], eps=hyper["eps"], amsgrad=False, maximize=False)
+        recv.copy_(state["master"])
+        self.all_gather(recv, send, stream)
+        off = 0
+        for p in params:
+            p.view(-1).copy_(send[off:off + p.numel()], non_blocking=True)
+            off += p.numel()
+        return True
 
     def destroy(self):
         if self.comm:

@@ -41,7 +41,7 @@ def parse_args():
     ap.add_argument("--reduction", default="MEAN")
     ap.add_argument("--sweep", default="auto", choices=["auto", "off", "full"],
                     help="message-size sweep beside the headline (auto: up to 256 MiB)")
-    ap.add_argument("--configs", default="auto", choices=["auto", "off"],
+    ap.add_argument("--configs", default="auto", choices=["auto", "off", "zero"],
                     help="operator configurations (gradient buckets, gather/broadcast shapes) beside the headline")
     ap.add_argument("--no-nccl", action="store_true", help="skip the NCCL comparison in the sweep")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -427,7 +427,11 @@ def bench_multi(args):
     busbw = S / (ms * 1e-3) / 1e9 * factor
 
     sweep = run_sweep(args, comm, nccl, rank, world, dev, stream, barrier, max_over_ranks) if args.sweep != "off" else []
-    extras = run_operator_configs(comm, nccl, rank, world, dev, barrier, max_over_ranks) if args.configs != "off" else {}
+    extras = {}
+    if args.configs == "auto":
+        extras = run_operator_configs(comm, nccl, rank, world, dev, barrier, max_over_ranks)
+    if args.configs != "off":
+        extras["zero_adamw_bert_base_fp16"] = run_zero_config(comm, nccl, rank, world, dev, barrier, max_over_ranks)
 
     line = None
     if rank == 0:
@@ -550,6 +554,49 @@ def run_operator_configs(comm, nccl, rank, world, dev, barrier, max_over_ranks):
         out[label] = row
         del x, y
     return out
+
+
+def run_zero_config(comm, nccl, rank, world, dev, barrier, max_over_ranks):
+    """One sharded AdamW step over the BERT-base parameter list (199 fp16
+    tensors, one bucket, overflow check on): ours is two kernels per step
+    (dgn_zero_adamw); the baseline is the sequence the reference's ZeroAdamW
+    operator enqueues, with NCCL for its two collectives."""
+    import torch
+    from dragon_b200 import workloads
+    from dragon_b200.zero import ZeroAdamW
+    shapes = workloads.bert_base_shapes()
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    gp = torch.Generator(device=dev).manual_seed(5)
+    params = [torch.randn(workloads.numel(s), generator=gp, device=dev).to(torch.float16) for s in shapes]
+    grads = [(torch.randn(workloads.numel(s), generator=g, device=dev) * 1e-2).to(torch.float16) for s in shapes]
+    for p, gr in zip(params, grads):
+        p.grad = gr
+    total = sum(p.numel() for p in params)
+    found = torch.zeros(1, dtype=torch.float32, device=dev)
+    opt = ZeroAdamW(params[::-1], comm, lr=1e-4, weight_decay=0.01)
+
+    def timed(fn, iters=10, warm=3):
+        _, ms = time_steps(fn, iters, warm, barrier)
+        return max_over_ranks(ms) / iters
+
+    row = {"tensors": len(params), "bytes": total * 2, "shard_elements": -(-total // world),
+           "ours_us": timed(lambda: opt.step(found_inf=found)) * 1e3, "found_inf": float(found.item())}
+    if nccl is not None:
+        rc = -(-total // world)
+        state = {"flat": torch.zeros(rc * (world + 1), dtype=torch.float16, device=dev),
+                 "master": torch.zeros(rc, device=dev), "m": torch.zeros(rc, device=dev),
+                 "v": torch.zeros(rc, device=dev), "step": torch.ones(1, device=dev)}
+        hyper = {"lr": 1e-4, "beta1": 0.9, "beta2": 0.999, "eps": 1e-8, "weight_decay": 0.01,
+                 "grad_scale": 1.0 / world}
+        stream_of = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+        try:
+            row["nccl_us"] = timed(lambda: nccl.operator_zero_adamw(grads, params, state, hyper, stream_of())) * 1e3
+            row["speedup"] = row["nccl_us"] / row["ours_us"]
+        except (RuntimeError, TypeError, AttributeError) as e:  # e.g. a torch build without the fused AdamW op
+            row["nccl_error"] = str(e)[:200]
+    # Link bytes per rank and direction: (n-1)/n of the gradients out, the same of the parameters in.
+    row["ours_busbw"] = total * 2 / (row["ours_us"] * 1e-6) / 1e9 * 2.0 * (world - 1) / world
+    return row
 
 
 def time_graph(fn, ops_per_graph, replays, barrier):

@@ -167,6 +167,27 @@ def test_gather_broadcast_reducescatter_across_gpus(comms):
 
 
 @needs_two
+def test_sharded_adamw_step_across_gpus(comms):
+    """The sharded optimizer step with one rank per GPU: shard slices and the
+    updated parameters travel over NVLink; same bit-exact bar as on virtual ranks."""
+    from tests.test_zero_gpu import RAGGED, Harness, _grads
+    n = len(comms)
+    devices = ["cuda:{}".format(r) for r in range(n)]
+    for dtype in (oracle.F16, oracle.F32):
+        h = Harness(comms, RAGGED, dtype, devices=devices)
+        found = [torch.zeros(1, dtype=torch.float32, device=d) for d in devices]
+        for step in range(3):
+            assert h.step([_grads(r, step, RAGGED, dtype) for r in range(n)], found_inf=found) == 0.0
+            h.check(what="multi-GPU step {}".format(step))
+        assert all(f.item() == 0.0 for f in found)
+    # A bucket of several staging rounds: 8 Mi + 3 elements in one tensor.
+    counts = [(1 << 23) + 3]
+    h = Harness(comms, counts, oracle.BF16, devices=devices)
+    h.step([_grads(r, 0, counts, oracle.BF16) for r in range(n)])
+    h.check(what="multi-GPU large bucket")
+
+
+@needs_two
 def test_two_processes_over_ipc_and_file_rendezvous():
     with tempfile.TemporaryDirectory() as rdv:
         procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "mp_gpu_worker.py"), str(r), "2", rdv],

@@ -69,14 +69,15 @@ def _flat(tensors, dtype):
 class Harness(object):
     """n virtual ranks with their own parameters, optimizer and oracle state."""
 
-    def __init__(self, comms, counts, dtype, offset_elems=0, lr_scales=None, **opt_kwargs):
+    def __init__(self, comms, counts, dtype, offset_elems=0, lr_scales=None, devices=None, **opt_kwargs):
         from dragon_b200.zero import ZeroAdamW
         self.comms, self.counts, self.dtype, self.n = comms, counts, dtype, len(comms)
+        self.devices = devices or [DEV] * self.n  # one device per rank; virtual ranks share one
         self.offset_elems = offset_elems
         self.lr_scales = lr_scales
         total = int(sum(counts))
         p0 = oracle.from_f32(np.random.default_rng(5).normal(0, 1, total).astype(np.float32), dtype)
-        self.params = [_split(p0, counts, dtype, DEV, offset_elems) for _ in range(self.n)]
+        self.params = [_split(p0, counts, dtype, self.devices[r], offset_elems) for r in range(self.n)]
         if lr_scales is not None:
             for plist in self.params:
                 for p, s in zip(plist, lr_scales):
@@ -97,12 +98,14 @@ class Harness(object):
         """grads: per-rank flat numpy storage.  Returns the oracle's verdict."""
         self.t += 1
         for r in range(self.n):
-            pieces = _split(grads[r], self.counts, self.dtype, DEV, self.offset_elems)
+            pieces = _split(grads[r], self.counts, self.dtype, self.devices[r], self.offset_elems)
             for p, g in zip(self.params[r], pieces):
                 p.grad = g
         for r in range(self.n):
-            self.opts[r].step(found_inf=None if found_inf is None else found_inf[r])
-        torch.cuda.synchronize()
+            with torch.cuda.device(self.devices[r]):
+                self.opts[r].step(found_inf=None if found_inf is None else found_inf[r])
+        for d in set(self.devices):
+            torch.cuda.synchronize(d)
         assert all(c.status() == 0 for c in self.comms)
         a = self.opts[0].kernel_args(self.t)
         hyper = dict(lr=a.lr, beta1=a.beta1, beta2=a.beta2, eps=a.eps, weight_decay=a.weight_decay,
