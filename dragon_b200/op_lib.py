@@ -86,8 +86,10 @@ def collective_args(**kwargs):
     }
 
 
-def _def_text(op_type, in_names, out_names, device_index, args, cache_key=None):
+def _def_text(op_type, in_names, out_names, device_index, args, cache_key=None, name=None):
     lines = ["type {}".format(op_type)]
+    if name:
+        lines.append("name {}".format(name))
     lines += ["input {}".format(n) for n in in_names]
     lines += ["output {}".format(n) for n in out_names]
     lines.append("device 1 {}".format(device_index))
@@ -96,8 +98,12 @@ def _def_text(op_type, in_names, out_names, device_index, args, cache_key=None):
             continue
         if isinstance(value, str):
             lines.append("arg_s {} {}".format(key, value))
+        elif isinstance(value, (list, tuple)) and any(isinstance(v, float) for v in value):
+            lines.append("arg_floats {} {}".format(key, " ".join(repr(float(v)) for v in value)))
         elif isinstance(value, (list, tuple)):
             lines.append("arg_ints {} {}".format(key, " ".join(str(int(v)) for v in value)))
+        elif isinstance(value, float):
+            lines.append("arg_f {} {}".format(key, repr(value)))
         else:
             lines.append("arg_i {} {}".format(key, int(value)))
     if cache_key:
@@ -173,3 +179,89 @@ def run_collective(inputs, outputs=None, group_size=0, stream=None, cache_key=No
         for name in set(in_names + out_names):
             lib().dragon_workspace_remove_tensor(ws, name.encode())
     return outputs
+
+
+# ---- the ZeroAdamW operator -----------------------------------------------------------
+
+_HYPER_KEYS = ("lr", "beta1", "beta2", "eps", "weight_decay", "grad_scale", "clip_norm", "clip_value")
+
+
+def _feed_host_scalar(ws, name, value, keep):
+    """A one-element float32 host tensor (device id -1), as the optimizers of
+    the reference feed their hyper-parameters (torch/core/optim/zero.py:83-95)."""
+    import numpy as np
+    arr = np.array([value], dtype=np.float32)
+    keep.append(arr)  # must outlive the run
+    dims = (ctypes.c_int64 * 1)(1)
+    _check(lib().dragon_workspace_feed_external(ws, name.encode(), ctypes.c_void_p(arr.ctypes.data), dims, 0,
+                                                b"float32", -1, 4))
+
+
+def run_zero_adamw(grads, params, hyper, name="ZeroAdamW", bucket_name="Bucket_1", lr_scales=None,
+                   found_inf=None, stream=None, **group_args):
+    """Runs the `ZeroAdamW` operator eagerly on one bucket, the way the
+    reference's ZeroOptimizer._update_group does (torch/core/optim/zero.py:96-112):
+    gradients are the inputs, the parameters (plus `found_inf`, if given) the
+    outputs, the hyper-parameters travel as host tensors "<name>/<key>", and
+    the operator instance is cached per (name, bucket) so that its step count
+    and its state tensors "<name>/<bucket_name>/master|m|v" live on.
+
+    hyper: dict with lr, beta1, beta2, eps, weight_decay, grad_scale,
+    clip_norm, clip_value (plain values; grad_scale already divided by the
+    group size).  group_args: comm, group, backend, ranks."""
+    grads, params = list(grads), list(params)
+    if len(grads) != len(params) or not params:
+        raise ValueError("one gradient per parameter is required")
+    device = params[0].device
+    ws = get_workspace()
+    tag = next(_uid)
+    keep = []
+    for key in _HYPER_KEYS:
+        _feed_host_scalar(ws, "{}/{}".format(name, key), hyper[key], keep)
+    in_names = ["zero/{}/grad:{}".format(tag, i) for i in range(len(grads))]
+    out_names = ["zero/{}/param:{}".format(tag, i) for i in range(len(params))]
+    for n, t in zip(in_names + out_names, grads + params):
+        _feed(ws, n, t)
+    if found_inf is not None:
+        out_names.append("zero/{}/found_inf".format(tag))
+        _feed(ws, out_names[-1], found_inf)
+    scales = [float(x) for x in (lr_scales if lr_scales is not None else [1.0] * len(params))]
+    args = {
+        "bucket_name": bucket_name,
+        "lr_scales": scales,
+        "use_lr_scales": int(any(x != 1.0 for x in scales)),
+        "comm": group_args.get("comm", 0),
+        "group": group_args.get("group", 0),
+        "backend": group_args.get("backend", "MPI"),
+        "ranks": group_args.get("ranks", None),
+    }
+    cuda_stream = stream if stream is not None else torch.cuda.current_stream(device)
+    handle = cuda_stream if isinstance(cuda_stream, int) else cuda_stream.cuda_stream
+    lib().dragon_set_external_stream(device.index, ctypes.c_void_p(handle))
+    try:
+        _check(lib().dragon_workspace_run_operator(
+            ws, _def_text("ZeroAdamW", in_names, out_names, device.index, args,
+                          cache_key="{}/{}".format(name, bucket_name), name=name), 0, 0))
+    finally:
+        for n in set(in_names + out_names):
+            lib().dragon_workspace_remove_tensor(ws, n.encode())
+
+
+class _DevicePointer(object):
+    def __init__(self, ptr, count):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
+def zero_state(name, bucket_name, key, device):
+    """A copy of the operator's fp32 state tensor "<name>/<bucket_name>/<key>"
+    (master, m or v) in this thread's workspace."""
+    dims = (ctypes.c_int64 * 8)()
+    ndim, ptr = ctypes.c_int(), ctypes.c_void_p()
+    dtype = ctypes.create_string_buffer(16)
+    h = lib()
+    h.dragon_workspace_tensor_info.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_int64),
+                                               ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_char_p,
+                                               ctypes.c_int, ctypes.POINTER(ctypes.c_void_p)]
+    _check(h.dragon_workspace_tensor_info(get_workspace(), "{}/{}/{}".format(name, bucket_name, key).encode(),
+                                          dims, 8, ctypes.byref(ndim), dtype, 16, ctypes.byref(ptr)))
+    return torch.as_tensor(_DevicePointer(ptr.value, int(dims[0])), device=device).clone()

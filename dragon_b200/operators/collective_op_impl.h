@@ -102,6 +102,20 @@ class CollectiveOpImpl {
     DGN_CHECK(dgn_allgather(comm_, x, y, N, DgnTypeOf<T>::value, stream));
   }
 
+  // The sharded AdamW step of one bucket (the body of the reference's
+  // ZeroUpdateOpBase::DoRunWithType, zero_update_op_base.cc:103-143, which
+  // issues ReduceScatter and AllGather around its update kernels).
+  void ZeroInitMaster(const vector<void*>& params, const vector<int64_t>& N, int dtype, float* master, void* stream) {
+    DGN_CHECK(dgn_zero_init_master(comm_, const_cast<const void* const*>(params.data()), N.data(),
+                                   static_cast<int>(N.size()), dtype, master, stream));
+  }
+  void ZeroAdamW(const vector<const void*>& grads, const vector<void*>& params, const vector<int64_t>& N, int dtype,
+                 float* master, float* m, float* v, float* grad_shard, const float* lr_scales,
+                 const dgn_adamw_args& args, float* found_inf, void* stream) {
+    DGN_CHECK(dgn_zero_adamw(comm_, grads.data(), params.data(), N.data(), static_cast<int>(N.size()), dtype,
+                             master, m, v, grad_shard, lr_scales, &args, found_inf, stream));
+  }
+
   int comm_rank() const { return comm_rank_; }
   int comm_size() const { return comm_size_; }
   int comm_root() const { return comm_root_; }

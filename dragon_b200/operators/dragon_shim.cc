@@ -38,7 +38,7 @@ OperatorDef OperatorDef::Parse(const string& text) {
       def.output.push_back(v);
     } else if (key == "device") {
       in >> def.device_option.device_type >> def.device_option.device_id;
-    } else if (key == "arg_i" || key == "arg_s" || key == "arg_ints" || key == "arg_f") {
+    } else if (key == "arg_i" || key == "arg_s" || key == "arg_ints" || key == "arg_f" || key == "arg_floats") {
       Argument a;
       in >> a.name;
       if (key == "arg_i") {
@@ -48,6 +48,9 @@ OperatorDef OperatorDef::Parse(const string& text) {
       } else if (key == "arg_s") {
         in >> std::ws;
         std::getline(in, a.s);
+      } else if (key == "arg_floats") {
+        double v;
+        while (in >> v) a.floats.push_back(v);
       } else {
         int64_t v;
         while (in >> v) a.ints.push_back(v);
@@ -219,6 +222,7 @@ Tensor& OperatorBase::Input(int i) {
 }
 
 Tensor* OperatorBase::Output(int i) {
+  if (i < 0) i += OutputSize();  // Output(-1) is the last output, as in the reference
   CHECK(i >= 0 && i < OutputSize()) << "\nOutput index " << i << " is out of range.";
   return outputs_[i];
 }

@@ -110,14 +110,17 @@ struct OperatorDef {
 
   // Line-oriented wire form used by the C entry points (the reference ships a
   // serialised protobuf through pybind at the same place):
-  //   type Collective | input X | output Y | device 1 0 |
-  //   arg_i name 3 | arg_s name TEXT | arg_ints name 0 1 2
+  //   type Collective | name OpName | input X | output Y | device 1 0 |
+  //   arg_i name 3 | arg_f name 0.5 | arg_s name TEXT | arg_ints name 0 1 2 | arg_floats name 1 0.5
   static OperatorDef Parse(const string& text);
 };
 
 // ---- tensors ---------------------------------------------------------------------
 
 class CUDAContext;
+// Tag for host-side access, as in data<T, CPUContext>().  A tensor fed with
+// device id -1 holds host memory (the hyper tensors of the update operators).
+class CPUContext {};
 
 class Tensor {
  public:
@@ -243,6 +246,7 @@ class OperatorBase {
   int InputSize() const { return static_cast<int>(inputs_.size()); }
   int OutputSize() const { return static_cast<int>(outputs_.size()); }
   const string& type() const { return def_.type; }
+  const string& name() const { return def_.name; }
   const OperatorDef& def() const { return def_; }
   Workspace* workspace() const { return ws_; }
 
@@ -340,6 +344,7 @@ class OpSchema {
 // Numerical list; any other type is fatal and names the op.
 namespace dtypes {
 struct Numerical {};
+struct Floating {};  // float16, bfloat16, float32, float64 (dragon/core/types.h)
 }
 template <class Types> struct DispatchHelper;
 template <>
@@ -362,6 +367,22 @@ struct DispatchHelper<dtypes::Numerical> {
   }
 };
 
+template <>
+struct DispatchHelper<dtypes::Floating> {
+  template <class Op>
+  static void Call(Op* op, const Tensor& x) {
+    switch (x.dtype()) {
+      case DType::kFloat16: return op->template DoRunWithType<float16>();
+      case DType::kBFloat16: return op->template DoRunWithType<bfloat16>();
+      case DType::kFloat32: return op->template DoRunWithType<float>();
+      case DType::kFloat64: return op->template DoRunWithType<double>();
+      default:
+        DRAGON_FATAL << "Unsupported type: " << dtype_name(x.dtype()) << "\n<" << op->type()
+                     << "Op> supports the floating types only.";
+    }
+  }
+};
+
 // ---- argument access ------------------------------------------------------------------------
 
 template <> inline int64_t OperatorBase::GetArgument<int64_t>(const string& name, const int64_t& dflt) {
@@ -375,6 +396,16 @@ template <> inline string OperatorBase::GetArgument<string>(const string& name, 
 template <> inline vector<int64_t> OperatorBase::GetArgument<vector<int64_t>>(const string& name) {
   const Argument* a = FindArg(name);
   return a ? a->ints : vector<int64_t>();
+}
+template <> inline float OperatorBase::GetArgument<float>(const string& name, const float& dflt) {
+  const Argument* a = FindArg(name);
+  return a ? static_cast<float>(a->f) : dflt;
+}
+template <> inline vector<float> OperatorBase::GetArgument<vector<float>>(const string& name) {
+  const Argument* a = FindArg(name);
+  vector<float> out;
+  if (a) out.assign(a->floats.begin(), a->floats.end());
+  return out;
 }
 
 }  // namespace dragon

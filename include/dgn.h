@@ -112,7 +112,8 @@ int dgn_comm_create(int rank, int nranks, int device, const char* rendezvous_dir
  * cooperative kernel covering every virtual rank) when the last of the
  * `nranks` communicators has issued its call, so a single host thread may
  * call them one after another; calls queue per rank, so one rank may issue
- * several collectives before the others follow.  All calls of one collective
+ * several collectives before the others follow; the buffers of a queued call
+ * must stay valid until the last rank has issued it.  All calls of one collective
  * must use the same stream.  Used to exercise the multi-rank kernels where fewer GPUs
  * than ranks are available. */
 int dgn_comm_create_emulated(int nranks, int device, dgn_comm_t* comms /* [nranks] */);
