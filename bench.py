@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--configs", default="auto", choices=["auto", "off", "zero"],
                     help="operator configurations (gradient buckets, gather/broadcast shapes) beside the headline")
     ap.add_argument("--no-nccl", action="store_true", help="skip the NCCL comparison in the sweep")
+    ap.add_argument("--no-symm", action="store_true", help="N>=2: skip the symmetric-memory (in-place multicast) rows")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-emulated", action="store_true", help="N=1: skip the emulated 8-rank timings")
     ap.add_argument("--emulated-only", action="store_true",
@@ -308,6 +309,25 @@ def bench_emulated(args):
 
             per, total = time_steps(step, 10, 3)
             out[label] = {"ms_per_allreduce": total / 10, "launch": comms[0].last_launch()}
+        # The sharded AdamW step: eight fp16 tensors of 4 Mi elements per rank (64 MiB), overflow check on.
+        from dragon_b200.zero import ZeroAdamW
+        opts, found = [], []
+        for r, c in enumerate(comms):
+            g = torch.Generator(device="cuda:0").manual_seed(1000 + r)
+            params = [torch.randn(4 << 20, generator=g, device="cuda:0").to(torch.float16) for _ in range(8)]
+            for p in params:
+                p.grad = (torch.randn(4 << 20, generator=g, device="cuda:0") * 1e-2).to(torch.float16)
+            opts.append(ZeroAdamW(params, c, lr=1e-4))
+            found.append(torch.zeros(1, device="cuda:0"))
+
+        def zero_step():
+            for o, f in zip(opts, found):
+                o.step(found_inf=f)
+
+        per, total = time_steps(zero_step, 10, 3)
+        out["zero_adamw_64MiB_fp16"] = {"ms_per_step": total / 10, "launch": comms[0].last_launch(),
+                                        "found_inf": float(found[0].item())}
+        del opts
     finally:
         torch.cuda.synchronize()
         for c in comms:
@@ -359,7 +379,8 @@ def bench_multi(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    comm = Communicator.init_local(rank, world, local)
+    # 256 MiB of symmetric memory per rank for the in-place multicast rows.
+    comm = Communicator.init_local(rank, world, local, symm_bytes=0 if args.no_symm else 256 * MiB)
     handles = [None] * world
     dist.all_gather_object(handles, comm.handle_bytes())
     comm.connect(handles)
@@ -433,6 +454,14 @@ def bench_multi(args):
     if args.configs != "off":
         extras["zero_adamw_bert_base_fp16"] = run_zero_config(comm, nccl, rank, world, dev, barrier, max_over_ranks)
 
+    # Last, so that a failure here cannot cost the numbers above.
+    symmetric = None
+    if not args.no_symm:
+        try:
+            symmetric = run_symmetric(comm, rank, world, barrier, max_over_ranks)
+        except Exception as e:  # noqa: BLE001 - report, do not lose the line
+            symmetric = {"error": str(e)[:300]}
+
     line = None
     if rank == 0:
         achieved = S / (kernel_ms * 1e-3) / 1e9 * factor
@@ -466,6 +495,7 @@ def bench_multi(args):
             "sweep": sweep,
             "operator_configs": extras,
             "nvls": comm.has_nvls(),
+            "symmetric_memory": symmetric,
         }
     barrier()
     torch.cuda.synchronize()
@@ -554,6 +584,46 @@ def run_operator_configs(comm, nccl, rank, world, dev, barrier, max_over_ranks):
         out[label] = row
         del x, y
     return out
+
+
+def run_symmetric(comm, rank, world, barrier, max_over_ranks):
+    """MEAN all-reduce in place on buffers from the communicator's symmetric
+    arena (dgn_comm_symm_alloc): the switch reduces the buffers themselves,
+    nothing is staged.  Each size rotates over views that cover 256 MiB."""
+    import torch
+    if not comm.has_nvls() or comm.symm_capacity() < 256 * MiB:
+        return {"available": False}
+    factor = 2.0 * (world - 1) / world
+    rows = []
+    for dtype_name, sizes in (("f32", (1, 4, 16, 64, 128, 256)), ("f16", (64, 256))):
+        tdtype = torch_dtype_of(dtype_name)
+        esize = 2 if dtype_name == "f16" else 4
+        comm.symm_reset()
+        arena = comm.symm_empty(256 * MiB // esize, tdtype)
+        arena.copy_(make_message(rank, arena.numel(), dtype_name, arena.device))
+        for mib in sizes:
+            count = mib * MiB // esize
+            nbuf = max(1, 256 // mib)
+            views = [arena[k * count:(k + 1) * count] for k in range(nbuf)]
+            ops = [comm.prepare_all_reduce([v], [v], "MEAN") for v in views]
+            state = {"i": 0}
+
+            def step():
+                ops[state["i"] % nbuf]()
+                state["i"] += 1
+
+            iters = 40 if mib <= 64 else 10
+            _, total = time_steps(step, iters, 5, barrier)
+            t = max_over_ranks(total) / iters
+            busbw = mib * MiB / (t * 1e-3) / 1e9 * factor
+            rows.append({"dtype": dtype_name, "bytes": mib * MiB, "us": t * 1e3, "busbw": busbw,
+                         "frac_of_900": busbw / NVLINK_NOMINAL_GBS, "variant": comm.last_launch()["variant"],
+                         "launch": comm.last_launch()})
+            del ops, views
+        del arena
+    comm.symm_reset()
+    return {"available": True, "rows": rows,
+            "note": "buffers allocated with dgn_comm_symm_alloc (same offset on every rank), reduced in place"}
 
 
 def run_zero_config(comm, nccl, rank, world, dev, barrier, max_over_ranks):

@@ -17,7 +17,7 @@ OK, ERR_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_PEER, ERR_STATE, ERR_UNSUPPORTED = range
 
 U8, I8, I32, I64, F16, BF16, F32, F64 = range(8)
 SUM, MEAN, PROD, MIN, MAX = range(5)
-VARIANT_AUTO, VARIANT_ONESHOT, VARIANT_TWOSHOT, VARIANT_NVLS, VARIANT_LL, VARIANT_LL2 = range(6)
+VARIANT_AUTO, VARIANT_ONESHOT, VARIANT_TWOSHOT, VARIANT_NVLS, VARIANT_LL, VARIANT_LL2, VARIANT_SYMM = range(7)
 
 REDOPS = {"SUM": SUM, "MEAN": MEAN, "PROD": PROD, "MIN": MIN, "MAX": MAX}
 
@@ -72,6 +72,10 @@ class AdamWArgs(ctypes.Structure):
 
 
 SIGNATURES.update({
+    "dgn_comm_init_symmetric": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, _c_void_pp]),
+    "dgn_comm_symm_capacity": (ctypes.c_int64, [ctypes.c_void_p]),
+    "dgn_comm_symm_alloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, _c_void_pp]),
+    "dgn_comm_symm_reset": (ctypes.c_int, [ctypes.c_void_p]),
     "dgn_zero_shard_count": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64]),
     "dgn_zero_state_count": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int]),
     "dgn_zero_state_offset": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int]),

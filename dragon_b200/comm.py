@@ -54,6 +54,13 @@ def _check_tensor(t, device):
         raise ValueError("tensor must be contiguous")
 
 
+class _RawDeviceBytes(object):
+    """Device memory owned by the library, exposed to torch without a copy."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
 class PreparedAllReduce(object):
     """An all-reduce over a fixed tensor list with its argument arrays built once."""
 
@@ -98,10 +105,15 @@ class Communicator(object):
 
     # -- construction ------------------------------------------------------
     @classmethod
-    def init_local(cls, rank, nranks, device):
-        """Step 1 of the handle-exchange bootstrap."""
+    def init_local(cls, rank, nranks, device, symm_bytes=None):
+        """Step 1 of the handle-exchange bootstrap.  `symm_bytes` asks for a
+        symmetric arena of that size (see symm_empty); every rank must ask for
+        the same."""
         h = ctypes.c_void_p()
-        _C.check(_C.lib().dgn_comm_init_local(rank, nranks, device, ctypes.byref(h)))
+        if symm_bytes is None:
+            _C.check(_C.lib().dgn_comm_init_local(rank, nranks, device, ctypes.byref(h)))
+        else:
+            _C.check(_C.lib().dgn_comm_init_symmetric(rank, nranks, device, int(symm_bytes), ctypes.byref(h)))
         return cls(h.value)
 
     def handle_bytes(self):
@@ -144,6 +156,26 @@ class Communicator(object):
     def has_nvls(self):
         """True if the NVSwitch multicast variant was set up for this communicator."""
         return bool(_C.lib().dgn_comm_has_nvls(self._h))
+
+    # -- symmetric memory --------------------------------------------------------
+    def symm_capacity(self):
+        """Bytes of the symmetric arena (0 without NVSwitch multicast)."""
+        return int(_C.lib().dgn_comm_symm_capacity(self._h))
+
+    def symm_empty(self, numel, dtype):
+        """A tensor of `numel` elements in the symmetric arena.  Every rank must
+        make the same sequence of symm_empty calls.  An in-place all-reduce on
+        it (a whole number of 16-byte vectors) is done by the switch on the
+        buffers themselves.  The memory belongs to the communicator."""
+        nbytes = int(numel) * torch.empty((), dtype=dtype).element_size()
+        p = ctypes.c_void_p()
+        _C.check(_C.lib().dgn_comm_symm_alloc(self._h, nbytes, ctypes.byref(p)))
+        holder = _RawDeviceBytes(p.value, max(nbytes, 1))
+        flat = torch.as_tensor(holder, device=torch.device("cuda", self.device))
+        return flat[:nbytes].view(dtype)
+
+    def symm_reset(self):
+        _C.check(_C.lib().dgn_comm_symm_reset(self._h))
 
     def set_wait_limit_ms(self, ms):
         _C.check(_C.lib().dgn_comm_set_wait_limit_ms(self._h, int(ms)))

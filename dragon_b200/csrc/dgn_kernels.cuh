@@ -1285,6 +1285,57 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_nvls_kernel(const __grid_co
 }
 
 // ---------------------------------------------------------------------------
+// ALLREDUCE through NVSwitch multicast, in place on a buffer that itself lives
+// in the multicast-bound memory of the communicator (dgn_comm_symm_alloc; the
+// same offset on every rank).  Nothing is staged: after one flag exchange
+// ("every rank's input is complete") each rank reduces its own shard with
+// multimem.ld_reduce straight from all ranks' buffers, scales, and writes the
+// result into all ranks' buffers with multimem.st; a second flag exchange
+// ("every rank's stores have been issued and published") ends the kernel, so
+// when it has finished on a rank that rank's buffer is complete and no peer
+// touches it any more.  A rank sends and receives about S(1 + 1/n) bytes.
+// Only the owner of a shard reads or writes that shard, so working in place
+// is safe.  Epochs: ready = base+1 on channel A, done = base+2 on channel B.
+
+template <typename T>
+__global__ void __launch_bounds__(kMaxThreads, 1) ar_nvls_inplace_kernel(const __grid_constant__ OpParams P) {
+  const PeerTable& pt = P.peers[blockIdx.y];
+  const RankArgs& ra = P.ra[blockIdx.y];
+  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
+  Turn turn;
+  if (!begin_collective(pt, b, P, &turn)) return;
+  signal_peers(pt, b, kChanA, turn.base + 1);
+  if (!wait_peers(pt, b, kChanA, turn.base + 1, P.wait_ns)) return;
+
+  const long long vs = (P.nvec + n - 1) / n;
+  const long long lo = (long long)r * vs;
+  const long long len = clampll(P.nvec - lo, 0, vs);
+  char* mc = pt.nvls_mc + (static_cast<char*>(ra.out) - pt.nvls_uc) + lo * 16;
+  const bool mean = P.redop == kMean;
+  constexpr int U = 8;  // a multimem.ld_reduce is a round trip through the switch: keep eight in flight
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long v0 = (long long)b * blockDim.x + threadIdx.x; v0 < len; v0 += U * step) {
+    uint4 x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * step;
+      if (v < len) x[u] = Multimem<T>::ld_reduce(mc + v * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * step;
+      if (v < len) {
+        uint4 y = x[u];
+        if (mean) y = reduce_vectors<T, kSum, 1>(&y, 1, true, P.scale);
+        Multimem<T>::st(mc + v * 16, y);
+      }
+    }
+  }
+  end_collective(pt, b, turn, turn.base + 2);  // barrier, then the release store of "done"
+  wait_peers(pt, b, kChanB, turn.base + 2, P.wait_ns);
+}
+
+// ---------------------------------------------------------------------------
 // ALLGATHER (bytes).  Per round: copy my slice to my outbox and to my own
 // block of the output, signal (A), then pull every peer's outbox into its
 // block of my output and signal (B) that the outbox may be overwritten.

@@ -74,7 +74,8 @@ typedef enum {
   DGN_VARIANT_TWOSHOT = 2, /* reduce-scatter by peer stores + all-gather by peer loads */
   DGN_VARIANT_NVLS = 3,    /* NVSwitch multicast (multimem) where the box exposes it */
   DGN_VARIANT_LL = 4,      /* one-shot with flag-in-data lines, no barrier (small messages) */
-  DGN_VARIANT_LL2 = 5      /* two-shot with flag-in-data lines (medium messages) */
+  DGN_VARIANT_LL2 = 5,     /* two-shot with flag-in-data lines (medium messages) */
+  DGN_VARIANT_SYMM = 6     /* NVSwitch multicast in place, on a buffer from dgn_comm_symm_alloc */
 } dgn_variant;
 
 /* ---- library ----------------------------------------------------------- */
@@ -100,6 +101,27 @@ const char* dgn_status_string(int status);
 int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm);
 int dgn_comm_get_handle(dgn_comm_t comm, void* handle /* DGN_HANDLE_BYTES */);
 int dgn_comm_connect(dgn_comm_t comm, const void* all_handles /* nranks * DGN_HANDLE_BYTES */);
+
+/* Symmetric memory.  dgn_comm_init_symmetric is dgn_comm_init_local with an
+ * arena of `symm_bytes` (environment DGN_SYMM_BYTES for the other bootstrap
+ * calls) inside the memory that is bound to the communicator's NVSwitch
+ * multicast object.  After dgn_comm_connect, dgn_comm_symm_alloc hands out
+ * 256-byte aligned pieces of it; every rank must make the same sequence of
+ * allocations, so that a buffer sits at the same offset on every rank.  An
+ * all-reduce (SUM / MEAN; float32, float16, bfloat16) that runs in place on
+ * such a buffer, over a whole number of 16-byte vectors, is done by the switch
+ * on the buffers themselves -- nothing is staged and each rank moves about
+ * S(1 + 1/n) bytes per direction instead of 2S(n-1)/n.  This is what NCCL
+ * offers through ncclMemAlloc + buffer registration; Dragon would place its
+ * "BufferShared" bucket tensor (collective_op.cc:19-21) there.  The arena
+ * lives as long as the communicator; dgn_comm_symm_reset forgets all
+ * allocations (the caller makes sure nothing uses them any more).  Where the
+ * box exposes no multicast the capacity is 0 and dgn_comm_symm_alloc returns
+ * DGN_ERR_UNSUPPORTED; ordinary device memory always works. */
+int dgn_comm_init_symmetric(int rank, int nranks, int device, int64_t symm_bytes, dgn_comm_t* comm);
+int64_t dgn_comm_symm_capacity(dgn_comm_t comm);
+int dgn_comm_symm_alloc(dgn_comm_t comm, int64_t bytes, void** ptr);
+int dgn_comm_symm_reset(dgn_comm_t comm);
 
 /* Convenience bootstrap without any external channel: ranks meet through
  * files in `rendezvous_dir` (a directory all ranks of this node can write),

@@ -29,7 +29,7 @@ needs_two = pytest.mark.skipif(gpu_count() < 2, reason="needs at least two GPUs"
 def comms(dgn_lib):
     from dragon_b200.comm import Communicator
     n = min(gpu_count(), 8)
-    made = [Communicator.init_local(r, n, r) for r in range(n)]
+    made = [Communicator.init_local(r, n, r, symm_bytes=64 << 20) for r in range(n)]
     handles = [c.handle_bytes() for c in made]
     for c in made:
         c.connect(handles)
@@ -101,6 +101,86 @@ def test_nvls_allreduce_across_gpus(comms):
     finally:
         for c in comms:
             c.set_tuning()
+
+
+@needs_two
+def test_symmetric_memory_allreduce_in_place_across_gpus(comms):
+    """Buffers from the symmetric arena are reduced in place by the switch.
+    With two ranks a + b has one possible order, so float32 results equal the
+    oracle bit for bit (for the 16-bit types the switch's final rounding is its
+    own); otherwise the tolerance contract applies, and all ranks must always
+    hold identical bits."""
+    n = len(comms)
+    if not comms[0].has_nvls() or comms[0].symm_capacity() == 0:
+        pytest.skip("NVSwitch multicast is not available on this box")
+    assert all(c.symm_capacity() == 64 << 20 for c in comms)
+    torch_dtype = {oracle.F32: torch.float32, oracle.F16: torch.float16, oracle.BF16: torch.bfloat16}
+    cases = ((oracle.F32, "MEAN", 1 << 20), (oracle.F16, "MEAN", (1 << 21) + 8), (oracle.BF16, "SUM", 1 << 19),
+             (oracle.F32, "SUM", 4), (oracle.F32, "MEAN", (1 << 22) + 4))
+    try:
+        for dtype, redop, count in cases:
+            for c in comms:
+                c.symm_reset()
+                c.set_tuning(variant=6)
+            arrays = [H.make_input(r, count, dtype) for r in range(n)]
+            xs = []
+            for r in range(n):
+                with torch.cuda.device(r):
+                    pad = comms[r].symm_empty(100, torch.uint8)  # buffers need not start the arena
+                    x = comms[r].symm_empty(count, torch_dtype[dtype])
+                    x.copy_(H.to_torch(arrays[r], dtype, "cuda:{}".format(r)))
+                    xs.append(x)
+                    del pad
+            for rep in range(2):
+                for r in range(n):
+                    with torch.cuda.device(r):
+                        comms[r].all_reduce([xs[r]], None, redop)
+                sync_all(n)
+                assert comms[0].last_launch()["variant"] == 6
+                got0 = H.to_numpy(xs[0], dtype)
+                for r in range(n):
+                    assert comms[r].status() == 0
+                    H.assert_bits_equal(H.to_numpy(xs[r], dtype), got0, "rank {} differs from rank 0".format(r))
+                if rep == 0:
+                    ref = oracle.fp64_sum(arrays, dtype, mean=(redop == "MEAN"))
+                    assert oracle.max_rel_err(got0, ref, dtype) <= oracle.TOLERANCE[dtype]
+                    if n == 2 and dtype == oracle.F32:
+                        H.assert_bits_equal(got0, oracle.allreduce(arrays, dtype, redop), "two ranks: one order")
+        # Automatic choice: in place through the switch from 4 MiB on, the usual
+        # kernels below; a ragged tail (not a whole number of vectors) and an
+        # out-of-place call never take the in-place path.
+        for c in comms:
+            c.symm_reset()
+            c.set_tuning()
+        for count, want_symm in ((1 << 20, True), (1 << 10, False), ((1 << 20) + 1, False)):
+            arrays = [H.make_input(r, count, oracle.F32) for r in range(n)]
+            xs = []
+            for r in range(n):
+                with torch.cuda.device(r):
+                    comms[r].symm_reset()
+                    x = comms[r].symm_empty(count, torch.float32)
+                    x.copy_(H.to_torch(arrays[r], oracle.F32, "cuda:{}".format(r)))
+                    xs.append(x)
+            for r in range(n):
+                with torch.cuda.device(r):
+                    comms[r].all_reduce([xs[r]], None, "SUM")
+            sync_all(n)
+            assert (comms[0].last_launch()["variant"] == 6) == want_symm
+            ref = oracle.fp64_sum(arrays, oracle.F32)
+            for r in range(n):
+                assert oracle.max_rel_err(H.to_numpy(xs[r], oracle.F32), ref, oracle.F32) <= 1e-6
+        outs = [torch.empty(1 << 20, device="cuda:{}".format(r)) for r in range(n)]
+        for r in range(n):
+            with torch.cuda.device(r):
+                comms[r].all_reduce([xs[r][:1 << 20]], [outs[r]], "SUM")
+        sync_all(n)
+        assert comms[0].last_launch()["variant"] != 6
+        with pytest.raises(Exception, match="exhausted"):
+            comms[0].symm_empty(65 << 20, torch.uint8)
+    finally:
+        for c in comms:
+            c.set_tuning()
+            c.symm_reset()
 
 
 @needs_two
