@@ -254,6 +254,10 @@ struct dgn_comm {
   // dgn_comm_symm_alloc; buffers in it can be reduced in place by the switch.
   size_t symm_bytes = 0, symm_off = 0, symm_used = 0;
   long long symm_min_bytes = 0;
+  // Pipelined multicast all-reduce for ordinary tensors: smallest message,
+  // chunk size and number of blocks that drive the switch.
+  long long pipe_min_bytes = 0, pipe_chunk_bytes = 0;
+  int pipe_switch_blocks = 32;
 };
 
 namespace {
@@ -276,7 +280,7 @@ const void* reduce_fn(int dtype, int kind, bool table);
 int preload_kernels() {
   cudaFuncAttributes attr;
   for (int dtype = 0; dtype < 8; ++dtype) {
-    for (int kind = 0; kind <= 7; ++kind) {
+    for (int kind = 0; kind <= 8; ++kind) {
       for (int table = 0; table < 2; ++table) {
         const void* fn = reduce_fn(dtype, kind, table != 0);
         if (fn) DGN_CUDA(cudaFuncGetAttributes(&attr, fn));
@@ -444,6 +448,34 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
         p.blocks = (int)b;
         p.cv = (int)(ceil_div(vs, b) > 0x7fffffff ? 0x7fffffff : ceil_div(vs, b));
         p.rounds = 1;
+        return p;
+      }
+    }
+    {
+      // Pipelined over launches: chunks through three staging buffers.
+      bool pipe = bytes >= c->pipe_min_bytes && c->tune_variant == DGN_VARIANT_AUTO;
+      if (c->tune_variant == DGN_VARIANT_NVLS_PIPE) pipe = true;
+      const long long zone = (long long)(c->symm_off ? c->symm_off : c->nvls_bytes);  // staging before the arena
+      if (pipe && zone >= 3 * 4096) {
+        long long chunk = c->pipe_chunk_bytes;
+        if (c->tune_chunk >= 4096) chunk = c->tune_chunk;
+        if (chunk <= 0) {
+          // Two chunks up to 128 MiB, then 64 MiB pieces: per launch the flag
+          // exchange costs about 10 us, the switch moves a MiB in about 2 us.
+          chunk = bytes <= (128ll << 20) ? ceil_div(bytes, 2) : (64ll << 20);
+        }
+        if (chunk > zone / 3) chunk = zone / 3;
+        long long cvq = ceil_div(chunk, 16 * (long long)n) * n;  // whole vectors, equal shards
+        if (cvq * 16 > zone / 3) cvq = (zone / 3) / (16 * (long long)n) * n;
+        if (cvq < n) cvq = n;
+        p.variant = DGN_VARIANT_NVLS_PIPE;
+        p.threads = 256;
+        int nsw = c->tune_blocks > 0 ? c->tune_blocks : c->pipe_switch_blocks;
+        if (nsw > c->geo.max_blocks) nsw = c->geo.max_blocks;
+        if (nsw < 1) nsw = 1;
+        p.blocks = nsw;                      // blocks that drive the switch; copy blocks are added at launch
+        p.cv = (int)(cvq > 0x7fffffff ? 0x7fffffff : cvq);
+        p.rounds = (int)ceil_div(d.nvec, cvq);  // chunks
         return p;
       }
     }
@@ -615,7 +647,7 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
   const bool table = d.ntensors > 1;
   switch (d.kind) {
     case kOpAllReduce:
-      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_SYMM ? 7 : p.variant == DGN_VARIANT_NVLS ? 6 : p.variant == DGN_VARIANT_LL2 ? 5 : p.variant == DGN_VARIANT_LL ? 3 : (p.variant == DGN_VARIANT_ONESHOT ? 0 : (p.threads >= 96 && p.rounds >= 3 && !c->fused_twoshot ? 4 : 1)), table);
+      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_NVLS_PIPE ? 8 : p.variant == DGN_VARIANT_SYMM ? 7 : p.variant == DGN_VARIANT_NVLS ? 6 : p.variant == DGN_VARIANT_LL2 ? 5 : p.variant == DGN_VARIANT_LL ? 3 : (p.variant == DGN_VARIANT_ONESHOT ? 0 : (p.threads >= 96 && p.rounds >= 3 && !c->fused_twoshot ? 4 : 1)), table);
       k.smem = table ? table_smem_bytes(d.ntensors) : 0;
       break;
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
@@ -699,7 +731,24 @@ int issue(dgn_comm* c, const OpDesc& d) {
     KernelChoice k = choose_kernel(c, d, p);
     if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
     int rc;
-    if (is_zero_kind(d.kind)) {
+    if (d.kind == kOpAllReduce && p.variant == DGN_VARIANT_NVLS_PIPE) {
+      // K chunks take K + 2 launches: copy in / switch / copy out, one chunk apart.
+      OpParams P;
+      fill_params(&P, c, d, p);
+      P.peers[0] = c->table;
+      P.ra[0].in = d.in;
+      P.ra[0].out = d.out;
+      P.ra[0].table = d.table;
+      P.pipe_cv = p.cv;
+      P.pipe_chunks = p.rounds;
+      P.pipe_switch_blocks = p.blocks;
+      const int grid = p.blocks + c->num_sms * 3;
+      rc = DGN_OK;
+      for (int s = 0; s < p.rounds + 2 && rc == DGN_OK; ++s) {
+        P.pipe_step = s;
+        rc = launch(k.fn, dim3(grid, 1), p.threads, k.smem, d.stream, &P, false);
+      }
+    } else if (is_zero_kind(d.kind)) {
       ZeroParams Z;
       fill_zero_params(&Z, c, d, p);
       Z.base.peers[0] = c->table;
@@ -1136,6 +1185,11 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
     // 25 us at 1 MiB and 33 us at 4 MiB, where the low-latency kernels take
     // 15-20 us and about 30 us.
     c->symm_min_bytes = env_ll("DGN_SYMM_MIN_BYTES", 4ll << 20);
+    // Opt-in until it has been measured beside the other large-message kernels
+    // at every rank count.
+    c->pipe_min_bytes = env_ll("DGN_NVLS_PIPE_MIN_BYTES", 1ll << 62);
+    c->pipe_chunk_bytes = env_ll("DGN_NVLS_PIPE_CHUNK_BYTES", 0);
+    c->pipe_switch_blocks = (int)env_ll("DGN_NVLS_PIPE_SWITCH_BLOCKS", 32);
     c->nvls_capable = nvls_device_supported(device);
     if (c->nvls_capable && rank == 0) {
       // Rank 0 owns the multicast object and the rendezvous socket.
@@ -1389,9 +1443,9 @@ int dgn_comm_set_wait_limit_ms(dgn_comm_t c, int ms) {
 
 int dgn_comm_set_tuning(dgn_comm_t c, int variant, int blocks, int threads, int64_t chunk_bytes) {
   if (!c) return fail(DGN_ERR_ARG, "null communicator");
-  if (variant < 0 || variant > DGN_VARIANT_SYMM || blocks < 0 || threads < 0 || chunk_bytes < 0)
+  if (variant < 0 || variant > DGN_VARIANT_NVLS_PIPE || blocks < 0 || threads < 0 || chunk_bytes < 0)
     return fail(DGN_ERR_ARG, "bad tuning value");
-  if ((variant == DGN_VARIANT_NVLS || variant == DGN_VARIANT_SYMM) && !c->nvls)
+  if ((variant == DGN_VARIANT_NVLS || variant == DGN_VARIANT_SYMM || variant == DGN_VARIANT_NVLS_PIPE) && !c->nvls)
     return fail(DGN_ERR_UNSUPPORTED, "the NVLS variants are not set up on this communicator");
   c->tune_variant = variant;
   c->tune_blocks = blocks;

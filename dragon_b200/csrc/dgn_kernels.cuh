@@ -128,6 +128,11 @@ struct OpParams {
   int redop;
   int root;
   int warps_a, warps_b;        // warp split of the multicast kernel (0: default)
+  // pipelined multicast all-reduce (ar_nvls_pipe_kernel): one launch per step
+  long long pipe_cv;           // vectors per chunk
+  int pipe_step, pipe_chunks;  // this launch's step; chunks of the message
+  int pipe_switch_blocks;      // blocks [0, this) drive the switch, the rest copy
+  int reserved3;
 };
 
 // ---------------------------------------------------------------------------
@@ -1333,6 +1338,102 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_nvls_inplace_kernel(const _
   }
   end_collective(pt, b, turn, turn.base + 2);  // barrier, then the release store of "done"
   wait_peers(pt, b, kChanB, turn.base + 2, P.wait_ns);
+}
+
+// ---------------------------------------------------------------------------
+// ALLREDUCE through NVSwitch multicast for ordinary tensors, pipelined over
+// launches.  The message is cut into chunks; three chunk buffers live in the
+// multicast-bound staging memory.  Launch number s of a message runs, side by
+// side in one grid,
+//   copy blocks   : chunk s   from the input tensors into buffer s % 3, and
+//                   chunk s-2 from buffer (s-2) % 3 into the output tensors
+//                   (local HBM traffic, no peer involved);
+//   switch blocks : chunk s-1, in place in buffer (s-1) % 3, exactly as
+//                   ar_nvls_inplace_kernel does (ready / done flag exchange
+//                   around multimem.ld_reduce + multimem.st of the own shard).
+// The kernel boundary orders the stages of one chunk on this rank; a peer's
+// "ready" flag of launch s is sent after its launch s-1 has finished, i.e.
+// after its copy of chunk s-1 is complete; this rank's launch s ends only after
+// every peer's "done", i.e. after nobody reads or writes buffer (s-1) % 3 any
+// more.  With K chunks a message takes K + 2 launches, and in the steady state
+// the link (switch blocks) and local HBM (copy blocks) work at the same time.
+
+template <typename T, bool TABLE>
+__global__ void __launch_bounds__(256, 3) ar_nvls_pipe_kernel(const __grid_constant__ OpParams P) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  constexpr int ES = (int)sizeof(T);
+  const PeerTable& pt = P.peers[0];
+  const RankArgs& ra = P.ra[0];
+  const int r = pt.rank, n = pt.nranks;
+  const int s = P.pipe_step, K = P.pipe_chunks, nsw = P.pipe_switch_blocks;
+  const long long CV = P.pipe_cv;
+  if ((int)blockIdx.x < nsw) {
+    const int j = s - 1, b = blockIdx.x;
+    if (j < 0 || j >= K) return;
+    Turn turn;
+    if (!begin_collective(pt, b, P, &turn)) return;
+    signal_peers(pt, b, kChanA, turn.base + 1);
+    if (!wait_peers(pt, b, kChanA, turn.base + 1, P.wait_ns)) return;
+    const long long clen = clampll(P.nvec - (long long)j * CV, 0, CV);
+    const long long vs = (clen + n - 1) / n;
+    const long long lo = (long long)r * vs;
+    const long long len = clampll(clen - lo, 0, vs);
+    char* mc = pt.nvls_mc + (long long)(j % 3) * CV * 16 + lo * 16;
+    const bool mean = P.redop == kMean;
+    constexpr int U = 4;
+    const long long step = (long long)nsw * blockDim.x;
+    for (long long v0 = (long long)b * blockDim.x + threadIdx.x; v0 < len; v0 += U * step) {
+      uint4 x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * step;
+        if (v < len) x[u] = Multimem<T>::ld_reduce(mc + v * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * step;
+        if (v < len) {
+          uint4 y = x[u];
+          if (mean) y = reduce_vectors<T, kSum, 1>(&y, 1, true, P.scale);
+          Multimem<T>::st(mc + v * 16, y);
+        }
+      }
+    }
+    end_collective(pt, b, turn, turn.base + 2);
+    wait_peers(pt, b, kChanB, turn.base + 2, P.wait_ns);
+    return;
+  }
+  // copy blocks
+  const Message<ES, TABLE> msg = make_message<ES, TABLE>(P, ra, smem);
+  const long long cstep = (long long)(gridDim.x - nsw) * blockDim.x;
+  const long long first = (long long)(blockIdx.x - nsw) * blockDim.x + threadIdx.x;
+  if (s < K) {  // chunk s: tensors -> buffer
+    const long long clen = clampll(P.nvec - (long long)s * CV, 0, CV);
+    char* dst = pt.nvls_uc + (long long)(s % 3) * CV * 16;
+    const long long base = (long long)s * CV;
+    long long v = first;
+    for (; v + 3 * cstep < clen; v += 4 * cstep) {
+      const uint4 a = msg.load(base + v), b2 = msg.load(base + v + cstep), c = msg.load(base + v + 2 * cstep),
+                  d = msg.load(base + v + 3 * cstep);
+      stv(dst + v * 16, a); stv(dst + (v + cstep) * 16, b2); stv(dst + (v + 2 * cstep) * 16, c);
+      stv(dst + (v + 3 * cstep) * 16, d);
+    }
+    for (; v < clen; v += cstep) stv(dst + v * 16, msg.load(base + v));
+  }
+  if (s >= 2 && s - 2 < K) {  // chunk s-2: buffer -> tensors
+    const int j = s - 2;
+    const long long clen = clampll(P.nvec - (long long)j * CV, 0, CV);
+    const char* src = pt.nvls_uc + (long long)(j % 3) * CV * 16;
+    const long long base = (long long)j * CV;
+    long long v = first;
+    for (; v + 3 * cstep < clen; v += 4 * cstep) {
+      const uint4 a = ldv(src + v * 16), b2 = ldv(src + (v + cstep) * 16), c = ldv(src + (v + 2 * cstep) * 16),
+                  d = ldv(src + (v + 3 * cstep) * 16);
+      msg.store(base + v, a); msg.store(base + v + cstep, b2); msg.store(base + v + 2 * cstep, c);
+      msg.store(base + v + 3 * cstep, d);
+    }
+    for (; v < clen; v += cstep) msg.store(base + v, ldv(src + v * 16));
+  }
 }
 
 // ---------------------------------------------------------------------------

@@ -34,7 +34,7 @@ typedef double InstT;
 // kind: 0 one-shot, 1 two-shot (lock-step), 2 reduce-scatter, 3 low-latency one-shot,
 //       4 two-shot (warp-specialised), 5 low-latency two-shot,
 //       6 NVSwitch multicast (float, half and bfloat16 only), 7 the same in place
-//       on symmetric memory
+//       on symmetric memory, 8 the same pipelined over launches for ordinary tensors
 const void* DGN_CAT(reduce_kernel_fn_, DGN_INST)(int kind, bool table) {
   switch (kind) {
     case 0:
@@ -54,6 +54,9 @@ const void* DGN_CAT(reduce_kernel_fn_, DGN_INST)(int kind, bool table) {
                    : (const void*)ar_nvls_kernel<InstT, false>;
     case 7:
       return table ? nullptr : (const void*)ar_nvls_inplace_kernel<InstT>;
+    case 8:
+      return table ? (const void*)ar_nvls_pipe_kernel<InstT, true>
+                   : (const void*)ar_nvls_pipe_kernel<InstT, false>;
 #endif
     case 5:
       return table ? (const void*)ar_twoshot_ll_kernel<InstT, true>

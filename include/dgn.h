@@ -7,7 +7,8 @@
  * dgn_status; nothing aborts and nothing throws.  Device pointers are ordinary
  * CUDA device pointers valid on the communicator's device, `stream` is a
  * cudaStream_t passed as void*.  All collectives are asynchronous with respect
- * to the host: they enqueue exactly one kernel on `stream` and return.
+ * to the host: they enqueue their kernel on `stream` (one launch; a few for
+ * the pipelined multicast variant and the sharded optimizer step) and return.
  *
  * Reference interfaces replaced (paths relative to the Dragon source tree):
  *   dragon/operators/distributed/collective_op_impl_mpi.cc:50-85   (MPI_Bcast /
@@ -75,7 +76,8 @@ typedef enum {
   DGN_VARIANT_NVLS = 3,    /* NVSwitch multicast (multimem) where the box exposes it */
   DGN_VARIANT_LL = 4,      /* one-shot with flag-in-data lines, no barrier (small messages) */
   DGN_VARIANT_LL2 = 5,     /* two-shot with flag-in-data lines (medium messages) */
-  DGN_VARIANT_SYMM = 6     /* NVSwitch multicast in place, on a buffer from dgn_comm_symm_alloc */
+  DGN_VARIANT_SYMM = 6,    /* NVSwitch multicast in place, on a buffer from dgn_comm_symm_alloc */
+  DGN_VARIANT_NVLS_PIPE = 7 /* NVSwitch multicast for any tensors, chunks pipelined over several launches */
 } dgn_variant;
 
 /* ---- library ----------------------------------------------------------- */

@@ -184,6 +184,60 @@ def test_symmetric_memory_allreduce_in_place_across_gpus(comms):
 
 
 @needs_two
+def test_pipelined_multicast_allreduce_across_gpus(comms):
+    """The multicast variant for ordinary tensors, pipelined over launches:
+    single chunk, many chunks, ragged sizes, a tensor list, out of place."""
+    n = len(comms)
+    if not comms[0].has_nvls():
+        pytest.skip("NVSwitch multicast is not available on this box")
+    cases = ((oracle.F32, "MEAN", 5, 0), (oracle.F32, "SUM", (1 << 20) + 3, 0), (oracle.F16, "MEAN", 1 << 24, 4 << 20),
+             (oracle.BF16, "SUM", (1 << 22) + 1, 1 << 20), (oracle.F32, "MEAN", 1 << 22, 1 << 20))
+    try:
+        for dtype, redop, count, chunk in cases:
+            for c in comms:
+                c.set_tuning(variant=7, chunk_bytes=chunk)
+            arrays = [H.make_input(r, count, dtype) for r in range(n)]
+            xs = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
+            outs = [torch.empty_like(x) for x in xs]
+            for r in range(n):
+                with torch.cuda.device(r):
+                    comms[r].all_reduce([xs[r]], [outs[r]], redop)   # out of place
+                    comms[r].all_reduce([xs[r]], None, redop)        # in place, back to back
+            sync_all(n)
+            launch = comms[0].last_launch()
+            assert launch["variant"] == 7
+            if chunk:
+                assert launch["rounds"] >= 4
+            ref = oracle.fp64_sum(arrays, dtype, mean=(redop == "MEAN"))
+            got0 = H.to_numpy(outs[0], dtype)
+            assert oracle.max_rel_err(got0, ref, dtype) <= oracle.TOLERANCE[dtype]
+            for r in range(n):
+                assert comms[r].status() == 0
+                H.assert_bits_equal(H.to_numpy(outs[r], dtype), got0, "out of place, rank {}".format(r))
+                H.assert_bits_equal(H.to_numpy(xs[r], dtype), got0, "in place, rank {}".format(r))
+            if n == 2 and dtype == oracle.F32:
+                H.assert_bits_equal(got0, oracle.allreduce(arrays, dtype, redop), "two ranks: one order")
+        # A bucket of ragged tensors as one message, three chunks.
+        for c in comms:
+            c.set_tuning(variant=7, chunk_bytes=1 << 20)
+        sizes = [70001, 3, 1 << 19, 257]
+        host = [[H.make_input(r, k, oracle.F32, seed=77 + i) for i, k in enumerate(sizes)] for r in range(n)]
+        dev = [[H.to_torch(a, oracle.F32, "cuda:{}".format(r)) for a in host[r]] for r in range(n)]
+        for r in range(n):
+            with torch.cuda.device(r):
+                comms[r].all_reduce(dev[r], None, "MEAN")
+        sync_all(n)
+        assert comms[0].last_launch()["variant"] == 7
+        for i in range(len(sizes)):
+            ref = oracle.fp64_sum([host[r][i] for r in range(n)], oracle.F32, mean=True)
+            for r in range(n):
+                assert oracle.max_rel_err(H.to_numpy(dev[r][i], oracle.F32), ref, oracle.F32) <= 1e-6
+    finally:
+        for c in comms:
+            c.set_tuning()
+
+
+@needs_two
 def test_back_to_back_mixed_collectives_across_gpus(comms):
     n = len(comms)
     steps = 12
