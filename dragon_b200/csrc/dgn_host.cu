@@ -870,7 +870,9 @@ int get_table(dgn_comm* c, const void* const* in, void* const* out, const int64_
       return DGN_OK;
     }
   }
-  if (c->tables.size() >= 32) {  // evict the least recently used entry
+  // Evict the least recently used entry -- unless calls of this virtual rank
+  // are still queued: they hold table pointers that are not on the device yet.
+  if (c->tables.size() >= 32 && !(c->team && !c->team->pending[c->rank].empty())) {
     size_t lru = 0;
     for (size_t i = 1; i < c->tables.size(); ++i)
       if (c->tables[i].last_use < c->tables[lru].last_use) lru = i;
@@ -919,7 +921,7 @@ int get_zero_table(dgn_comm* c, const void* const* grads, void* const* params, c
       return DGN_OK;
     }
   }
-  if (c->zero_tables.size() >= 16) {  // evict the least recently used entry
+  if (c->zero_tables.size() >= 16 && !(c->team && !c->team->pending[c->rank].empty())) {  // as above
     size_t lru = 0;
     for (size_t i = 1; i < c->zero_tables.size(); ++i)
       if (c->zero_tables[i].last_use < c->zero_tables[lru].last_use) lru = i;
