@@ -45,6 +45,7 @@ const void* allgather_kernel_fn();
 const void* allgather_ll_kernel_fn();
 const void* broadcast_kernel_fn();
 const void* broadcast_scatter_kernel_fn();
+const void* broadcast_nvls_kernel_fn();
 const void* local_copy_kernel_fn(int es, bool table);
 const void* zero_kernel_fn(int dtype, int which);  // dgn_zero_inst.cu
 }  // namespace dgn
@@ -258,6 +259,7 @@ struct dgn_comm {
   // chunk size and number of blocks that drive the switch.
   long long pipe_min_bytes = 0, pipe_chunk_bytes = 0;
   int pipe_switch_blocks = 32;
+  long long nvls_bcast_min_bytes = 0;  // smallest broadcast that goes through the switch
 };
 
 namespace {
@@ -291,6 +293,7 @@ int preload_kernels() {
   DGN_CUDA(cudaFuncGetAttributes(&attr, allgather_ll_kernel_fn()));
   DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_kernel_fn()));
   DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_scatter_kernel_fn()));
+  DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_nvls_kernel_fn()));
   const int sizes[4] = {1, 2, 4, 8};
   for (int es : sizes)
     for (int table = 0; table < 2; ++table)
@@ -603,6 +606,29 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
       return p;
     }
   }
+  if (d.kind == kOpBroadcast && c->nvls && !c->team) {
+    // Through the switch: the root stores the message once and the switch
+    // replicates it into every rank's staging memory.
+    const long long bytes = d.nvec * 16;
+    bool nvls = bytes >= c->nvls_bcast_min_bytes && c->tune_variant == DGN_VARIANT_AUTO;
+    if (c->tune_variant == DGN_VARIANT_NVLS) nvls = true;
+    if (nvls) {
+      long long cap_v = 2 * (long long)n * c->nvls_slot_bytes / 16;  // both areas of one staging half
+      if (c->tune_chunk >= 16 && c->tune_chunk / 16 < cap_v) cap_v = c->tune_chunk / 16;
+      long long nb = c->tune_blocks > 0 ? c->tune_blocks : 64;
+      if (nb > c->nvls_max_blocks) nb = c->nvls_max_blocks;
+      long long b = ceil_div(d.nvec, 512);
+      if (b > nb) b = nb;
+      if (b < 1) b = 1;
+      long long cv = ceil_div(d.nvec, b);
+      if (cv > cap_v) cv = cap_v;
+      p.variant = DGN_VARIANT_NVLS;
+      p.blocks = (int)b;
+      p.cv = (int)cv;
+      p.rounds = (int)ceil_div(d.nvec, b * cv);
+      return p;
+    }
+  }
   // Multi-round kernels: two-shot all-reduce, reduce-scatter, all-gather,
   // broadcast.  `per` = vectors each block column has to cover.
   long long per = d.nvec;
@@ -653,7 +679,9 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
     case kOpAllGather: k.fn = p.variant == DGN_VARIANT_LL ? allgather_ll_kernel_fn() : allgather_kernel_fn(); break;
     case kOpBroadcast:
-      k.fn = p.variant == DGN_VARIANT_TWOSHOT ? broadcast_scatter_kernel_fn() : broadcast_kernel_fn();
+      k.fn = p.variant == DGN_VARIANT_NVLS      ? broadcast_nvls_kernel_fn()
+             : p.variant == DGN_VARIANT_TWOSHOT ? broadcast_scatter_kernel_fn()
+                                                : broadcast_kernel_fn();
       break;
     case kOpZeroReduce:
     case kOpZeroUpdate:
@@ -1189,6 +1217,7 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
     c->symm_min_bytes = env_ll("DGN_SYMM_MIN_BYTES", 4ll << 20);
     // Opt-in until it has been measured beside the other large-message kernels
     // at every rank count.
+    c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", 1ll << 62);
     c->pipe_min_bytes = env_ll("DGN_NVLS_PIPE_MIN_BYTES", 1ll << 62);
     c->pipe_chunk_bytes = env_ll("DGN_NVLS_PIPE_CHUNK_BYTES", 0);
     c->pipe_switch_blocks = (int)env_ll("DGN_NVLS_PIPE_SWITCH_BLOCKS", 32);

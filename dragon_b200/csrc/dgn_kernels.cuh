@@ -1657,6 +1657,50 @@ __global__ void __launch_bounds__(kMaxThreads, 1) broadcast_scatter_kernel(const
 }
 
 // ---------------------------------------------------------------------------
+// BROADCAST in place through NVSwitch multicast: the root stores every slice
+// once, with multimem.st, into the staging memory of ALL ranks (the switch
+// replicates it), so it sends S bytes instead of (n-1) S when the peers pull or
+// about 2 S (n-1)/n with scatter + all-gather; the peers copy the slices from
+// their own staging memory into their buffers.  Per round and block the 2n
+// slots of one staging half form one buffer.  Epochs as in broadcast_kernel:
+// published(i) = base+2i+1 on channel A (root -> peers), emptied(i) = base+2i+2
+// on channel B (peers -> root); a half is refilled after every peer has
+// emptied it.
+
+template <int kUnused>
+__global__ void __launch_bounds__(kMaxThreads, 1) broadcast_nvls_kernel(const __grid_constant__ OpParams P) {
+  const PeerTable& pt = P.peers[blockIdx.y];
+  const RankArgs& ra = P.ra[blockIdx.y];
+  const int r = pt.rank, b = blockIdx.x, root = P.root;
+  Turn turn;
+  if (!begin_collective(pt, b, P, &turn)) return;
+  char* buf = static_cast<char*>(ra.out);
+  const bool al = is_al16(buf);
+  const long long cv = P.cv;
+
+  for (int round = 0; round < P.rounds; ++round) {
+    const long long off = ((long long)round * gridDim.x + b) * cv;
+    const long long len = clampll(P.nvec - off, 0, cv);
+    const u64 e_pub = turn.base + 2 * (u64)round + 1, e_got = e_pub + 1;
+    const long long so = nvls_offset(pt, turn.parity, b, round & 1, 0, 0);
+    if (r == root) {
+      if (round >= 2 && !wait_peers(pt, b, kChanB, turn.base + 2 * (u64)(round - 2) + 2, P.wait_ns)) return;
+      char* dst = pt.nvls_mc + so;
+      copy_vectors(len, [&](long long v) { return load_vec<1>(buf, off + v, P.count, al); },
+                   [&](long long v, uint4 x) { Multimem<float>::st(dst + v * 16, x); });
+      signal_peers(pt, b, kChanA, e_pub);
+    } else {
+      if (!wait_peers(pt, b, kChanA, e_pub, P.wait_ns, root)) return;
+      const char* src = pt.nvls_uc + so;
+      copy_vectors(len, [&](long long v) { return ldv(src + v * 16); },
+                   [&](long long v, uint4 x) { store_vec<1>(buf, off + v, P.count, al, x); });
+      signal_peers(pt, b, kChanB, e_got, root);
+    }
+  }
+  end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
+}
+
+// ---------------------------------------------------------------------------
 // Single-rank path: out = in (the MEAN factor is 1 at n = 1), one pass over
 // HBM.  Also serves the table form (bucket -> per-tensor copies).
 

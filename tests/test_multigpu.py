@@ -322,6 +322,39 @@ def test_sharded_adamw_step_across_gpus(comms):
 
 
 @needs_two
+def test_multicast_broadcast_across_gpus(comms):
+    """BROADCAST through the switch (the root stores once, every rank receives):
+    byte-exact for every root, ragged sizes, several rounds, back to back."""
+    n = len(comms)
+    if not comms[0].has_nvls():
+        pytest.skip("NVSwitch multicast is not available on this box")
+    for c in comms:
+        c.set_tuning(variant=3)
+    try:
+        for dtype, count in ((oracle.I64, 65536), (oracle.U8, 13), (oracle.BF16, (1 << 20) + 5),
+                             (oracle.I64, (5 << 20) + 3), (oracle.F32, 1)):
+            for root in sorted({0, n - 1}):
+                arrays = [H.make_input(r, count, dtype, seed=500 + root) for r in range(n)]
+                if dtype == oracle.BF16:
+                    arrays[root][:4] = [0x7FC1, 0xFFFF, 0x8000, 0x0001]  # NaN payloads, -0, a subnormal
+                xs = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
+                for rep in range(2):
+                    for r in range(n):
+                        with torch.cuda.device(r):
+                            comms[r].broadcast(xs[r], root)
+                sync_all(n)
+                assert comms[0].last_launch()["variant"] == 3
+                if count > (4 << 20):
+                    assert comms[0].last_launch()["rounds"] >= 2
+                for r in range(n):
+                    assert comms[r].status() == 0
+                    H.assert_bits_equal(H.to_numpy(xs[r], dtype), arrays[root], "root {} rank {}".format(root, r))
+    finally:
+        for c in comms:
+            c.set_tuning()
+
+
+@needs_two
 def test_two_processes_over_ipc_and_file_rendezvous():
     with tempfile.TemporaryDirectory() as rdv:
         procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "mp_gpu_worker.py"), str(r), "2", rdv],
