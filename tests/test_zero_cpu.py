@@ -86,6 +86,35 @@ def test_oracle_zero_step_against_unsharded_float64(dtype):
     assert np.array_equal(params[0], before)
 
 
+@pytest.mark.parametrize("dtype", [oracle.F16, oracle.F32])
+def test_oracle_zero_step_does_not_depend_on_the_number_of_shards(dtype):
+    """Without clipping by norm (the one place where the shard shows: the norm
+    is taken over the local shard) the update is elementwise, so cutting the
+    same summed gradient into 1, 2, 3 or 8 shards must give identical bits."""
+    rng = np.random.default_rng(21)
+    counts = [33, 1, 400, 7]
+    total = sum(counts)
+    g = oracle.from_f32(rng.normal(0, 1e-2, total).astype(np.float32), dtype)
+    zero = np.zeros(total, dtype=oracle.NP_STORAGE[dtype])
+    p0 = oracle.from_f32(rng.normal(0, 1, total).astype(np.float32), dtype)
+    hyper = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=1e-5, grad_scale=0.5,
+                 clip_norm=0.0, clip_value=0.004)
+    results = []
+    for n in (1, 2, 3, 8):
+        grads = [g.copy()] + [zero.copy() for _ in range(n - 1)]  # x + 0 is exact: every n sees the same sum
+        params = [p0.copy() for _ in range(n)]
+        rc = oracle.zero_shard_count(total, n)
+        masters = oracle.zero_init_master(p0, n, dtype)
+        states = [dict(master=masters[r], m=np.zeros(rc, np.float32), v=np.zeros(rc, np.float32)) for r in range(n)]
+        for _ in range(2):
+            oracle.zero_adamw_step(grads, params, states, counts, dtype, hyper, lr_scales=[1, 0.5, 1, 2])
+        results.append(params[0])
+        flat_master = np.concatenate([s["master"] for s in states])[:total]
+        results.append(flat_master)
+    for k in range(2, len(results), 2):
+        assert np.array_equal(results[k], results[0]) and np.array_equal(results[k + 1], results[1])
+
+
 @pytest.mark.parametrize("dtype,E", [(4, 8), (5, 8), (6, 4)])
 def test_shard_geometry_covers_the_bucket_once(dgn_lib, dtype, E):
     """Every flat element belongs to exactly one rank's shard, and its slot in

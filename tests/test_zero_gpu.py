@@ -221,6 +221,22 @@ def test_resnet50_shaped_bucket_eight_ranks(teams):
     h.check(what="resnet50 bucket")
 
 
+def test_bert_base_shaped_fp16_bucket_eight_ranks(teams):
+    """The BERT-base parameter list (199 fp16 tensors, 109,482,240 elements) as
+    one bucket on eight ranks, overflow check on: bit for bit against the
+    oracle, and every rank ends with the same parameters."""
+    from dragon_b200 import workloads
+    counts = [int(np.prod(s)) for s in workloads.bert_base_shapes()]
+    n, dtype = 8, oracle.F16
+    h = Harness(teams(n), counts, dtype)
+    found = [torch.zeros(1, dtype=torch.float32, device=DEV) for _ in range(n)]
+    assert h.step([_grads(r, 0, counts, dtype) for r in range(n)], found_inf=found) == 0.0
+    h.check(what="bert-base bucket")
+    first = _flat(h.params[0], dtype)
+    assert all(np.array_equal(_flat(h.params[r], dtype), first) for r in range(1, n))
+    assert all(f.item() == 0.0 for f in found)
+
+
 def test_argument_errors(teams, dgn_lib):
     import ctypes
     from dragon_b200 import _C
