@@ -36,6 +36,90 @@ def test_oracle_adamw_against_float64(wd, scaled):
     np.testing.assert_allclose(y, wy, rtol=3e-7, atol=1e-7)
 
 
+# ---- exact rational arithmetic: an independent model of every IEEE operation ----
+
+def _rn32(x):
+    """Fraction -> nearest float32 (ties to even), as a Fraction; exact integer arithmetic."""
+    from fractions import Fraction
+    if x == 0:
+        return Fraction(0)
+    sign = -1 if x < 0 else 1
+    a = abs(x)
+    e = a.numerator.bit_length() - a.denominator.bit_length()  # 2^(e-1) <= a < 2^(e+1)
+    if Fraction(2) ** e > a:
+        e -= 1
+    e = max(e, -126)                      # below 2^-126 the spacing stays 2^-149
+    ulp = Fraction(2) ** (e - 23)
+    q = a / ulp
+    m = q.numerator // q.denominator
+    rest = q - m
+    if rest > Fraction(1, 2) or (rest == Fraction(1, 2) and m % 2 == 1):
+        m += 1
+    r = m * ulp
+    assert r < Fraction(2) ** 128, "overflow is not part of this test"
+    return sign * r
+
+
+def _sqrt32(x):
+    """Correctly rounded float32 square root of a non-negative Fraction."""
+    from fractions import Fraction
+    from math import isqrt
+    if x == 0:
+        return Fraction(0)
+    k = 200
+    s = isqrt(x.numerator * x.denominator << (2 * k))  # floor(sqrt(p q) 2^k)
+    approx = Fraction(s, x.denominator << k)            # within 2^-k of sqrt(p/q) from below
+    lo, hi = _rn32(approx), _rn32(approx + Fraction(1, 1 << (k - 8)))
+    assert lo == hi, "rounding boundary within the approximation error"
+    return lo
+
+
+def _adamw_exact(g, m, v, y, lr, b1, b2, eps, wd, ls=None):
+    """The reference's AdamW kernel, one element, every operation rounded to float32 once."""
+    from fractions import Fraction
+    F = lambda t: Fraction(float(np.float32(t)))  # noqa: E731
+    g, m, v, y, lr, b1, b2, eps, wd = map(F, (g, m, v, y, lr, b1, b2, eps, wd))
+    one = Fraction(1)
+    mi = _rn32(b1 * m + _rn32(_rn32(one - b1) * g))                       # fma(b1, m, (1-b1)*g)
+    vi = _rn32(b2 * v + _rn32(_rn32(_rn32(one - b2) * g) * g))            # fma(b2, v, ((1-b2)*g)*g)
+    den = _rn32(_sqrt32(vi) + eps)
+    if ls is None:
+        step = _rn32(_rn32(lr * mi) / den)
+        dec = _rn32(wd * y + step) if wd > 0 else step                  # fma(wd, y, step)
+    else:
+        ls = F(ls)
+        step = _rn32(_rn32(_rn32(lr * ls) * mi) / den)
+        dec = _rn32(_rn32(wd * ls) * y + step) if wd > 0 else step
+    return float(mi), float(vi), float(_rn32(y - dec))
+
+
+@pytest.mark.parametrize("wd", [0.0, 0.003])
+@pytest.mark.parametrize("scaled", [False, True])
+def test_oracle_adamw_bit_exact_against_exact_rational_arithmetic(wd, scaled):
+    """Pins the C restatement bit for bit: every multiply, add, fused
+    multiply-add, square root and divide must be the correctly rounded float32
+    operation, in the order of the reference's kernel (no contraction, no fast
+    math).  The model uses integers and fractions only."""
+    rng = np.random.default_rng(2024)
+    n = 96
+    g = rng.normal(0, 1e-2, n).astype(np.float32)
+    m = rng.normal(0, 1e-3, n).astype(np.float32)
+    v = (rng.normal(0, 1e-3, n) ** 2).astype(np.float32)
+    y = rng.normal(0, 1, n).astype(np.float32)
+    g[:4] = [0.0, 1e-30, -3.0, 1e-20]  # zero and tiny gradients: subnormal products, eps-dominated denominators
+    v[:2] = 0.0
+    lrs = rng.uniform(0.1, 2.0, n).astype(np.float32) if scaled else None
+    f32 = np.float32
+    lr, b1, b2, eps = float(f32(3e-4)), float(f32(0.9)), float(f32(0.999)), float(f32(1e-8))
+    want = [_adamw_exact(g[i], m[i], v[i], y[i], lr, b1, b2, eps, wd, None if lrs is None else lrs[i])
+            for i in range(n)]
+    oracle.adamw(g, m, v, y, lr, b1, b2, eps, float(f32(wd)), lrs)
+    wm, wv, wy = (np.array(col, dtype=np.float32) for col in zip(*want))
+    assert np.array_equal(m.view(np.uint32), wm.view(np.uint32))
+    assert np.array_equal(v.view(np.uint32), wv.view(np.uint32))
+    assert np.array_equal(y.view(np.uint32), wy.view(np.uint32))
+
+
 def test_oracle_adamw_known_answer():
     """First step from zero moments: m = (1-b1) g, v = (1-b2) g^2 and the step
     is lr * m / (sqrt(v) + eps); values chosen so that every product is exact."""
