@@ -100,18 +100,29 @@ class ZeroAdamW(object):
     """AdamW with optimizer state and the update sharded over the group.
 
     ``params`` are torch CUDA tensors whose ``.grad`` holds this rank's
-    gradient; ``comm`` is a dragon_b200.comm.Communicator.  Keyword arguments
-    and defaults follow the reference (torch/core/optim/adam.py:165-174,
-    optimizer.py:56-59)."""
+    gradient.  The process group is ``comm`` (a dragon_b200.comm.Communicator)
+    or ``group`` (a dragon_b200.distributed ProcessGroup); with neither, the
+    default group of dragon_b200.distributed is taken, as the reference's
+    ``step`` takes ``dist_backend.get_group()`` (torch/core/optim/zero.py:114-118).
+    Keyword arguments and defaults follow the reference
+    (torch/core/optim/adam.py:165-174, optimizer.py:56-59)."""
 
-    def __init__(self, params, comm, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
-                 grad_scale=1, clip_norm=0, clip_value=0, bucket_size=536870912):
+    def __init__(self, params, comm=None, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
+                 grad_scale=1, clip_norm=0, clip_value=0, bucket_size=536870912, group=None):
         params = list(params)
         if len(params) == 0:
             raise ValueError("<params> is an empty sequence.")
         for p in params:
             if p.dtype not in _ZERO_DTYPES:
                 raise TypeError("Unsupported data type: {}".format(p.dtype))
+        if comm is None:
+            from dragon_b200.distributed import backend as dist_backend
+            group = group or dist_backend.get_group()
+            if group is None:
+                raise ValueError("<group> is required.")
+            comm = dist_backend.communicator(group)
+            if comm is None:
+                raise ValueError("This rank is not a member of the group.")
         self.comm = comm
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.grad_scale, self.clip_norm, self.clip_value = grad_scale, clip_norm, clip_value

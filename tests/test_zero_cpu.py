@@ -239,3 +239,14 @@ def test_bucketing_rule_of_the_host_layer():
     assert buckets[0].params[0] is h[4] and buckets[2].params[0] is h[0]
     assert buckets[3].params[0] is f[2] and buckets[4].params[0] is f[1] and buckets[4].size == 400
     assert ZeroReduceBucket.new([]) == []
+
+
+def test_zero_adamw_needs_a_group_and_supported_dtypes():
+    import torch
+    from dragon_b200.zero import ZeroAdamW
+    with pytest.raises(ValueError, match="<group> is required"):
+        ZeroAdamW([torch.zeros(4)])
+    with pytest.raises(ValueError, match="empty sequence"):
+        ZeroAdamW([], comm=object())
+    with pytest.raises(TypeError, match="Unsupported data type"):
+        ZeroAdamW([torch.zeros(4, dtype=torch.float64)], comm=object())
