@@ -45,6 +45,9 @@ def parse_args():
                     help="operator configurations (gradient buckets, gather/broadcast shapes) beside the headline")
     ap.add_argument("--no-nccl", action="store_true", help="skip the NCCL comparison in the sweep")
     ap.add_argument("--no-symm", action="store_true", help="N>=2: skip the symmetric-memory (in-place multicast) rows")
+    ap.add_argument("--tune", default="off", choices=["off", "symm", "pipe", "bcast", "all"],
+                    help="N>=2: instead of the benchmark, time the multicast kernels over launch shapes, chunk "
+                         "sizes and variants and print one JSON object of rows (input for the thresholds)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-emulated", action="store_true", help="N=1: skip the emulated 8-rank timings")
     ap.add_argument("--emulated-only", action="store_true",
@@ -586,6 +589,95 @@ def run_operator_configs(comm, nccl, rank, world, dev, barrier, max_over_ranks):
     return out
 
 
+def run_tuning(args):
+    """Times the NVSwitch-multicast kernels beside the other variants over the
+    knobs that set their defaults: blocks and threads of the in-place kernel on
+    symmetric memory; chunk size and switch blocks of the pipelined variant
+    against the automatic choice, the two-shot and the staged kernel; blocks of
+    the broadcast through the switch against the automatic choice."""
+    import torch
+    import torch.distributed as dist
+    from dragon_b200.comm import Communicator
+
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group(backend="gloo")
+    comm = Communicator.init_local(rank, world, local, symm_bytes=256 * MiB)
+    handles = [None] * world
+    dist.all_gather_object(handles, comm.handle_bytes())
+    comm.connect(handles)
+    dist.barrier()
+
+    def max_over_ranks(v):
+        t = torch.tensor([float(v)], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, iters):
+        _, total = time_steps(fn, iters, 3, dist.barrier)
+        return max_over_ranks(total) / iters * 1e3  # us
+
+    factor = 2.0 * (world - 1) / world
+    rows = []
+    what = args.tune
+    if not comm.has_nvls():
+        rows.append({"error": "NVSwitch multicast is not available on this box"})
+        what = "none"
+    if what in ("symm", "all"):
+        arena = comm.symm_empty(64 * MiB, torch.float32)
+        arena.uniform_(-1, 1)
+        for mib in (4, 16, 64, 256):
+            count = mib * MiB // 4
+            nbuf = max(1, 256 // mib)
+            views = [arena[k * count:(k + 1) * count] for k in range(nbuf)]
+            for blocks in (16, 32, 64, 100, 148):
+                for threads in (128, 256, 512):
+                    comm.set_tuning(variant=6, blocks=blocks, threads=threads)
+                    ops = [comm.prepare_all_reduce([v], [v], "MEAN") for v in views]
+                    state = {"i": 0}
+
+                    def step():
+                        ops[state["i"] % nbuf]()
+                        state["i"] += 1
+
+                    us = timed(step, 20)
+                    rows.append({"kernel": "symm", "mib": mib, "blocks": blocks, "threads": threads, "us": us,
+                                 "busbw": mib * MiB / us / 1e3 * factor})
+        del arena
+        comm.symm_reset()
+    if what in ("pipe", "all"):
+        for mib in (8, 16, 64, 256, 1024):
+            x = torch.empty(mib * MiB // 4, device="cuda").uniform_(-1, 1)
+            shapes = [(0, 0, 0), (2, 0, 0), (3, 0, 0), (7, 0, 0)]
+            shapes += [(7, c * MiB, b) for c in (4, 16, 32, 64) if c * 2 <= mib for b in (16, 32, 64)]
+            for variant, chunk, blocks in shapes:
+                comm.set_tuning(variant=variant, chunk_bytes=chunk, blocks=blocks)
+                op = comm.prepare_all_reduce([x], [x], "MEAN")
+                us = timed(op, 10)
+                rows.append({"kernel": "pipe", "mib": mib, "variant": variant, "chunk_mib": chunk // MiB,
+                             "switch_blocks": blocks, "us": us, "busbw": mib * MiB / us / 1e3 * factor,
+                             "launch": comm.last_launch()})
+            del x
+    if what in ("bcast", "all"):
+        for mib in (1, 4, 16, 64, 256):
+            x = torch.empty(mib * MiB // 4, device="cuda").uniform_(-1, 1)
+            for variant, blocks, threads in ((0, 0, 0), (1, 0, 0), (2, 0, 0), (3, 0, 0), (3, 32, 0), (3, 148, 0),
+                                             (3, 64, 256)):
+                comm.set_tuning(variant=variant, blocks=blocks, threads=threads)
+                us = timed(lambda: comm.broadcast(x, 0), 10)
+                rows.append({"kernel": "bcast", "mib": mib, "variant": variant, "blocks": blocks, "threads": threads,
+                             "us": us, "gbs": mib * MiB / us / 1e3, "launch": comm.last_launch()})
+            del x
+    comm.set_tuning()
+    dist.barrier()
+    torch.cuda.synchronize()
+    comm.destroy()
+    dist.destroy_process_group()
+    return {"tuning": args.tune, "n_gpus": world, "rows": rows} if rank == 0 else None
+
+
 def run_symmetric(comm, rank, world, barrier, max_over_ranks):
     """MEAN all-reduce in place on buffers from the communicator's symmetric
     arena (dgn_comm_symm_alloc): the switch reduces the buffers themselves,
@@ -812,6 +904,8 @@ def main():
         line = {"emulated_ranks_one_gpu": bench_emulated(args)}
     elif args.gpus <= 1 and int(os.environ.get("WORLD_SIZE", "1")) <= 1:
         line = bench_single(args)
+    elif args.tune != "off":
+        line = run_tuning(args)
     else:
         line = bench_multi(args)
     if line is not None:
