@@ -77,6 +77,9 @@ SIGNATURES.update({
     "dgn_comm_symm_capacity": (ctypes.c_int64, [ctypes.c_void_p]),
     "dgn_comm_symm_alloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, _c_void_pp]),
     "dgn_comm_symm_reset": (ctypes.c_int, [ctypes.c_void_p]),
+    "dgn_plan_query": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int,
+                                      ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int,
+                                      _c_int_p, _c_int_p, _c_int_p, _c_i64_p, _c_int_p]),
     "dgn_zero_shard_count": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64]),
     "dgn_zero_state_count": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int]),
     "dgn_zero_state_offset": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int]),

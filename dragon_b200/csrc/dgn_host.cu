@@ -260,6 +260,7 @@ struct dgn_comm {
   long long pipe_min_bytes = 0, pipe_chunk_bytes = 0;
   int pipe_switch_blocks = 32;
   long long nvls_bcast_min_bytes = 0;  // smallest broadcast that goes through the switch
+  bool plan_query = false, plan_query_in_symm = false;  // dgn_plan_query: no device, no real buffers
 };
 
 namespace {
@@ -401,6 +402,8 @@ long long default_oneshot_max(int n) {
 // reduces whole vectors, so a ragged tail would touch its neighbour's bytes).
 bool symm_inplace_ok(const dgn_comm* c, const OpDesc& d) {
   if (!c->nvls || c->symm_bytes == 0 || d.ntensors != 1 || d.in != d.out || !d.in) return false;
+  if (c->plan_query)
+    return c->plan_query_in_symm && ((d.count * (long long)kElemSize[d.dtype]) & 15) == 0;
   char *uc = nullptr, *mc = nullptr;
   nvls_pointers(c->nvls, &uc, &mc);
   const char* lo = uc + c->symm_off;
@@ -661,6 +664,58 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
   p.rounds = (int)ceil_div(per, b * cv);
   if (p.rounds < 1) p.rounds = 1;
   return p;
+}
+
+// Geometry, wait limit and variant thresholds of a communicator of
+// c->nranks ranks, from the environment and the measured defaults.  No device
+// is touched.
+void load_thresholds(dgn_comm* c) {
+  const int nranks = c->nranks;
+  c->geo = make_geometry(nranks);
+  c->wait_ns = (u64)env_ll("DGN_WAIT_LIMIT_MS", 5000) * 1000000ull;
+  c->oneshot_max_bytes = env_ll("DGN_ONESHOT_MAX_BYTES", -1);
+  c->ll_max_bytes = env_ll("DGN_LL_MAX_BYTES", -1);
+  c->ll2_max_bytes = env_ll("DGN_LL2_MAX_BYTES", -1);
+  c->fused_twoshot = env_ll("DGN_TWOSHOT_FUSED", 0) != 0;
+  c->bcast_scatter_min_bytes = env_ll("DGN_BCAST_SCATTER_MIN_BYTES", 1ll << 20);
+  // Every rank receives (n - 1) * 2 * S bytes of lines: 15.7 us against 26.2 us
+  // for pulling at 2 ranks and 512 KiB blocks, but no gain at 8 ranks there.
+  c->ll_allgather_max_bytes =
+      env_ll("DGN_LL_ALLGATHER_MAX_BYTES", nranks <= 2 ? (512ll << 10) : nranks <= 4 ? (256ll << 10) : (64ll << 10));
+  c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
+}
+
+// Sizes and thresholds of the NVSwitch multicast paths; `symm_request` is the
+// size of the symmetric arena asked for.  No device is touched.
+void load_nvls_settings(dgn_comm* c, long long symm_request) {
+  const int nranks = c->nranks;
+  c->nvls_max_blocks = c->geo.max_blocks;
+  c->nvls_slot_bytes = env_ll("DGN_NVLS_SLOT_BYTES", 64 * 1024);
+  if (c->nvls_slot_bytes < 4096) c->nvls_slot_bytes = 4096;
+  c->nvls_slot_bytes = (c->nvls_slot_bytes + 4095) & ~4095ll;
+  // Measured at n = 8 against the store-only two-shot kernel: 507 vs 561 GB/s
+  // at 128 MiB, 630 vs 605 at 256 MiB, 725 vs 635 at 512 MiB, 764 vs 621 at
+  // 1 GiB.  With fewer ranks the switch saves too little traffic (1.5 S per
+  // direction at n = 2 against 1.0 S), so the variant is opt-in there.
+  c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", nranks >= 8 ? (256ll << 20) : (1ll << 62));
+  c->nvls_bytes = 2 * (size_t)c->nvls_max_blocks * 2 * 2 * (size_t)nranks * (size_t)c->nvls_slot_bytes;
+  // Optional symmetric arena behind the staging area (2 MiB granules).
+  if (symm_request > 0) {
+    const size_t gran = (size_t)2 << 20;
+    c->symm_off = (c->nvls_bytes + gran - 1) / gran * gran;
+    c->symm_bytes = ((size_t)symm_request + gran - 1) / gran * gran;
+    c->nvls_bytes = c->symm_off + c->symm_bytes;
+  }
+  // In place through the switch from this size on.  Measured at 2 ranks:
+  // 25 us at 1 MiB and 33 us at 4 MiB, where the low-latency kernels take
+  // 15-20 us and about 30 us.
+  c->symm_min_bytes = env_ll("DGN_SYMM_MIN_BYTES", 4ll << 20);
+  // Opt-in until it has been measured beside the other large-message kernels
+  // at every rank count.
+  c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", 1ll << 62);
+  c->pipe_min_bytes = env_ll("DGN_NVLS_PIPE_MIN_BYTES", 1ll << 62);
+  c->pipe_chunk_bytes = env_ll("DGN_NVLS_PIPE_CHUNK_BYTES", 0);
+  c->pipe_switch_blocks = (int)env_ll("DGN_NVLS_PIPE_SWITCH_BLOCKS", 32);
 }
 
 struct KernelChoice {
@@ -1170,18 +1225,7 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
   c->rank = rank;
   c->nranks = nranks;
   c->device = device;
-  c->geo = make_geometry(nranks);
-  c->wait_ns = (u64)env_ll("DGN_WAIT_LIMIT_MS", 5000) * 1000000ull;
-  c->oneshot_max_bytes = env_ll("DGN_ONESHOT_MAX_BYTES", -1);
-  c->ll_max_bytes = env_ll("DGN_LL_MAX_BYTES", -1);
-  c->ll2_max_bytes = env_ll("DGN_LL2_MAX_BYTES", -1);
-  c->fused_twoshot = env_ll("DGN_TWOSHOT_FUSED", 0) != 0;
-  c->bcast_scatter_min_bytes = env_ll("DGN_BCAST_SCATTER_MIN_BYTES", 1ll << 20);
-  // Every rank receives (n - 1) * 2 * S bytes of lines: 15.7 us against 26.2 us
-  // for pulling at 2 ranks and 512 KiB blocks, but no gain at 8 ranks there.
-  c->ll_allgather_max_bytes =
-      env_ll("DGN_LL_ALLGATHER_MAX_BYTES", nranks <= 2 ? (512ll << 10) : nranks <= 4 ? (256ll << 10) : (64ll << 10));
-  c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
+  load_thresholds(c);
   int rc = alloc_workspace(c);
   if (rc != DGN_OK) {
     free_comm(c);
@@ -1193,34 +1237,7 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
   }
   if (nranks > 1 && !g_skip_nvls && env_ll("DGN_NVLS", 1) != 0) {
     DeviceGuard g(device);
-    c->nvls_max_blocks = c->geo.max_blocks;
-    c->nvls_slot_bytes = env_ll("DGN_NVLS_SLOT_BYTES", 64 * 1024);
-    if (c->nvls_slot_bytes < 4096) c->nvls_slot_bytes = 4096;
-    c->nvls_slot_bytes = (c->nvls_slot_bytes + 4095) & ~4095ll;
-    // Measured at n = 8 against the store-only two-shot kernel: 507 vs 561 GB/s
-    // at 128 MiB, 630 vs 605 at 256 MiB, 725 vs 635 at 512 MiB, 764 vs 621 at
-    // 1 GiB.  With fewer ranks the switch saves too little traffic (1.5 S per
-    // direction at n = 2 against 1.0 S), so the variant is opt-in there.
-    c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", nranks >= 8 ? (256ll << 20) : (1ll << 62));
-    c->nvls_bytes = 2 * (size_t)c->nvls_max_blocks * 2 * 2 * (size_t)nranks * (size_t)c->nvls_slot_bytes;
-    // Optional symmetric arena behind the staging area (2 MiB granules).
-    const long long want = g_symm_request >= 0 ? g_symm_request : env_ll("DGN_SYMM_BYTES", 0);
-    if (want > 0) {
-      const size_t gran = (size_t)2 << 20;
-      c->symm_off = (c->nvls_bytes + gran - 1) / gran * gran;
-      c->symm_bytes = ((size_t)want + gran - 1) / gran * gran;
-      c->nvls_bytes = c->symm_off + c->symm_bytes;
-    }
-    // In place through the switch from this size on.  Measured at 2 ranks:
-    // 25 us at 1 MiB and 33 us at 4 MiB, where the low-latency kernels take
-    // 15-20 us and about 30 us.
-    c->symm_min_bytes = env_ll("DGN_SYMM_MIN_BYTES", 4ll << 20);
-    // Opt-in until it has been measured beside the other large-message kernels
-    // at every rank count.
-    c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", 1ll << 62);
-    c->pipe_min_bytes = env_ll("DGN_NVLS_PIPE_MIN_BYTES", 1ll << 62);
-    c->pipe_chunk_bytes = env_ll("DGN_NVLS_PIPE_CHUNK_BYTES", 0);
-    c->pipe_switch_blocks = (int)env_ll("DGN_NVLS_PIPE_SWITCH_BLOCKS", 32);
+    load_nvls_settings(c, g_symm_request >= 0 ? g_symm_request : env_ll("DGN_SYMM_BYTES", 0));
     c->nvls_capable = nvls_device_supported(device);
     if (c->nvls_capable && rank == 0) {
       // Rank 0 owns the multicast object and the rendezvous socket.
@@ -1761,6 +1778,41 @@ int dgn_zero_adamw(dgn_comm_t c, const void* const* grad_ptrs, void* const* para
   if (rc != DGN_OK) return rc;
   d.kind = kOpZeroUpdate;
   return issue(c, d);
+}
+
+int dgn_plan_query(int nranks, int num_sms, int has_nvls, int64_t symm_bytes, int in_symm, int op, int dtype,
+                   int redop, int64_t count, int ntensors, int* variant, int* blocks, int* threads,
+                   int64_t* chunk_bytes, int* rounds) {
+  if (nranks < 2 || nranks > DGN_MAX_RANKS) return fail(DGN_ERR_ARG, "nranks %d outside 2..%d", nranks, DGN_MAX_RANKS);
+  const size_t es = dgn_dtype_size(dtype);
+  if (es == 0 || count <= 0 || num_sms < 1 || ntensors < 1 || op < kOpAllReduce || op > kOpBroadcast)
+    return fail(DGN_ERR_ARG, "bad plan query");
+  dgn_comm q;
+  q.nranks = nranks;
+  q.num_sms = num_sms;
+  load_thresholds(&q);
+  if (has_nvls) {
+    load_nvls_settings(&q, symm_bytes);
+    q.nvls = reinterpret_cast<NvlsBuffer*>(&q);  // only its presence is looked at
+  }
+  q.plan_query = true;
+  q.plan_query_in_symm = in_symm != 0;
+  OpDesc d;
+  d.kind = op;
+  d.dtype = (op == kOpAllGather || op == kOpBroadcast) ? (int)DGN_U8 : dtype;
+  d.redop = redop;
+  d.ntensors = ntensors;
+  d.count = (op == kOpAllGather || op == kOpBroadcast) ? count * (long long)es : count;
+  d.nvec = ceil_div(count * (long long)es, 16);
+  d.in = d.out = reinterpret_cast<void*>(16);  // in place
+  const Plan p = make_plan(&q, d, 0);
+  q.nvls = nullptr;
+  if (variant) *variant = p.variant;
+  if (blocks) *blocks = p.blocks;
+  if (threads) *threads = p.threads;
+  if (chunk_bytes) *chunk_bytes = (int64_t)p.cv * 16;
+  if (rounds) *rounds = p.rounds;
+  return DGN_OK;
 }
 
 int64_t dgn_launch_count(void) { return g_launches.load(); }

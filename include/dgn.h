@@ -285,6 +285,18 @@ int dgn_allreduce_static(int nranks, const void* const* in_ptrs, void* const* ou
 
 /* ---- introspection for benchmarks and tests ------------------------------ */
 
+/* The variant and launch shape the library would choose for one collective on a
+ * communicator of `nranks` ranks (2..8) on GPUs with `num_sms` SMs, with or
+ * without NVSwitch multicast, with a symmetric arena of `symm_bytes`, for a
+ * buffer inside (in_symm != 0) or outside it; the environment knobs apply as
+ * they do to a real communicator.  op: 0 ALLREDUCE, 1 REDUCESCATTER (count per
+ * rank), 2 ALLGATHER (count per rank), 3 BROADCAST; the operation is taken to
+ * be in place; ntensors > 1 describes a bucket.  Touches no device: tests and
+ * documentation of the thresholds use it. */
+int dgn_plan_query(int nranks, int num_sms, int has_nvls, int64_t symm_bytes, int in_symm, int op,
+                   int dtype, int redop, int64_t count, int ntensors, int* variant, int* blocks,
+                   int* threads, int64_t* chunk_bytes, int* rounds);
+
 /* Number of kernels this library has launched from the calling process. */
 int64_t dgn_launch_count(void);
 /* Variant / grid the last collective of `comm` used (any pointer may be NULL). */

@@ -1,0 +1,124 @@
+"""Which kernel serves which message: the thresholds of the planner, queried
+without a GPU (dgn_plan_query).  The expectations are the measured crossovers
+the library documents: low-latency one-shot up to 1 MiB / 512 KiB / 128 KiB at
+2 / 4 / 8 ranks, low-latency two-shot up to 2 MiB from 3 ranks, the store-only
+two-shot kernel above, NVSwitch multicast from 256 MiB at 8 ranks, in place on
+symmetric memory from 4 MiB."""
+
+import ctypes
+
+import pytest
+
+from dragon_b200 import _C
+
+AR, RS, AG, BC = range(4)
+KiB, MiB = 1 << 10, 1 << 20
+
+
+def plan(lib, n, op, nbytes, dtype=_C.F32, redop=_C.MEAN, nvls=True, symm=0, in_symm=False, ntensors=1, sms=148):
+    es = lib.dgn_dtype_size(dtype)
+    v, b, t, r = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    cb = ctypes.c_int64()
+    rc = lib.dgn_plan_query(n, sms, int(nvls), symm, int(in_symm), op, dtype, redop, nbytes // es, ntensors,
+                            ctypes.byref(v), ctypes.byref(b), ctypes.byref(t), ctypes.byref(cb), ctypes.byref(r))
+    assert rc == _C.OK, lib.dgn_last_error_string()
+    return {"variant": v.value, "blocks": b.value, "threads": t.value, "chunk_bytes": cb.value, "rounds": r.value}
+
+
+@pytest.fixture(autouse=True)
+def clean_env(monkeypatch):
+    for name in ("DGN_FORCE_VARIANT", "DGN_LL_MAX_BYTES", "DGN_LL2_MAX_BYTES", "DGN_ONESHOT_MAX_BYTES",
+                 "DGN_NVLS_MIN_BYTES", "DGN_SYMM_MIN_BYTES", "DGN_NVLS_PIPE_MIN_BYTES", "DGN_NVLS_BCAST_MIN_BYTES",
+                 "DGN_MAX_BLOCKS", "DGN_SLOT_BYTES", "DGN_LL_ALLGATHER_MAX_BYTES", "DGN_BCAST_SCATTER_MIN_BYTES"):
+        monkeypatch.delenv(name, raising=False)
+
+
+def test_allreduce_variant_by_size_and_rank_count(dgn_lib):
+    expect = {
+        2: [(1 * KiB, _C.VARIANT_LL), (1 * MiB, _C.VARIANT_LL), (2 * MiB, _C.VARIANT_TWOSHOT),
+            (1024 * MiB, _C.VARIANT_TWOSHOT)],
+        4: [(64 * KiB, _C.VARIANT_LL), (512 * KiB, _C.VARIANT_LL), (1 * MiB, _C.VARIANT_LL2),
+            (2 * MiB, _C.VARIANT_LL2), (4 * MiB, _C.VARIANT_TWOSHOT), (1024 * MiB, _C.VARIANT_TWOSHOT)],
+        8: [(1 * KiB, _C.VARIANT_LL), (128 * KiB, _C.VARIANT_LL), (256 * KiB, _C.VARIANT_LL2),
+            (2 * MiB, _C.VARIANT_LL2), (4 * MiB, _C.VARIANT_TWOSHOT), (128 * MiB, _C.VARIANT_TWOSHOT),
+            (256 * MiB, _C.VARIANT_NVLS), (1024 * MiB, _C.VARIANT_NVLS)],
+    }
+    for n, rows in expect.items():
+        for nbytes, variant in rows:
+            for dtype in (_C.F32, _C.F16):
+                got = plan(dgn_lib, n, AR, nbytes, dtype)
+                assert got["variant"] == variant, (n, nbytes, dtype, got)
+    # Without the switch, integers and other reductions stay on the peer-store kernels.
+    assert plan(dgn_lib, 8, AR, 512 * MiB, nvls=False)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 8, AR, 512 * MiB, dtype=_C.I32, redop=_C.SUM)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 8, AR, 512 * MiB, redop=_C.MAX)["variant"] == _C.VARIANT_TWOSHOT
+
+
+def test_launch_shapes_stay_inside_the_workspace(dgn_lib):
+    for n in (2, 4, 8):
+        for nbytes in (4 * MiB, 64 * MiB, 1024 * MiB):
+            p = plan(dgn_lib, n, AR, nbytes, nvls=False)
+            assert 1 <= p["blocks"] <= 148 and p["chunk_bytes"] <= 128 * KiB  # one block per SM, one staging slot
+            per_rank = -(-nbytes // n)
+            assert p["blocks"] * p["chunk_bytes"] * p["rounds"] >= per_rank   # the rounds cover every shard
+        p = plan(dgn_lib, n, AR, 64 * KiB)
+        assert p["rounds"] == 1 and p["blocks"] <= 64 and p["chunk_bytes"] * 2 <= 64 * KiB  # lines are half flags
+    p = plan(dgn_lib, 8, AR, 512 * MiB)
+    assert p["variant"] == _C.VARIANT_NVLS and p["chunk_bytes"] <= 64 * KiB and p["blocks"] <= 148
+
+
+def test_symmetric_memory_and_opt_in_variants(dgn_lib, monkeypatch):
+    arena = 256 * MiB
+    assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=True)["variant"] == _C.VARIANT_SYMM
+    assert plan(dgn_lib, 2, AR, 4 * MiB, symm=arena, in_symm=True)["variant"] == _C.VARIANT_SYMM
+    small = plan(dgn_lib, 8, AR, 1 * MiB, symm=arena, in_symm=True)
+    assert small["variant"] == _C.VARIANT_LL2                       # below 4 MiB the low-latency kernels win
+    assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=False)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 8, AR, 64 * MiB + 4, symm=arena, in_symm=True)["variant"] == _C.VARIANT_TWOSHOT  # ragged
+    assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=True, nvls=False)["variant"] == _C.VARIANT_TWOSHOT
+    shape = plan(dgn_lib, 8, AR, 256 * MiB, symm=arena, in_symm=True)
+    assert shape["blocks"] <= 64 and shape["threads"] == 256 and shape["rounds"] == 1
+    # The pipelined variant and the broadcast through the switch are opt-in.
+    assert plan(dgn_lib, 8, AR, 64 * MiB)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 8, BC, 64 * MiB)["variant"] == _C.VARIANT_TWOSHOT
+    monkeypatch.setenv("DGN_NVLS_PIPE_MIN_BYTES", str(32 * MiB))
+    monkeypatch.setenv("DGN_NVLS_BCAST_MIN_BYTES", str(1 * MiB))
+    pipe = plan(dgn_lib, 8, AR, 64 * MiB)
+    assert pipe["variant"] == _C.VARIANT_NVLS_PIPE and pipe["rounds"] == 2 and pipe["chunk_bytes"] == 32 * MiB
+    big = plan(dgn_lib, 8, AR, 1024 * MiB)
+    assert big["variant"] == _C.VARIANT_NVLS_PIPE and big["chunk_bytes"] == 64 * MiB and big["rounds"] == 16
+    assert plan(dgn_lib, 8, AR, 16 * MiB)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 8, BC, 64 * MiB)["variant"] == _C.VARIANT_NVLS
+    assert plan(dgn_lib, 8, BC, 64 * KiB)["variant"] == _C.VARIANT_ONESHOT
+
+
+def test_allgather_and_broadcast_variants(dgn_lib):
+    for n, limit in ((2, 512 * KiB), (4, 256 * KiB), (8, 64 * KiB)):
+        assert plan(dgn_lib, n, AG, limit)["variant"] == _C.VARIANT_LL
+        assert plan(dgn_lib, n, AG, limit * 2)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 2, BC, 64 * MiB)["variant"] == _C.VARIANT_ONESHOT      # two ranks: peers pull
+    assert plan(dgn_lib, 8, BC, 512 * KiB)["variant"] == _C.VARIANT_ONESHOT
+    assert plan(dgn_lib, 8, BC, 1 * MiB)["variant"] == _C.VARIANT_TWOSHOT       # scatter + all-gather
+    assert plan(dgn_lib, 4, RS, 16 * MiB)["variant"] == _C.VARIANT_TWOSHOT
+
+
+def test_environment_overrides(dgn_lib, monkeypatch):
+    monkeypatch.setenv("DGN_FORCE_VARIANT", "2")
+    assert plan(dgn_lib, 8, AR, 1 * KiB)["variant"] == _C.VARIANT_TWOSHOT
+    monkeypatch.delenv("DGN_FORCE_VARIANT")
+    monkeypatch.setenv("DGN_LL_MAX_BYTES", "0")
+    monkeypatch.setenv("DGN_LL2_MAX_BYTES", "0")
+    assert plan(dgn_lib, 8, AR, 64 * KiB)["variant"] == _C.VARIANT_ONESHOT
+    assert plan(dgn_lib, 8, AR, 512 * KiB)["variant"] == _C.VARIANT_TWOSHOT
+    monkeypatch.setenv("DGN_NVLS_MIN_BYTES", str(64 * MiB))
+    assert plan(dgn_lib, 4, AR, 64 * MiB)["variant"] == _C.VARIANT_NVLS
+
+
+def test_bad_queries_are_rejected(dgn_lib):
+    z = ctypes.c_int()
+    cb = ctypes.c_int64()
+    args = (ctypes.byref(z), ctypes.byref(z), ctypes.byref(z), ctypes.byref(cb), ctypes.byref(z))
+    assert dgn_lib.dgn_plan_query(1, 148, 1, 0, 0, AR, _C.F32, _C.SUM, 1024, 1, *args) == _C.ERR_ARG
+    assert dgn_lib.dgn_plan_query(8, 148, 1, 0, 0, 7, _C.F32, _C.SUM, 1024, 1, *args) == _C.ERR_ARG
+    assert dgn_lib.dgn_plan_query(8, 148, 1, 0, 0, AR, 99, _C.SUM, 1024, 1, *args) == _C.ERR_ARG
+    assert dgn_lib.dgn_plan_query(8, 148, 1, 0, 0, AR, _C.F32, _C.SUM, 0, 1, *args) == _C.ERR_ARG
