@@ -261,6 +261,7 @@ struct dgn_comm {
   int pipe_switch_blocks = 32;
   long long nvls_bcast_min_bytes = 0;  // smallest broadcast that goes through the switch
   bool plan_query = false, plan_query_in_symm = false;  // dgn_plan_query: no device, no real buffers
+  bool zero_ws = false;  // DGN_ZERO_WS=1: warp-specialised kernels of the sharded optimizer step
 };
 
 namespace {
@@ -303,6 +304,12 @@ int preload_kernels() {
   for (int dtype : zero_types)
     for (int which = 0; which < 3; ++which)
       DGN_CUDA(cudaFuncGetAttributes(&attr, zero_kernel_fn(dtype, which)));
+  // Opt-in kernels: loaded ahead of time as well, but a failure here must not
+  // cost the communicator.
+  for (int dtype : zero_types) {
+    for (int which = 3; which < 5; ++which)
+      if (cudaFuncGetAttributes(&attr, zero_kernel_fn(dtype, which)) != cudaSuccess) cudaGetLastError();
+  }
   return DGN_OK;
 }
 
@@ -683,6 +690,7 @@ void load_thresholds(dgn_comm* c) {
   c->ll_allgather_max_bytes =
       env_ll("DGN_LL_ALLGATHER_MAX_BYTES", nranks <= 2 ? (512ll << 10) : nranks <= 4 ? (256ll << 10) : (64ll << 10));
   c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
+  c->zero_ws = env_ll("DGN_ZERO_WS", 0) != 0;
 }
 
 // Sizes and thresholds of the NVSwitch multicast paths; `symm_request` is the
@@ -740,7 +748,8 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
       break;
     case kOpZeroReduce:
     case kOpZeroUpdate:
-      k.fn = zero_kernel_fn(d.dtype, d.kind == kOpZeroReduce ? 0 : 1);
+      // The warp-specialised versions need two warps at least.
+      k.fn = zero_kernel_fn(d.dtype, (d.kind == kOpZeroReduce ? 0 : 1) + (c->zero_ws && p.threads >= 64 ? 3 : 0));
       k.smem = zero_smem_bytes(d.ntensors);
       break;
   }
