@@ -63,6 +63,12 @@ class Rank(object):
         self.steps.append(("wait", chan, tuple(sources), value))
 
     def signal(self, chan, targets, value):
+        # Every epoch a collective signals lies above the epoch the block had
+        # when it began; together with `end` (below) this is why a flag left by
+        # an earlier collective can never satisfy a wait of a later one.
+        if chan != D:
+            assert value > self.epoch, "signalled epoch {} is not above the base {}".format(value, self.epoch)
+            self.high = max(getattr(self, "high", 0), value)
         self.steps.append(("signal", chan, tuple(targets), value))
 
     def data(self, *accesses):
@@ -82,6 +88,7 @@ class Rank(object):
 
     def end(self, parity, done):
         self.signal(B, self.peers, done)
+        assert self.high <= done, "an epoch above the collective's last one ({}) was signalled".format(done)
         self.epoch, self.ops = done, self.ops + 1
         self.last_done[parity] = done
 
@@ -447,6 +454,7 @@ def _join_and_end(roles, c, parity, done):
         for other in roles:
             rk.local_wait("joined{}".format(other.role), c + 1)
     first.signal(B, first.peers, done)
+    assert all(getattr(rk, "high", 0) <= done for rk in roles)
     first.local_set("ended", c + 1)
     for rk in roles:
         rk.local_wait("ended", c + 1)
