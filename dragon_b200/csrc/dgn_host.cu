@@ -258,7 +258,7 @@ struct dgn_comm {
   // Pipelined multicast all-reduce for ordinary tensors: smallest message,
   // chunk size and number of blocks that drive the switch.
   long long pipe_min_bytes = 0, pipe_chunk_bytes = 0;
-  int pipe_switch_blocks = 32;
+  int pipe_switch_blocks = 32, pipe_copy_blocks = 0, pipe_unroll = 4;
   long long nvls_bcast_min_bytes = 0;  // smallest broadcast that goes through the switch
   bool plan_query = false, plan_query_in_symm = false;  // dgn_plan_query: no device, no real buffers
   bool zero_ws = false;  // DGN_ZERO_WS=1: warp-specialised kernels of the sharded optimizer step
@@ -724,6 +724,8 @@ void load_nvls_settings(dgn_comm* c, long long symm_request) {
   c->pipe_min_bytes = env_ll("DGN_NVLS_PIPE_MIN_BYTES", 1ll << 62);
   c->pipe_chunk_bytes = env_ll("DGN_NVLS_PIPE_CHUNK_BYTES", 0);
   c->pipe_switch_blocks = (int)env_ll("DGN_NVLS_PIPE_SWITCH_BLOCKS", 32);
+  c->pipe_copy_blocks = (int)env_ll("DGN_NVLS_PIPE_COPY_BLOCKS", 0);  // 0: three per SM
+  c->pipe_unroll = env_ll("DGN_NVLS_PIPE_UNROLL", 4) == 8 ? 8 : 4;
 }
 
 struct KernelChoice {
@@ -834,7 +836,8 @@ int issue(dgn_comm* c, const OpDesc& d) {
       P.pipe_cv = p.cv;
       P.pipe_chunks = p.rounds;
       P.pipe_switch_blocks = p.blocks;
-      const int grid = p.blocks + c->num_sms * 3;
+      P.pipe_unroll = c->pipe_unroll;
+      const int grid = p.blocks + (c->pipe_copy_blocks > 0 ? c->pipe_copy_blocks : c->num_sms * 3);
       rc = DGN_OK;
       for (int s = 0; s < p.rounds + 2 && rc == DGN_OK; ++s) {
         P.pipe_step = s;

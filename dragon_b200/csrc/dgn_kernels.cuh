@@ -132,7 +132,7 @@ struct OpParams {
   long long pipe_cv;           // vectors per chunk
   int pipe_step, pipe_chunks;  // this launch's step; chunks of the message
   int pipe_switch_blocks;      // blocks [0, this) drive the switch, the rest copy
-  int reserved3;
+  int pipe_unroll;             // multimem loads in flight per thread of a switch block: 4 or 8
 };
 
 // ---------------------------------------------------------------------------
@@ -1358,6 +1358,30 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_nvls_inplace_kernel(const _
 // more.  With K chunks a message takes K + 2 launches, and in the steady state
 // the link (switch blocks) and local HBM (copy blocks) work at the same time.
 
+// multimem.ld_reduce + multimem.st over vectors first, first + step, ... of a
+// slice, U loads in flight per thread.
+template <typename T, int U>
+__device__ __forceinline__ void switch_reduce_slice(char* mc, long long first, long long len, long long step,
+                                                    bool mean, double scale) {
+  for (long long v0 = first; v0 < len; v0 += U * step) {
+    uint4 x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * step;
+      if (v < len) x[u] = Multimem<T>::ld_reduce(mc + v * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * step;
+      if (v < len) {
+        uint4 y = x[u];
+        if (mean) y = reduce_vectors<T, kSum, 1>(&y, 1, true, scale);
+        Multimem<T>::st(mc + v * 16, y);
+      }
+    }
+  }
+}
+
 template <typename T, bool TABLE>
 __global__ void __launch_bounds__(256, 3) ar_nvls_pipe_kernel(const __grid_constant__ OpParams P) {
   extern __shared__ __align__(16) unsigned char smem[];
@@ -1380,25 +1404,10 @@ __global__ void __launch_bounds__(256, 3) ar_nvls_pipe_kernel(const __grid_const
     const long long len = clampll(clen - lo, 0, vs);
     char* mc = pt.nvls_mc + (long long)(j % 3) * CV * 16 + lo * 16;
     const bool mean = P.redop == kMean;
-    constexpr int U = 4;
     const long long step = (long long)nsw * blockDim.x;
-    for (long long v0 = (long long)b * blockDim.x + threadIdx.x; v0 < len; v0 += U * step) {
-      uint4 x[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long v = v0 + u * step;
-        if (v < len) x[u] = Multimem<T>::ld_reduce(mc + v * 16);
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long v = v0 + u * step;
-        if (v < len) {
-          uint4 y = x[u];
-          if (mean) y = reduce_vectors<T, kSum, 1>(&y, 1, true, P.scale);
-          Multimem<T>::st(mc + v * 16, y);
-        }
-      }
-    }
+    const long long first = (long long)b * blockDim.x + threadIdx.x;
+    if (P.pipe_unroll == 8) switch_reduce_slice<T, 8>(mc, first, len, step, mean, P.scale);
+    else switch_reduce_slice<T, 4>(mc, first, len, step, mean, P.scale);
     end_collective(pt, b, turn, turn.base + 2);
     wait_peers(pt, b, kChanB, turn.base + 2, P.wait_ns);
     return;
