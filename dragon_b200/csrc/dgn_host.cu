@@ -5,7 +5,9 @@
 // The reference reaches its collectives through CollectiveOpImpl
 // (dragon/operators/distributed/collective_op_impl.h:22-158), which forwards
 // to MPI_* or nccl* library calls; here each entry point plans and launches
-// exactly one hand-written kernel (dgn_kernels.cuh) on the caller's stream.
+// its hand-written kernel (dgn_kernels.cuh, dgn_zero.cuh) on the caller's
+// stream: one launch per collective, two for the sharded optimizer step, one
+// per pipeline step for the opt-in pipelined multicast variant.
 #include <cuda_runtime.h>
 
 #include <dirent.h>
