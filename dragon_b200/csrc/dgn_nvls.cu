@@ -416,7 +416,7 @@ int nvls_root_finish(NvlsBuffer* b, int timeout_ms, std::string* err) {
   }
   close(fd);
   if (!ok) return fail(err, "a rank did not join the multicast rendezvous in time");
-  // Round 1: every device added.  Round 2: every buffer bound and mapped.
+  // First exchange: every device added.  Second exchange: every buffer bound and mapped.
   for (int round = 0; round < 2; ++round) {
     char mine = (round == 0 ? add_device(b, err) : bind_and_map(b, err)) == 0 ? '1' : '0';
     char all = mine;
