@@ -23,34 +23,40 @@ namespace dragon {
 template <class Context>
 class ZeroUpdateOpBase : public Operator<Context> {
  public:
-  ZeroUpdateOpBase(const OperatorDef& def, Workspace* ws)
-      : Operator<Context>(def, ws),
-        bucket_name_(OP_SINGLE_ARG(string, "bucket_name", "")),
-        use_lr_scales_(OP_SINGLE_ARG(int64_t, "use_lr_scales", 0)),
-        lr_scales_(OP_REPEATED_ARG(float, "lr_scales")) {
+  ZeroUpdateOpBase(const OperatorDef& def, Workspace* ws) : Operator<Context>(def, ws) {
+    bucket_name_ = OP_SINGLE_ARG(string, "bucket_name", "");
+    lr_scales_ = OP_REPEATED_ARG(float, "lr_scales");
+    use_lr_scales_ = OP_SINGLE_ARG(int64_t, "use_lr_scales", 0);
     coll_impl_.SetBackend(OP_SINGLE_ARG(string, "backend", "MPI"));
-    coll_impl_.SetComm(
-        OP_SINGLE_ARG(int64_t, "comm", 0),
-        OP_SINGLE_ARG(int64_t, "group", 0),
-        OP_REPEATED_ARG(int64_t, "ranks"));
+    coll_impl_.SetComm(OP_SINGLE_ARG(int64_t, "comm", 0), OP_SINGLE_ARG(int64_t, "group", 0),
+                       OP_REPEATED_ARG(int64_t, "ranks"));
   }
   USE_OPERATOR_FUNCTIONS;
 
+  // float16 / bfloat16 / float32 gradients (float64 is refused by the library).
   void RunOnDevice() override { DispatchHelper<dtypes::Floating>::Call(this, Input(0)); }
 
   template <typename T>
+  void DoRunWithType();
+
+ protected:
+  // A hyper-parameter: the first element of the host tensor "<name>/<key>".
+  template <typename T>
   T GetHyper(const string& key) {
-    return this->workspace()->GetTensor(this->name() + "/" + key)->template data<T, CPUContext>()[0];
+    const Tensor* h = this->workspace()->GetTensor(this->name() + "/" + key);
+    return h->template data<T, CPUContext>()[0];
   }
 
+  // A state tensor of this bucket: "<name>/<bucket_name>/<key>".
   Tensor* GetState(const string& key) {
     return this->workspace()->CreateTensor(this->name() + "/" + bucket_name_ + "/" + key);
   }
 
+  // Gradient transform and decay; the `weight_decay` argument, if given, wins over the hyper tensor.
   virtual void GetArguments() {
+    const float wd_arg = OP_SINGLE_ARG(float, "weight_decay", -1.f);
+    weight_decay_ = wd_arg < 0.f ? GetHyper<float>("weight_decay") : wd_arg;
     grad_scale_ = GetHyper<float>("grad_scale");
-    weight_decay_ = OP_SINGLE_ARG(float, "weight_decay", -1.f);
-    if (weight_decay_ < 0.f) weight_decay_ = GetHyper<float>("weight_decay");
     clip_norm_ = GetHyper<float>("clip_norm");
     clip_value_ = GetHyper<float>("clip_value");
   }
@@ -58,15 +64,11 @@ class ZeroUpdateOpBase : public Operator<Context> {
   // What the update kernel receives; the gradient transform is filled in by the base.
   virtual dgn_adamw_args KernelArguments() = 0;
 
-  template <typename T>
-  void DoRunWithType();
-
- protected:
-  string bucket_name_;
-  float grad_scale_ = 1.f, weight_decay_ = 0.f, clip_norm_ = 0.f, clip_value_ = 0.f;
-  int64_t use_lr_scales_;
-  vector<float> lr_scales_;
   CollectiveOpImpl coll_impl_;
+  string bucket_name_;
+  vector<float> lr_scales_;
+  int64_t use_lr_scales_ = 0;
+  float grad_scale_ = 1.f, weight_decay_ = 0.f, clip_norm_ = 0.f, clip_value_ = 0.f;
 };
 
 template <class Context>
