@@ -667,6 +667,18 @@ def test_warp_specialised_sharded_optimizer_step(n, steps):
     assert run_roles(n, lambda me, n_: zero_ws_roles(me, n_, steps)) > 0
 
 
+def test_eight_ranks():
+    """The rank count of the target machine, with fewer rounds."""
+    assert run(8, lambda rk: [nvls_inplace(rk, c) for c in range(2)]) > 0
+    assert run(8, lambda rk: nvls_pipe(rk, 0, 3)) > 0
+    assert run(8, lambda rk: [twoshot_allreduce(rk, c, 2) for c in range(2)]) > 0
+    assert run(8, lambda rk: [(zero_reduce(rk, 2 * c, 3), zero_update(rk, 2 * c + 1, 3)) for c in range(2)]) > 0
+    assert run(8, lambda rk: broadcast_nvls(rk, 0, 3, root=5)) > 0
+    assert run(8, lambda rk: broadcast_scatter(rk, 0, 3, root=5)) > 0
+    assert run(8, lambda rk: allgather(rk, 0, 3)) > 0
+    assert run_roles(5, lambda me, n: zero_ws_roles(me, n, ((3, False),))) > 0
+
+
 def test_the_model_catches_a_missing_wait():
     """The checker itself: without the wait for "pushed" a reduce stage can run
     before the peer's slice has arrived, and with the pusher running two rounds
