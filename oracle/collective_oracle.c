@@ -5,11 +5,20 @@
  * against and the CPU baseline that benchmarks time beside it.  Nothing in the
  * product (the dgn library, the Python package) may call it.
  *
- * PARITY UNPINNED: the reference holds no golden vectors for this path
- * (test/dragon/test_distributed.py:25-52 never moves a byte between ranks) and
- * its arithmetic lives in Open MPI 4.1.2 (third_party/mpi/build.sh:6-12), which
- * is absent from the reference tree and from this machine.  What is restated
- * here is therefore the operator's semantics at its MPI call sites:
+ * PARITY: the 16-bit float converters and the optimizer loops below are pinned
+ * to the reference's own code -- dragon/utils/conversions.h:42-149 and
+ * dragon/kernels/training/cpu/{adam,sgd}_kernel.cc compile on their own behind
+ * the stand-in headers of ref_stub/ (see the Makefile's `ref` target), and
+ * tests/test_oracle_ref.py compares every function here with them, directly
+ * and through committed vectors.  The one intended difference: a float32 above
+ * the float16 range converts to infinity here (IEEE / CUDA / NCCL behaviour),
+ * where conversions.h:52-54 clamps to 0x7bff.
+ * The REDUCTION ORDER stays UNPINNED: the reference holds no golden vectors for
+ * the collectives (test/dragon/test_distributed.py:25-52 never moves a byte
+ * between ranks) and their arithmetic lives in Open MPI 4.1.2
+ * (third_party/mpi/build.sh:6-12), which is absent from the reference tree and
+ * from this machine.  What is restated here is therefore the operator's
+ * semantics at its MPI call sites:
  *
  *   dragon/operators/distributed/collective_op.cc:37-85     operation switch,
  *       output layout of ALLGATHER ([n, *dims]) and REDUCESCATTER (dims[0]/n)
@@ -376,5 +385,29 @@ void orc_adamw(int64_t n, float lr, float beta1, float beta2, float eps, float w
     } else {
       y[i] -= wd > 0.f ? fmaf(wd, y[i], lr * mi / (sqrtf(vi) + eps)) : lr * mi / (sqrtf(vi) + eps);
     }
+  }
+}
+
+/* Adam with coupled weight decay (dragon/kernels/training/cuda/adam_kernel.cu:10-31,
+ * CPU twin cpu/adam_kernel.cc:11-32): x is the parameter before the step; the
+ * callers here pass x == y, as the update operators do. */
+void orc_adam(int64_t n, float lr, float beta1, float beta2, float eps, float wd, const float* g, float* m,
+              float* v, float* y) {
+  for (int64_t i = 0; i < n; ++i) {
+    const float gi = wd > 0.f ? fmaf(wd, y[i], g[i]) : g[i];
+    const float mi = m[i] = fmaf(beta1, m[i], (1.f - beta1) * gi);
+    const float vi = v[i] = fmaf(beta2, v[i], (1.f - beta2) * gi * gi);
+    y[i] -= lr * mi / (sqrtf(vi) + eps);
+  }
+}
+
+/* SGD with momentum, plain or Nesterov (dragon/kernels/training/cuda/sgd_kernel.cu:10-51,
+ * CPU twin cpu/sgd_kernel.cc:10-45). */
+void orc_momentum_sgd(int64_t n, float lr, float momentum, float wd, int nesterov, const float* g, float* m,
+                      float* y) {
+  for (int64_t i = 0; i < n; ++i) {
+    const float gi = wd > 0.f ? fmaf(wd, y[i], g[i]) : g[i];
+    const float mi = m[i] = fmaf(momentum, m[i], gi);
+    y[i] -= nesterov ? lr * fmaf(momentum, mi, gi) : lr * mi;
   }
 }

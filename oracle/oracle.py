@@ -8,10 +8,13 @@ Two checkers live here:
 * the fp64 host sum the tolerance contract is written against
   (max relative error 1e-6 fp32 / 2e-3 fp16 / 1e-2 bf16).
 
-PARITY UNPINNED: the reference has no golden vectors for this path and cannot
-be built or imported on this machine (no MPI, no protoc); see the header of
-collective_oracle.c.  Only tests, the smoke check and the benchmark's CPU
-baseline may import this module.
+PARITY: the 16-bit converters and the optimizer loops are pinned to reference
+code (`ref_lib()`: oracle/_ref/libdragon_ref.so, compiled by `make -C oracle ref`
+from dragon/utils/conversions.h and dragon/kernels/training/cpu/*.cc where they
+lie; tests/test_oracle_ref.py).  The reduction order of the collectives stays
+unpinned: the reference has no golden vectors for them and its MPI library is
+absent; see the header of collective_oracle.c.  Only tests, the smoke check and
+the benchmark's CPU baseline may import this module.
 """
 
 import ctypes
@@ -44,6 +47,41 @@ def build():
     return _LIB
 
 
+_REF_LIB = os.path.join(_DIR, "_ref", "libdragon_ref.so")
+_REFERENCE = os.environ.get("DRAGON_REFERENCE", "/root/reference")
+_ref = None
+
+
+def build_ref():
+    """Compile the reference's converters and CPU optimizer loops (Makefile
+    target `ref`) when the reference tree is present; returns the library path
+    or None.  A prebuilt library is used as it is where the tree is absent."""
+    if os.path.isdir(os.path.join(_REFERENCE, "dragon", "utils")):
+        subprocess.run(["make", "-C", _DIR, "ref", "REFERENCE=" + _REFERENCE], check=True, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT)
+    return _REF_LIB if os.path.exists(_REF_LIB) else None
+
+
+def ref_lib():
+    """ctypes handle of the compiled reference pieces, or None if unavailable."""
+    global _ref
+    if _ref is None:
+        path = build_ref()
+        if path is None:
+            return None
+        h = ctypes.CDLL(path)
+        for name in ("ref_f32_to_f16", "ref_f16_to_f32", "ref_f32_to_bf16", "ref_bf16_to_f32"):
+            getattr(h, name).restype = None
+            getattr(h, name).argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
+        for name in ("ref_adamw", "ref_adam"):
+            getattr(h, name).restype = None
+            getattr(h, name).argtypes = [ctypes.c_int] + [ctypes.c_float] * 5 + [ctypes.c_void_p] * 6 + [ctypes.c_int]
+        h.ref_momentum_sgd.restype = None
+        h.ref_momentum_sgd.argtypes = [ctypes.c_int] + [ctypes.c_float] * 3 + [ctypes.c_void_p] * 5 + [ctypes.c_int] * 2
+        _ref = h
+    return _ref
+
+
 def lib():
     global _lib
     if _lib is None:
@@ -71,6 +109,10 @@ def lib():
         h.orc_bf16_to_f32.argtypes = [ctypes.c_uint16]
         h.orc_adamw.restype = None
         h.orc_adamw.argtypes = [ctypes.c_int64] + [ctypes.c_float] * 5 + [ctypes.c_void_p] * 5
+        h.orc_adam.restype = None
+        h.orc_adam.argtypes = [ctypes.c_int64] + [ctypes.c_float] * 5 + [ctypes.c_void_p] * 4
+        h.orc_momentum_sgd.restype = None
+        h.orc_momentum_sgd.argtypes = [ctypes.c_int64] + [ctypes.c_float] * 3 + [ctypes.c_int] + [ctypes.c_void_p] * 3
         _lib = h
     return _lib
 
@@ -208,6 +250,20 @@ def adamw(g, m, v, y, lr, beta1, beta2, eps, wd, lrs=None):
         lrs = np.ascontiguousarray(lrs, dtype=np.float32)
     lib().orc_adamw(g.size, lr, beta1, beta2, eps, wd, lrs.ctypes.data if lrs is not None else None,
                     g.ctypes.data, m.ctypes.data, v.ctypes.data, y.ctypes.data)
+
+
+def adam(g, m, v, y, lr, beta1, beta2, eps, wd):
+    """In-place Adam (coupled weight decay) on fp32 arrays (orc_adam)."""
+    for a in (g, m, v, y):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    lib().orc_adam(g.size, lr, beta1, beta2, eps, wd, g.ctypes.data, m.ctypes.data, v.ctypes.data, y.ctypes.data)
+
+
+def momentum_sgd(g, m, y, lr, momentum, wd, nesterov=False):
+    """In-place SGD with momentum, plain or Nesterov (orc_momentum_sgd)."""
+    for a in (g, m, y):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    lib().orc_momentum_sgd(g.size, lr, momentum, wd, 1 if nesterov else 0, g.ctypes.data, m.ctypes.data, y.ctypes.data)
 
 
 def zero_shard_count(total, n):
