@@ -18,7 +18,7 @@ OK, ERR_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_PEER, ERR_STATE, ERR_UNSUPPORTED = range
 U8, I8, I32, I64, F16, BF16, F32, F64 = range(8)
 SUM, MEAN, PROD, MIN, MAX = range(5)
 (VARIANT_AUTO, VARIANT_ONESHOT, VARIANT_TWOSHOT, VARIANT_NVLS, VARIANT_LL, VARIANT_LL2, VARIANT_SYMM,
- VARIANT_NVLS_PIPE) = range(8)
+ VARIANT_RING) = range(8)
 
 REDOPS = {"SUM": SUM, "MEAN": MEAN, "PROD": PROD, "MIN": MIN, "MAX": MAX}
 
@@ -45,6 +45,7 @@ SIGNATURES = {
     "dgn_comm_set_wait_limit_ms": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "dgn_comm_set_tuning": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                            ctypes.c_int64]),
+    "dgn_comm_set_knob": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int64]),
     "dgn_comm_has_nvls": (ctypes.c_int, [ctypes.c_void_p]),
     "dgn_allreduce": (ctypes.c_int, [ctypes.c_void_p, _c_void_pp, _c_void_pp, _c_i64_p, ctypes.c_int,
                                      ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),

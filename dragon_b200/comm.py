@@ -183,6 +183,10 @@ class Communicator(object):
     def set_tuning(self, variant=0, blocks=0, threads=0, chunk_bytes=0):
         _C.check(_C.lib().dgn_comm_set_tuning(self._h, variant, blocks, threads, chunk_bytes))
 
+    def set_knob(self, name, value):
+        """Named launch parameter or size threshold (dgn_comm_set_knob); 0 restores the default."""
+        _C.check(_C.lib().dgn_comm_set_knob(self._h, name.encode(), int(value)))
+
     def last_launch(self):
         v, b, t, r = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
         cb = ctypes.c_int64()

@@ -6,8 +6,7 @@
 // (dragon/operators/distributed/collective_op_impl.h:22-158), which forwards
 // to MPI_* or nccl* library calls; here each entry point plans and launches
 // its hand-written kernel (dgn_kernels.cuh, dgn_zero.cuh) on the caller's
-// stream: one launch per collective, two for the sharded optimizer step, one
-// per pipeline step for the opt-in pipelined multicast variant.
+// stream: one launch per collective, two for the sharded optimizer step.
 #include <cuda_runtime.h>
 
 #include <dirent.h>
@@ -131,11 +130,13 @@ uint64_t host_identity() {
 struct Geometry {
   int nranks = 1, max_blocks = 0, ll_max_blocks = 0;
   long long slot_bytes = 0, ll_slot_bytes = 0;
-  size_t flags_bytes = 0, blk_off = 0, stage_off = 0, ll_off = 0, ll2_off = 0, total = 0;
+  size_t flags_bytes = 0, blk_off = 0, flow_state_off = 0, flow_flags_off = 0, stage_off = 0, ll_off = 0,
+         ll2_off = 0, ring_off = 0, ring_bytes = 0, total = 0;
 };
 
-// Workspace layout: [flags][block states] | [staging] | [low-latency region] |
-// [two-shot low-latency region].
+// Workspace layout: [flags][block states][flow state][flow flags] | [staging] |
+// [low-latency region] | [two-shot low-latency region] | [ring of the staged
+// dataflow all-reduce without the switch].
 Geometry make_geometry(int nranks) {
   Geometry g;
   g.nranks = nranks;
@@ -154,10 +155,19 @@ Geometry make_geometry(int nranks) {
   g.flags_bytes = (size_t)g.max_blocks * kChannels * kMaxRanks * sizeof(u64);
   g.blk_off = g.flags_bytes;
   size_t head = g.blk_off + (size_t)g.max_blocks * sizeof(BlockState);
+  g.flow_state_off = (head + 255) & ~(size_t)255;
+  g.flow_flags_off = g.flow_state_off + ((sizeof(FlowState) + 255) & ~(size_t)255);
+  head = g.flow_flags_off + 2 * (size_t)kFlowSlots * kMaxRanks * sizeof(u64);
   g.stage_off = (head + 4095) & ~(size_t)4095;
   g.ll_off = g.stage_off + 2 * (size_t)g.max_blocks * 2 * (size_t)(2 * nranks) * (size_t)g.slot_bytes;
   g.ll2_off = g.ll_off + 2 * (size_t)g.ll_max_blocks * (size_t)nranks * (size_t)g.ll_slot_bytes;
-  g.total = g.ll2_off + 2 * (size_t)g.ll_max_blocks * 2 * (size_t)nranks * (size_t)g.ll_slot_bytes;
+  g.ring_off = g.ll2_off + 2 * (size_t)g.ll_max_blocks * 2 * (size_t)nranks * (size_t)g.ll_slot_bytes;
+  // The multicast version keeps its ring in the multicast-bound buffer; this
+  // one serves communicators without the switch (and virtual ranks).
+  long long ring = nranks > 1 ? env_ll("DGN_RING_BYTES", 64ll << 20) : 0;
+  if (ring < 0) ring = 0;
+  g.ring_bytes = ((size_t)ring + 4095) & ~(size_t)4095;
+  g.total = g.ring_off + g.ring_bytes;
   return g;
 }
 
@@ -175,6 +185,9 @@ struct TableEntry {
 
 struct Plan {
   int variant = 0, blocks = 1, threads = 512, cv = 1, rounds = 1;
+  int unroll = 8;  // multicast kernels: loads in flight per thread
+  // staged dataflow all-reduce: reducing / copy-in blocks (the rest copy out), ring slots, groups
+  int flow_nsw = 0, flow_nin = 0, flow_depth = 0, flow_groups = 1;
 };
 
 enum OpKind { kOpAllReduce = 0, kOpReduceScatter, kOpAllGather, kOpBroadcast, kOpZeroReduce, kOpZeroUpdate };
@@ -257,10 +270,11 @@ struct dgn_comm {
   // dgn_comm_symm_alloc; buffers in it can be reduced in place by the switch.
   size_t symm_bytes = 0, symm_off = 0, symm_used = 0;
   long long symm_min_bytes = 0;
-  // Pipelined multicast all-reduce for ordinary tensors: smallest message,
-  // chunk size and number of blocks that drive the switch.
-  long long pipe_min_bytes = 0, pipe_chunk_bytes = 0;
-  int pipe_switch_blocks = 32, pipe_copy_blocks = 0, pipe_unroll = 4;
+  // Staged dataflow all-reduce (ar_flow_kernel): ring inside the multicast-bound
+  // buffer, chunk size, block split, groups, ring slots, loads in flight (0: automatic).
+  size_t flow_ring_off = 0, flow_ring_bytes = 0;
+  long long flow_chunk_bytes = 0;
+  int flow_switch_blocks = 0, flow_in_blocks = 0, flow_out_blocks = 0, flow_groups = 0, flow_depth = 0, unroll = 0;
   long long nvls_bcast_min_bytes = 0;  // smallest broadcast that goes through the switch
   bool plan_query = false, plan_query_in_symm = false;  // dgn_plan_query: no device, no real buffers
   bool zero_ws = false;  // DGN_ZERO_WS=1: warp-specialised kernels of the sharded optimizer step
@@ -364,6 +378,10 @@ void fill_peer_table(const dgn_comm* c, PeerTable* t) {
   if (c->nvls) nvls_pointers(c->nvls, &t->nvls_uc, &t->nvls_mc);
   t->nvls_slot_bytes = c->nvls_slot_bytes;
   t->nvls_max_blocks = c->nvls_max_blocks;
+  t->flow_state_off = (long long)c->geo.flow_state_off;
+  t->flow_flags_off = (long long)c->geo.flow_flags_off;
+  t->ring_off = (long long)c->geo.ring_off;
+  t->nvls_ring_off = (long long)c->flow_ring_off;
 }
 
 const void* reduce_fn(int dtype, int kind, bool table) {
@@ -422,6 +440,68 @@ bool symm_inplace_ok(const dgn_comm* c, const OpDesc& d) {
   return ((uintptr_t)p & 15u) == 0 && (bytes & 15) == 0;
 }
 
+// Launch shape of the staged dataflow all-reduce (ar_flow_kernel) over a ring of
+// `ring_bytes`; false if the ring or the grid is too small for it.
+bool plan_flow(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring_bytes, int variant, Plan* out) {
+  const int n = c->nranks;
+  const long long bytes = d.nvec * 16;
+  int total = c->num_sms;  // one block per SM, all resident (the blocks wait for one another)
+  if (total > c->geo.max_blocks) total = c->geo.max_blocks;
+  if (block_cap > 0 && block_cap < total) total = block_cap;
+  if (total < 3 || ring_bytes < 2 * 4096) return false;
+  // Chunks: an eighth of the message, between 1 and 32 MiB.  Small chunks fill
+  // and drain the pipeline quickly; large ones keep more loads of one rank's
+  // shard (1/n of a chunk) in flight.
+  long long chunk = c->flow_chunk_bytes;
+  if (c->tune_chunk >= 4096) chunk = c->tune_chunk;
+  if (chunk <= 0) {
+    chunk = ceil_div(bytes, 8);
+    if (chunk < (1ll << 20)) chunk = 1ll << 20;
+    if (chunk > (32ll << 20)) chunk = 32ll << 20;
+  }
+  if (chunk > ring_bytes / 2) chunk = ring_bytes / 2;
+  long long cv = ceil_div(chunk, 16 * (long long)n) * n;  // whole vectors, equal shards
+  if (cv * 16 > ring_bytes / 2) cv = (ring_bytes / 2) / (16 * (long long)n) * n;
+  if (cv < n || cv > 0x7fffffff) return false;
+  const long long K = ceil_div(d.nvec, cv);
+  if (K > 0x7fffffff) return false;
+  int groups = c->flow_groups > 0 ? c->flow_groups : 2;
+  long long depth = ring_bytes / (cv * 16);
+  if (depth > kFlowSlots) depth = kFlowSlots;
+  if (c->flow_depth > 0 && c->flow_depth < depth) depth = c->flow_depth;
+  if (depth > K) depth = K;
+  if (groups > depth) groups = (int)depth;
+  if (groups < 1) groups = 1;
+  depth = depth / groups * groups;
+  int nsw = c->flow_switch_blocks > 0 ? c->flow_switch_blocks : (total >= 148 ? 64 : (total * 3) / 7);
+  if (c->tune_blocks > 0) nsw = c->tune_blocks;
+  if (nsw > total - 2) nsw = total - 2;
+  if (nsw < groups) nsw = groups;
+  if (nsw > total - 2) return false;
+  int nin = c->flow_in_blocks > 0 ? c->flow_in_blocks : (total - nsw) / 2;
+  if (nin > total - nsw - 1) nin = total - nsw - 1;
+  if (nin < 1) nin = 1;
+  int nout = c->flow_out_blocks > 0 ? c->flow_out_blocks : total - nsw - nin;
+  if (nout > total - nsw - nin) nout = total - nsw - nin;
+  if (nout < 1) return false;
+  Plan p;
+  p.variant = variant;
+  p.threads = c->tune_threads > 0 ? c->tune_threads : 512;
+  if (p.threads > kMaxThreads) p.threads = kMaxThreads;
+  p.threads = p.threads / 32 * 32;
+  if (p.threads < 32) p.threads = 32;
+  p.blocks = nsw + nin + nout;
+  p.cv = (int)cv;
+  p.rounds = (int)K;
+  p.unroll = c->unroll > 0 ? c->unroll : 8;
+  p.flow_nsw = nsw;
+  p.flow_nin = nin;
+  p.flow_depth = (int)depth;
+  p.flow_groups = groups;
+  *out = p;
+  return true;
+}
+
 // Chooses variant and launch shape.  `block_cap` bounds the grid (cooperative
 // launches must be fully resident).
 Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
@@ -448,80 +528,30 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
       bool symm = bytes >= c->symm_min_bytes && c->tune_variant == DGN_VARIANT_AUTO;
       if (c->tune_variant == DGN_VARIANT_SYMM) symm = true;
       if (symm) {
-        // No staging: the grid only has to keep enough multimem loads in
-        // flight, and more than about 16 K threads slow the switch path down.
-        // Measured at 2 ranks, 256 MiB: 32 or 64 blocks x 256 threads 668 us,
-        // 64 x 512 700 us, 148 x 512 699 us (64 MiB: 179 / 190 / 194 us).
+        // No staging: the grid only has to keep enough multimem loads in flight.
         if (c->tune_threads <= 0) p.threads = 256;
         const long long vs = ceil_div(d.nvec, n);
         long long b = ceil_div(vs, p.threads);
         int nb = 64;
         if (c->tune_blocks > 0) nb = c->tune_blocks < c->geo.max_blocks ? c->tune_blocks : c->geo.max_blocks;
+        if (block_cap > 0 && nb > block_cap) nb = block_cap;
         if (b > nb) b = nb;
         if (b < 1) b = 1;
         p.variant = DGN_VARIANT_SYMM;
         p.blocks = (int)b;
         p.cv = (int)(ceil_div(vs, b) > 0x7fffffff ? 0x7fffffff : ceil_div(vs, b));
         p.rounds = 1;
-        return p;
-      }
-    }
-    {
-      // Pipelined over launches: chunks through three staging buffers.
-      bool pipe = bytes >= c->pipe_min_bytes && c->tune_variant == DGN_VARIANT_AUTO;
-      if (c->tune_variant == DGN_VARIANT_NVLS_PIPE) pipe = true;
-      const long long zone = (long long)(c->symm_off ? c->symm_off : c->nvls_bytes);  // staging before the arena
-      if (pipe && zone >= 3 * 4096) {
-        long long chunk = c->pipe_chunk_bytes;
-        if (c->tune_chunk >= 4096) chunk = c->tune_chunk;
-        if (chunk <= 0) {
-          // Two chunks up to 128 MiB, then 64 MiB pieces: per launch the flag
-          // exchange costs about 10 us, the switch moves a MiB in about 2 us.
-          chunk = bytes <= (128ll << 20) ? ceil_div(bytes, 2) : (64ll << 20);
-        }
-        if (chunk > zone / 3) chunk = zone / 3;
-        long long cvq = ceil_div(chunk, 16 * (long long)n) * n;  // whole vectors, equal shards
-        if (cvq * 16 > zone / 3) cvq = (zone / 3) / (16 * (long long)n) * n;
-        if (cvq < n) cvq = n;
-        p.variant = DGN_VARIANT_NVLS_PIPE;
-        p.threads = 256;
-        int nsw = c->tune_blocks > 0 ? c->tune_blocks : c->pipe_switch_blocks;
-        if (nsw > c->geo.max_blocks) nsw = c->geo.max_blocks;
-        if (nsw < 1) nsw = 1;
-        p.blocks = nsw;                      // blocks that drive the switch; copy blocks are added at launch
-        p.cv = (int)(cvq > 0x7fffffff ? 0x7fffffff : cvq);
-        p.rounds = (int)ceil_div(d.nvec, cvq);  // chunks
+        p.unroll = c->unroll > 0 ? c->unroll : 8;
         return p;
       }
     }
     bool nvls = bytes >= c->nvls_min_bytes && c->tune_variant == DGN_VARIANT_AUTO;
     if (c->tune_variant == DGN_VARIANT_NVLS) nvls = true;
-    if (nvls) {
-      const long long vs = ceil_div(d.nvec, n);
-      long long cap_v = c->nvls_slot_bytes / 16;
-      if (c->tune_chunk >= 16 && c->tune_chunk / 16 < cap_v) cap_v = c->tune_chunk / 16;
-      int nb = c->nvls_max_blocks < c->num_sms ? c->nvls_max_blocks : c->num_sms;
-      if (c->tune_blocks > 0 && c->tune_blocks < c->nvls_max_blocks) nb = c->tune_blocks;
-      // Full slots in as few rounds as the grid allows, then the smallest
-      // grid that still fills them: 256 MiB at 8 ranks becomes 4 rounds of
-      // 128 blocks x 64 KiB (measured 673 GB/s against 626 for 148 blocks x
-      // 55 KiB); small forced cases get one round.
-      long long rounds = ceil_div(vs, cap_v * nb);
-      if (rounds < 1) rounds = 1;
-      long long b = ceil_div(vs, cap_v * rounds);
-      if (b > nb) b = nb;
-      if (b < 1) b = 1;
-      long long cv = ceil_div(vs, b * rounds);
-      if (cv > cap_v) cv = cap_v;
-      if (cv < 1) cv = 1;
-      p.variant = DGN_VARIANT_NVLS;
-      p.blocks = (int)b;
-      p.cv = (int)cv;
-      p.rounds = (int)ceil_div(vs, b * cv);
-      if (p.threads < 96) p.threads = 96;
-      return p;
-    }
+    if (nvls && plan_flow(c, d, block_cap, (long long)c->flow_ring_bytes, DGN_VARIANT_NVLS, &p)) return p;
   }
+  if (d.kind == kOpAllReduce && c->tune_variant == DGN_VARIANT_RING &&
+      plan_flow(c, d, block_cap, (long long)c->geo.ring_bytes, DGN_VARIANT_RING, &p))
+    return p;
   if (d.kind == kOpAllReduce) {
     const long long bytes = d.nvec * 16;
     // Low-latency one-shot: flag-in-data lines, no barrier at all.
@@ -699,35 +729,42 @@ void load_thresholds(dgn_comm* c) {
 // size of the symmetric arena asked for.  No device is touched.
 void load_nvls_settings(dgn_comm* c, long long symm_request) {
   const int nranks = c->nranks;
-  c->nvls_max_blocks = c->geo.max_blocks;
+  // Layout of the multicast-bound buffer: [staging of the broadcast through the
+  // switch][ring of the staged dataflow all-reduce][symmetric arena].
+  c->nvls_max_blocks = c->geo.max_blocks < 64 ? c->geo.max_blocks : 64;
   c->nvls_slot_bytes = env_ll("DGN_NVLS_SLOT_BYTES", 64 * 1024);
   if (c->nvls_slot_bytes < 4096) c->nvls_slot_bytes = 4096;
   c->nvls_slot_bytes = (c->nvls_slot_bytes + 4095) & ~4095ll;
-  // Measured at n = 8 against the store-only two-shot kernel: 507 vs 561 GB/s
-  // at 128 MiB, 630 vs 605 at 256 MiB, 725 vs 635 at 512 MiB, 764 vs 621 at
-  // 1 GiB.  With fewer ranks the switch saves too little traffic (1.5 S per
-  // direction at n = 2 against 1.0 S), so the variant is opt-in there.
-  c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", nranks >= 8 ? (256ll << 20) : (1ll << 62));
+  const size_t gran = (size_t)2 << 20;
   c->nvls_bytes = 2 * (size_t)c->nvls_max_blocks * 2 * 2 * (size_t)nranks * (size_t)c->nvls_slot_bytes;
-  // Optional symmetric arena behind the staging area (2 MiB granules).
+  c->flow_ring_off = (c->nvls_bytes + gran - 1) / gran * gran;
+  long long ring = env_ll("DGN_NVLS_RING_BYTES", 256ll << 20);
+  if (ring < 0) ring = 0;
+  c->flow_ring_bytes = ((size_t)ring + gran - 1) / gran * gran;
+  c->nvls_bytes = c->flow_ring_off + c->flow_ring_bytes;
+  // Optional symmetric arena behind it (2 MiB granules).
   if (symm_request > 0) {
-    const size_t gran = (size_t)2 << 20;
-    c->symm_off = (c->nvls_bytes + gran - 1) / gran * gran;
+    c->symm_off = c->nvls_bytes;
     c->symm_bytes = ((size_t)symm_request + gran - 1) / gran * gran;
     c->nvls_bytes = c->symm_off + c->symm_bytes;
   }
-  // In place through the switch from this size on.  Measured at 2 ranks:
-  // 25 us at 1 MiB and 33 us at 4 MiB, where the low-latency kernels take
-  // 15-20 us and about 30 us.
-  c->symm_min_bytes = env_ll("DGN_SYMM_MIN_BYTES", 4ll << 20);
-  // Opt-in until it has been measured beside the other large-message kernels
-  // at every rank count.
+  // Staged through the switch from this size on (any tensors, buckets included).
+  // With two ranks the switch saves nothing (1.5 S per direction against 1.0 S
+  // for the store-only two-shot kernel), so it is opt-in there.
+  c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", nranks >= 8 ? (32ll << 20) : (1ll << 62));
+  // In place on symmetric memory from this size on; never by default at two
+  // ranks (measured there: 401 GB/s against 577 GB/s for two-shot at 256 MiB).
+  c->symm_min_bytes = env_ll("DGN_SYMM_MIN_BYTES", nranks <= 2 ? (1ll << 62) : (4ll << 20));
+  // Opt-in until it has been measured beside the other broadcast kernels at
+  // every rank count.
   c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", 1ll << 62);
-  c->pipe_min_bytes = env_ll("DGN_NVLS_PIPE_MIN_BYTES", 1ll << 62);
-  c->pipe_chunk_bytes = env_ll("DGN_NVLS_PIPE_CHUNK_BYTES", 0);
-  c->pipe_switch_blocks = (int)env_ll("DGN_NVLS_PIPE_SWITCH_BLOCKS", 32);
-  c->pipe_copy_blocks = (int)env_ll("DGN_NVLS_PIPE_COPY_BLOCKS", 0);  // 0: three per SM
-  c->pipe_unroll = env_ll("DGN_NVLS_PIPE_UNROLL", 4) == 8 ? 8 : 4;
+  c->flow_chunk_bytes = env_ll("DGN_FLOW_CHUNK_BYTES", 0);
+  c->flow_switch_blocks = (int)env_ll("DGN_FLOW_SWITCH_BLOCKS", 0);
+  c->flow_in_blocks = (int)env_ll("DGN_FLOW_IN_BLOCKS", 0);
+  c->flow_out_blocks = (int)env_ll("DGN_FLOW_OUT_BLOCKS", 0);
+  c->flow_groups = (int)env_ll("DGN_FLOW_GROUPS", 0);
+  c->flow_depth = (int)env_ll("DGN_FLOW_DEPTH", 0);
+  c->unroll = (int)env_ll("DGN_NVLS_UNROLL", 0);
 }
 
 struct KernelChoice {
@@ -740,7 +777,7 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
   const bool table = d.ntensors > 1;
   switch (d.kind) {
     case kOpAllReduce:
-      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_NVLS_PIPE ? 8 : p.variant == DGN_VARIANT_SYMM ? 7 : p.variant == DGN_VARIANT_NVLS ? 6 : p.variant == DGN_VARIANT_LL2 ? 5 : p.variant == DGN_VARIANT_LL ? 3 : (p.variant == DGN_VARIANT_ONESHOT ? 0 : (p.threads >= 96 && p.rounds >= 3 && !c->fused_twoshot ? 4 : 1)), table);
+      k.fn = reduce_fn(d.dtype, p.variant == DGN_VARIANT_RING ? 8 : p.variant == DGN_VARIANT_SYMM ? 7 : p.variant == DGN_VARIANT_NVLS ? 6 : p.variant == DGN_VARIANT_LL2 ? 5 : p.variant == DGN_VARIANT_LL ? 3 : (p.variant == DGN_VARIANT_ONESHOT ? 0 : (p.threads >= 96 && p.rounds >= 3 && !c->fused_twoshot ? 4 : 1)), table);
       k.smem = table ? table_smem_bytes(d.ntensors) : 0;
       break;
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
@@ -771,8 +808,13 @@ void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p)
   P->cv = p.cv;
   P->redop = d.redop;
   P->root = d.root;
-  P->warps_a = (int)env_ll("DGN_NVLS_WARPS_IN", 0);
-  P->warps_b = (int)env_ll("DGN_NVLS_WARPS_REDUCE", 0);
+  P->unroll = p.unroll;
+  P->flow_cv = p.cv;
+  P->flow_chunks = p.rounds;
+  P->flow_depth = p.flow_depth;
+  P->flow_nsw = p.flow_nsw;
+  P->flow_nin = p.flow_nin;
+  P->flow_groups = p.flow_groups;
 }
 
 void fill_zero_params(ZeroParams* Z, const dgn_comm* c, const OpDesc& d, const Plan& p) {
@@ -827,24 +869,15 @@ int issue(dgn_comm* c, const OpDesc& d) {
     KernelChoice k = choose_kernel(c, d, p);
     if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
     int rc;
-    if (d.kind == kOpAllReduce && p.variant == DGN_VARIANT_NVLS_PIPE) {
-      // K chunks take K + 2 launches: copy in / switch / copy out, one chunk apart.
+    if (d.kind == kOpAllReduce && (p.variant == DGN_VARIANT_NVLS || p.variant == DGN_VARIANT_RING)) {
+      // The blocks of the dataflow kernel wait for one another: cooperative launch.
       OpParams P;
       fill_params(&P, c, d, p);
       P.peers[0] = c->table;
       P.ra[0].in = d.in;
       P.ra[0].out = d.out;
       P.ra[0].table = d.table;
-      P.pipe_cv = p.cv;
-      P.pipe_chunks = p.rounds;
-      P.pipe_switch_blocks = p.blocks;
-      P.pipe_unroll = c->pipe_unroll;
-      const int grid = p.blocks + (c->pipe_copy_blocks > 0 ? c->pipe_copy_blocks : c->num_sms * 3);
-      rc = DGN_OK;
-      for (int s = 0; s < p.rounds + 2 && rc == DGN_OK; ++s) {
-        P.pipe_step = s;
-        rc = launch(k.fn, dim3(grid, 1), p.threads, k.smem, d.stream, &P, false);
-      }
+      rc = launch(k.fn, dim3(p.blocks, 1), p.threads, k.smem, d.stream, &P, true);
     } else if (is_zero_kind(d.kind)) {
       ZeroParams Z;
       fill_zero_params(&Z, c, d, p);
@@ -1505,14 +1538,33 @@ int dgn_comm_set_wait_limit_ms(dgn_comm_t c, int ms) {
 
 int dgn_comm_set_tuning(dgn_comm_t c, int variant, int blocks, int threads, int64_t chunk_bytes) {
   if (!c) return fail(DGN_ERR_ARG, "null communicator");
-  if (variant < 0 || variant > DGN_VARIANT_NVLS_PIPE || blocks < 0 || threads < 0 || chunk_bytes < 0)
+  if (variant < 0 || variant > DGN_VARIANT_RING || blocks < 0 || threads < 0 || chunk_bytes < 0)
     return fail(DGN_ERR_ARG, "bad tuning value");
-  if ((variant == DGN_VARIANT_NVLS || variant == DGN_VARIANT_SYMM || variant == DGN_VARIANT_NVLS_PIPE) && !c->nvls)
+  if ((variant == DGN_VARIANT_NVLS || variant == DGN_VARIANT_SYMM) && !c->nvls)
     return fail(DGN_ERR_UNSUPPORTED, "the NVLS variants are not set up on this communicator");
   c->tune_variant = variant;
   c->tune_blocks = blocks;
   c->tune_threads = threads;
   c->tune_chunk = chunk_bytes;
+  return DGN_OK;
+}
+
+int dgn_comm_set_knob(dgn_comm_t c, const char* name, int64_t value) {
+  if (!c || !name) return fail(DGN_ERR_ARG, "null argument");
+  if (value < 0) return fail(DGN_ERR_ARG, "knob %s: negative value", name);
+  const std::string k(name);
+  if (k == "flow_chunk_bytes") c->flow_chunk_bytes = value;
+  else if (k == "flow_switch_blocks") c->flow_switch_blocks = (int)value;
+  else if (k == "flow_in_blocks") c->flow_in_blocks = (int)value;
+  else if (k == "flow_out_blocks") c->flow_out_blocks = (int)value;
+  else if (k == "flow_groups") c->flow_groups = (int)value;
+  else if (k == "flow_depth") c->flow_depth = (int)value;
+  else if (k == "nvls_unroll") c->unroll = (int)value;
+  else if (k == "nvls_min_bytes") c->nvls_min_bytes = value;
+  else if (k == "symm_min_bytes") c->symm_min_bytes = value;
+  else if (k == "nvls_bcast_min_bytes") c->nvls_bcast_min_bytes = value;
+  else if (k == "bcast_scatter_min_bytes") c->bcast_scatter_min_bytes = value;
+  else return fail(DGN_ERR_ARG, "unknown knob '%s'", name);
   return DGN_OK;
 }
 

@@ -98,6 +98,11 @@ struct PeerTable {
   char* nvls_mc;
   long long nvls_slot_bytes;
   int nvls_max_blocks, reserved2;
+  // Staged ring of the dataflow all-reduce (ar_flow_kernel).  Offsets from a
+  // rank's workspace base (= flags[j]): its FlowState, the flag words peers
+  // write, and the ring in ordinary (peer-mapped) memory; the ring of the
+  // multicast version lies at nvls_ring_off inside the multicast-bound buffer.
+  long long flow_state_off, flow_flags_off, ring_off, nvls_ring_off;
 };
 
 // One tensor of a bucket; `vbegin` is its first 16-byte vector in the flat
@@ -127,12 +132,13 @@ struct OpParams {
   int cv;                      // vectors per block per round (<= slot_bytes / 16)
   int redop;
   int root;
-  int warps_a, warps_b;        // warp split of the multicast kernel (0: default)
-  // pipelined multicast all-reduce (ar_nvls_pipe_kernel): one launch per step
-  long long pipe_cv;           // vectors per chunk
-  int pipe_step, pipe_chunks;  // this launch's step; chunks of the message
-  int pipe_switch_blocks;      // blocks [0, this) drive the switch, the rest copy
-  int pipe_unroll;             // multimem loads in flight per thread of a switch block: 4 or 8
+  int unroll;                  // multicast kernels: loads in flight per thread (4, 8 or 16)
+  // staged dataflow all-reduce (ar_flow_kernel)
+  long long flow_cv;           // vectors per chunk
+  int flow_chunks;             // chunks of the message
+  int flow_depth;              // ring slots in use (a multiple of flow_groups)
+  int flow_nsw, flow_nin;      // blocks [0, nsw) reduce, [nsw, nsw + nin) copy in, the rest copy out
+  int flow_groups;             // reducing blocks split into this many groups that take chunks in turn
 };
 
 // ---------------------------------------------------------------------------
@@ -1097,25 +1103,14 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_twoshot_ws_kernel(const __g
 }
 
 // ---------------------------------------------------------------------------
-// ALLREDUCE through NVSwitch multicast ("NVLS"): the switch adds the ranks'
-// copies on a multimem.ld_reduce and replicates a multimem.st to all ranks,
-// so a rank sends and receives about S(1 + 1/n) bytes instead of 2S(n-1)/n.
-// Each rank owns a staging buffer that is bound to one multicast object;
-// for parity p, block b, half h it holds an "in" area and an "out" area of
-// n slots (slot s = the slice rank s owns).  Three warp roles per block:
-//   stage-in : copy my input slices into my "in" area          signal A
-//   reducer  : wait A from all; for my own slice: ld_reduce over all ranks'
-//              "in" slots, scale, multimem.st into everyone's "out" slot
-//                                                              signal B
-//   stage-out: wait B from all; copy my "out" area to my output signal C
-// Flags and epochs are those of the warp-specialised two-shot kernel.  The
-// dependencies between this rank's own roles (my reducer reads my "in" area
-// through the switch, my stage-out reads my "out" area) go through three
-// counters in shared memory.  No TMA and no cluster multicast is involved: multimem
-// instructions address an NVSwitch multicast mapping.
-// The order in which the switch adds is not specified: results satisfy the
-// tolerance contract, are identical on all ranks, but need not match the
-// ascending-rank order of the other kernels bit for bit.
+// NVSwitch multicast ("NVLS"): the switch adds the ranks' copies on a
+// multimem.ld_reduce and replicates a multimem.st to all ranks, so a rank
+// sends and receives about S(1 + 1/n) bytes instead of 2S(n-1)/n.  The
+// instructions address a multicast mapping of memory that every rank has
+// bound to one multicast object at the same offset.  No TMA and no cluster
+// multicast is involved.  The order in which the switch adds is not specified:
+// results satisfy the tolerance contract and are identical on all ranks, but
+// need not match the ascending-rank order of the other kernels bit for bit.
 
 template <typename T> struct Multimem;
 template <> struct Multimem<float> {
@@ -1154,139 +1149,43 @@ template <> struct Multimem<__nv_bfloat16> {
                  :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
   }
 };
-
-// Byte offset of slot `slot` of area `area` (0 in, 1 out) of (parity, block, half).
+// Byte offset of slot `slot` of area `area` (0 in, 1 out) of (parity, block, half)
+// in the multicast-bound staging memory (used by the broadcast through the switch).
 __device__ __forceinline__ long long nvls_offset(const PeerTable& pt, int parity, int b, int half, int area, int slot) {
   const long long idx = ((((long long)parity * pt.nvls_max_blocks + b) * 2 + half) * 2 + area) * pt.nranks + slot;
   return idx * pt.nvls_slot_bytes;
 }
 
-// Spins on a shared-memory counter written by another role of this block.
-__device__ __forceinline__ bool wait_local(const Role& g, volatile int* counter, int target, u64 wait_ns,
-                                           volatile int* abort_flag) {
-  bool ok = true;
-  if (g.t == 0 && *counter < target) {
-    const u64 t0 = global_timer_ns();
-    unsigned spins = 0;
-    while (*counter < target) {
-      if ((++spins & 63u) == 0u && (*abort_flag || global_timer_ns() - t0 > wait_ns)) { ok = false; break; }
+// multimem.ld_reduce + multimem.st over vectors first, first + step, ... of a
+// slice, U loads in flight per thread (a multimem.ld_reduce is a round trip
+// through the switch).  Whole batches of U first, then the remainder in batches
+// of U/2, U/4, ... so that a tail costs a few round trips, not one per vector.
+template <typename T, int U>
+__device__ __forceinline__ void switch_reduce_slice(char* mc, long long first, long long len, long long step,
+                                                    bool mean, double scale) {
+  const long long sb = step * 16;
+  long long v0 = first;
+  for (; v0 + (U - 1) * step < len; v0 += U * step) {
+    char* p = mc + v0 * 16;
+    uint4 x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) x[u] = Multimem<T>::ld_reduce(p + u * sb);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      uint4 y = x[u];
+      if (mean) y = reduce_vectors<T, kSum, 1>(&y, 1, true, scale);
+      Multimem<T>::st(p + u * sb, y);
     }
   }
-  return role_all(g, ok && *abort_flag == 0);
+  if constexpr (U > 1) switch_reduce_slice<T, U / 2>(mc, v0, len, step, mean, scale);
 }
 
-template <typename T, bool TABLE>
-__global__ void __launch_bounds__(kMaxThreads, 1) ar_nvls_kernel(const __grid_constant__ OpParams P) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ int s_abort, s_staged, s_reduced, s_emptied;
-  constexpr int ES = (int)sizeof(T);
-  const PeerTable& pt = P.peers[blockIdx.y];
-  const RankArgs& ra = P.ra[blockIdx.y];
-  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
-  const Message<ES, TABLE> msg = make_message<ES, TABLE>(P, ra, smem);
-  if (threadIdx.x == 0) { s_abort = 0; s_staged = 0; s_reduced = 0; s_emptied = 0; }
-  Turn turn;
-  if (!begin_collective(pt, b, P, &turn)) return;
-
-  const long long vs = (P.nvec + n - 1) / n;
-  auto shard_len = [&](int s) -> long long { return clampll(P.nvec - (long long)s * vs, 0, vs); };
-  const int rounds = P.rounds;
-  const long long cv = P.cv;
-  const long long stride = (long long)gridDim.x * cv;
-  const u64 base = turn.base;
-
-  const int nwarps = blockDim.x >> 5;
-  // A multimem.ld_reduce takes a round trip through the switch, so each
-  // reducer thread keeps eight of them in flight.
-  // The reducer touches 1/n of what the copy roles move.  Measured at n = 8
-  // with 16 warps: 2 reducer warps 674 GB/s, 3: 643, 4: 622, 8: 597 (256 MiB).
-  int w_red = (2 * nwarps) / (n + 8);
-  if (w_red < 2) w_red = 2;
-  int w_in = (nwarps - w_red) >> 1;
-  if (P.warps_a > 0 && P.warps_b > 0 && P.warps_a + P.warps_b < nwarps) { w_in = P.warps_a; w_red = P.warps_b; }
-  if (w_in < 1) w_in = 1;
-  if (w_red < 1) w_red = 1;
-  const int warp = threadIdx.x >> 5;
-  Role g;
-  int role;
-  if (warp < w_in) { role = 0; g.id = 1; g.t = threadIdx.x; g.n = w_in * 32; }
-  else if (warp < w_in + w_red) { role = 1; g.id = 2; g.t = threadIdx.x - w_in * 32; g.n = w_red * 32; }
-  else { role = 2; g.id = 3; g.t = threadIdx.x - (w_in + w_red) * 32; g.n = (nwarps - w_in - w_red) * 32; }
-  volatile int* abort_flag = &s_abort;
-  bool alive = true;
-
-  if (role == 0) {  // stage-in
-    for (int i = 0; i < rounds; ++i) {
-      if (i >= kDepth) {
-        if (!role_wait(pt, g, b, kChanB, base + (u64)(i - kDepth) + 1, P.wait_ns, abort_flag) ||
-            !wait_local(g, &s_reduced, i - kDepth + 1, P.wait_ns, abort_flag)) { alive = false; break; }
-      }
-      const long long off = (long long)i * stride + (long long)b * cv;
-      for (int s = 0; s < n; ++s) {
-        const long long len = clampll(shard_len(s) - off, 0, cv);
-        char* dst = pt.nvls_uc + nvls_offset(pt, turn.parity, b, i % kDepth, 0, s);
-        const long long ibase = (long long)s * vs + off;
-        role_copy<8>(g, len, [&](long long v) { return msg.load(ibase + v); },
-                     [&](long long v, uint4 x) { stv(dst + v * 16, x); });
-      }
-      role_signal(pt, g, b, kChanA, base + (u64)i + 1);
-      // The switch also reads this rank's own copy: tell my reducer it is complete.
-      if (g.t == 0) { __threadfence_system(); s_staged = i + 1; }
-    }
-  } else if (role == 1) {  // reducer
-    const long long mylen_total = shard_len(r);
-    const bool mean = P.redop == kMean;
-    for (int j = 0; j < rounds; ++j) {
-      if (!role_wait(pt, g, b, kChanA, base + (u64)j + 1, P.wait_ns, abort_flag) ||
-          !wait_local(g, &s_staged, j + 1, P.wait_ns, abort_flag)) { alive = false; break; }
-      if (j >= kDepth) {
-        if (!role_wait(pt, g, b, kChanC, base + (u64)(j - kDepth) + 1, P.wait_ns, abort_flag) ||
-            !wait_local(g, &s_emptied, j - kDepth + 1, P.wait_ns, abort_flag)) { alive = false; break; }
-      }
-      const long long off = (long long)j * stride + (long long)b * cv;
-      const long long len = clampll(mylen_total - off, 0, cv);
-      const char* src = pt.nvls_mc + nvls_offset(pt, turn.parity, b, j % kDepth, 0, r);
-      char* dst = pt.nvls_mc + nvls_offset(pt, turn.parity, b, j % kDepth, 1, r);
-      constexpr int kRed = 8;
-      for (long long v0 = g.t; v0 < len; v0 += (long long)kRed * g.n) {
-        uint4 x[kRed];
-#pragma unroll
-        for (int u = 0; u < kRed; ++u) {
-          const long long v = v0 + (long long)u * g.n;
-          if (v < len) x[u] = Multimem<T>::ld_reduce(src + v * 16);
-        }
-#pragma unroll
-        for (int u = 0; u < kRed; ++u) {
-          const long long v = v0 + (long long)u * g.n;
-          if (v < len) {
-            uint4 y = x[u];
-            if (mean) y = reduce_vectors<T, kSum, 1>(&y, 1, true, P.scale);
-            Multimem<T>::st(dst + v * 16, y);
-          }
-        }
-      }
-      role_signal(pt, g, b, kChanB, base + (u64)j + 1);  // barrier inside: the whole role is done
-      // My own stage-out reads what my multimem stores left in my memory.
-      if (g.t == 0) { __threadfence_system(); s_reduced = j + 1; }
-    }
-  } else {  // stage-out
-    for (int j = 0; j < rounds; ++j) {
-      if (!role_wait(pt, g, b, kChanB, base + (u64)j + 1, P.wait_ns, abort_flag) ||
-          !wait_local(g, &s_reduced, j + 1, P.wait_ns, abort_flag)) { alive = false; break; }
-      const long long off = (long long)j * stride + (long long)b * cv;
-      for (int s = 0; s < n; ++s) {
-        const long long len = clampll(shard_len(s) - off, 0, cv);
-        const char* src = pt.nvls_uc + nvls_offset(pt, turn.parity, b, j % kDepth, 1, s);
-        const long long obase = (long long)s * vs + off;
-        role_copy<8>(g, len, [&](long long v) { return ldv(src + v * 16); },
-                     [&](long long v, uint4 x) { msg.store(obase + v, x); });
-      }
-      role_signal(pt, g, b, kChanC, base + (u64)j + 1);
-      if (g.t == 0) { __threadfence_block(); s_emptied = j + 1; }
-    }
-  }
-  if (__syncthreads_or(!alive)) return;
-  end_collective(pt, b, turn, base + (u64)rounds + 1);
+template <typename T>
+__device__ __forceinline__ void switch_reduce_dispatch(int unroll, char* mc, long long first, long long len,
+                                                       long long step, bool mean, double scale) {
+  if (unroll >= 16) switch_reduce_slice<T, 16>(mc, first, len, step, mean, scale);
+  else if (unroll >= 8) switch_reduce_slice<T, 8>(mc, first, len, step, mean, scale);
+  else switch_reduce_slice<T, 4>(mc, first, len, step, mean, scale);
 }
 
 // ---------------------------------------------------------------------------
@@ -1316,140 +1215,260 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_nvls_inplace_kernel(const _
   const long long lo = (long long)r * vs;
   const long long len = clampll(P.nvec - lo, 0, vs);
   char* mc = pt.nvls_mc + (static_cast<char*>(ra.out) - pt.nvls_uc) + lo * 16;
-  const bool mean = P.redop == kMean;
-  constexpr int U = 8;  // a multimem.ld_reduce is a round trip through the switch: keep eight in flight
   const long long step = (long long)gridDim.x * blockDim.x;
-  for (long long v0 = (long long)b * blockDim.x + threadIdx.x; v0 < len; v0 += U * step) {
-    uint4 x[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + u * step;
-      if (v < len) x[u] = Multimem<T>::ld_reduce(mc + v * 16);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + u * step;
-      if (v < len) {
-        uint4 y = x[u];
-        if (mean) y = reduce_vectors<T, kSum, 1>(&y, 1, true, P.scale);
-        Multimem<T>::st(mc + v * 16, y);
-      }
-    }
-  }
+  switch_reduce_dispatch<T>(P.unroll, mc, (long long)b * blockDim.x + threadIdx.x, len, step, P.redop == kMean,
+                            P.scale);
   end_collective(pt, b, turn, turn.base + 2);  // barrier, then the release store of "done"
   wait_peers(pt, b, kChanB, turn.base + 2, P.wait_ns);
 }
 
 // ---------------------------------------------------------------------------
-// ALLREDUCE through NVSwitch multicast for ordinary tensors, pipelined over
-// launches.  The message is cut into chunks; three chunk buffers live in the
-// multicast-bound staging memory.  Launch number s of a message runs, side by
-// side in one grid,
-//   copy blocks   : chunk s   from the input tensors into buffer s % 3, and
-//                   chunk s-2 from buffer (s-2) % 3 into the output tensors
-//                   (local HBM traffic, no peer involved);
-//   switch blocks : chunk s-1, in place in buffer (s-1) % 3, exactly as
-//                   ar_nvls_inplace_kernel does (ready / done flag exchange
-//                   around multimem.ld_reduce + multimem.st of the own shard).
-// The kernel boundary orders the stages of one chunk on this rank; a peer's
-// "ready" flag of launch s is sent after its launch s-1 has finished, i.e.
-// after its copy of chunk s-1 is complete; this rank's launch s ends only after
-// every peer's "done", i.e. after nobody reads or writes buffer (s-1) % 3 any
-// more.  With K chunks a message takes K + 2 launches, and in the steady state
-// the link (switch blocks) and local HBM (copy blocks) work at the same time.
+// ALLREDUCE of ordinary tensors (one tensor or a bucket) through a staged ring,
+// as one persistent dataflow kernel.  The message is cut into chunks of
+// flow_cv vectors; a ring of flow_depth chunk buffers lives at the same offset
+// in every rank's memory.  Three groups of thread blocks work side by side:
+//   copy-in  blocks: tensors -> ring slot of chunk c, as soon as the slot is free
+//   reducing blocks: own shard of chunk c, in place in the ring on all ranks
+//   copy-out blocks: ring slot of chunk c -> tensors
+// SWITCH = true: the ring lies in multicast-bound memory; the reducing blocks
+// use multimem.ld_reduce (the switch adds all ranks' copies) and multimem.st
+// (the switch writes the result into every rank's ring): about S(1 + 1/n) link
+// bytes per direction.  SWITCH = false: the ring lies in the peer-mapped
+// workspace; the reducing blocks load the n copies of their shard from the
+// ranks' rings, add in ascending rank order and store the result into every
+// ring (bit-identical to the other ordered kernels; works on any communicator,
+// virtual ranks on one device included).
+//
+// Dependencies, per chunk c in ring slot s = c % depth (FlowState counters are
+// local to the rank, flag words are written by peers):
+//   in_done[s]    += 1 per copy-in block          the last one sends ready(c)
+//   ready(c) from every rank, in_done complete    -> reduce chunk c
+//   sw_done[s]    += 1 per reducing warp          the last one sends done(c)
+//   done(c) from every rank, sw_done complete     -> copy chunk c out
+//   out_done[s]   += 1 per copy-out block; complete for chunk c -> copy-in of chunk c + depth
+// done(c) from a peer also means that the peer has stopped reading this rank's
+// slot s, so refilling the slot after the copy-out is safe.  Reducing warps
+// never wait for a barrier: each warp streams through its chunks on its own,
+// so the load round trips of different warps overlap across chunk borders.
+// The reducing blocks are split into flow_groups groups that take chunks in
+// turn (depth is a multiple of the group count, so a slot always belongs to
+// one group).  Flag values are base + c + 1 with base = chunks moved by all
+// earlier launches of this kernel (kept in FlowState, advanced by the last
+// block to leave), separate per ring slot so that they only ever grow.
+// The kernel is launched cooperatively: its blocks wait for one another.
 
-// multimem.ld_reduce + multimem.st over vectors first, first + step, ... of a
-// slice, U loads in flight per thread.
-template <typename T, int U>
-__device__ __forceinline__ void switch_reduce_slice(char* mc, long long first, long long len, long long step,
-                                                    bool mean, double scale) {
-  for (long long v0 = first; v0 < len; v0 += U * step) {
-    uint4 x[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + u * step;
-      if (v < len) x[u] = Multimem<T>::ld_reduce(mc + v * 16);
+constexpr int kFlowSlots = 8;
+
+struct FlowState {
+  u64 base;                       // chunks published by earlier launches; equal on all ranks
+  unsigned exit_count;            // blocks that have left the running launch
+  unsigned reserved;
+  unsigned in_done[kFlowSlots];   // zero between launches
+  unsigned sw_done[kFlowSlots];
+  unsigned out_done[kFlowSlots];
+};
+
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ FlowState* flow_state(const PeerTable& pt) {
+  return reinterpret_cast<FlowState*>(reinterpret_cast<char*>(pt.flags[pt.rank]) + pt.flow_state_off);
+}
+// Flag word of kind (0 ready, 1 done), ring slot s, written by rank `src`, in rank `owner`'s workspace.
+__device__ __forceinline__ u64* flow_flag(const PeerTable& pt, int owner, int kind, int s, int src) {
+  return reinterpret_cast<u64*>(reinterpret_cast<char*>(pt.flags[owner]) + pt.flow_flags_off) +
+         ((size_t)kind * kFlowSlots + s) * kMaxRanks + src;
+}
+
+// One thread waits until a local counter reaches `target`; false when the limit ran out.
+__device__ __forceinline__ bool flow_wait_counter(const unsigned* counter, unsigned target, u64 wait_ns, int* status) {
+  if (ld_acquire_gpu_u32(counter) >= target) return true;
+  const u64 t0 = global_timer_ns();
+  unsigned spins = 0;
+  for (;;) {
+    if (ld_acquire_gpu_u32(counter) >= target) return true;
+    if ((++spins & 31u) == 0u && global_timer_ns() - t0 > wait_ns) {
+      *(volatile int*)status = kErrTimeout;
+      return false;
     }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + u * step;
-      if (v < len) {
-        uint4 y = x[u];
-        if (mean) y = reduce_vectors<T, kSum, 1>(&y, 1, true, scale);
-        Multimem<T>::st(mc + v * 16, y);
-      }
+  }
+}
+__device__ __forceinline__ bool flow_wait_flag(const u64* flag, u64 target, u64 wait_ns, int* status) {
+  if (ld_acquire_sys(flag) >= target) return true;
+  const u64 t0 = global_timer_ns();
+  unsigned spins = 0;
+  for (;;) {
+    if (ld_acquire_sys(flag) >= target) return true;
+    if ((++spins & 31u) == 0u && global_timer_ns() - t0 > wait_ns) {
+      *(volatile int*)status = kErrTimeout;
+      return false;
     }
   }
 }
 
-template <typename T, bool TABLE>
-__global__ void __launch_bounds__(256, 3) ar_nvls_pipe_kernel(const __grid_constant__ OpParams P) {
+// Thread 0 of a block (after a barrier) or lane 0 of a warp (after __syncwarp)
+// adds one to `counter`; when that completes `target` it tells every peer, on
+// flag (kind, s), that epoch `val` is reached.  The fences make everything the
+// counted blocks or warps have written visible before the flag.
+__device__ __forceinline__ void flow_arrive(const PeerTable& pt, unsigned* counter, unsigned target, int kind, int s,
+                                            u64 val) {
+  __threadfence_system();
+  const unsigned old = atomicAdd(counter, 1u);
+  if (old + 1u == target) {
+    __threadfence_system();
+    for (int j = 0; j < pt.nranks; ++j)
+      if (j != pt.rank) st_release_sys(flow_flag(pt, j, kind, s, pt.rank), val);
+  }
+}
+
+// Reduce stage without the switch: vectors first, first + step, ... of the own
+// shard; n loads (one per rank's ring), ascending-rank reduction, n stores.
+template <typename T>
+__device__ __forceinline__ void plain_reduce_slice(const PeerTable& pt, long long ring_byte_off, long long first,
+                                                   long long len, long long step, int redop, double scale) {
+  const int n = pt.nranks;
+  for (long long v = first; v < len; v += step) {
+    uint4 x[kMaxRanks];
+#pragma unroll
+    for (int j = 0; j < kMaxRanks; ++j)
+      if (j < n) x[j] = ldv(reinterpret_cast<char*>(pt.flags[j]) + pt.ring_off + ring_byte_off + v * 16);
+    const uint4 y = reduce_dispatch<T>(x, n, redop, scale);
+#pragma unroll
+    for (int j = 0; j < kMaxRanks; ++j)
+      if (j < n) stv(reinterpret_cast<char*>(pt.flags[j]) + pt.ring_off + ring_byte_off + v * 16, y);
+  }
+}
+
+template <typename T, bool TABLE, bool SWITCH>
+__global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_constant__ OpParams P) {
   extern __shared__ __align__(16) unsigned char smem[];
   constexpr int ES = (int)sizeof(T);
-  const PeerTable& pt = P.peers[0];
-  const RankArgs& ra = P.ra[0];
-  const int r = pt.rank, n = pt.nranks;
-  const int s = P.pipe_step, K = P.pipe_chunks, nsw = P.pipe_switch_blocks;
-  const long long CV = P.pipe_cv;
-  if ((int)blockIdx.x < nsw) {
-    const int j = s - 1, b = blockIdx.x;
-    if (j < 0 || j >= K) return;
-    Turn turn;
-    if (!begin_collective(pt, b, P, &turn)) return;
-    signal_peers(pt, b, kChanA, turn.base + 1);
-    if (!wait_peers(pt, b, kChanA, turn.base + 1, P.wait_ns)) return;
-    const long long clen = clampll(P.nvec - (long long)j * CV, 0, CV);
-    const long long vs = (clen + n - 1) / n;
-    const long long lo = (long long)r * vs;
-    const long long len = clampll(clen - lo, 0, vs);
-    char* mc = pt.nvls_mc + (long long)(j % 3) * CV * 16 + lo * 16;
-    const bool mean = P.redop == kMean;
-    const long long step = (long long)nsw * blockDim.x;
-    const long long first = (long long)b * blockDim.x + threadIdx.x;
-    if (P.pipe_unroll == 8) switch_reduce_slice<T, 8>(mc, first, len, step, mean, P.scale);
-    else switch_reduce_slice<T, 4>(mc, first, len, step, mean, P.scale);
-    end_collective(pt, b, turn, turn.base + 2);
-    wait_peers(pt, b, kChanB, turn.base + 2, P.wait_ns);
-    return;
-  }
-  // copy blocks
-  const Message<ES, TABLE> msg = make_message<ES, TABLE>(P, ra, smem);
-  const long long cstep = (long long)(gridDim.x - nsw) * blockDim.x;
-  const long long first = (long long)(blockIdx.x - nsw) * blockDim.x + threadIdx.x;
-  if (s < K) {  // chunk s: tensors -> buffer
-    const long long clen = clampll(P.nvec - (long long)s * CV, 0, CV);
-    char* dst = pt.nvls_uc + (long long)(s % 3) * CV * 16;
-    const long long base = (long long)s * CV;
-    long long v = first;
-    for (; v + 3 * cstep < clen; v += 4 * cstep) {
-      const uint4 a = msg.load(base + v), b2 = msg.load(base + v + cstep), c = msg.load(base + v + 2 * cstep),
-                  d = msg.load(base + v + 3 * cstep);
-      stv(dst + v * 16, a); stv(dst + (v + cstep) * 16, b2); stv(dst + (v + 2 * cstep) * 16, c);
-      stv(dst + (v + 3 * cstep) * 16, d);
+  const PeerTable& pt = P.peers[blockIdx.y];
+  const RankArgs& ra = P.ra[blockIdx.y];
+  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
+  FlowState* fs = flow_state(pt);
+  const u64 base = fs->base;  // written by the last block of the previous launch
+  const int K = P.flow_chunks, D = P.flow_depth, G = P.flow_groups;
+  const int nsw = P.flow_nsw, nin = P.flow_nin, nout = (int)gridDim.x - nsw - nin;
+  const long long CV = P.flow_cv;
+  char* const ring = SWITCH ? pt.nvls_uc + pt.nvls_ring_off : reinterpret_cast<char*>(pt.flags[r]) + pt.ring_off;
+  const int nwarps = blockDim.x >> 5;
+  bool ok = true;
+
+  if (b < nsw) {
+    // Reducing block: every warp on its own.
+    const int g = b % G, bi = b / G;
+    const int group_blocks = (nsw - g + G - 1) / G;
+    const unsigned warps_per_chunk = (unsigned)(group_blocks * nwarps);
+    const int lane = threadIdx.x & 31;
+    const long long gw = (long long)bi * nwarps + (threadIdx.x >> 5);  // warp index inside the group
+    const long long step = (long long)warps_per_chunk * 32;
+    for (int c = g; c < K && ok; c += G) {
+      const int s = c % D;
+      const unsigned use = (unsigned)(c / D) + 1u;
+      if (lane == 0) ok = flow_wait_counter(&fs->in_done[s], (unsigned)nin * use, P.wait_ns, pt.status);
+      else if (lane <= n && lane - 1 != r && lane - 1 < n)
+        ok = flow_wait_flag(flow_flag(pt, r, 0, s, lane - 1), base + (u64)c + 1, P.wait_ns, pt.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
+      const long long vs = (clen + n - 1) / n;
+      const long long lo = (long long)r * vs;
+      const long long len = clampll(clen - lo, 0, vs);
+      const long long off = ((long long)s * CV + lo) * 16;
+      if constexpr (SWITCH)
+        switch_reduce_dispatch<T>(P.unroll, pt.nvls_mc + pt.nvls_ring_off + off, gw * 32 + lane, len, step,
+                                  P.redop == kMean, P.scale);
+      else
+        plain_reduce_slice<T>(pt, off, gw * 32 + lane, len, step, P.redop, P.scale);
+      __syncwarp();
+      if (lane == 0) flow_arrive(pt, &fs->sw_done[s], warps_per_chunk * use, 1, s, base + (u64)c + 1);
     }
-    for (; v < clen; v += cstep) stv(dst + v * 16, msg.load(base + v));
-  }
-  if (s >= 2 && s - 2 < K) {  // chunk s-2: buffer -> tensors
-    const int j = s - 2;
-    const long long clen = clampll(P.nvec - (long long)j * CV, 0, CV);
-    const char* src = pt.nvls_uc + (long long)(j % 3) * CV * 16;
-    const long long base = (long long)j * CV;
-    long long v = first;
-    for (; v + 3 * cstep < clen; v += 4 * cstep) {
-      const uint4 a = ldv(src + v * 16), b2 = ldv(src + (v + cstep) * 16), c = ldv(src + (v + 2 * cstep) * 16),
-                  d = ldv(src + (v + 3 * cstep) * 16);
-      msg.store(base + v, a); msg.store(base + v + cstep, b2); msg.store(base + v + 2 * cstep, c);
-      msg.store(base + v + 3 * cstep, d);
+  } else if (b < nsw + nin) {
+    const Message<ES, TABLE> msg = make_message<ES, TABLE>(P, ra, smem);
+    const long long first = (long long)(b - nsw) * blockDim.x + threadIdx.x;
+    const long long step = (long long)nin * blockDim.x;
+    for (int c = 0; c < K; ++c) {
+      const int s = c % D;
+      const unsigned use = (unsigned)(c / D) + 1u;
+      if (c >= D) {  // the slot is free once chunk c - D has been copied out
+        if (threadIdx.x == 0) ok = flow_wait_counter(&fs->out_done[s], (unsigned)nout * (use - 1u), P.wait_ns, pt.status);
+        ok = __syncthreads_and(ok) != 0;
+        if (!ok) break;
+      }
+      const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
+      const long long vbase = (long long)c * CV;
+      char* dst = ring + (long long)s * CV * 16;
+      long long v = first;
+      for (; v + 3 * step < clen; v += 4 * step) {
+        const uint4 x0 = msg.load(vbase + v), x1 = msg.load(vbase + v + step), x2 = msg.load(vbase + v + 2 * step),
+                    x3 = msg.load(vbase + v + 3 * step);
+        stv(dst + v * 16, x0); stv(dst + (v + step) * 16, x1); stv(dst + (v + 2 * step) * 16, x2);
+        stv(dst + (v + 3 * step) * 16, x3);
+      }
+      for (; v < clen; v += step) stv(dst + v * 16, msg.load(vbase + v));
+      __syncthreads();
+      if (threadIdx.x == 0) flow_arrive(pt, &fs->in_done[s], (unsigned)nin * use, 0, s, base + (u64)c + 1);
     }
-    for (; v < clen; v += cstep) msg.store(base + v, ldv(src + v * 16));
+  } else {
+    const Message<ES, TABLE> msg = make_message<ES, TABLE>(P, ra, smem);
+    const long long first = (long long)(b - nsw - nin) * blockDim.x + threadIdx.x;
+    const long long step = (long long)nout * blockDim.x;
+    for (int c = 0; c < K; ++c) {
+      const int s = c % D;
+      const unsigned use = (unsigned)(c / D) + 1u;
+      const int g = c % G;
+      const unsigned warps_per_chunk = (unsigned)(((nsw - g + G - 1) / G) * nwarps);
+      const int t = threadIdx.x;
+      if (t == 0) ok = flow_wait_counter(&fs->sw_done[s], warps_per_chunk * use, P.wait_ns, pt.status);
+      else if (t <= n && t - 1 != r)
+        ok = flow_wait_flag(flow_flag(pt, r, 1, s, t - 1), base + (u64)c + 1, P.wait_ns, pt.status);
+      ok = __syncthreads_and(ok) != 0;
+      if (!ok) break;
+      const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
+      const long long vbase = (long long)c * CV;
+      const char* src = ring + (long long)s * CV * 16;
+      long long v = first;
+      for (; v + 3 * step < clen; v += 4 * step) {
+        const uint4 x0 = ldv(src + v * 16), x1 = ldv(src + (v + step) * 16), x2 = ldv(src + (v + 2 * step) * 16),
+                    x3 = ldv(src + (v + 3 * step) * 16);
+        msg.store(vbase + v, x0); msg.store(vbase + v + step, x1); msg.store(vbase + v + 2 * step, x2);
+        msg.store(vbase + v + 3 * step, x3);
+      }
+      for (; v < clen; v += step) msg.store(vbase + v, ldv(src + v * 16));
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(&fs->out_done[s], 1u);
+      }
+    }
+  }
+  // The last block to leave resets the counters and advances the epoch base.
+  if (!__syncthreads_and(ok)) return;  // a wait ran out: the communicator is unusable from here on
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&fs->exit_count, 1u) + 1u == gridDim.x) {
+      for (int s = 0; s < kFlowSlots; ++s) { fs->in_done[s] = 0u; fs->sw_done[s] = 0u; fs->out_done[s] = 0u; }
+      fs->exit_count = 0u;
+      fs->base = base + (u64)K;
+      __threadfence();
+    }
   }
 }
 
 // ---------------------------------------------------------------------------
-// ALLGATHER (bytes).  Per round: copy my slice to my outbox and to my own
-// block of the output, signal (A), then pull every peer's outbox into its
-// block of my output and signal (B) that the outbox may be overwritten.
-// Outbox halves alternate per round, so the wait for B lags one round.
+// ALLGATHER (bytes), stores only.  Per round every rank stores its slice into
+// gather box [r] of every peer (and into its own block of the output), signals
+// (A), waits for all peers' slices, copies its gather boxes into the peers'
+// blocks of the output and signals (B) that the boxes are empty.  The push of
+// round i + 1 is issued before the local copy of round i, so the link keeps
+// working while boxes are emptied; box halves alternate per round, and a half
+// is refilled only after B of the round that used it came from every peer.
+// Peer traffic is remote stores exclusively (the fastest pattern on NVLink).
+// Epochs of round i: A = base+2i+1, B = base+2i+2; done = base+2*rounds+1 (B).
 // `count` is bytes per rank here.
 
 template <int kUnused>
@@ -1465,32 +1484,45 @@ __global__ void __launch_bounds__(kMaxThreads, 1) allgather_kernel(const __grid_
   char* mine = out + (long long)r * P.count;
   const bool mine_al = is_al16(mine);
   const long long cv = P.cv;
+  const int R = P.rounds;
 
-  for (int round = 0; round < P.rounds; ++round) {
+  auto push = [&](int round) -> bool {
+    // Peers emptied this half two rounds ago.
+    if (round >= 2 && !wait_peers(pt, b, kChanB, turn.base + 2 * (u64)(round - 2) + 2, P.wait_ns)) return false;
     const long long off = ((long long)round * gridDim.x + b) * cv;
     const long long len = clampll(P.nvec - off, 0, cv);
-    const u64 e_pub = turn.base + 2 * (u64)round + 1, e_got = e_pub + 1;
-    // The half written now was pulled by the peers two rounds ago.
-    if (round >= 2 && !wait_peers(pt, b, kChanB, turn.base + 2 * (u64)(round - 2) + 2, P.wait_ns)) return;
-    char* outbox = slot_ptr(pt, r, turn.parity, b, round & 1, n);
+    char* dst[kMaxRanks];
+#pragma unroll
+    for (int k = 1; k < kMaxRanks; ++k)
+      dst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, turn.parity, b, round & 1, n + r) : nullptr;
     copy_vectors(len, [&](long long v) { return load_vec<1>(in, off + v, P.count, in_al); },
                  [&](long long v, uint4 x) {
-                   stv(outbox + v * 16, x);
                    if (mine != in) store_vec<1>(mine, off + v, P.count, mine_al, x);
+#pragma unroll
+                   for (int k = 1; k < kMaxRanks; ++k)
+                     if (k < n) stv(dst[k] + v * 16, x);
                  });
-    signal_peers(pt, b, kChanA, e_pub);
-    if (!wait_peers(pt, b, kChanA, e_pub, P.wait_ns)) return;
+    signal_peers(pt, b, kChanA, turn.base + 2 * (u64)round + 1);
+    return true;
+  };
+
+  if (!push(0)) return;
+  for (int round = 0; round < R; ++round) {
+    if (round + 1 < R && !push(round + 1)) return;
+    if (!wait_peers(pt, b, kChanA, turn.base + 2 * (u64)round + 1, P.wait_ns)) return;
+    const long long off = ((long long)round * gridDim.x + b) * cv;
+    const long long len = clampll(P.nvec - off, 0, cv);
     for (int k = 1; k < n; ++k) {
-      const int peer = (r + 1 + (k - 1 + b) % (n - 1)) % n;
-      const char* src = slot_ptr(pt, peer, turn.parity, b, round & 1, n);
+      const int peer = (r + k) % n;
+      const char* src = slot_ptr(pt, r, turn.parity, b, round & 1, n + peer);
       char* dst = out + (long long)peer * P.count;
       const bool dst_al = is_al16(dst);
       copy_vectors(len, [&](long long v) { return ldv(src + v * 16); },
                    [&](long long v, uint4 x) { store_vec<1>(dst, off + v, P.count, dst_al, x); });
     }
-    signal_peers(pt, b, kChanB, e_got);
+    signal_peers(pt, b, kChanB, turn.base + 2 * (u64)round + 2);
   }
-  end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
+  end_collective(pt, b, turn, turn.base + 2 * (u64)R + 1);
 }
 
 // ---------------------------------------------------------------------------

@@ -33,8 +33,9 @@ typedef double InstT;
 #if DGN_INST < 8
 // kind: 0 one-shot, 1 two-shot (lock-step), 2 reduce-scatter, 3 low-latency one-shot,
 //       4 two-shot (warp-specialised), 5 low-latency two-shot,
-//       6 NVSwitch multicast (float, half and bfloat16 only), 7 the same in place
-//       on symmetric memory, 8 the same pipelined over launches for ordinary tensors
+//       6 staged ring through NVSwitch multicast (float, half and bfloat16 only),
+//       7 NVSwitch multicast in place on symmetric memory (the same types),
+//       8 staged ring with peer loads and stores (every type)
 const void* DGN_CAT(reduce_kernel_fn_, DGN_INST)(int kind, bool table) {
   switch (kind) {
     case 0:
@@ -50,14 +51,14 @@ const void* DGN_CAT(reduce_kernel_fn_, DGN_INST)(int kind, bool table) {
                    : (const void*)ar_twoshot_ws_kernel<InstT, false>;
 #if DGN_INST >= 4 && DGN_INST <= 6
     case 6:
-      return table ? (const void*)ar_nvls_kernel<InstT, true>
-                   : (const void*)ar_nvls_kernel<InstT, false>;
+      return table ? (const void*)ar_flow_kernel<InstT, true, true>
+                   : (const void*)ar_flow_kernel<InstT, false, true>;
     case 7:
       return table ? nullptr : (const void*)ar_nvls_inplace_kernel<InstT>;
-    case 8:
-      return table ? (const void*)ar_nvls_pipe_kernel<InstT, true>
-                   : (const void*)ar_nvls_pipe_kernel<InstT, false>;
 #endif
+    case 8:
+      return table ? (const void*)ar_flow_kernel<InstT, true, false>
+                   : (const void*)ar_flow_kernel<InstT, false, false>;
     case 5:
       return table ? (const void*)ar_twoshot_ll_kernel<InstT, true>
                    : (const void*)ar_twoshot_ll_kernel<InstT, false>;

@@ -7,8 +7,8 @@
  * dgn_status; nothing aborts and nothing throws.  Device pointers are ordinary
  * CUDA device pointers valid on the communicator's device, `stream` is a
  * cudaStream_t passed as void*.  All collectives are asynchronous with respect
- * to the host: they enqueue their kernel on `stream` (one launch; a few for
- * the pipelined multicast variant and the sharded optimizer step) and return.
+ * to the host: they enqueue their kernel on `stream` (one launch; two for the
+ * sharded optimizer step) and return.
  *
  * Reference interfaces replaced (paths relative to the Dragon source tree):
  *   dragon/operators/distributed/collective_op_impl_mpi.cc:50-85   (MPI_Bcast /
@@ -73,11 +73,11 @@ typedef enum {
   DGN_VARIANT_AUTO = 0,
   DGN_VARIANT_ONESHOT = 1, /* every rank pushes its whole message to every peer */
   DGN_VARIANT_TWOSHOT = 2, /* reduce-scatter by peer stores + all-gather by peer loads */
-  DGN_VARIANT_NVLS = 3,    /* NVSwitch multicast (multimem) where the box exposes it */
+  DGN_VARIANT_NVLS = 3,    /* staged ring reduced through NVSwitch multicast (multimem), any tensors */
   DGN_VARIANT_LL = 4,      /* one-shot with flag-in-data lines, no barrier (small messages) */
   DGN_VARIANT_LL2 = 5,     /* two-shot with flag-in-data lines (medium messages) */
   DGN_VARIANT_SYMM = 6,    /* NVSwitch multicast in place, on a buffer from dgn_comm_symm_alloc */
-  DGN_VARIANT_NVLS_PIPE = 7 /* NVSwitch multicast for any tensors, chunks pipelined over several launches */
+  DGN_VARIANT_RING = 7     /* the same staged ring reduced with peer loads and stores (no switch needed; never chosen automatically) */
 } dgn_variant;
 
 /* ---- library ----------------------------------------------------------- */
@@ -164,6 +164,15 @@ int dgn_comm_set_wait_limit_ms(dgn_comm_t comm, int ms);
  * thread blocks, threads per block, bytes per block per round. */
 int dgn_comm_set_tuning(dgn_comm_t comm, int variant, int blocks, int threads,
                         int64_t chunk_bytes);
+
+/* Named launch parameters beyond dgn_comm_set_tuning (0 restores the automatic
+ * choice): "flow_chunk_bytes", "flow_switch_blocks", "flow_in_blocks",
+ * "flow_out_blocks", "flow_groups", "flow_depth" shape the staged ring
+ * all-reduce, "nvls_unroll" (4, 8 or 16) is the number of multimem loads a
+ * thread keeps in flight; "nvls_min_bytes", "symm_min_bytes",
+ * "nvls_bcast_min_bytes" and "bcast_scatter_min_bytes" move the size thresholds
+ * of the corresponding variants.  Every rank must set the same values. */
+int dgn_comm_set_knob(dgn_comm_t comm, const char* name, int64_t value);
 
 /* 1 if the NVSwitch-multicast variant was set up for this communicator. */
 int dgn_comm_has_nvls(dgn_comm_t comm);

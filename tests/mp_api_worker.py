@@ -26,6 +26,26 @@ def main():
     from oracle import oracle
     from tests import helpers as H
 
+    # The parent starts the workers with DGN_NVLS=0, so that a worker that leaves
+    # early is never bound to an NVSwitch multicast object; every wait below is
+    # bounded (gloo timeout, device-side wait limit), so a failure ends all ranks.
+    ok = False
+    try:
+        body(rank, world, dev, dist, distributed, tdist, oracle, H, np, torch)
+        ok = True
+    finally:
+        try:
+            dist.barrier()
+            distributed.finalize()
+            dist.barrier()
+        except Exception:  # noqa: BLE001 - a peer may be gone already
+            pass
+        dist.destroy_process_group()
+    if ok:
+        print("WORKER_OK", rank)
+
+
+def body(rank, world, dev, dist, distributed, tdist, oracle, H, np, torch):
     assert distributed.get_rank() == rank and distributed.get_world_size() == world
     group = distributed.new_group(list(range(world)), backend="NCCL")
     assert group.size == world and distributed.get_rank(group) == rank
@@ -65,11 +85,6 @@ def main():
         expect = float(world - 1) if rank < world - 1 else 1.0
         assert torch.equal(w, torch.full((64,), expect, device=dev))
 
-    dist.barrier()
-    distributed.finalize()
-    dist.barrier()
-    dist.destroy_process_group()
-    print("WORKER_OK", rank)
 
 
 if __name__ == "__main__":

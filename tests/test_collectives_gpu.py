@@ -66,7 +66,7 @@ def check_allreduce(comms, count, dtype, redop, inplace=False):
 @pytest.mark.parametrize("dtype", H.ALL_DTYPES, ids=H.NAMES)
 def test_allreduce_sum_all_sizes(teams, n, dtype):
     comms = teams(n)
-    for variant in (1, 2, 4, 5):
+    for variant in (1, 2, 4, 5, 7):
         for c in comms:
             c.set_tuning(variant=variant)
         for count in SIZES:
@@ -79,7 +79,7 @@ def test_allreduce_sum_all_sizes(teams, n, dtype):
 @pytest.mark.parametrize("dtype", H.FLOAT_DTYPES, ids=[H.NAMES[d] for d in H.FLOAT_DTYPES])
 def test_allreduce_mean_inplace(teams, n, dtype):
     comms = teams(n)
-    for variant in (1, 2, 4, 5):
+    for variant in (1, 2, 4, 5, 7):
         for c in comms:
             c.set_tuning(variant=variant)
         for count in (5, 4099, 1 << 18):
@@ -119,6 +119,41 @@ def test_allreduce_multi_round_small_chunks(teams, n):
             c.set_tuning()
 
 
+@pytest.mark.parametrize("n", [2, 3, 8])
+def test_allreduce_staged_ring_many_chunks(teams, n):
+    """The staged dataflow kernel (copy-in, reducing and copy-out blocks around
+    a ring of chunk buffers) with chunks so small that every ring slot is
+    reused several times, for one tensor and for a bucket, with one, two and
+    four groups of reducing blocks."""
+    comms = teams(n)
+    try:
+        for groups, depth, chunk in ((1, 2, 4096), (2, 4, 8192), (4, 8, 4096), (2, 0, 65536)):
+            for c in comms:
+                c.set_tuning(variant=7, chunk_bytes=chunk)
+                c.set_knob("flow_groups", groups)
+                c.set_knob("flow_depth", depth)
+            for dtype, redop in ((oracle.F32, "MEAN"), (oracle.BF16, "SUM"), (oracle.I64, "SUM")):
+                check_allreduce(comms, 200011, dtype, redop, inplace=True)
+            info = comms[0].last_launch()
+            assert info["variant"] == 7 and info["rounds"] >= 8, info
+            counts = [64, 1, 0, 40999, 7, 1 << 16, 33, 2048]
+            arrays = [[H.make_input(r, k, oracle.F16, seed=7 + 13 * i) for i, k in enumerate(counts)] for r in range(n)]
+            ins = [[H.to_torch(a, oracle.F16, "cuda:0") for a in row] for row in arrays]
+            for r in range(n):
+                comms[r].all_reduce(ins[r], None, "MEAN")
+            torch.cuda.synchronize()
+            assert all(c.status() == 0 for c in comms)
+            for i in range(len(counts)):
+                want = oracle.allreduce([arrays[r][i] for r in range(n)], oracle.F16, "MEAN")
+                for r in range(n):
+                    H.assert_bits_equal(H.to_numpy(ins[r][i], oracle.F16), want, "tensor {} rank {}".format(i, r))
+    finally:
+        for c in comms:
+            c.set_tuning()
+            c.set_knob("flow_groups", 0)
+            c.set_knob("flow_depth", 0)
+
+
 def test_config1_fp32_16mib_two_ranks(teams):
     """16 MiB fp32 SUM on 2 ranks (the reference's CPU-runnable case)."""
     from dragon_b200 import workloads
@@ -138,7 +173,7 @@ def test_back_to_back_collectives_reuse_staging(teams):
     comms = teams(4)
     n = 4
     dev = "cuda:0"
-    for variant in (1, 2, 4, 5):
+    for variant in (1, 2, 4, 5, 7):
         for c in comms:
             c.set_tuning(variant=variant)
         steps = 24
@@ -164,7 +199,7 @@ def test_allreduce_bucket_of_tensors(teams, n):
     dev = "cuda:0"
     counts = [64, 1, 0, 4099, 7, 1 << 16, 33, 2048]
     for dtype, redop in ((oracle.F32, "MEAN"), (oracle.F16, "MEAN"), (oracle.I32, "SUM")):
-        for variant in (1, 2, 4, 5):
+        for variant in (1, 2, 4, 5, 7):
             for c in comms:
                 c.set_tuning(variant=variant)
             arrays = [[H.make_input(r, k, dtype, seed=7 + 13 * i) for i, k in enumerate(counts)] for r in range(n)]
@@ -189,7 +224,7 @@ def test_allreduce_unaligned_views(teams):
         full = [H.to_torch(a, dtype, dev) for a in arrays]
         views = [t[1:4998] for t in full]
         outs = [torch.zeros(5001, dtype=t.dtype, device=dev)[3:5000] for t in full]
-        for variant in (1, 2, 4, 5):
+        for variant in (1, 2, 4, 5, 7):
             for c in comms:
                 c.set_tuning(variant=variant)
             for r in range(2):
@@ -206,13 +241,16 @@ def test_allreduce_unaligned_views(teams):
 def test_allgather_bit_exact(teams, n):
     comms = teams(n)
     dev = "cuda:0"
-    # variant 0: automatic (low-latency lines for small blocks, pull above);
-    # variant 2: always publish-and-pull.
-    for variant, dtype, count in ((0, oracle.I64, 65536), (0, oracle.BF16, 70001), (0, oracle.U8, 13), (0, oracle.F64, 1),
-                                  (0, oracle.F32, (1 << 20) + 3), (2, oracle.I64, 65536), (2, oracle.BF16, 70001),
-                                  (2, oracle.U8, 13), (4, oracle.F32, 100003)):
+    # variant 0: automatic (low-latency lines for small blocks, the pushing
+    # kernel above); variant 2: always the pushing kernel; the last shape
+    # forces many rounds of it, so that both halves of the gather boxes are reused.
+    for variant, dtype, count, shape in (
+            (0, oracle.I64, 65536, {}), (0, oracle.BF16, 70001, {}), (0, oracle.U8, 13, {}), (0, oracle.F64, 1, {}),
+            (0, oracle.F32, (1 << 20) + 3, {}), (2, oracle.I64, 65536, {}), (2, oracle.BF16, 70001, {}),
+            (2, oracle.U8, 13, {}), (4, oracle.F32, 100003, {}),
+            (2, oracle.F32, 50021, dict(blocks=3, threads=64, chunk_bytes=512))):
         for c in comms:
-            c.set_tuning(variant=variant)
+            c.set_tuning(variant=variant, **shape)
         arrays = [H.make_input(r, count, dtype) for r in range(n)]
         if dtype == oracle.BF16:  # NaN payloads, infinities, signed zeros, subnormals travel untouched
             arrays[0][:6] = np.array([0x7FC1, 0xFFFF, 0x7F80, 0x8000, 0x0001, 0xFF80], dtype=np.uint16)
@@ -224,6 +262,8 @@ def test_allgather_bit_exact(teams, n):
         want = oracle.allgather(arrays, dtype)
         for r in range(n):
             H.assert_bits_equal(H.to_numpy(outs[r], dtype), want, "allgather variant {} rank {}".format(variant, r))
+        if shape:
+            assert comms[0].last_launch()["rounds"] > 4
     for c in comms:
         c.set_tuning()
 

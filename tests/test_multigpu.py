@@ -46,7 +46,7 @@ def sync_all(n):
 
 
 @needs_two
-@pytest.mark.parametrize("variant", [4, 5, 1, 2])
+@pytest.mark.parametrize("variant", [4, 5, 1, 2, 7])
 def test_allreduce_across_gpus(comms, variant):
     n = len(comms)
     for c in comms:
@@ -72,35 +72,66 @@ def test_allreduce_across_gpus(comms, variant):
 
 @needs_two
 def test_nvls_allreduce_across_gpus(comms):
-    """The NVSwitch multicast variant, where the box exposes it: the switch
-    chooses the order of the additions, so the check is the tolerance contract
-    against an fp64 host sum plus identical bits on every rank."""
+    """The staged ring reduced through NVSwitch multicast, where the box exposes
+    it: one chunk, many chunks with every ring slot reused, ragged sizes, out of
+    place and in place back to back, a bucket of tensors.  The switch chooses
+    the order of the additions, so the check is the tolerance contract against
+    an fp64 host sum plus identical bits on every rank (with two ranks a + b has
+    one order, so float32 also equals the oracle bit for bit)."""
     n = len(comms)
     if not comms[0].has_nvls():
         pytest.skip("NVSwitch multicast is not available on this box")
     assert all(c.has_nvls() for c in comms)
-    for c in comms:
-        c.set_tuning(variant=3)
+    cases = ((oracle.F32, "MEAN", 5, 0, 1), (oracle.F32, "SUM", (1 << 20) + 3, 0, 2),
+             (oracle.F16, "MEAN", 1 << 24, 1 << 20, 2), (oracle.BF16, "SUM", (1 << 22) + 1, 256 << 10, 4),
+             (oracle.F32, "MEAN", 1 << 22, 1 << 20, 1), (oracle.F32, "SUM", 1 << 24, 0, 2))
     try:
-        for dtype, redop, count in ((oracle.F32, "MEAN", 100003), (oracle.F16, "MEAN", (1 << 22) + 5),
-                                    (oracle.BF16, "SUM", 70001), (oracle.F32, "SUM", 1 << 24), (oracle.F32, "SUM", 7)):
+        for dtype, redop, count, chunk, groups in cases:
+            for c in comms:
+                c.set_tuning(variant=3, chunk_bytes=chunk)
+                c.set_knob("flow_groups", groups)
             arrays = [H.make_input(r, count, dtype) for r in range(n)]
-            for rep in range(2):
-                xs = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
-                for r in range(n):
-                    with torch.cuda.device(r):
-                        comms[r].all_reduce([xs[r]], None, redop)
-                sync_all(n)
-                assert comms[0].last_launch()["variant"] == 3
-                ref = oracle.fp64_sum(arrays, dtype, mean=(redop == "MEAN"))
-                got0 = H.to_numpy(xs[0], dtype)
-                assert oracle.max_rel_err(got0, ref, dtype) <= oracle.TOLERANCE[dtype]
-                for r in range(n):
-                    assert comms[r].status() == 0
-                    H.assert_bits_equal(H.to_numpy(xs[r], dtype), got0, "rank {} differs from rank 0".format(r))
+            xs = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
+            outs = [torch.empty_like(x) for x in xs]
+            for r in range(n):
+                with torch.cuda.device(r):
+                    comms[r].all_reduce([xs[r]], [outs[r]], redop)   # out of place
+                    comms[r].all_reduce([xs[r]], None, redop)        # in place, back to back
+            sync_all(n)
+            launch = comms[0].last_launch()
+            assert launch["variant"] == 3
+            if chunk:
+                assert launch["rounds"] >= 16   # more chunks than ring slots
+            ref = oracle.fp64_sum(arrays, dtype, mean=(redop == "MEAN"))
+            got0 = H.to_numpy(outs[0], dtype)
+            assert oracle.max_rel_err(got0, ref, dtype) <= oracle.TOLERANCE[dtype]
+            for r in range(n):
+                assert comms[r].status() == 0
+                H.assert_bits_equal(H.to_numpy(outs[r], dtype), got0, "out of place, rank {}".format(r))
+                H.assert_bits_equal(H.to_numpy(xs[r], dtype), got0, "in place, rank {}".format(r))
+            if n == 2 and dtype == oracle.F32:
+                H.assert_bits_equal(got0, oracle.allreduce(arrays, dtype, redop), "two ranks: one order")
+        # A bucket of ragged tensors as one message, several chunks.
+        for c in comms:
+            c.set_tuning(variant=3, chunk_bytes=1 << 20)
+            c.set_knob("flow_groups", 2)
+        sizes = [70001, 3, 1 << 19, 257, (1 << 20) + 1]
+        host = [[H.make_input(r, k, oracle.F32, seed=77 + i) for i, k in enumerate(sizes)] for r in range(n)]
+        dev = [[H.to_torch(a, oracle.F32, "cuda:{}".format(r)) for a in host[r]] for r in range(n)]
+        for r in range(n):
+            with torch.cuda.device(r):
+                comms[r].all_reduce(dev[r], None, "MEAN")
+        sync_all(n)
+        assert comms[0].last_launch()["variant"] == 3
+        for i in range(len(sizes)):
+            ref = oracle.fp64_sum([host[r][i] for r in range(n)], oracle.F32, mean=True)
+            for r in range(n):
+                assert oracle.max_rel_err(H.to_numpy(dev[r][i], oracle.F32), ref, oracle.F32) <= 1e-6
+                H.assert_bits_equal(H.to_numpy(dev[r][i], oracle.F32), H.to_numpy(dev[0][i], oracle.F32))
     finally:
         for c in comms:
             c.set_tuning()
+            c.set_knob("flow_groups", 0)
 
 
 @needs_two
@@ -146,12 +177,14 @@ def test_symmetric_memory_allreduce_in_place_across_gpus(comms):
                     assert oracle.max_rel_err(got0, ref, dtype) <= oracle.TOLERANCE[dtype]
                     if n == 2 and dtype == oracle.F32:
                         H.assert_bits_equal(got0, oracle.allreduce(arrays, dtype, redop), "two ranks: one order")
-        # Automatic choice: in place through the switch from 4 MiB on, the usual
-        # kernels below; a ragged tail (not a whole number of vectors) and an
-        # out-of-place call never take the in-place path.
+        # Automatic choice: in place through the switch from 4 MiB on (the
+        # default at three ranks and more; set here for any rank count), the
+        # usual kernels below; a ragged tail (not a whole number of vectors)
+        # and an out-of-place call never take the in-place path.
         for c in comms:
             c.symm_reset()
             c.set_tuning()
+            c.set_knob("symm_min_bytes", 4 << 20)
         for count, want_symm in ((1 << 20, True), (1 << 10, False), ((1 << 20) + 1, False)):
             arrays = [H.make_input(r, count, oracle.F32) for r in range(n)]
             xs = []
@@ -181,60 +214,7 @@ def test_symmetric_memory_allreduce_in_place_across_gpus(comms):
         for c in comms:
             c.set_tuning()
             c.symm_reset()
-
-
-@needs_two
-def test_pipelined_multicast_allreduce_across_gpus(comms):
-    """The multicast variant for ordinary tensors, pipelined over launches:
-    single chunk, many chunks, ragged sizes, a tensor list, out of place."""
-    n = len(comms)
-    if not comms[0].has_nvls():
-        pytest.skip("NVSwitch multicast is not available on this box")
-    cases = ((oracle.F32, "MEAN", 5, 0), (oracle.F32, "SUM", (1 << 20) + 3, 0), (oracle.F16, "MEAN", 1 << 24, 4 << 20),
-             (oracle.BF16, "SUM", (1 << 22) + 1, 1 << 20), (oracle.F32, "MEAN", 1 << 22, 1 << 20))
-    try:
-        for dtype, redop, count, chunk in cases:
-            for c in comms:
-                c.set_tuning(variant=7, chunk_bytes=chunk)
-            arrays = [H.make_input(r, count, dtype) for r in range(n)]
-            xs = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
-            outs = [torch.empty_like(x) for x in xs]
-            for r in range(n):
-                with torch.cuda.device(r):
-                    comms[r].all_reduce([xs[r]], [outs[r]], redop)   # out of place
-                    comms[r].all_reduce([xs[r]], None, redop)        # in place, back to back
-            sync_all(n)
-            launch = comms[0].last_launch()
-            assert launch["variant"] == 7
-            if chunk:
-                assert launch["rounds"] >= 4
-            ref = oracle.fp64_sum(arrays, dtype, mean=(redop == "MEAN"))
-            got0 = H.to_numpy(outs[0], dtype)
-            assert oracle.max_rel_err(got0, ref, dtype) <= oracle.TOLERANCE[dtype]
-            for r in range(n):
-                assert comms[r].status() == 0
-                H.assert_bits_equal(H.to_numpy(outs[r], dtype), got0, "out of place, rank {}".format(r))
-                H.assert_bits_equal(H.to_numpy(xs[r], dtype), got0, "in place, rank {}".format(r))
-            if n == 2 and dtype == oracle.F32:
-                H.assert_bits_equal(got0, oracle.allreduce(arrays, dtype, redop), "two ranks: one order")
-        # A bucket of ragged tensors as one message, three chunks.
-        for c in comms:
-            c.set_tuning(variant=7, chunk_bytes=1 << 20)
-        sizes = [70001, 3, 1 << 19, 257]
-        host = [[H.make_input(r, k, oracle.F32, seed=77 + i) for i, k in enumerate(sizes)] for r in range(n)]
-        dev = [[H.to_torch(a, oracle.F32, "cuda:{}".format(r)) for a in host[r]] for r in range(n)]
-        for r in range(n):
-            with torch.cuda.device(r):
-                comms[r].all_reduce(dev[r], None, "MEAN")
-        sync_all(n)
-        assert comms[0].last_launch()["variant"] == 7
-        for i in range(len(sizes)):
-            ref = oracle.fp64_sum([host[r][i] for r in range(n)], oracle.F32, mean=True)
-            for r in range(n):
-                assert oracle.max_rel_err(H.to_numpy(dev[r][i], oracle.F32), ref, oracle.F32) <= 1e-6
-    finally:
-        for c in comms:
-            c.set_tuning()
+            c.set_knob("symm_min_bytes", 0)
 
 
 @needs_two
@@ -358,16 +338,14 @@ def test_multicast_broadcast_across_gpus(comms):
 @needs_two
 def test_two_processes_over_ipc_and_file_rendezvous():
     with tempfile.TemporaryDirectory() as rdv:
+        env = dict(os.environ, DGN_NVLS="0")  # workers may leave early: keep them off the multicast object
         procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "mp_gpu_worker.py"), str(r), "2", rdv],
-                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env) for r in range(2)]
+        # Every wait in a worker is bounded (rendezvous, device-side waits), so the
+        # workers leave on their own, with a closing barrier, also when a check fails.
+        outs = [p.communicate()[0] for p in procs]
         for r, p in enumerate(procs):
-            try:
-                out, _ = p.communicate(timeout=300)
-            except subprocess.TimeoutExpired:
-                for q in procs:
-                    q.kill()
-                raise
-            assert p.returncode == 0 and "WORKER_OK {}".format(r) in out, out[-3000:]
+            assert p.returncode == 0 and "WORKER_OK {}".format(r) in outs[r], outs[r][-3000:]
 
 
 def test_rendezvous_gives_up_on_a_rank_that_never_arrives(dgn_lib):

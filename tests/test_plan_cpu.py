@@ -2,8 +2,8 @@
 without a GPU (dgn_plan_query).  The expectations are the measured crossovers
 the library documents: low-latency one-shot up to 1 MiB / 512 KiB / 128 KiB at
 2 / 4 / 8 ranks, low-latency two-shot up to 2 MiB from 3 ranks, the store-only
-two-shot kernel above, NVSwitch multicast from 256 MiB at 8 ranks, in place on
-symmetric memory from 4 MiB."""
+two-shot kernel above, the staged ring through NVSwitch multicast from 32 MiB at
+8 ranks, in place on symmetric memory from 4 MiB (never by default at 2 ranks)."""
 
 import ctypes
 
@@ -28,7 +28,8 @@ def plan(lib, n, op, nbytes, dtype=_C.F32, redop=_C.MEAN, nvls=True, symm=0, in_
 @pytest.fixture(autouse=True)
 def clean_env(monkeypatch):
     for name in ("DGN_FORCE_VARIANT", "DGN_LL_MAX_BYTES", "DGN_LL2_MAX_BYTES", "DGN_ONESHOT_MAX_BYTES",
-                 "DGN_NVLS_MIN_BYTES", "DGN_SYMM_MIN_BYTES", "DGN_NVLS_PIPE_MIN_BYTES", "DGN_NVLS_BCAST_MIN_BYTES",
+                 "DGN_NVLS_MIN_BYTES", "DGN_SYMM_MIN_BYTES", "DGN_NVLS_BCAST_MIN_BYTES", "DGN_FLOW_CHUNK_BYTES",
+                 "DGN_FLOW_SWITCH_BLOCKS", "DGN_FLOW_GROUPS", "DGN_FLOW_DEPTH", "DGN_NVLS_RING_BYTES", "DGN_RING_BYTES",
                  "DGN_MAX_BLOCKS", "DGN_SLOT_BYTES", "DGN_LL_ALLGATHER_MAX_BYTES", "DGN_BCAST_SCATTER_MIN_BYTES"):
         monkeypatch.delenv(name, raising=False)
 
@@ -40,8 +41,8 @@ def test_allreduce_variant_by_size_and_rank_count(dgn_lib):
         4: [(64 * KiB, _C.VARIANT_LL), (512 * KiB, _C.VARIANT_LL), (1 * MiB, _C.VARIANT_LL2),
             (2 * MiB, _C.VARIANT_LL2), (4 * MiB, _C.VARIANT_TWOSHOT), (1024 * MiB, _C.VARIANT_TWOSHOT)],
         8: [(1 * KiB, _C.VARIANT_LL), (128 * KiB, _C.VARIANT_LL), (256 * KiB, _C.VARIANT_LL2),
-            (2 * MiB, _C.VARIANT_LL2), (4 * MiB, _C.VARIANT_TWOSHOT), (128 * MiB, _C.VARIANT_TWOSHOT),
-            (256 * MiB, _C.VARIANT_NVLS), (1024 * MiB, _C.VARIANT_NVLS)],
+            (2 * MiB, _C.VARIANT_LL2), (4 * MiB, _C.VARIANT_TWOSHOT), (16 * MiB, _C.VARIANT_TWOSHOT),
+            (32 * MiB, _C.VARIANT_NVLS), (256 * MiB, _C.VARIANT_NVLS), (1024 * MiB, _C.VARIANT_NVLS)],
     }
     for n, rows in expect.items():
         for nbytes, variant in rows:
@@ -63,31 +64,41 @@ def test_launch_shapes_stay_inside_the_workspace(dgn_lib):
             assert p["blocks"] * p["chunk_bytes"] * p["rounds"] >= per_rank   # the rounds cover every shard
         p = plan(dgn_lib, n, AR, 64 * KiB)
         assert p["rounds"] == 1 and p["blocks"] <= 64 and p["chunk_bytes"] * 2 <= 64 * KiB  # lines are half flags
-    p = plan(dgn_lib, 8, AR, 512 * MiB)
-    assert p["variant"] == _C.VARIANT_NVLS and p["chunk_bytes"] <= 64 * KiB and p["blocks"] <= 148
+    # The staged ring: all blocks resident (they wait for one another), chunks
+    # an eighth of the message between 1 and 32 MiB, the ring never overrun.
+    for nbytes, chunk, chunks in ((32 * MiB, 4 * MiB, 8), (512 * MiB, 32 * MiB, 16), (100 * MiB + 16, None, 8)):
+        p = plan(dgn_lib, 8, AR, nbytes)
+        assert p["variant"] == _C.VARIANT_NVLS and 3 <= p["blocks"] <= 148 and p["rounds"] == chunks, p
+        assert chunk is None or p["chunk_bytes"] == chunk
+        assert p["chunk_bytes"] * p["rounds"] >= nbytes and p["chunk_bytes"] * 2 <= 256 * MiB
+    p = plan(dgn_lib, 8, AR, 512 * MiB, ntensors=161)
+    assert p["variant"] == _C.VARIANT_NVLS                            # buckets go the same way
 
 
 def test_symmetric_memory_and_opt_in_variants(dgn_lib, monkeypatch):
     arena = 256 * MiB
     assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=True)["variant"] == _C.VARIANT_SYMM
+    assert plan(dgn_lib, 4, AR, 4 * MiB, symm=arena, in_symm=True)["variant"] == _C.VARIANT_SYMM
+    # Two ranks: the switch moves 1.5 S per direction where two-shot moves 1.0 S; off unless asked for.
+    assert plan(dgn_lib, 2, AR, 256 * MiB, symm=arena, in_symm=True)["variant"] == _C.VARIANT_TWOSHOT
+    monkeypatch.setenv("DGN_SYMM_MIN_BYTES", str(4 * MiB))
     assert plan(dgn_lib, 2, AR, 4 * MiB, symm=arena, in_symm=True)["variant"] == _C.VARIANT_SYMM
+    monkeypatch.delenv("DGN_SYMM_MIN_BYTES")
     small = plan(dgn_lib, 8, AR, 1 * MiB, symm=arena, in_symm=True)
     assert small["variant"] == _C.VARIANT_LL2                       # below 4 MiB the low-latency kernels win
-    assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=False)["variant"] == _C.VARIANT_TWOSHOT
-    assert plan(dgn_lib, 8, AR, 64 * MiB + 4, symm=arena, in_symm=True)["variant"] == _C.VARIANT_TWOSHOT  # ragged
+    assert plan(dgn_lib, 8, AR, 16 * MiB, symm=arena, in_symm=False)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=False)["variant"] == _C.VARIANT_NVLS   # staged
+    assert plan(dgn_lib, 8, AR, 64 * MiB + 4, symm=arena, in_symm=True)["variant"] == _C.VARIANT_NVLS  # ragged: staged
     assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=True, nvls=False)["variant"] == _C.VARIANT_TWOSHOT
     shape = plan(dgn_lib, 8, AR, 256 * MiB, symm=arena, in_symm=True)
     assert shape["blocks"] <= 64 and shape["threads"] == 256 and shape["rounds"] == 1
-    # The pipelined variant and the broadcast through the switch are opt-in.
-    assert plan(dgn_lib, 8, AR, 64 * MiB)["variant"] == _C.VARIANT_TWOSHOT
+    # The broadcast through the switch is opt-in; chunk size and block split of the staged ring can be set.
     assert plan(dgn_lib, 8, BC, 64 * MiB)["variant"] == _C.VARIANT_TWOSHOT
-    monkeypatch.setenv("DGN_NVLS_PIPE_MIN_BYTES", str(32 * MiB))
     monkeypatch.setenv("DGN_NVLS_BCAST_MIN_BYTES", str(1 * MiB))
-    pipe = plan(dgn_lib, 8, AR, 64 * MiB)
-    assert pipe["variant"] == _C.VARIANT_NVLS_PIPE and pipe["rounds"] == 2 and pipe["chunk_bytes"] == 32 * MiB
-    big = plan(dgn_lib, 8, AR, 1024 * MiB)
-    assert big["variant"] == _C.VARIANT_NVLS_PIPE and big["chunk_bytes"] == 64 * MiB and big["rounds"] == 16
-    assert plan(dgn_lib, 8, AR, 16 * MiB)["variant"] == _C.VARIANT_TWOSHOT
+    monkeypatch.setenv("DGN_FLOW_CHUNK_BYTES", str(2 * MiB))
+    monkeypatch.setenv("DGN_FLOW_SWITCH_BLOCKS", "32")
+    ring = plan(dgn_lib, 8, AR, 64 * MiB)
+    assert ring["variant"] == _C.VARIANT_NVLS and ring["rounds"] == 32 and ring["chunk_bytes"] == 2 * MiB
     assert plan(dgn_lib, 8, BC, 64 * MiB)["variant"] == _C.VARIANT_NVLS
     assert plan(dgn_lib, 8, BC, 64 * KiB)["variant"] == _C.VARIANT_ONESHOT
 

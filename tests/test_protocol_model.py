@@ -21,7 +21,8 @@ The programs restate, step for step, the waits, stores, loads and signals of
   broadcast_nvls_kernel    the root stores through the switch, peers copy out
   ar_nvls_inplace_kernel   in place on symmetric memory, followed by the
                            caller's next write to the buffer
-  ar_nvls_pipe_kernel      three chunk buffers, one launch per step
+  ar_flow_kernel           staged ring: copy-in, reducing and copy-out blocks
+  allgather_kernel         stores only: push into the peers' gather boxes
 
 (dragon_b200/csrc/dgn_kernels.cuh, dgn_zero.cuh), including the bookkeeping
 that carries over from one collective to the next -- epoch, parity, last "done"
@@ -303,27 +304,51 @@ def nvls_inplace(rk, c):
     rk.data(*[("peek", me, ("user", s), (c, "result")) for s in range(n)])
 
 
-def nvls_pipe(rk, c, chunks, order=("in", "switch", "out")):
-    """ar_nvls_pipe_kernel: launch s copies chunk s in, switch-reduces chunk s-1 in
-    place and copies chunk s-2 out.  Launches of one rank run one after
-    another; inside a launch the three parts run side by side (`order` fixes one
-    order per run, the test tries several)."""
-    n, me = rk.n, rk.me
-    for s in range(chunks + 2):
-        for part in order:
-            if part == "in" and s < chunks:
-                rk.data(*[("store", me, ("chunk", s % 3, sh), (c, s, "in")) for sh in range(n)])
-            if part == "switch" and 0 <= s - 1 < chunks:
-                j = s - 1
-                base, parity = rk.begin()
-                rk.signal(A, rk.peers, base + 1)
-                rk.wait(A, rk.peers, base + 1)
-                rk.data(*([("peek", t, ("chunk", j % 3, me), (c, j, "in")) for t in range(n)] +
-                          [("store", t, ("chunk", j % 3, me), (c, j, "out")) for t in range(n)]))
-                rk.end(parity, base + 2)
-                rk.wait(B, rk.peers, base + 2)
-            if part == "out" and 0 <= s - 2 < chunks:
-                rk.data(*[("peek", me, ("chunk", (s - 2) % 3, sh), (c, s - 2, "out")) for sh in range(n)])
+def flow_roles(me, n, collectives, depth, groups):
+    """ar_flow_kernel: the copy-in blocks, each group of reducing blocks and the
+    copy-out blocks of one rank as processes of their own.  `collectives` lists
+    the number of chunks of consecutive launches; a launch ends when all roles
+    have finished (the kernel boundary), and the epoch base grows by its chunk
+    count.  Counters in_done / sw_done / out_done are per ring slot and local;
+    ready / done flags are per ring slot and travel to the peers."""
+    cin = Rank(me, n, 0)
+    sws = [Rank(me, n, 1 + g) for g in range(groups)]
+    cout = Rank(me, n, 1 + groups)
+    roles = [cin] + sws + [cout]
+    everyone = list(range(n))
+    base = 0
+    for c, K in enumerate(collectives):
+        D = max(groups, min(depth, K) // groups * groups)
+        for k in range(K):
+            s, use = k % D, k // D + 1
+            if k >= D:
+                cin.local_wait(("out", c, s), use - 1)
+            cin.data(*[("store", me, ("ring", s, sh), (c, k, "in")) for sh in everyone])
+            cin.local_set(("in", c, s), use)
+            cin.signal(("ready", s), cin.peers, base + k + 1)
+        for g, sw in enumerate(sws):
+            for k in range(g, K, groups):
+                s, use = k % D, k // D + 1
+                sw.local_wait(("in", c, s), use)
+                sw.wait(("ready", s), sw.peers, base + k + 1)
+                sw.data(*([("peek", t, ("ring", s, me), (c, k, "in")) for t in everyone] +     # ld_reduce / n loads
+                          [("store", t, ("ring", s, me), (c, k, "out")) for t in everyone]))   # multimem.st / n stores
+                sw.local_set(("sw", c, s), use)
+                sw.signal(("done", s), sw.peers, base + k + 1)
+        for k in range(K):
+            s, use = k % D, k // D + 1
+            cout.local_wait(("sw", c, s), use)
+            cout.wait(("done", s), cout.peers, base + k + 1)
+            cout.data(*[("peek", me, ("ring", s, sh), (c, k, "out")) for sh in everyone])
+            cout.local_set(("out", c, s), use)
+        # kernel boundary: the next launch starts when every block has left
+        for rk in roles:
+            rk.local_set(("left", c, rk.role), 1)
+        for rk in roles:
+            for other in roles:
+                rk.local_wait(("left", c, other.role), 1)
+        base += K
+    return roles
 
 
 def ll_oneshot(rk, c):
@@ -349,18 +374,24 @@ def ll_twoshot(rk, c):
 
 
 def allgather(rk, c, rounds):
-    """allgather_kernel: publish in the outbox, peers pull."""
-    n = rk.n
+    """allgather_kernel: every rank stores its slice into gather box [me] of every
+    peer; the push of round i + 1 is issued before the boxes of round i are emptied."""
+    n, me = rk.n, rk.me
     base, parity = rk.begin()
-    for rnd in range(rounds):
-        e_pub, e_got = base + 2 * rnd + 1, base + 2 * rnd + 2
+
+    def push(rnd):
         if rnd >= 2:
             rk.wait(B, rk.peers, base + 2 * (rnd - 2) + 2)
-        rk.data(("store", rk.me, (parity, rnd & 1, n), (c, rnd, rk.me, "outbox")))
-        rk.signal(A, rk.peers, e_pub)
-        rk.wait(A, rk.peers, e_pub)
-        rk.data(*[("peek", p, (parity, rnd & 1, n), (c, rnd, p, "outbox")) for p in rk.peers])
-        rk.signal(B, rk.peers, e_got)
+        rk.data(*[("write", p, (parity, rnd & 1, n + me), (c, rnd, me, "slice")) for p in rk.peers])
+        rk.signal(A, rk.peers, base + 2 * rnd + 1)
+
+    push(0)
+    for rnd in range(rounds):
+        if rnd + 1 < rounds:
+            push(rnd + 1)
+        rk.wait(A, rk.peers, base + 2 * rnd + 1)
+        rk.data(*[("read", (parity, rnd & 1, n + p), (c, rnd, p, "slice")) for p in rk.peers])
+        rk.signal(B, rk.peers, base + 2 * rnd + 2)
     rk.end(parity, base + 2 * rounds + 1)
 
 
@@ -460,45 +491,6 @@ def _join_and_end(roles, c, parity, done):
         rk.local_wait("ended", c + 1)
         rk.epoch, rk.ops = done, rk.ops + 1
         rk.last_done[parity] = done
-
-
-def nvls_staged_roles(me, n, collectives):
-    """ar_nvls_kernel: stage-in, reducer (through the switch) and stage-out."""
-    roles = [Rank(me, n, role) for role in range(3)]
-    sin, red, out = roles
-    everyone = list(range(n))
-    staged = reduced = emptied = 0  # the block's shared counters count rounds of ALL collectives in the model
-    for c, rounds in enumerate(collectives):
-        base, parity = sin.epoch, sin.ops & 1
-        for rk in roles:
-            rk.wait(B, rk.peers, sin.last_done[parity])
-        s0, r0, e0 = staged, reduced, emptied  # the kernel resets its counters per launch; offsets keep them monotonic here
-        for i in range(rounds):
-            if i >= DEPTH:
-                sin.wait(B, sin.peers, base + (i - DEPTH) + 1)
-                sin.local_wait("reduced", r0 + i - DEPTH + 1)
-            sin.data(*[("store", me, ("in", parity, i % DEPTH, s), (c, i, me)) for s in everyone])
-            sin.signal(A, sin.peers, base + i + 1)
-            sin.local_set("staged", s0 + i + 1)
-        for j in range(rounds):
-            red.wait(A, red.peers, base + j + 1)
-            red.local_wait("staged", s0 + j + 1)
-            if j >= DEPTH:
-                red.wait(C, red.peers, base + (j - DEPTH) + 1)
-                red.local_wait("emptied", e0 + j - DEPTH + 1)
-            red.data(*([("peek", t, ("in", parity, j % DEPTH, me), (c, j, t)) for t in everyone] +
-                       [("write", t, ("out", parity, j % DEPTH, me), (c, j, me)) for t in everyone]))
-            red.signal(B, red.peers, base + j + 1)
-            red.local_set("reduced", r0 + j + 1)
-        for j in range(rounds):
-            out.wait(B, out.peers, base + j + 1)
-            out.local_wait("reduced", r0 + j + 1)
-            out.data(*[("read", ("out", parity, j % DEPTH, s), (c, j, s)) for s in everyone])
-            out.signal(C, out.peers, base + j + 1)
-            out.local_set("emptied", e0 + j + 1)
-        staged, reduced, emptied = s0 + rounds, r0 + rounds, e0 + rounds
-        _join_and_end(roles, c, parity, base + rounds + 1)
-    return roles
 
 
 def zero_ws_roles(me, n, steps):
@@ -608,21 +600,11 @@ def test_in_place_multicast_allreduce_and_buffer_reuse(n):
     assert run(n, build) > 0
 
 
-@pytest.mark.parametrize("order", list(itertools.permutations(("in", "switch", "out"))))
-def test_pipelined_multicast_allreduce(order):
-    def build(rk):
-        nvls_pipe(rk, 0, 5, order)
-        nvls_pipe(rk, 1, 1, order)   # a single chunk right behind: the buffers are reused at once
-        nvls_pipe(rk, 2, 2, order)
-    assert run(2, build) > 0
-
-
-@pytest.mark.parametrize("n", [3, 4])
-def test_pipelined_multicast_allreduce_more_ranks(n):
-    def build(rk):
-        nvls_pipe(rk, 0, 4)
-        nvls_pipe(rk, 1, 2)
-    assert run(n, build) > 0
+@pytest.mark.parametrize("n,collectives,depth,groups", [(2, (5, 1, 3), 2, 1), (2, (6, 2), 4, 2), (3, (4, 3), 2, 2),
+                                                        (3, (5,), 3, 1), (4, (3, 2), 2, 1)])
+def test_staged_ring_allreduce(n, collectives, depth, groups):
+    """More chunks than ring slots, launches back to back, one and two groups of reducing blocks."""
+    assert run_roles(n, lambda me, n_: flow_roles(me, n_, collectives, depth, groups)) > 0
 
 
 @pytest.mark.parametrize("n", [2, 3, 4])
@@ -656,11 +638,6 @@ def test_warp_specialised_twoshot(n, collectives):
     assert run_roles(n, lambda me, n_: twoshot_ws_roles(me, n_, collectives)) > 0
 
 
-@pytest.mark.parametrize("n,collectives", [(2, (5, 2)), (3, (4, 3)), (4, (3,))])
-def test_staged_multicast_allreduce(n, collectives):
-    assert run_roles(n, lambda me, n_: nvls_staged_roles(me, n_, collectives)) > 0
-
-
 @pytest.mark.parametrize("n,steps", [(2, ((5, False), (2, True), (3, False))), (3, ((4, False), (3, False))),
                                      (4, ((3, False),))])
 def test_warp_specialised_sharded_optimizer_step(n, steps):
@@ -670,12 +647,12 @@ def test_warp_specialised_sharded_optimizer_step(n, steps):
 def test_eight_ranks():
     """The rank count of the target machine, with fewer rounds."""
     assert run(8, lambda rk: [nvls_inplace(rk, c) for c in range(2)]) > 0
-    assert run(8, lambda rk: nvls_pipe(rk, 0, 3)) > 0
+    assert run_roles(4, lambda me, n: flow_roles(me, n, (3,), 2, 1)) > 0
     assert run(8, lambda rk: [twoshot_allreduce(rk, c, 2) for c in range(2)]) > 0
     assert run(8, lambda rk: [(zero_reduce(rk, 2 * c, 3), zero_update(rk, 2 * c + 1, 3)) for c in range(2)]) > 0
     assert run(8, lambda rk: broadcast_nvls(rk, 0, 3, root=5)) > 0
     assert run(8, lambda rk: broadcast_scatter(rk, 0, 3, root=5)) > 0
-    assert run(8, lambda rk: allgather(rk, 0, 3)) > 0
+    assert run(5, lambda rk: allgather(rk, 0, 2)) > 0   # the pushing kernel branches more: five ranks
     assert run_roles(5, lambda me, n: zero_ws_roles(me, n, ((3, False),))) > 0
 
 
