@@ -59,6 +59,7 @@ SIGNATURES = {
                                           ctypes.c_int, ctypes.c_int]),
     "dgn_allreduce_static": (ctypes.c_int, [ctypes.c_int, _c_void_pp, _c_void_pp, ctypes.c_int64, ctypes.c_int,
                                             ctypes.c_int, ctypes.c_void_p]),
+    "dgn_allreduce_static_status": (ctypes.c_int, [ctypes.c_int]),
     "dgn_launch_count": (ctypes.c_int64, []),
     "dgn_comm_last_launch": (ctypes.c_int, [ctypes.c_void_p, _c_int_p, _c_int_p, _c_int_p, _c_i64_p,
                                             _c_int_p]),

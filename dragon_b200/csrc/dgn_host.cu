@@ -12,6 +12,7 @@
 #include <dirent.h>
 #include <errno.h>
 #include <fcntl.h>
+#include <signal.h>
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -108,6 +109,7 @@ struct Handle {  // what one rank tells the others; padded to DGN_HANDLE_BYTES
   int32_t nvls_capable;
   char nvls_sock[64];  // rank 0: name of the multicast rendezvous socket
   uint64_t symm_bytes;  // symmetric arena; must agree on all ranks
+  uint64_t session;     // drawn when the communicator is created: tells this run's rendezvous files from stale ones
 };
 static_assert(sizeof(Handle) <= DGN_HANDLE_BYTES, "handle too large");
 
@@ -181,6 +183,8 @@ struct TableEntry {
   int nt = 0;                    // non-empty tensors
   long long nvec = 0;
   uint64_t last_use = 0;
+  cudaStream_t upload_stream = nullptr;  // the table was copied to the device on this stream ...
+  cudaEvent_t uploaded = nullptr;        // ... and this event follows the copy
 };
 
 struct Plan {
@@ -224,6 +228,8 @@ struct ZeroTableEntry {
   int nt = 0;                  // non-empty tensors
   long long total = 0;
   uint64_t last_use = 0;
+  cudaStream_t upload_stream = nullptr;
+  cudaEvent_t uploaded = nullptr;
 };
 
 struct Team;
@@ -257,6 +263,7 @@ struct dgn_comm {
   cudaStream_t host_stream = nullptr;
   void* host_dev = nullptr;
   void* host_pin = nullptr;
+  uint64_t session = 0;                // pid and creation time; goes into the handle
   cudaStream_t last_stream = nullptr;  // stream of the latest collective
   bool has_last_stream = false;
   // NVSwitch multicast staging (optional)
@@ -996,6 +1003,8 @@ int get_table(dgn_comm* c, const void* const* in, void* const* out, const int64_
         memcmp(e.out.data(), out, sizeof(void*) * nt) == 0 &&
         memcmp(e.counts.data(), counts, sizeof(int64_t) * nt) == 0) {
       e.last_use = ++c->table_clock;
+      // A call on another stream than the one that uploaded the table must not overtake the upload.
+      if (stream != e.upload_stream && e.uploaded) DGN_CUDA(cudaStreamWaitEvent(stream, e.uploaded, 0));
       *result = &e;
       return DGN_OK;
     }
@@ -1008,6 +1017,7 @@ int get_table(dgn_comm* c, const void* const* in, void* const* out, const int64_
       if (c->tables[i].last_use < c->tables[lru].last_use) lru = i;
     cudaFree(c->tables[lru].d_table);  // synchronises with any kernel still reading it
     cudaFreeHost(c->tables[lru].h_table);
+    if (c->tables[lru].uploaded) cudaEventDestroy(c->tables[lru].uploaded);
     c->tables.erase(c->tables.begin() + lru);
   }
   TableEntry e;
@@ -1029,8 +1039,18 @@ int get_table(dgn_comm* c, const void* const* in, void* const* out, const int64_
   }
   e.nt = k;
   e.nvec = v;
-  DGN_CUDA(cudaMalloc((void**)&e.d_table, sizeof(TensorEnt) * (size_t)(nt + 1)));
-  DGN_CUDA(cudaMemcpyAsync(e.d_table, e.h_table, sizeof(TensorEnt) * (size_t)k, cudaMemcpyHostToDevice, stream));
+  cudaError_t err = cudaMalloc((void**)&e.d_table, sizeof(TensorEnt) * (size_t)(nt + 1));
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(e.d_table, e.h_table, sizeof(TensorEnt) * (size_t)k, cudaMemcpyHostToDevice, stream);
+  if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e.uploaded, cudaEventDisableTiming);
+  if (err == cudaSuccess) err = cudaEventRecord(e.uploaded, stream);
+  if (err != cudaSuccess) {
+    cudaFree(e.d_table);
+    cudaFreeHost(e.h_table);
+    if (e.uploaded) cudaEventDestroy(e.uploaded);
+    return fail(DGN_ERR_CUDA, "bucket table: %s", cudaGetErrorString(err));
+  }
+  e.upload_stream = stream;
   e.last_use = ++c->table_clock;
   c->tables.push_back(std::move(e));
   *result = &c->tables.back();
@@ -1047,6 +1067,7 @@ int get_zero_table(dgn_comm* c, const void* const* grads, void* const* params, c
         memcmp(e.counts.data(), counts, sizeof(int64_t) * nt) == 0 &&
         (lrs ? (e.lrs.size() == (size_t)nt && memcmp(e.lrs.data(), lrs, sizeof(float) * nt) == 0) : e.lrs.empty())) {
       e.last_use = ++c->table_clock;
+      if (stream != e.upload_stream && e.uploaded) DGN_CUDA(cudaStreamWaitEvent(stream, e.uploaded, 0));
       *result = &e;
       return DGN_OK;
     }
@@ -1057,6 +1078,7 @@ int get_zero_table(dgn_comm* c, const void* const* grads, void* const* params, c
       if (c->zero_tables[i].last_use < c->zero_tables[lru].last_use) lru = i;
     cudaFree(c->zero_tables[lru].d_table);  // synchronises with any kernel still reading it
     cudaFreeHost(c->zero_tables[lru].h_table);
+    if (c->zero_tables[lru].uploaded) cudaEventDestroy(c->zero_tables[lru].uploaded);
     c->zero_tables.erase(c->zero_tables.begin() + lru);
   }
   ZeroTableEntry e;
@@ -1083,11 +1105,15 @@ int get_zero_table(dgn_comm* c, const void* const* grads, void* const* params, c
   cudaError_t err = cudaMalloc((void**)&e.d_table, sizeof(ZeroEnt) * (size_t)(nt + 1));
   if (err == cudaSuccess)
     err = cudaMemcpyAsync(e.d_table, e.h_table, sizeof(ZeroEnt) * (size_t)k, cudaMemcpyHostToDevice, stream);
+  if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e.uploaded, cudaEventDisableTiming);
+  if (err == cudaSuccess) err = cudaEventRecord(e.uploaded, stream);
   if (err != cudaSuccess) {
     cudaFree(e.d_table);
     cudaFreeHost(e.h_table);
+    if (e.uploaded) cudaEventDestroy(e.uploaded);
     return fail(DGN_ERR_CUDA, "bucket table of the sharded optimizer step: %s", cudaGetErrorString(err));
   }
+  e.upload_stream = stream;
   e.last_use = ++c->table_clock;
   c->zero_tables.push_back(std::move(e));
   *result = &c->zero_tables.back();
@@ -1123,10 +1149,12 @@ void free_comm(dgn_comm* c) {
   for (TableEntry& e : c->tables) {
     cudaFree(e.d_table);
     cudaFreeHost(e.h_table);
+    if (e.uploaded) cudaEventDestroy(e.uploaded);
   }
   for (ZeroTableEntry& e : c->zero_tables) {
     cudaFree(e.d_table);
     cudaFreeHost(e.h_table);
+    if (e.uploaded) cudaEventDestroy(e.uploaded);
   }
   for (int j = 0; j < c->nranks; ++j)
     if (j != c->rank && c->peer_ipc[j] && c->peer_base[j]) cudaIpcCloseMemHandle(c->peer_base[j]);
@@ -1272,6 +1300,11 @@ int dgn_comm_init_local(int rank, int nranks, int device, dgn_comm_t* comm) {
   c->rank = rank;
   c->nranks = nranks;
   c->device = device;
+  {
+    struct timespec ts;
+    clock_gettime(CLOCK_REALTIME, &ts);
+    c->session = ((uint64_t)getpid() << 40) ^ ((uint64_t)ts.tv_sec << 20) ^ (uint64_t)ts.tv_nsec ^ (uint64_t)rank;
+  }
   load_thresholds(c);
   int rc = alloc_workspace(c);
   if (rc != DGN_OK) {
@@ -1357,6 +1390,7 @@ int dgn_comm_get_handle(dgn_comm_t c, void* handle) {
   h.nvls_capable = c->nvls_capable ? 1 : 0;
   memcpy(h.nvls_sock, c->nvls_sock, sizeof(h.nvls_sock));
   h.symm_bytes = c->symm_bytes;
+  h.session = c->session;
   memset(handle, 0, DGN_HANDLE_BYTES);
   memcpy(handle, &h, sizeof(h));
   return DGN_OK;
@@ -1434,6 +1468,14 @@ int dgn_comm_create(int rank, int nranks, int device, const char* rendezvous_dir
   auto name = [&](int r, const char* suffix) {
     return dir + "/" + tag + "." + std::to_string(r) + suffix;
   };
+  auto drop_mine = [&]() {
+    unlink(name(rank, ".h").c_str());
+    unlink(name(rank, ".ok").c_str());
+  };
+  // A run that crashed may have left files under this tag: remove this rank's
+  // own before writing.  A peer's stale handle is recognised by its writer
+  // being gone; a stale ".ok" by a session number that is not this run's.
+  drop_mine();
   char mine[DGN_HANDLE_BYTES];
   rc = dgn_comm_get_handle(c, mine);
   if (rc != DGN_OK) {
@@ -1447,9 +1489,16 @@ int dgn_comm_create(int rank, int nranks, int device, const char* rendezvous_dir
   std::vector<char> all((size_t)nranks * DGN_HANDLE_BYTES);
   const double deadline = now_s() + 1e-3 * (timeout_ms > 0 ? timeout_ms : 60000);
   for (int r = 0; r < nranks; ++r) {
-    while (!read_file_exact(name(r, ".h"), all.data() + (size_t)r * DGN_HANDLE_BYTES, DGN_HANDLE_BYTES)) {
+    char* slot = all.data() + (size_t)r * DGN_HANDLE_BYTES;
+    for (;;) {
+      if (read_file_exact(name(r, ".h"), slot, DGN_HANDLE_BYTES)) {
+        Handle h;
+        memcpy(&h, slot, sizeof(h));
+        // kill(pid, 0): does the writer still exist?  (EPERM means it does.)
+        if (h.magic == kMagic && (r == rank || kill((pid_t)h.pid, 0) == 0 || errno == EPERM)) break;
+      }
       if (now_s() > deadline) {
-        unlink(name(rank, ".h").c_str());
+        drop_mine();
         free_comm(c);
         return fail(DGN_ERR_TIMEOUT, "rank %d never arrived at rendezvous '%s'", r, tag);
       }
@@ -1458,17 +1507,21 @@ int dgn_comm_create(int rank, int nranks, int device, const char* rendezvous_dir
   }
   rc = dgn_comm_connect(c, all.data());
   if (rc != DGN_OK) {
-    unlink(name(rank, ".h").c_str());
+    drop_mine();
     free_comm(c);
     return rc;
   }
   // Second phase: nobody removes its handle file before everyone has read it.
-  char one = 1;
-  write_file_atomic(name(rank, ".ok"), &one, 1);
+  // Each ".ok" carries the session number of rank 0's handle as its writer saw it.
+  Handle h0;
+  memcpy(&h0, all.data(), sizeof(h0));
+  const uint64_t session = h0.session;
+  write_file_atomic(name(rank, ".ok"), &session, sizeof(session));
   for (int r = 0; r < nranks; ++r) {
-    char b;
-    while (!read_file_exact(name(r, ".ok"), &b, 1)) {
+    uint64_t seen = 0;
+    while (!read_file_exact(name(r, ".ok"), &seen, sizeof(seen)) || seen != session) {
       if (now_s() > deadline) {
+        drop_mine();
         free_comm(c);
         return fail(DGN_ERR_TIMEOUT, "rank %d never finished rendezvous '%s'", r, tag);
       }

@@ -32,9 +32,10 @@ using namespace dgn;
 
 constexpr int kStaticBlocks = 4;            // thread blocks per buffer, at most
 constexpr long long kStaticSlot = 8192;     // bytes of lines per (block, source): 256 data vectors
-constexpr size_t kStaticHead = 512;         // block counters (4 x 64 B) and the status word
+constexpr size_t kStaticHead = 512;         // block counters (4 x 64 B), cleared by every call
 constexpr size_t kStaticRankBytes = kStaticHead + 2 * (size_t)kStaticBlocks * DGN_MAX_RANKS * kStaticSlot;
-constexpr size_t kStaticBytes = (size_t)DGN_MAX_RANKS * kStaticRankBytes;  // 4,198,400 bytes
+constexpr size_t kStaticStatusOff = (size_t)DGN_MAX_RANKS * kStaticRankBytes;  // error words, never cleared by a call
+constexpr size_t kStaticBytes = kStaticStatusOff + 256;  // 4,198,656 bytes
 constexpr long long kStaticMaxMessage = (long long)kStaticBlocks * (kStaticSlot / 32) * 16;  // 16 KiB
 
 // The scratch memory.  Every device that loads this library holds one copy
@@ -130,7 +131,10 @@ extern "C" int dgn_allreduce_static(int nranks, const void* const* in_ptrs, void
     }
     unsigned char* mine = base + (size_t)r * kStaticRankBytes;
     t.blk = reinterpret_cast<BlockState*>(mine);
-    t.status = reinterpret_cast<int*>(mine + kStaticBlocks * sizeof(BlockState));
+    // One error word per buffer, behind everything a call clears: a block that
+    // gives up leaves DGN_ERR_TIMEOUT there until dgn_allreduce_static_status
+    // reads (and, if asked, clears) it.
+    t.status = reinterpret_cast<int*>(base + kStaticStatusOff) + r;
     t.rank = r;
     t.nranks = nranks;
     t.max_blocks = kStaticBlocks;
@@ -159,4 +163,26 @@ extern "C" int dgn_allreduce_static(int nranks, const void* const* in_ptrs, void
     return report_error(DGN_ERR_CUDA, cudaGetErrorString(e));
   }
   return DGN_OK;
+}
+
+// Error word of the static path on the current device: DGN_OK, or
+// DGN_ERR_TIMEOUT once a block of an earlier dgn_allreduce_static call gave up
+// waiting (its outputs are then incomplete).  Waits for the device's work on
+// the legacy default stream's terms (a blocking 32-byte copy); allocates nothing.
+extern "C" int dgn_allreduce_static_status(int clear) {
+  unsigned char* base = nullptr;
+  int rc = scratch_address(&base);
+  if (rc != DGN_OK) return rc;
+  int words[DGN_MAX_RANKS] = {};
+  cudaError_t e = cudaMemcpy(words, base + kStaticStatusOff, sizeof(words), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return report_error(DGN_ERR_CUDA, cudaGetErrorString(e));
+  int status = DGN_OK;
+  for (int r = 0; r < DGN_MAX_RANKS; ++r)
+    if (words[r] != 0) status = words[r];
+  if (status != DGN_OK && clear) {
+    e = cudaMemset(base + kStaticStatusOff, 0, sizeof(words));
+    if (e != cudaSuccess) return report_error(DGN_ERR_CUDA, cudaGetErrorString(e));
+  }
+  if (status != DGN_OK) report_error(status, "a block of dgn_allreduce_static gave up waiting; outputs of that call are incomplete");
+  return status;
 }

@@ -247,6 +247,50 @@ def run_zero_adamw(grads, params, hyper, name="ZeroAdamW", bucket_name="Bucket_1
             lib().dragon_workspace_remove_tensor(ws, n.encode())
 
 
+def run_sync_bn_stats(stats, batch_size, count_on_device=False, stream=None, **group_args):
+    """Runs the `SyncBNStats` operator eagerly: the statistics exchange of
+    synchronized batch normalization (normalization/batch_norm_op.cc:29-43).
+
+    stats: float32 CUDA tensor of 2C partial sums (sum and sum of squares per
+    channel), reduced in place; with count_on_device it holds 2C + 1 values and
+    this function writes float(batch_size) into the last one first, so that the
+    global count arrives with the statistics and nothing blocks.  Otherwise the
+    count goes through the blocking host all-reduce, as in the reference, and
+    is returned.  group_args: comm, group, backend, ranks."""
+    import numpy as np
+    device = stats.device
+    ws = get_workspace()
+    tag = next(_uid)
+    name = "syncbn/{}/stats".format(tag)
+    _feed(ws, name, stats)
+    out_names = [name]
+    total = np.zeros(1, dtype=np.int64)
+    if count_on_device:
+        stats[-1] = float(batch_size)
+    else:
+        out_names.append("syncbn/{}/count".format(tag))
+        dims = (ctypes.c_int64 * 1)(1)
+        _check(lib().dragon_workspace_feed_external(ws, out_names[1].encode(), ctypes.c_void_p(total.ctypes.data), dims,
+                                                    1, b"int64", -1, 8))
+    args = {
+        "batch_size": int(batch_size),
+        "count_on_device": int(bool(count_on_device)),
+        "comm": group_args.get("comm", 0),
+        "group": group_args.get("group", 0),
+        "backend": group_args.get("backend", "MPI"),
+        "ranks": group_args.get("ranks", None),
+    }
+    cuda_stream = stream if stream is not None else torch.cuda.current_stream(device)
+    handle = cuda_stream if isinstance(cuda_stream, int) else cuda_stream.cuda_stream
+    lib().dragon_set_external_stream(device.index, ctypes.c_void_p(handle))
+    try:
+        _check(lib().dragon_workspace_run_operator(ws, _def_text("SyncBNStats", [name], out_names, device.index, args), 0, 0))
+    finally:
+        for n in out_names:
+            lib().dragon_workspace_remove_tensor(ws, n.encode())
+    return None if count_on_device else int(total[0])
+
+
 class _DevicePointer(object):
     def __init__(self, ptr, count):
         self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 2}

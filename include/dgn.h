@@ -179,7 +179,11 @@ int dgn_comm_has_nvls(dgn_comm_t comm);
 
 /* ---- collectives --------------------------------------------------------
  * Every rank of the communicator must issue the same sequence of
- * collectives with the same counts, dtype and reduction. */
+ * collectives with the same counts, dtype and reduction.  The kernels of one
+ * communicator share its workspace and its device-resident protocol state, so
+ * they must not overlap on the GPU: issue them on one stream, or order the
+ * streams with events (dgn_allreduce_host waits for the latest collective
+ * itself).  Different communicators are independent. */
 
 /* ALLREDUCE over a list of tensors (replaces MPI_Allreduce /
  * ncclAllReduce at collective_op_impl_mpi.cc:60-66, _nccl.cc:43-50 together
@@ -275,7 +279,7 @@ int dgn_zero_adamw(dgn_comm_t comm, const void* const* grad_ptrs, void* const* p
  * the allocator's device-wide synchronisation, a plug-in invoked where its
  * host forbids allocation.  Such callers cannot create a dgn communicator,
  * whose workspace is allocated; here the kernel's scratch memory is a fixed
- * 4,198,400-byte array inside the library image (each GPU that loads the
+ * 4,198,656-byte array inside the library image (each GPU that loads the
  * library holds it until the process exits).
  *
  * in_ptrs[r] / out_ptrs[r] (r < nranks <= 8) are device buffers of `count`
@@ -288,9 +292,22 @@ int dgn_zero_adamw(dgn_comm_t comm, const void* const* grad_ptrs, void* const* p
  * memset of the scratch it uses and one kernel on `stream` and returns; it
  * calls no allocating routine.  All calls share the one array per device:
  * two calls whose work overlaps on the GPU (different streams, no ordering
- * between them) race and give undefined results -- order them. */
+ * between them) race and give undefined results -- order them.
+ * DGN_OK from this call means "enqueued".  Should a block of the kernel give up
+ * waiting (2 s; it cannot happen while the launch is intact, since all blocks
+ * run in one cooperative grid), the outputs of that call are incomplete and an
+ * error word in the array is set; nothing reports it by itself --
+ * dgn_allreduce_static_status does. */
 int dgn_allreduce_static(int nranks, const void* const* in_ptrs, void* const* out_ptrs,
                          int64_t count, int dtype, int redop, void* stream);
+
+/* Error word of the static path on the CURRENT device (no counterpart in the
+ * reference either): DGN_OK, or DGN_ERR_TIMEOUT if a block of any earlier
+ * dgn_allreduce_static call on this device gave up.  The word stays set until
+ * this function is called with clear != 0.  It copies 32 bytes back with a
+ * blocking cudaMemcpy, so it also waits for the calls enqueued so far; it
+ * allocates nothing. */
+int dgn_allreduce_static_status(int clear);
 
 /* ---- introspection for benchmarks and tests ------------------------------ */
 

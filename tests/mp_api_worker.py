@@ -76,6 +76,17 @@ def body(rank, world, dev, dist, distributed, tdist, oracle, H, np, torch):
     assert np.array_equal(g.cpu().numpy(), np.stack([np.arange(5) + 10 * r for r in range(world)]))
     assert torch.equal(b, torch.full((3,), float(world - 1), device=dev))
 
+    # SyncBatchNorm statistics the way the reference runs them: the batch count
+    # through the blocking host all-reduce, 2C floats through the device kernel.
+    from dragon_b200 import op_lib
+    channels = 256
+    parts = [np.random.default_rng(40 + r).normal(0, 8, 2 * channels).astype(np.float32) for r in range(world)]
+    stats = torch.from_numpy(parts[rank].copy()).to(dev)
+    total = op_lib.run_sync_bn_stats(stats, 16 + rank, **group.arguments)
+    torch.cuda.synchronize()
+    assert total == sum(16 + r for r in range(world))
+    H.assert_bits_equal(H.to_numpy(stats, oracle.F32), oracle.allreduce(parts, oracle.F32, "SUM"))
+
     # A sub-group that leaves the last rank out: every process still calls new_group.
     if world > 2:
         sub = distributed.new_group(list(range(world - 1)))

@@ -358,3 +358,27 @@ def test_rendezvous_gives_up_on_a_rank_that_never_arrives(dgn_lib):
             Communicator.create(0, 2, 0, rdv, "lonely", timeout_ms=300)
         assert e.value.status == _C.ERR_TIMEOUT and "never arrived" in str(e.value)
         assert os.listdir(rdv) == []
+
+
+def test_rendezvous_ignores_files_of_a_run_that_died(dgn_lib):
+    """Leftovers under the same tag -- this rank's own stale files, a peer's
+    handle whose writer no longer exists, a stale ".ok" -- must not be taken for
+    the peer: creation still ends with "never arrived", and removes its own files."""
+    import struct
+    from dragon_b200 import _C
+    from dragon_b200.comm import Communicator
+    donor = Communicator.init_local(1, 2, 0)
+    try:
+        stale = bytearray(donor.handle_bytes())
+    finally:
+        donor.destroy()
+    struct.pack_into("<i", stale, 8, 4190000)  # pid field: a process that does not exist
+    with tempfile.TemporaryDirectory() as rdv:
+        for name, data in (("again.1.h", bytes(stale)), ("again.1.ok", b"\1" * 8), ("again.0.h", b"junk"),
+                           ("again.0.ok", b"\1" * 8)):
+            with open(os.path.join(rdv, name), "wb") as f:
+                f.write(data)
+        with pytest.raises(_C.DgnError) as e:
+            Communicator.create(0, 2, 0, rdv, "again", timeout_ms=300)
+        assert e.value.status == _C.ERR_TIMEOUT and "rank 1 never arrived" in str(e.value)
+        assert sorted(os.listdir(rdv)) == ["again.1.h", "again.1.ok"]

@@ -7,8 +7,8 @@ synchronisation.  They cannot build a communicator (it allocates a
 workspace), so the library offers one entry point whose scratch memory is a
 fixed array inside the library image.  This test calls it through the C-ABI
 twice in a row and checks both results, bit for bit, against the regular
-entry point (dgn_allreduce on an emulated communicator), which the other tests
-have already checked against the oracle.
+entry point (dgn_allreduce on an emulated communicator) and against the CPU
+oracle directly, and watches the driver's free-memory figure around the calls.
 
 This file sorts last on purpose: if the extra entry point ever breaks, a run
 that stops at the first failure has already exercised everything else.
@@ -64,17 +64,35 @@ def test_static_scratch_allreduce_matches_regular_entry_point(dgn_lib):
         outs = [torch.full_like(t, float("nan")) for t in ins]
         inputs.append(ins)
         outputs.append(outs)
-    before = torch.cuda.memory_allocated()
+    # First calls outside the watched region: they look up the array's address
+    # and load the kernel of each element type, which the driver may back with
+    # memory of its own.
+    for dtype in sorted({c[2] for c in cases}, key=str):
+        warm = [torch.zeros(4, dtype=dtype, device=dev) for _ in range(2)]
+        _static_allreduce(dgn_lib, warm, warm, dgn_dtype(dtype), _C.SUM)
+    torch.cuda.synchronize()
+    # torch's counter cannot see a cudaMalloc inside the library; the driver's
+    # free-bytes figure can (nothing else runs on this device meanwhile).
+    before_torch = torch.cuda.memory_allocated()
+    free_before, _ = torch.cuda.mem_get_info()
     for (n, count, dtype, reduction), ins, outs in zip(cases, inputs, outputs):
         _static_allreduce(dgn_lib, ins, outs, dgn_dtype(dtype), _C.REDOPS[reduction])
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before
+    free_after, _ = torch.cuda.mem_get_info()
+    assert torch.cuda.memory_allocated() == before_torch
+    assert free_after == free_before, "device memory in use changed by {} bytes".format(free_before - free_after)
+    assert dgn_lib.dgn_allreduce_static_status(0) == _C.OK   # no block gave up
+    from oracle import oracle
+    kinds = {torch.float32: oracle.F32, torch.float16: oracle.F16}
     for (n, count, dtype, reduction), ins, outs in zip(cases, inputs, outputs):
         want = _reference_allreduce(n, ins, reduction)
+        want_oracle = oracle.allreduce([t.cpu().numpy() for t in ins], kinds[dtype], reduction)
         for r in range(n):
             got_bits = outs[r].cpu().numpy().view(np.uint8)
             want_bits = want[r].cpu().numpy().view(np.uint8)
             assert np.array_equal(got_bits, want_bits), "rank {} of the {}-rank call differs".format(r, n)
+            assert np.array_equal(got_bits, np.ascontiguousarray(want_oracle).view(np.uint8)), \
+                "rank {} of the {}-rank call differs from the oracle".format(r, n)
 
 
 def test_static_scratch_allreduce_in_place_and_repeatable(dgn_lib):
