@@ -117,6 +117,18 @@ class NcclBackend(object):
             for t in tensors:
                 t.mul_(alpha)
 
+    def operator_all_reduce_sgd(self, grads, params, momenta, hyper, stream, bucket=None):
+        """What the reference's data-parallel SGD step enqueues
+        (torch/core/optim/optimizer.py:134-164, :250-272): the bucketed SUM
+        all-reduce of the gradients, then the update operator -- one Scale per
+        tensor for grad_scale / dist_size and the momentum kernel.  The update of
+        all tensors is ONE fused multi-tensor call here, where the reference
+        launches one kernel per tensor: in the baseline's favour."""
+        self.operator_all_reduce(grads, "SUM", stream, bucket)
+        torch._foreach_mul_(grads, hyper["grad_scale"])
+        torch._fused_sgd_(params, grads, momenta, weight_decay=hyper["weight_decay"], momentum=hyper["momentum"],
+                          lr=hyper["lr"], dampening=0.0, nesterov=False, maximize=False, is_first_step=False)
+
     def reduce_scatter_sum(self, src, dst, stream):
         self._check(self.lib.ncclReduceScatter(src.data_ptr(), dst.data_ptr(), dst.numel(), _NCCL_DTYPE[src.dtype],
                                                NCCL_SUM, self.comm, ctypes.c_void_p(stream)))

@@ -928,7 +928,30 @@ def run_operator_configs(comm, nccl, rank, world, dev, barrier, max_over_ranks):
         del scratch
     row["ours_busbw"] = nbytes / (row["ours_us"] * 1e-6) / 1e9 * 2.0 * (world - 1) / world
     out["resnet50_fp32_one_bucket_mean"] = row
-    del grads, op
+    del op
+
+    # The same gradients with the optimizer update fused into the all-reduce
+    # (momentum SGD on all 161 tensors): one kernel against the reference's
+    # all-reduce followed by its update operator.
+    from dragon_b200.fused_optim import FusedSGD
+    params = gen(shapes, 1.0, torch.float32)
+    for p, g in zip(params, grads):
+        p.grad = g
+    opt = FusedSGD(params, 0.1, momentum=0.9, weight_decay=1e-4, comm=comm)
+    row = {"tensors": len(grads), "bytes": nbytes, "ours_us": timed(opt.step) * 1e3, "launch": comm.last_launch()}
+    if nccl is not None:
+        scratch = torch.empty(nbytes // 4, device=dev)
+        momenta = [torch.zeros_like(p) for p in params]
+        hyper = {"lr": 0.1, "momentum": 0.9, "weight_decay": 1e-4, "grad_scale": 1.0 / world}
+        try:
+            row["nccl_us"] = timed(lambda: nccl.operator_all_reduce_sgd(grads, params, momenta, hyper, stream_of(),
+                                                                          bucket=scratch)) * 1e3
+            row["speedup"] = row["nccl_us"] / row["ours_us"]
+        except (RuntimeError, TypeError, AttributeError) as e:  # a torch build without the fused SGD op
+            row["nccl_error"] = str(e)[:200]
+        del scratch, momenta
+    out["resnet50_fp32_allreduce_fused_with_sgd"] = row
+    del grads, params, opt
 
     # BERT-base: 199 fp16 tensors in 25 MiB buckets, MEAN with fp32 accumulation.
     shapes = workloads.bert_base_shapes()

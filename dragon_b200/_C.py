@@ -74,7 +74,18 @@ class AdamWArgs(ctypes.Structure):
                 ("clip_norm", ctypes.c_float), ("clip_value", ctypes.c_float)]
 
 
+class UpdateArgs(ctypes.Structure):
+    """dgn_update_args of include/dgn.h."""
+    _fields_ = [("kind", ctypes.c_int), ("lr", ctypes.c_float), ("momentum", ctypes.c_float),
+                ("beta1", ctypes.c_float), ("beta2", ctypes.c_float), ("eps", ctypes.c_float),
+                ("weight_decay", ctypes.c_float), ("grad_scale", ctypes.c_float), ("clip_value", ctypes.c_float)]
+
+
+UPDATE_MOMENTUM_SGD, UPDATE_NESTEROV_SGD, UPDATE_ADAM, UPDATE_ADAMW = range(4)
+
 SIGNATURES.update({
+    "dgn_allreduce_update": (ctypes.c_int, [ctypes.c_void_p, _c_void_pp, _c_void_pp, _c_void_pp, _c_void_pp, _c_i64_p,
+                                            ctypes.c_int, ctypes.c_int, ctypes.POINTER(UpdateArgs), ctypes.c_void_p]),
     "dgn_comm_init_symmetric": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, _c_void_pp]),
     "dgn_comm_symm_capacity": (ctypes.c_int64, [ctypes.c_void_p]),
     "dgn_comm_symm_alloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, _c_void_pp]),

@@ -31,6 +31,7 @@
 #include "../../include/dgn.h"
 #include "dgn_kernels.cuh"
 #include "dgn_nvls.h"
+#include "dgn_update.cuh"
 #include "dgn_zero.cuh"
 
 namespace dgn {
@@ -50,6 +51,7 @@ const void* broadcast_scatter_kernel_fn();
 const void* broadcast_nvls_kernel_fn();
 const void* local_copy_kernel_fn(int es, bool table);
 const void* zero_kernel_fn(int dtype, int which);  // dgn_zero_inst.cu
+const void* update_kernel_fn(int kind);             // dgn_update_inst.cu
 }  // namespace dgn
 
 using namespace dgn;
@@ -194,7 +196,8 @@ struct Plan {
   int flow_nsw = 0, flow_nin = 0, flow_depth = 0, flow_groups = 1;
 };
 
-enum OpKind { kOpAllReduce = 0, kOpReduceScatter, kOpAllGather, kOpBroadcast, kOpZeroReduce, kOpZeroUpdate };
+enum OpKind { kOpAllReduce = 0, kOpReduceScatter, kOpAllGather, kOpBroadcast, kOpZeroReduce, kOpZeroUpdate,
+              kOpAllReduceUpdate };
 
 inline bool is_zero_kind(int kind) { return kind == kOpZeroReduce || kind == kOpZeroUpdate; }
 
@@ -202,6 +205,12 @@ inline bool is_zero_kind(int kind) { return kind == kOpZeroReduce || kind == kOp
 struct ZeroHyper {
   float lr = 0, beta1 = 0, beta2 = 0, eps = 0, wd = 0, grad_scale = 1, clip_norm = 0, clip_value = 0;
   int check_finite = 0, use_lr_scales = 0;
+};
+
+// Hyper-parameters of the all-reduce fused with the optimizer update; identical on every rank.
+struct UpdHyper {
+  int kind = 0;
+  float lr = 0, a = 0, b = 0, eps = 0, wd = 0, grad_scale = 1, clip_value = 0;
 };
 
 struct OpDesc {
@@ -214,6 +223,8 @@ struct OpDesc {
   cudaStream_t stream = nullptr;
   ZeroRank zr = {};  // sharded optimizer step only
   ZeroHyper zh;
+  const UpdEnt* utable = nullptr;  // all-reduce fused with the optimizer update only
+  UpdHyper uh;
 };
 
 // Device table of a sharded optimizer step, cached on the tensor list.
@@ -227,6 +238,20 @@ struct ZeroTableEntry {
   ZeroEnt* h_table = nullptr;  // pinned
   int nt = 0;                  // non-empty tensors
   long long total = 0;
+  uint64_t last_use = 0;
+  cudaStream_t upload_stream = nullptr;
+  cudaEvent_t uploaded = nullptr;
+};
+
+// Device table of an all-reduce fused with the optimizer update, cached on the tensor list.
+struct UpdTableEntry {
+  std::vector<const void*> grads;
+  std::vector<void*> params, m, v;
+  std::vector<int64_t> counts;
+  UpdEnt* d_table = nullptr;
+  UpdEnt* h_table = nullptr;  // pinned
+  int nt = 0;
+  long long nvec = 0;
   uint64_t last_use = 0;
   cudaStream_t upload_stream = nullptr;
   cudaEvent_t uploaded = nullptr;
@@ -256,6 +281,7 @@ struct dgn_comm {
   Team* team = nullptr;
   std::vector<TableEntry> tables;
   std::vector<ZeroTableEntry> zero_tables;
+  std::vector<UpdTableEntry> upd_tables;
   uint64_t table_clock = 0;
   Plan last_plan;
   std::string rdv_ok_file;
@@ -327,6 +353,7 @@ int preload_kernels() {
   for (int dtype : zero_types)
     for (int which = 0; which < 3; ++which)
       DGN_CUDA(cudaFuncGetAttributes(&attr, zero_kernel_fn(dtype, which)));
+  for (int kind = 0; kind < 4; ++kind) DGN_CUDA(cudaFuncGetAttributes(&attr, update_kernel_fn(kind)));
   // Opt-in kernels: loaded ahead of time as well, but a failure here must not
   // cost the communicator.
   for (int dtype : zero_types) {
@@ -681,7 +708,7 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
   // Multi-round kernels: two-shot all-reduce, reduce-scatter, all-gather,
   // broadcast.  `per` = vectors each block column has to cover.
   long long per = d.nvec;
-  if (d.kind == kOpAllReduce) per = ceil_div(d.nvec, n);
+  if (d.kind == kOpAllReduce || d.kind == kOpAllReduceUpdate) per = ceil_div(d.nvec, n);
   // Sharded optimizer step: the longest shard, ceil(total / n) elements, may
   // begin and end inside a vector.
   if (is_zero_kind(d.kind)) per = ceil_div(ceil_div(d.count, n), 16 / (long long)kElemSize[d.dtype]) + 1;
@@ -794,6 +821,10 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
              : p.variant == DGN_VARIANT_TWOSHOT ? broadcast_scatter_kernel_fn()
                                                 : broadcast_kernel_fn();
       break;
+    case kOpAllReduceUpdate:
+      k.fn = update_kernel_fn(d.uh.kind);
+      k.smem = update_smem_bytes(d.ntensors);
+      break;
     case kOpZeroReduce:
     case kOpZeroUpdate:
       // The warp-specialised versions need two warps at least.
@@ -839,6 +870,19 @@ void fill_zero_params(ZeroParams* Z, const dgn_comm* c, const OpDesc& d, const P
   Z->clip_value = d.zh.clip_value;
   Z->check_finite = d.zh.check_finite;
   Z->use_lr_scales = d.zh.use_lr_scales;
+}
+
+void fill_update_params(UpdParams* U, const dgn_comm* c, const OpDesc& d, const Plan& p) {
+  memset(U, 0, sizeof(*U));
+  fill_params(&U->base, c, d, p);
+  U->kind = d.uh.kind;
+  U->lr = d.uh.lr;
+  U->a = d.uh.a;
+  U->b = d.uh.b;
+  U->eps = d.uh.eps;
+  U->wd = d.uh.wd;
+  U->grad_scale = d.uh.grad_scale;
+  U->clip_value = d.uh.clip_value;
 }
 
 int launch(const void* fn, dim3 grid, int threads, size_t smem, cudaStream_t stream, void* P,
@@ -891,6 +935,12 @@ int issue(dgn_comm* c, const OpDesc& d) {
       Z.base.peers[0] = c->table;
       Z.zr[0] = d.zr;
       rc = launch(k.fn, dim3(p.blocks, 1), p.threads, k.smem, d.stream, &Z, false);
+    } else if (d.kind == kOpAllReduceUpdate) {
+      UpdParams U;
+      fill_update_params(&U, c, d, p);
+      U.base.peers[0] = c->table;
+      U.table[0] = d.utable;
+      rc = launch(k.fn, dim3(p.blocks, 1), p.threads, k.smem, d.stream, &U, false);
     } else {
       OpParams P;
       fill_params(&P, c, d, p);
@@ -917,7 +967,7 @@ int issue(dgn_comm* c, const OpDesc& d) {
       const OpDesc& o = t->pending[r].front();
       if (f.kind != o.kind || f.dtype != o.dtype || f.redop != o.redop || f.root != o.root ||
           f.count != o.count || f.nvec != o.nvec || f.ntensors != o.ntensors || f.stream != o.stream ||
-          memcmp(&f.zh, &o.zh, sizeof(ZeroHyper)) != 0) {
+          memcmp(&f.zh, &o.zh, sizeof(ZeroHyper)) != 0 || memcmp(&f.uh, &o.uh, sizeof(UpdHyper)) != 0) {
         for (int q = 0; q < t->n; ++q) t->pending[q].clear();
         return fail(DGN_ERR_ARG, "virtual rank %d issued a collective that differs from rank 0's", r);
       }
@@ -944,14 +994,19 @@ int issue(dgn_comm* c, const OpDesc& d) {
     if (!fits) return fail(DGN_ERR_UNSUPPORTED, "no resident launch shape for the emulated team");
     OpParams P;
     ZeroParams Z;
-    const bool zero = is_zero_kind(f.kind);
+    UpdParams U;
+    const bool zero = is_zero_kind(f.kind), upd = f.kind == kOpAllReduceUpdate;
     if (zero) fill_zero_params(&Z, c, f, p);
+    else if (upd) fill_update_params(&U, c, f, p);
     else fill_params(&P, c, f, p);
     for (int r = 0; r < t->n; ++r) {
       const OpDesc& o = t->pending[r].front();
       if (zero) {
         Z.base.peers[r] = t->members[r]->table;
         Z.zr[r] = o.zr;
+      } else if (upd) {
+        U.base.peers[r] = t->members[r]->table;
+        U.table[r] = o.utable;
       } else {
         P.peers[r] = t->members[r]->table;
         P.ra[r].in = o.in;
@@ -960,7 +1015,8 @@ int issue(dgn_comm* c, const OpDesc& d) {
       }
     }
     for (int r = 0; r < t->n; ++r) t->pending[r].pop_front();
-    int rc = launch(k.fn, dim3(p.blocks, t->n), p.threads, k.smem, f.stream, zero ? (void*)&Z : (void*)&P, true);
+    int rc = launch(k.fn, dim3(p.blocks, t->n), p.threads, k.smem, f.stream,
+                    zero ? (void*)&Z : upd ? (void*)&U : (void*)&P, true);
     if (rc != DGN_OK) return rc;
     for (dgn_comm* m : t->members) m->last_plan = p;
   }
@@ -1120,6 +1176,69 @@ int get_zero_table(dgn_comm* c, const void* const* grads, void* const* params, c
   return DGN_OK;
 }
 
+// Device table of an all-reduce fused with the optimizer update, cached like the bucket tables.
+int get_update_table(dgn_comm* c, const void* const* grads, void* const* params, void* const* m, void* const* v,
+                     const int64_t* counts, int nt, cudaStream_t stream, const UpdTableEntry** result) {
+  for (UpdTableEntry& e : c->upd_tables) {
+    if ((int)e.grads.size() == nt && memcmp(e.grads.data(), grads, sizeof(void*) * nt) == 0 &&
+        memcmp(e.params.data(), params, sizeof(void*) * nt) == 0 && memcmp(e.m.data(), m, sizeof(void*) * nt) == 0 &&
+        (v ? (e.v.size() == (size_t)nt && memcmp(e.v.data(), v, sizeof(void*) * nt) == 0) : e.v.empty()) &&
+        memcmp(e.counts.data(), counts, sizeof(int64_t) * nt) == 0) {
+      e.last_use = ++c->table_clock;
+      if (stream != e.upload_stream && e.uploaded) DGN_CUDA(cudaStreamWaitEvent(stream, e.uploaded, 0));
+      *result = &e;
+      return DGN_OK;
+    }
+  }
+  if (c->upd_tables.size() >= 16 && !(c->team && !c->team->pending[c->rank].empty())) {
+    size_t lru = 0;
+    for (size_t i = 1; i < c->upd_tables.size(); ++i)
+      if (c->upd_tables[i].last_use < c->upd_tables[lru].last_use) lru = i;
+    cudaFree(c->upd_tables[lru].d_table);  // synchronises with any kernel still reading it
+    cudaFreeHost(c->upd_tables[lru].h_table);
+    if (c->upd_tables[lru].uploaded) cudaEventDestroy(c->upd_tables[lru].uploaded);
+    c->upd_tables.erase(c->upd_tables.begin() + lru);
+  }
+  UpdTableEntry e;
+  e.grads.assign(grads, grads + nt);
+  e.params.assign(params, params + nt);
+  e.m.assign(m, m + nt);
+  if (v) e.v.assign(v, v + nt);
+  e.counts.assign(counts, counts + nt);
+  DGN_CUDA(cudaHostAlloc((void**)&e.h_table, sizeof(UpdEnt) * (size_t)(nt + 1), cudaHostAllocDefault));
+  long long vec = 0;
+  int k = 0;
+  for (int i = 0; i < nt; ++i) {
+    if (counts[i] == 0) continue;
+    e.h_table[k].grad = static_cast<const char*>(grads[i]);
+    e.h_table[k].param = static_cast<char*>(params[i]);
+    e.h_table[k].m = static_cast<char*>(m[i]);
+    e.h_table[k].v = v ? static_cast<char*>(v[i]) : nullptr;
+    e.h_table[k].count = counts[i];
+    e.h_table[k].vbegin = vec;
+    vec += ceil_div(counts[i] * 4, 16);
+    ++k;
+  }
+  e.nt = k;
+  e.nvec = vec;
+  cudaError_t err = cudaMalloc((void**)&e.d_table, sizeof(UpdEnt) * (size_t)(nt + 1));
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(e.d_table, e.h_table, sizeof(UpdEnt) * (size_t)k, cudaMemcpyHostToDevice, stream);
+  if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e.uploaded, cudaEventDisableTiming);
+  if (err == cudaSuccess) err = cudaEventRecord(e.uploaded, stream);
+  if (err != cudaSuccess) {
+    cudaFree(e.d_table);
+    cudaFreeHost(e.h_table);
+    if (e.uploaded) cudaEventDestroy(e.uploaded);
+    return fail(DGN_ERR_CUDA, "table of the fused update: %s", cudaGetErrorString(err));
+  }
+  e.upload_stream = stream;
+  e.last_use = ++c->table_clock;
+  c->upd_tables.push_back(std::move(e));
+  *result = &c->upd_tables.back();
+  return DGN_OK;
+}
+
 // Argument checks shared by the entry points of the sharded optimizer step.
 int check_zero_bucket(const void* const* a, const void* const* b, const int64_t* counts, int ntensors, int dtype,
                       long long* total, int* nonempty) {
@@ -1152,6 +1271,11 @@ void free_comm(dgn_comm* c) {
     if (e.uploaded) cudaEventDestroy(e.uploaded);
   }
   for (ZeroTableEntry& e : c->zero_tables) {
+    cudaFree(e.d_table);
+    cudaFreeHost(e.h_table);
+    if (e.uploaded) cudaEventDestroy(e.uploaded);
+  }
+  for (UpdTableEntry& e : c->upd_tables) {
     cudaFree(e.d_table);
     cudaFreeHost(e.h_table);
     if (e.uploaded) cudaEventDestroy(e.uploaded);
@@ -1896,6 +2020,58 @@ int dgn_zero_adamw(dgn_comm_t c, const void* const* grad_ptrs, void* const* para
   rc = issue(c, d);
   if (rc != DGN_OK) return rc;
   d.kind = kOpZeroUpdate;
+  return issue(c, d);
+}
+
+int dgn_allreduce_update(dgn_comm_t c, const void* const* grad_ptrs, void* const* param_ptrs, void* const* m_ptrs,
+                         void* const* v_ptrs, const int64_t* counts, int ntensors, int dtype,
+                         const dgn_update_args* args, void* stream) {
+  int rc = check_ready(c);
+  if (rc != DGN_OK) return rc;
+  if (!args) return fail(DGN_ERR_ARG, "null hyper-parameters");
+  if (dtype != DGN_F32) return fail(DGN_ERR_UNSUPPORTED, "the fused update takes float32 tensors, got dtype %d", dtype);
+  if (args->kind < DGN_UPDATE_MOMENTUM_SGD || args->kind > DGN_UPDATE_ADAMW)
+    return fail(DGN_ERR_ARG, "unknown update kind %d", args->kind);
+  const bool two = args->kind == DGN_UPDATE_ADAM || args->kind == DGN_UPDATE_ADAMW;
+  if (ntensors < 1 || !grad_ptrs || !param_ptrs || !m_ptrs || !counts || (two && !v_ptrs))
+    return fail(DGN_ERR_ARG, "null or empty tensor list");
+  long long total = 0;
+  int nonempty = 0;
+  for (int i = 0; i < ntensors; ++i) {
+    if (counts[i] < 0) return fail(DGN_ERR_ARG, "negative count for tensor %d", i);
+    if (counts[i] == 0) continue;
+    if (!grad_ptrs[i] || !param_ptrs[i] || !m_ptrs[i] || (two && !v_ptrs[i]))
+      return fail(DGN_ERR_ARG, "null pointer for tensor %d", i);
+    if (((uintptr_t)grad_ptrs[i] | (uintptr_t)param_ptrs[i] | (uintptr_t)m_ptrs[i] | (two ? (uintptr_t)v_ptrs[i] : 0)) & 3u)
+      return fail(DGN_ERR_ARG, "tensor %d is not aligned to its element size", i);
+    total += counts[i];
+    ++nonempty;
+  }
+  if (total == 0) return DGN_OK;
+  if (nonempty > 512) return fail(DGN_ERR_UNSUPPORTED, "a fused update takes at most 512 tensors per call, got %d", nonempty);
+  DeviceGuard g(c->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const UpdTableEntry* te = nullptr;
+  rc = get_update_table(c, grad_ptrs, param_ptrs, m_ptrs, two ? v_ptrs : nullptr, counts, ntensors, s, &te);
+  if (rc != DGN_OK) return rc;
+  if (te->nvec >= (1ll << 32)) return fail(DGN_ERR_UNSUPPORTED, "bucket larger than 64 GiB");
+  OpDesc d;
+  d.kind = kOpAllReduceUpdate;
+  d.dtype = DGN_F32;
+  d.redop = DGN_SUM;
+  d.count = total;
+  d.nvec = te->nvec;
+  d.ntensors = te->nt;
+  d.stream = s;
+  d.utable = te->d_table;
+  d.uh.kind = args->kind;
+  d.uh.lr = args->lr;
+  d.uh.a = two ? args->beta1 : args->momentum;
+  d.uh.b = args->beta2;
+  d.uh.eps = args->eps;
+  d.uh.wd = args->weight_decay;
+  d.uh.grad_scale = args->grad_scale;
+  d.uh.clip_value = args->clip_value;
   return issue(c, d);
 }
 

@@ -270,6 +270,43 @@ int dgn_zero_adamw(dgn_comm_t comm, const void* const* grad_ptrs, void* const* p
                    float* grad_shard, const float* lr_scales, const dgn_adamw_args* args,
                    float* found_inf, void* stream);
 
+/* ---- gradient all-reduce fused with the optimizer update -------------------
+ * Data-parallel training without state sharding: every rank holds all
+ * parameters and all optimizer state.  One call replaces, for one list of
+ * float32 tensors, the reference's sequence "Collective ALLREDUCE SUM over the
+ * gradients, then the update operator" (torch/core/optim/optimizer.py:134-164,
+ * :250-272; operators/training/update_op_base.cc:21-38 for the gradient
+ * transform; kernels/training/cuda/sgd_kernel.cu:10-51 and adam_kernel.cu:10-55
+ * for the arithmetic).  It is ONE kernel: the two-shot all-reduce whose reduced
+ * vectors go straight into the update of the parameter and state vectors at
+ * the same position; the summed gradient is never written to memory and the
+ * gradient tensors are left untouched.  Results are bit-identical on all ranks
+ * and to the CPU restatement of the reference's loops. */
+typedef enum {
+  DGN_UPDATE_MOMENTUM_SGD = 0, /* m = momentum*m + g';  x -= lr*m           (g' = g + wd*x if wd > 0) */
+  DGN_UPDATE_NESTEROV_SGD = 1, /* m = momentum*m + g';  x -= lr*(momentum*m + g') */
+  DGN_UPDATE_ADAM = 2,         /* coupled decay: g' = g + wd*x */
+  DGN_UPDATE_ADAMW = 3         /* decoupled decay: x -= wd*x + lr*m/(sqrt(v)+eps) */
+} dgn_update_kind;
+
+typedef struct {
+  int kind;           /* dgn_update_kind */
+  float lr;           /* as the kernel applies it (Adam kinds: lr * sqrt(1-beta2^t)/(1-beta1^t), adam_op.cc:52) */
+  float momentum;     /* SGD kinds */
+  float beta1, beta2, eps; /* Adam kinds */
+  float weight_decay; /* as the kernel applies it (AdamW: lr * weight_decay, adam_op.cc:56); <= 0: none */
+  float grad_scale;   /* multiplies the summed gradient; callers fold 1/nranks in (optimizer.py:261-262) */
+  float clip_value;   /* > 0: clamp the scaled gradient to [-clip_value, clip_value]; clipping by norm is not fused */
+} dgn_update_args;
+
+/* Tensor i has counts[i] float32 elements in grad_ptrs[i], param_ptrs[i],
+ * m_ptrs[i] and, for the Adam kinds, v_ptrs[i] (NULL otherwise).  At most 512
+ * non-empty tensors per call.  dtype must be DGN_F32.  Every rank passes the
+ * same hyper-parameters. */
+int dgn_allreduce_update(dgn_comm_t comm, const void* const* grad_ptrs, void* const* param_ptrs,
+                         void* const* m_ptrs, void* const* v_ptrs, const int64_t* counts, int ntensors,
+                         int dtype, const dgn_update_args* args, void* stream);
+
 /* ALLREDUCE of `nranks` buffers that all live on the CURRENT device, without
  * allocating anything.  (No counterpart in the reference: Dragon's collectives
  * always go through a communicator that owns library-allocated buffers.)

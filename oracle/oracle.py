@@ -266,6 +266,33 @@ def momentum_sgd(g, m, y, lr, momentum, wd, nesterov=False):
     lib().orc_momentum_sgd(g.size, lr, momentum, wd, 1 if nesterov else 0, g.ctypes.data, m.ctypes.data, y.ctypes.data)
 
 
+def allreduce_update(grads, param, m, v, kind, hyper):
+    """The reference's data-parallel step for one float32 tensor, all ranks at
+    once: ALLREDUCE SUM of the per-rank gradients (ascending rank order), then
+    the update operator -- TransformGrad (scale by grad_scale, clamp to
+    +-clip_value; operators/training/update_op_base.cc:21-38) and the kernel
+    loop (kernels/training/cpu/sgd_kernel.cc, adam_kernel.cc).  `param`, `m`
+    and `v` (None for the SGD kinds) are updated in place; every rank ends up
+    with these values.  kind: "momentum_sgd", "nesterov_sgd", "adam", "adamw";
+    hyper: dict(lr, momentum | beta1, beta2, eps, weight_decay, grad_scale,
+    clip_value) with lr / weight_decay as the kernel receives them."""
+    g = allreduce(grads, F32, "SUM").copy()
+    f32 = np.float32
+    if hyper.get("grad_scale", 1.0) != 1.0:
+        g *= f32(hyper["grad_scale"])
+    if hyper.get("clip_value", 0.0) > 0:
+        cv = f32(hyper["clip_value"])
+        g = np.ascontiguousarray(np.maximum(-cv, np.minimum(g, cv)))
+    if kind in ("momentum_sgd", "nesterov_sgd"):
+        momentum_sgd(g, m, param, hyper["lr"], hyper["momentum"], hyper["weight_decay"], kind == "nesterov_sgd")
+    elif kind == "adam":
+        adam(g, m, v, param, hyper["lr"], hyper["beta1"], hyper["beta2"], hyper["eps"], hyper["weight_decay"])
+    elif kind == "adamw":
+        adamw(g, m, v, param, hyper["lr"], hyper["beta1"], hyper["beta2"], hyper["eps"], hyper["weight_decay"])
+    else:
+        raise ValueError("unknown update kind {}".format(kind))
+
+
 def zero_shard_count(total, n):
     return (total + n - 1) // n
 

@@ -68,3 +68,7 @@ def test_operator_layer_registry(dgn_lib):
     assert lib.dragon_registry_rejects_duplicate(b"Collective") == 1
     assert lib.dragon_schema_allows_inplace(b"Collective", 0, 0) == 1
     assert lib.dragon_schema_allows_inplace(b"Collective", 3, 3) == 1
+    for name in (b"ZeroAdamW", b"SyncBNStats"):
+        assert lib.dragon_operator_is_registered(name) == 1
+    assert lib.dragon_schema_allows_inplace(b"SyncBNStats", 0, 0) == 1
+    assert lib.dragon_schema_allows_inplace(b"SyncBNStats", 0, 1) == 0
