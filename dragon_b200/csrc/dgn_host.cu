@@ -310,7 +310,6 @@ struct dgn_comm {
   int flow_switch_blocks = 0, flow_in_blocks = 0, flow_out_blocks = 0, flow_groups = 0, flow_depth = 0, unroll = 0;
   long long nvls_bcast_min_bytes = 0;  // smallest broadcast that goes through the switch
   bool plan_query = false, plan_query_in_symm = false;  // dgn_plan_query: no device, no real buffers
-  bool zero_ws = false;  // DGN_ZERO_WS=1: warp-specialised kernels of the sharded optimizer step
 };
 
 namespace {
@@ -354,12 +353,6 @@ int preload_kernels() {
     for (int which = 0; which < 3; ++which)
       DGN_CUDA(cudaFuncGetAttributes(&attr, zero_kernel_fn(dtype, which)));
   for (int kind = 0; kind < 4; ++kind) DGN_CUDA(cudaFuncGetAttributes(&attr, update_kernel_fn(kind)));
-  // Opt-in kernels: loaded ahead of time as well, but a failure here must not
-  // cost the communicator.
-  for (int dtype : zero_types) {
-    for (int which = 3; which < 5; ++which)
-      if (cudaFuncGetAttributes(&attr, zero_kernel_fn(dtype, which)) != cudaSuccess) cudaGetLastError();
-  }
   return DGN_OK;
 }
 
@@ -756,7 +749,6 @@ void load_thresholds(dgn_comm* c) {
   c->ll_allgather_max_bytes =
       env_ll("DGN_LL_ALLGATHER_MAX_BYTES", nranks <= 2 ? (512ll << 10) : nranks <= 4 ? (256ll << 10) : (64ll << 10));
   c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
-  c->zero_ws = env_ll("DGN_ZERO_WS", 0) != 0;
 }
 
 // Sizes and thresholds of the NVSwitch multicast paths; `symm_request` is the
@@ -827,8 +819,7 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
       break;
     case kOpZeroReduce:
     case kOpZeroUpdate:
-      // The warp-specialised versions need two warps at least.
-      k.fn = zero_kernel_fn(d.dtype, (d.kind == kOpZeroReduce ? 0 : 1) + (c->zero_ws && p.threads >= 64 ? 3 : 0));
+      k.fn = zero_kernel_fn(d.dtype, d.kind == kOpZeroReduce ? 0 : 1);
       k.smem = zero_smem_bytes(d.ntensors);
       break;
   }

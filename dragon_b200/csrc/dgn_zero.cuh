@@ -512,290 +512,6 @@ __global__ void __launch_bounds__(kMaxThreads, 1) zero_update_kernel(const __gri
 }
 
 // ---------------------------------------------------------------------------
-// Warp-specialised versions of the two kernels (opt-in, DGN_ZERO_WS=1): the
-// same data movement and arithmetic, but the link stage and the local stage of
-// a round are run by two groups of warps, each in its own loop over the rounds
-// with its own named barrier, so that NVLink and local HBM work at the same
-// time and a group that waits for a peer does not stop the other one.
-//   reduce kernel : pusher  [wait reduced(i-kDepth) on B]  push(i)    signal pushed(i)    on A
-//                   reducer  wait pushed(j) on A           reduce(j)  signal reduced(j)   on B
-//   update kernel : updater [wait emptied(i-kDepth) on B]  update(i)  signal published(i) on A
-//                   gatherer wait published(j) on A        gather(j)  signal emptied(j)   on B
-// Epoch of round j on both channels: base + j + 1; done = base + rounds + 1 (B).
-// Every rank must make the same choice (the epochs differ from the lock-step kernels).
-
-// One reduce step of a thread: the body of the lock-step kernel's reduce loop.
-template <typename T, int ES, int E>
-__device__ __forceinline__ void zero_reduce_vector(const ZeroParams& Z, const ZeroRank& zr, const FlatBucket<ES>& fb,
-                                                   const ShardGeom& mine, int n, int r, const char* inbox0,
-                                                   long long slot_bytes, long long off, long long v, float* sq,
-                                                   int* bad) {
-  const long long g = mine.g_lo + off + v;
-  uint4 x[kMaxRanks];
-#pragma unroll
-  for (int s = 0; s < kMaxRanks; ++s) {
-    if (s < n) x[s] = (s == r) ? flat_load<ES>(fb, fb.grad, g) : ldv(inbox0 + s * slot_bytes + v * 16);
-  }
-  const uint4 y = reduce_vectors<T, kSum>(x, n, false, 1.0);
-  float yf[E], d[E];
-  Elem<T>::unpack(y, yf);
-  const long long e0 = g * E;
-  const int l0 = (int)clampll(mine.e_lo - e0, 0, E), l1 = (int)clampll(mine.e_hi - e0, 0, E);
-#pragma unroll
-  for (int l = 0; l < E; ++l) {
-    if (l >= l0 && l < l1) {
-      if (!finite_f32(yf[l])) *bad = 1;
-      d[l] = __fmul_rn(yf[l], Z.grad_scale);
-      *sq = __fmaf_rn(d[l], d[l], *sq);
-    } else {
-      d[l] = 0.f;
-    }
-  }
-  store_state<E>(zr.gshard, (off + v) * E, d, 0, E);
-}
-
-template <typename T>
-__global__ void __launch_bounds__(kMaxThreads, 1) zero_reduce_ws_kernel(const __grid_constant__ ZeroParams Z) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ float s_sq[kMaxThreads / 32];
-  __shared__ int s_bad[kMaxThreads / 32];
-  __shared__ int s_abort;
-  constexpr int ES = (int)sizeof(T);
-  constexpr int E = 16 / ES;
-  const OpParams& P = Z.base;
-  const PeerTable& pt = P.peers[blockIdx.y];
-  const ZeroRank& zr = Z.zr[blockIdx.y];
-  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
-  const FlatBucket<ES> fb = make_bucket<ES>(Z, zr, smem);
-  if (threadIdx.x == 0) s_abort = 0;
-  Turn turn;
-  if (!begin_collective(pt, b, P, &turn)) return;  // block-wide barrier inside: s_abort is visible
-
-  const ShardGeom mine = shard_geom(Z.total, Z.rc, r, E);
-  const int rounds = P.rounds;
-  const long long cv = P.cv;
-  const long long stride = (long long)gridDim.x * cv;
-  const u64 base = turn.base;
-  const int nwarps = blockDim.x >> 5;  // at least two
-  int w_push = (nwarps * 3) >> 3;
-  if (w_push < 1) w_push = 1;
-  const int warp = threadIdx.x >> 5;
-  Role g;
-  const bool pusher = warp < w_push;
-  if (pusher) { g.id = 1; g.t = threadIdx.x; g.n = w_push * 32; }
-  else { g.id = 2; g.t = threadIdx.x - w_push * 32; g.n = (nwarps - w_push) * 32; }
-  volatile int* abort_flag = &s_abort;
-  bool alive = true;
-  float sq = 0.f;
-  int bad = 0;
-
-  if (pusher) {
-    for (int i = 0; i < rounds; ++i) {
-      if (i >= kDepth && !role_wait(pt, g, b, kChanB, base + (u64)(i - kDepth) + 1, P.wait_ns, abort_flag)) { alive = false; break; }
-      const long long off = (long long)i * stride + (long long)b * cv;
-      for (int k = 1; k < n; ++k) {
-        const int peer = (r + 1 + (k - 1 + b) % (n - 1)) % n;
-        const ShardGeom sg = shard_geom(Z.total, Z.rc, peer, E);
-        const long long len = clampll(sg.nv - off, 0, cv);
-        char* dst = slot_ptr(pt, peer, turn.parity, b, i % kDepth, r);
-        const long long g0 = sg.g_lo + off;
-        role_copy(g, len, [&](long long v) { return flat_load<ES>(fb, fb.grad, g0 + v); },
-                  [&](long long v, uint4 x) { stv(dst + v * 16, x); });
-      }
-      role_signal(pt, g, b, kChanA, base + (u64)i + 1);
-    }
-  } else {
-    for (int j = 0; j < rounds; ++j) {
-      if (!role_wait(pt, g, b, kChanA, base + (u64)j + 1, P.wait_ns, abort_flag)) { alive = false; break; }
-      const long long off = (long long)j * stride + (long long)b * cv;
-      const long long len = clampll(mine.nv - off, 0, cv);
-      const char* inbox0 = slot_ptr(pt, r, turn.parity, b, j % kDepth, 0);
-      for (long long v = g.t; v < len; v += g.n)
-        zero_reduce_vector<T, ES, E>(Z, zr, fb, mine, n, r, inbox0, pt.slot_bytes, off, v, &sq, &bad);
-      role_signal(pt, g, b, kChanB, base + (u64)j + 1);
-    }
-  }
-  // Per-block partials in a fixed order (the pushers contribute zeros).
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    bad |= __shfl_xor_sync(0xffffffffu, bad, o);
-  }
-  if ((threadIdx.x & 31) == 0) { s_sq[warp] = sq; s_bad[warp] = bad; }
-  if (__syncthreads_or(!alive)) return;  // a role that gave up takes the whole block out
-  if (threadIdx.x == 0) {
-    float tsq = 0.f;
-    int tbad = 0;
-    for (int w = 0; w < nwarps; ++w) { tsq += s_sq[w]; tbad |= s_bad[w]; }
-    pt.blk[b].zero_part = (u64)__float_as_uint(tsq) | ((u64)(unsigned)tbad << 32);
-    if (b == 0) pt.blk[0].zero_blocks = (u64)gridDim.x;
-  }
-  end_collective(pt, b, turn, base + (u64)rounds + 1);
-}
-
-template <typename T>
-__global__ void __launch_bounds__(kMaxThreads, 1) zero_update_ws_kernel(const __grid_constant__ ZeroParams Z) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ float s_sumsq;
-  __shared__ int s_bad, s_abort;
-  constexpr int ES = (int)sizeof(T);
-  constexpr int E = 16 / ES;
-  const OpParams& P = Z.base;
-  const PeerTable& pt = P.peers[blockIdx.y];
-  const ZeroRank& zr = Z.zr[blockIdx.y];
-  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
-  const FlatBucket<ES> fb = make_bucket<ES>(Z, zr, smem);
-  if (threadIdx.x == 0) s_abort = 0;
-  Turn turn;
-  if (!begin_collective(pt, b, P, &turn)) return;
-
-  if (threadIdx.x < 32) {
-    const int nb1 = (int)pt.blk[0].zero_blocks;
-    float sq = 0.f;
-    int bad = 0;
-    for (int j = threadIdx.x; j < nb1; j += 32) {
-      const u64 w = pt.blk[j].zero_part;
-      sq += __uint_as_float((unsigned)w);
-      bad |= (int)(w >> 32);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      sq += __shfl_xor_sync(0xffffffffu, sq, o);
-      bad |= __shfl_xor_sync(0xffffffffu, bad, o);
-    }
-    if (threadIdx.x == 0) { s_sumsq = sq; s_bad = bad; }
-  }
-  const u64 tag = pt.blk[b].zero_ops + 1;
-  __syncthreads();
-
-  bool overflow = false;
-  if (Z.check_finite) {  // the whole block, before the roles split
-    const int t = threadIdx.x;
-    const u64 word = (tag << 1) | (u64)(s_bad != 0);
-    bool ok = true;
-    int peer_bad = 0;
-    if (t < n && t != r) {
-      st_release_sys(pt.flags[t] + ((size_t)b * kChannels + kChanD) * kMaxRanks + r, word);
-      const u64* f = pt.flags[r] + ((size_t)b * kChannels + kChanD) * kMaxRanks + t;
-      u64 w = ld_acquire_sys(f);
-      if ((w >> 1) < tag) {
-        const u64 t0 = global_timer_ns();
-        unsigned spins = 0;
-        for (;;) {
-          w = ld_acquire_sys(f);
-          if ((w >> 1) >= tag) break;
-          if ((++spins & 31u) == 0u && global_timer_ns() - t0 > P.wait_ns) {
-            *(volatile int*)pt.status = kErrTimeout;
-            ok = false;
-            break;
-          }
-        }
-      }
-      peer_bad = (int)(w & 1ull);
-    }
-    if (!__syncthreads_and(ok)) return;
-    overflow = __syncthreads_or(peer_bad | (s_bad != 0)) != 0;
-    if (t == 0) {
-      pt.blk[b].zero_ops = tag;
-      if (b == 0 && zr.found_inf) *zr.found_inf += overflow ? 1.f : 0.f;
-    }
-  }
-
-  const int rounds = P.rounds;
-  const u64 base = turn.base;
-  bool alive = true;
-  if (!overflow) {
-    const ShardGeom mine = shard_geom(Z.total, Z.rc, r, E);
-    const long long cv = P.cv;
-    const long long stride = (long long)gridDim.x * cv;
-    const int nwarps = blockDim.x >> 5;  // at least two
-    int w_upd = (nwarps * 3) >> 2;
-    if (w_upd < 1) w_upd = 1;
-    if (w_upd >= nwarps) w_upd = nwarps - 1;
-    const int warp = threadIdx.x >> 5;
-    Role g;
-    const bool updater = warp < w_upd;
-    if (updater) { g.id = 1; g.t = threadIdx.x; g.n = w_upd * 32; }
-    else { g.id = 2; g.t = threadIdx.x - w_upd * 32; g.n = (nwarps - w_upd) * 32; }
-    volatile int* abort_flag = &s_abort;
-
-    if (updater) {
-      float factor = 1.f;
-      if (Z.clip_norm > 0.f) {
-        const float norm = __fsqrt_rn(s_sumsq);
-        if (norm > Z.clip_norm) factor = __fdiv_rn(Z.clip_norm, norm);
-      }
-      const bool by_value = !(Z.clip_norm > 0.f) && Z.clip_value > 0.f;
-      const float omb1 = __fsub_rn(1.f, Z.beta1), omb2 = __fsub_rn(1.f, Z.beta2);
-      const bool scaled = Z.use_lr_scales != 0;
-      for (int i = 0; i < rounds; ++i) {
-        if (i >= kDepth && !role_wait(pt, g, b, kChanB, base + (u64)(i - kDepth) + 1, P.wait_ns, abort_flag)) { alive = false; break; }
-        const long long off = (long long)i * stride + (long long)b * cv;
-        const long long len = clampll(mine.nv - off, 0, cv);
-        char* gdst[kMaxRanks];  // gather box [r] of peer (r + k) % n
-#pragma unroll
-        for (int k = 1; k < kMaxRanks; ++k)
-          gdst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, turn.parity, b, i % kDepth, n + r) : nullptr;
-        for (long long v = g.t; v < len; v += g.n) {
-          const long long gv = mine.g_lo + off + v;
-          const long long e0 = gv * E, idx = (off + v) * E;
-          const int l0 = (int)clampll(mine.e_lo - e0, 0, E), l1 = (int)clampll(mine.e_hi - e0, 0, E);
-          float d[E], x[E], mm[E], vv[E];
-          load_state<E>(zr.gshard, idx, d);
-          load_state<E>(zr.master, idx, x);
-          load_state<E>(zr.m, idx, mm);
-          load_state<E>(zr.v, idx, vv);
-          int t = scaled ? fb.find(e0 + l0) : 0;
-#pragma unroll
-          for (int l = 0; l < E; ++l) {
-            if (l >= l0 && l < l1) {
-              float gl = d[l];
-              if (Z.clip_norm > 0.f) gl = __fmul_rn(gl, factor);
-              else if (by_value) gl = fmaxf(-Z.clip_value, fminf(gl, Z.clip_value));
-              float ls = 1.f;
-              if (scaled) {
-                while (e0 + l >= fb.ebeg[t + 1]) ++t;
-                ls = fb.lrs[t];
-              }
-              adamw_lane(gl, Z.lr, Z.beta1, Z.beta2, Z.eps, Z.wd, omb1, omb2, scaled, ls, &mm[l], &vv[l], &x[l]);
-            }
-          }
-          store_state<E>(zr.master, idx, x, l0, l1);
-          store_state<E>(zr.m, idx, mm, l0, l1);
-          store_state<E>(zr.v, idx, vv, l0, l1);
-          const uint4 y = Elem<T>::pack(x);
-          flat_store<ES>(fb, gv, y, l0, l1);
-#pragma unroll
-          for (int k = 1; k < kMaxRanks; ++k)
-            if (k < n) stv(gdst[k] + v * 16, y);
-        }
-        role_signal(pt, g, b, kChanA, base + (u64)i + 1);
-      }
-    } else {
-      for (int j = 0; j < rounds; ++j) {
-        if (!role_wait(pt, g, b, kChanA, base + (u64)j + 1, P.wait_ns, abort_flag)) { alive = false; break; }
-        const long long off = (long long)j * stride + (long long)b * cv;
-        for (int k = 1; k < n; ++k) {
-          const int peer = (r + 1 + (k - 1 + b) % (n - 1)) % n;
-          const ShardGeom sg = shard_geom(Z.total, Z.rc, peer, E);
-          const long long len = clampll(sg.nv - off, 0, cv);
-          const char* src = slot_ptr(pt, r, turn.parity, b, j % kDepth, n + peer);
-          for (long long v = g.t; v < len; v += g.n) {
-            const long long gv = sg.g_lo + off + v;
-            const long long e0 = gv * E;
-            const int l0 = (int)clampll(sg.e_lo - e0, 0, E), l1 = (int)clampll(sg.e_hi - e0, 0, E);
-            flat_store<ES>(fb, gv, ldv(src + v * 16), l0, l1);
-          }
-        }
-        role_signal(pt, g, b, kChanB, base + (u64)j + 1);
-      }
-    }
-  }
-  if (__syncthreads_or(!alive)) return;
-  end_collective(pt, b, turn, base + (u64)rounds + 1);
-}
-
-// ---------------------------------------------------------------------------
 // fp32 master copies of this rank's parameter shard (the reference's
 // InitMaster, zero_update_op_base.cc:21-44); padding lanes become zero.
 // Local work: no peer is involved.

@@ -7,15 +7,13 @@
 namespace dgn {
 
 // which: 0 reduce-scatter into the gradient shard, 1 update + all-gather,
-//        2 master initialisation, 3 / 4 the warp-specialised versions of 0 / 1.
+//        2 master initialisation.
 template <typename T>
 static const void* zero_kernels_of(int which) {
   switch (which) {
     case 0: return (const void*)zero_reduce_kernel<T>;
     case 1: return (const void*)zero_update_kernel<T>;
     case 2: return (const void*)zero_init_master_kernel<T>;
-    case 3: return (const void*)zero_reduce_ws_kernel<T>;
-    case 4: return (const void*)zero_update_ws_kernel<T>;
     default: return nullptr;
   }
 }

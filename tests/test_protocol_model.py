@@ -493,53 +493,6 @@ def _join_and_end(roles, c, parity, done):
         rk.last_done[parity] = done
 
 
-def zero_ws_roles(me, n, steps):
-    """zero_reduce_ws_kernel + zero_update_ws_kernel: two roles each.  Reduce:
-    pusher / reducer; update: updater (stores into the peers' gather boxes) /
-    gatherer.  `steps` lists (rounds, overflow) per optimizer step."""
-    roles = [Rank(me, n, role) for role in range(2)]
-    first, second = roles
-    c = 0
-    for rounds, overflow in steps:
-        # reduce-scatter
-        base, parity = first.epoch, first.ops & 1
-        for rk in roles:
-            rk.wait(B, rk.peers, first.last_done[parity])
-        for i in range(rounds):
-            if i >= DEPTH:
-                first.wait(B, first.peers, base + (i - DEPTH) + 1)
-            first.data(*[("write", p, (parity, i % DEPTH, me), (c, i, me, "pushed")) for p in first.peers])
-            first.signal(A, first.peers, base + i + 1)
-        for j in range(rounds):
-            second.wait(A, second.peers, base + j + 1)
-            second.data(*[("read", (parity, j % DEPTH, s), (c, j, s, "pushed")) for s in second.peers])
-            second.signal(B, second.peers, base + j + 1)
-        _join_and_end(roles, c, parity, base + rounds + 1)
-        c += 1
-        # verdict, update, all-gather
-        base, parity = first.epoch, first.ops & 1
-        for rk in roles:
-            rk.wait(B, rk.peers, first.last_done[parity])
-        tag = first.zero_ops + 1
-        first.signal(D, first.peers, tag)       # before the roles split: the whole block takes part
-        for rk in roles:
-            rk.wait(D, rk.peers, tag)
-            rk.zero_ops = tag
-        if not overflow:
-            for i in range(rounds):
-                if i >= DEPTH:
-                    first.wait(B, first.peers, base + (i - DEPTH) + 1)
-                first.data(*[("write", p, (parity, i % DEPTH, n + me), (c, i, me, "updated")) for p in first.peers])
-                first.signal(A, first.peers, base + i + 1)
-            for j in range(rounds):
-                second.wait(A, second.peers, base + j + 1)
-                second.data(*[("read", (parity, j % DEPTH, n + p), (c, j, p, "updated")) for p in second.peers])
-                second.signal(B, second.peers, base + j + 1)
-        _join_and_end(roles, c, parity, base + rounds + 1)
-        c += 1
-    return roles
-
-
 def run_roles(n, build):
     procs = []
     for me in range(n):
@@ -638,12 +591,6 @@ def test_warp_specialised_twoshot(n, collectives):
     assert run_roles(n, lambda me, n_: twoshot_ws_roles(me, n_, collectives)) > 0
 
 
-@pytest.mark.parametrize("n,steps", [(2, ((5, False), (2, True), (3, False))), (3, ((4, False), (3, False))),
-                                     (4, ((3, False),))])
-def test_warp_specialised_sharded_optimizer_step(n, steps):
-    assert run_roles(n, lambda me, n_: zero_ws_roles(me, n_, steps)) > 0
-
-
 def test_eight_ranks():
     """The rank count of the target machine, with fewer rounds."""
     assert run(8, lambda rk: [nvls_inplace(rk, c) for c in range(2)]) > 0
@@ -653,7 +600,6 @@ def test_eight_ranks():
     assert run(8, lambda rk: broadcast_nvls(rk, 0, 3, root=5)) > 0
     assert run(8, lambda rk: broadcast_scatter(rk, 0, 3, root=5)) > 0
     assert run(5, lambda rk: allgather(rk, 0, 2)) > 0   # the pushing kernel branches more: five ranks
-    assert run_roles(5, lambda me, n: zero_ws_roles(me, n, ((3, False),))) > 0
 
 
 def test_the_model_catches_a_missing_wait():

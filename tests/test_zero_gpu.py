@@ -239,43 +239,6 @@ def test_bert_base_shaped_fp16_bucket_eight_ranks(teams):
     assert all(f.item() == 0.0 for f in found)
 
 
-# Kernels that are built and whose flag protocol is model-checked
-# (tests/test_protocol_model.py) but that have not been timed yet, so nothing
-# selects them by default; DGN_TEST_OPT_IN=1 runs their parity tests.
-opt_in = pytest.mark.skipif(os.environ.get("DGN_TEST_OPT_IN") != "1",
-                            reason="opt-in kernels: set DGN_TEST_OPT_IN=1 to run their parity tests")
-
-
-@opt_in
-@pytest.mark.parametrize("n", [2, 3, 8])
-@pytest.mark.parametrize("dtype", [oracle.F16, oracle.F32], ids=["f16", "f32"])
-def test_warp_specialised_kernels_match_the_oracle(dgn_lib, monkeypatch, n, dtype):
-    """DGN_ZERO_WS=1 (read when a communicator is created): same bit-exact bar."""
-    from dragon_b200.comm import Communicator
-    monkeypatch.setenv("DGN_ZERO_WS", "1")
-    comms = Communicator.emulated(n, 0)
-    try:
-        h = Harness(comms, RAGGED, dtype, lr_scales=[1.0, 0.5, 1.0, 2.0, 1.0, 1.0, 0.25])
-        found = [torch.zeros(1, dtype=torch.float32, device=DEV) for _ in range(n)]
-        for step in range(3):
-            grads = [_grads(r, step, RAGGED, dtype) for r in range(n)]
-            if step == 1:
-                grads[0][5] = np.inf
-            assert h.step(grads, found_inf=found) == (1.0 if step == 1 else 0.0)
-            h.check(what="warp-specialised step {}".format(step))
-        assert all(f.item() == 1.0 for f in found)
-        from dragon_b200 import workloads
-        counts = [int(np.prod(s)) for s in workloads.resnet50_shapes()]
-        if n == 8 and dtype == oracle.F32:  # several rounds per block
-            big = Harness(comms, counts, dtype)
-            big.step([_grads(r, 0, counts, dtype, scale=1e-3) for r in range(n)])
-            big.check(what="warp-specialised resnet50 bucket")
-    finally:
-        torch.cuda.synchronize()
-        for c in comms:
-            c.destroy()
-
-
 def test_argument_errors(teams, dgn_lib):
     import ctypes
     from dragon_b200 import _C
