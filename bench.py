@@ -550,9 +550,9 @@ def parity_pass(comm, rank, world, dev, dist, headline):
                          "ok": all_ranks(ok)}
 
     def tune(variant=0, **kw):
-        knobs = {k: kw.pop(k) for k in list(kw) if k.startswith("flow_") or k.endswith("_bytes") and k != "chunk_bytes"}
+        knobs = {k: kw.pop(k) for k in list(kw) if k in ("flow_depth", "nvls_unroll")}
         comm.set_tuning(variant=variant, **kw)
-        for k in ("flow_groups", "flow_depth"):
+        for k in ("flow_depth", "nvls_unroll"):
             comm.set_knob(k, knobs.get(k, 0))
 
     def allreduce_case(name, variant, kind, count, redop, ordered=True, symm=False, shift=0, want_rounds=0, **shape):
@@ -606,14 +606,14 @@ def parity_pass(comm, rank, world, dev, dist, headline):
                    blocks=8, chunk_bytes=16 << 10)
     allreduce_case("allreduce/twoshot_int64_sum", 2, "i64", 70001, "SUM")
     allreduce_case("allreduce/staged_ring_peer", 7, "f16", 3000001, "MEAN", want_rounds=9, chunk_bytes=256 << 10,
-                   flow_groups=2)
+                   flow_depth=4)
     bucket_case("allreduce/bucket_twoshot", 2, "f32", ragged_bucket, "MEAN")
     bucket_case("allreduce/bucket_ll_twoshot", 5, "f16", [4099, 1, 77, 30000], "MEAN")
     if nvls:
         allreduce_case("allreduce/staged_ring_multicast_f32", 3, "f32", (1 << 22) + 3, "MEAN", ordered=(world == 2),
-                       want_rounds=9, chunk_bytes=1 << 20, flow_groups=2)
+                       want_rounds=9, chunk_bytes=1 << 20, nvls_unroll=4)
         allreduce_case("allreduce/staged_ring_multicast_f16", 3, "f16", (1 << 23) + 1, "MEAN", ordered=False,
-                       want_rounds=9, chunk_bytes=1 << 20, flow_groups=4)
+                       want_rounds=9, chunk_bytes=1 << 20, nvls_unroll=16, flow_depth=4)
         allreduce_case("allreduce/staged_ring_multicast_bf16_one_chunk", 3, "bf16", 70001, "SUM", ordered=False)
         bucket_case("allreduce/bucket_staged_ring_multicast", 3, "f32", ragged_bucket, "MEAN", ordered=(world == 2),
                     chunk_bytes=1 << 20)

@@ -192,8 +192,8 @@ struct TableEntry {
 struct Plan {
   int variant = 0, blocks = 1, threads = 512, cv = 1, rounds = 1;
   int unroll = 8;  // multicast kernels: loads in flight per thread
-  // staged dataflow all-reduce: reducing / copy-in blocks (the rest copy out), ring slots, groups
-  int flow_nsw = 0, flow_nin = 0, flow_depth = 0, flow_groups = 1;
+  // staged dataflow all-reduce: reducing / copy-in blocks (the rest copy out), ring slots
+  int flow_nsw = 0, flow_nin = 0, flow_depth = 0;
 };
 
 enum OpKind { kOpAllReduce = 0, kOpReduceScatter, kOpAllGather, kOpBroadcast, kOpZeroReduce, kOpZeroUpdate,
@@ -304,10 +304,10 @@ struct dgn_comm {
   size_t symm_bytes = 0, symm_off = 0, symm_used = 0;
   long long symm_min_bytes = 0;
   // Staged dataflow all-reduce (ar_flow_kernel): ring inside the multicast-bound
-  // buffer, chunk size, block split, groups, ring slots, loads in flight (0: automatic).
+  // buffer, chunk size, block split, ring slots, loads in flight (0: automatic).
   size_t flow_ring_off = 0, flow_ring_bytes = 0;
   long long flow_chunk_bytes = 0;
-  int flow_switch_blocks = 0, flow_in_blocks = 0, flow_out_blocks = 0, flow_groups = 0, flow_depth = 0, unroll = 0;
+  int flow_switch_blocks = 0, flow_in_blocks = 0, flow_out_blocks = 0, flow_depth = 0, unroll = 0;
   long long nvls_bcast_min_bytes = 0;  // smallest broadcast that goes through the switch
   bool plan_query = false, plan_query_in_symm = false;  // dgn_plan_query: no device, no real buffers
 };
@@ -492,19 +492,15 @@ bool plan_flow(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring
   if (cv < n || cv > 0x7fffffff) return false;
   const long long K = ceil_div(d.nvec, cv);
   if (K > 0x7fffffff) return false;
-  int groups = c->flow_groups > 0 ? c->flow_groups : 2;
   long long depth = ring_bytes / (cv * 16);
   if (depth > kFlowSlots) depth = kFlowSlots;
   if (c->flow_depth > 0 && c->flow_depth < depth) depth = c->flow_depth;
   if (depth > K) depth = K;
-  if (groups > depth) groups = (int)depth;
-  if (groups < 1) groups = 1;
-  depth = depth / groups * groups;
+  if (depth < 1) depth = 1;
   int nsw = c->flow_switch_blocks > 0 ? c->flow_switch_blocks : (total >= 148 ? 64 : (total * 3) / 7);
   if (c->tune_blocks > 0) nsw = c->tune_blocks;
   if (nsw > total - 2) nsw = total - 2;
-  if (nsw < groups) nsw = groups;
-  if (nsw > total - 2) return false;
+  if (nsw < 1) nsw = 1;
   int nin = c->flow_in_blocks > 0 ? c->flow_in_blocks : (total - nsw) / 2;
   if (nin > total - nsw - 1) nin = total - nsw - 1;
   if (nin < 1) nin = 1;
@@ -516,7 +512,7 @@ bool plan_flow(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring
   p.threads = c->tune_threads > 0 ? c->tune_threads : 512;
   if (p.threads > kMaxThreads) p.threads = kMaxThreads;
   p.threads = p.threads / 32 * 32;
-  if (p.threads < 32) p.threads = 32;
+  if (p.threads < 64) p.threads = 64;  // a reducing block needs a data warp and its signal warp
   p.blocks = nsw + nin + nout;
   p.cv = (int)cv;
   p.rounds = (int)K;
@@ -524,7 +520,6 @@ bool plan_flow(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring
   p.flow_nsw = nsw;
   p.flow_nin = nin;
   p.flow_depth = (int)depth;
-  p.flow_groups = groups;
   *out = p;
   return true;
 }
@@ -788,7 +783,6 @@ void load_nvls_settings(dgn_comm* c, long long symm_request) {
   c->flow_switch_blocks = (int)env_ll("DGN_FLOW_SWITCH_BLOCKS", 0);
   c->flow_in_blocks = (int)env_ll("DGN_FLOW_IN_BLOCKS", 0);
   c->flow_out_blocks = (int)env_ll("DGN_FLOW_OUT_BLOCKS", 0);
-  c->flow_groups = (int)env_ll("DGN_FLOW_GROUPS", 0);
   c->flow_depth = (int)env_ll("DGN_FLOW_DEPTH", 0);
   c->unroll = (int)env_ll("DGN_NVLS_UNROLL", 0);
 }
@@ -843,7 +837,6 @@ void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p)
   P->flow_depth = p.flow_depth;
   P->flow_nsw = p.flow_nsw;
   P->flow_nin = p.flow_nin;
-  P->flow_groups = p.flow_groups;
 }
 
 void fill_zero_params(ZeroParams* Z, const dgn_comm* c, const OpDesc& d, const Plan& p) {
@@ -1725,7 +1718,6 @@ int dgn_comm_set_knob(dgn_comm_t c, const char* name, int64_t value) {
   else if (k == "flow_switch_blocks") c->flow_switch_blocks = (int)value;
   else if (k == "flow_in_blocks") c->flow_in_blocks = (int)value;
   else if (k == "flow_out_blocks") c->flow_out_blocks = (int)value;
-  else if (k == "flow_groups") c->flow_groups = (int)value;
   else if (k == "flow_depth") c->flow_depth = (int)value;
   else if (k == "nvls_unroll") c->unroll = (int)value;
   else if (k == "nvls_min_bytes") c->nvls_min_bytes = value;

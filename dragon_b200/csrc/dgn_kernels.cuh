@@ -136,9 +136,8 @@ struct OpParams {
   // staged dataflow all-reduce (ar_flow_kernel)
   long long flow_cv;           // vectors per chunk
   int flow_chunks;             // chunks of the message
-  int flow_depth;              // ring slots in use (a multiple of flow_groups)
+  int flow_depth;              // ring slots in use
   int flow_nsw, flow_nin;      // blocks [0, nsw) reduce, [nsw, nsw + nin) copy in, the rest copy out
-  int flow_groups;             // reducing blocks split into this many groups that take chunks in turn
 };
 
 // ---------------------------------------------------------------------------
@@ -1243,18 +1242,25 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_nvls_inplace_kernel(const _
 // local to the rank, flag words are written by peers):
 //   in_done[s]    += 1 per copy-in block          the last one sends ready(c)
 //   ready(c) from every rank, in_done complete    -> reduce chunk c
-//   sw_done[s]    += 1 per reducing warp          the last one sends done(c)
+//   sw_done[s]    += 1 per reducing block         the last one sends done(c)
 //   done(c) from every rank, sw_done complete     -> copy chunk c out
 //   out_done[s]   += 1 per copy-out block; complete for chunk c -> copy-in of chunk c + depth
 // done(c) from a peer also means that the peer has stopped reading this rank's
-// slot s, so refilling the slot after the copy-out is safe.  Reducing warps
-// never wait for a barrier: each warp streams through its chunks on its own,
-// so the load round trips of different warps overlap across chunk borders.
-// The reducing blocks are split into flow_groups groups that take chunks in
-// turn (depth is a multiple of the group count, so a slot always belongs to
-// one group).  Flag values are base + c + 1 with base = chunks moved by all
-// earlier launches of this kernel (kept in FlowState, advanced by the last
-// block to leave), separate per ring slot so that they only ever grow.
+// slot s, so refilling the slot after the copy-out is safe.  A block is counted
+// into sw_done[s] for chunk c only after chunk c - depth has been copied out.
+// Inside a reducing block the warps never meet at a barrier.  The rank's shard
+// of every chunk is cut into batches of 32 x unroll vectors, and the batches of
+// all chunks, in order, are dealt round-robin to all data warps of all reducing
+// blocks: a warp waits for ready(c) only when its next batch lies in chunk c,
+// streams through its batches (unroll loads in flight per lane, as in the
+// in-place kernel) and, leaving chunk c, adds one to a counter in shared memory
+// without waiting.  The last warp of the block is its signal warp: when all data
+// warps have left chunk c it publishes their stores (one system-scope fence) and
+// counts the block into sw_done.  So the fence and the flag traffic stay off the
+// data path, and chunk borders cost the data warps nothing but a poll.
+// Flag values are base + c + 1 with base = chunks moved by all earlier launches
+// of this kernel (kept in FlowState, advanced by the last block to leave),
+// separate per ring slot so that they only ever grow.
 // The kernel is launched cooperatively: its blocks wait for one another.
 
 constexpr int kFlowSlots = 8;
@@ -1309,10 +1315,31 @@ __device__ __forceinline__ bool flow_wait_flag(const u64* flag, u64 target, u64 
   }
 }
 
-// Thread 0 of a block (after a barrier) or lane 0 of a warp (after __syncwarp)
-// adds one to `counter`; when that completes `target` it tells every peer, on
-// flag (kind, s), that epoch `val` is reached.  The fences make everything the
-// counted blocks or warps have written visible before the flag.
+// One thread waits until a counter in shared memory reaches `target`.
+__device__ __forceinline__ bool flow_wait_shared(volatile int* counter, int target, u64 wait_ns, int* status) {
+  if (*counter >= target) return true;
+  const u64 t0 = global_timer_ns();
+  unsigned spins = 0;
+  for (;;) {
+    if (*counter >= target) return true;
+    if ((++spins & 63u) == 0u && global_timer_ns() - t0 > wait_ns) {
+      *(volatile int*)status = kErrTimeout;
+      return false;
+    }
+  }
+}
+
+// Raises a flag word to `v` (never lowers it): flags of consecutive chunks of a
+// ring slot are sent by different threads, and a maximum cannot be overtaken.
+__device__ __forceinline__ void red_max_release_sys(u64* p, u64 v) {
+  asm volatile("red.release.sys.global.max.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// One thread, on behalf of a block whose other threads it has met at a barrier
+// (or whose data warps it has counted), adds one to `counter`; when that
+// completes `target` it tells every peer, on flag (kind, s), that epoch `val`
+// is reached.  The fences make everything the counted blocks have written
+// visible before the flag.
 __device__ __forceinline__ void flow_arrive(const PeerTable& pt, unsigned* counter, unsigned target, int kind, int s,
                                             u64 val) {
   __threadfence_system();
@@ -1320,7 +1347,7 @@ __device__ __forceinline__ void flow_arrive(const PeerTable& pt, unsigned* count
   if (old + 1u == target) {
     __threadfence_system();
     for (int j = 0; j < pt.nranks; ++j)
-      if (j != pt.rank) st_release_sys(flow_flag(pt, j, kind, s, pt.rank), val);
+      if (j != pt.rank) red_max_release_sys(flow_flag(pt, j, kind, s, pt.rank), val);
   }
 }
 
@@ -1351,7 +1378,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
   const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
   FlowState* fs = flow_state(pt);
   const u64 base = fs->base;  // written by the last block of the previous launch
-  const int K = P.flow_chunks, D = P.flow_depth, G = P.flow_groups;
+  __shared__ int s_left[kFlowSlots];  // reducing blocks: data warps that have left chunk c, per c % kFlowSlots
+  __shared__ volatile int s_signalled;  // reducing blocks: chunks the signal warp has dealt with
+  const int K = P.flow_chunks, D = P.flow_depth;
   const int nsw = P.flow_nsw, nin = P.flow_nin, nout = (int)gridDim.x - nsw - nin;
   const long long CV = P.flow_cv;
   char* const ring = SWITCH ? pt.nvls_uc + pt.nvls_ring_off : reinterpret_cast<char*>(pt.flags[r]) + pt.ring_off;
@@ -1359,33 +1388,71 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
   bool ok = true;
 
   if (b < nsw) {
-    // Reducing block: every warp on its own.
-    const int g = b % G, bi = b / G;
-    const int group_blocks = (nsw - g + G - 1) / G;
-    const unsigned warps_per_chunk = (unsigned)(group_blocks * nwarps);
-    const int lane = threadIdx.x & 31;
-    const long long gw = (long long)bi * nwarps + (threadIdx.x >> 5);  // warp index inside the group
-    const long long step = (long long)warps_per_chunk * 32;
-    for (int c = g; c < K && ok; c += G) {
-      const int s = c % D;
-      const unsigned use = (unsigned)(c / D) + 1u;
-      if (lane == 0) ok = flow_wait_counter(&fs->in_done[s], (unsigned)nin * use, P.wait_ns, pt.status);
-      else if (lane <= n && lane - 1 != r && lane - 1 < n)
-        ok = flow_wait_flag(flow_flag(pt, r, 0, s, lane - 1), base + (u64)c + 1, P.wait_ns, pt.status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
-      const long long vs = (clen + n - 1) / n;
-      const long long lo = (long long)r * vs;
-      const long long len = clampll(clen - lo, 0, vs);
-      const long long off = ((long long)s * CV + lo) * 16;
-      if constexpr (SWITCH)
-        switch_reduce_dispatch<T>(P.unroll, pt.nvls_mc + pt.nvls_ring_off + off, gw * 32 + lane, len, step,
-                                  P.redop == kMean, P.scale);
-      else
-        plain_reduce_slice<T>(pt, off, gw * 32 + lane, len, step, P.redop, P.scale);
-      __syncwarp();
-      if (lane == 0) flow_arrive(pt, &fs->sw_done[s], warps_per_chunk * use, 1, s, base + (u64)c + 1);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ndata = nwarps - 1;  // the last warp signals, the others move data
+    if (warp == 0 && lane < kFlowSlots) s_left[lane] = 0;
+    if (threadIdx.x == 0) s_signalled = 0;
+    __syncthreads();
+    const int U = P.unroll >= 16 ? 16 : (P.unroll >= 8 ? 8 : 4);
+    const long long per_batch = 32ll * U;
+    const long long W = (long long)nsw * ndata;  // data warps of this rank
+    const long long full_len = CV / n;           // this rank's shard of a full chunk (CV is a multiple of n)
+    const long long nb_full = (full_len + per_batch - 1) / per_batch;
+    if (warp < ndata) {
+      const long long gw = (long long)b * ndata + warp;
+      for (int c = 0; c < K && ok; ++c) {
+        const int s = c % D;
+        const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
+        const long long vs = (clen + n - 1) / n;
+        const long long lo = (long long)r * vs;
+        const long long len = clampll(clen - lo, 0, vs);
+        const long long nb = (len + per_batch - 1) / per_batch;
+        long long k = (gw - ((long long)c * nb_full) % W + W) % W;  // my first batch of this chunk
+        if (k < nb) {
+          const unsigned use = (unsigned)(c / D) + 1u;
+          if (lane == 0) ok = flow_wait_counter(&fs->in_done[s], (unsigned)nin * use, P.wait_ns, pt.status);
+          else if (lane <= n && lane - 1 != r)
+            ok = flow_wait_flag(flow_flag(pt, r, 0, s, lane - 1), base + (u64)c + 1, P.wait_ns, pt.status);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          const long long off = ((long long)s * CV + lo) * 16;
+          for (; k < nb; k += W) {
+            const long long hi = k * per_batch + per_batch < len ? k * per_batch + per_batch : len;
+            if constexpr (SWITCH)
+              switch_reduce_dispatch<T>(U, pt.nvls_mc + pt.nvls_ring_off + off, k * per_batch + lane, hi, 32,
+                                        P.redop == kMean, P.scale);
+            else
+              plain_reduce_slice<T>(pt, off, k * per_batch + lane, hi, 32, P.redop, P.scale);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          // The counter of this chunk is reused every kFlowSlots chunks: wait until the signal warp has emptied it.
+          if (c >= kFlowSlots) ok = flow_wait_shared(&s_signalled, c - kFlowSlots + 1, P.wait_ns, pt.status);
+          __threadfence_block();
+          atomicAdd(&s_left[c % kFlowSlots], 1);
+        }
+        ok = __all_sync(0xffffffffu, ok);
+      }
+    } else {
+      for (int c = 0; c < K && ok; ++c) {
+        const int s = c % D;
+        const unsigned use = (unsigned)(c / D) + 1u;
+        if (lane == 0) {
+          ok = flow_wait_shared(&s_left[c % kFlowSlots], ndata, P.wait_ns, pt.status);
+          // Data warps without a batch in a chunk pass it at once.  The block is
+          // counted into sw_done[s] for chunk c only after chunk c - D has left
+          // the slot (copied out), so that the counts of two chunks never mix.
+          if (ok && c >= D) ok = flow_wait_counter(&fs->out_done[s], (unsigned)nout * (use - 1u), P.wait_ns, pt.status);
+          if (ok) {
+            s_left[c % kFlowSlots] = 0;
+            flow_arrive(pt, &fs->sw_done[s], (unsigned)nsw * use, 1, s, base + (u64)c + 1);
+            __threadfence_block();
+            s_signalled = c + 1;
+          }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+      }
     }
   } else if (b < nsw + nin) {
     const Message<ES, TABLE> msg = make_message<ES, TABLE>(P, ra, smem);
@@ -1420,10 +1487,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
     for (int c = 0; c < K; ++c) {
       const int s = c % D;
       const unsigned use = (unsigned)(c / D) + 1u;
-      const int g = c % G;
-      const unsigned warps_per_chunk = (unsigned)(((nsw - g + G - 1) / G) * nwarps);
       const int t = threadIdx.x;
-      if (t == 0) ok = flow_wait_counter(&fs->sw_done[s], warps_per_chunk * use, P.wait_ns, pt.status);
+      if (t == 0) ok = flow_wait_counter(&fs->sw_done[s], (unsigned)nsw * use, P.wait_ns, pt.status);
       else if (t <= n && t - 1 != r)
         ok = flow_wait_flag(flow_flag(pt, r, 1, s, t - 1), base + (u64)c + 1, P.wait_ns, pt.status);
       ok = __syncthreads_and(ok) != 0;

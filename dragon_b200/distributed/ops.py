@@ -78,3 +78,21 @@ def all_reduce_coalesced(tensors, reduction="sum", group=None, bucket_size=512 *
     _execute(group, tensors, outputs=tensors, operation="ALLREDUCE", reduction=reduction.upper(),
              bucket_size=bucket_size)
     return tensors
+
+
+def sync_batch_norm_statistics(stats, batch_size, group=None, count_on_device=False):
+    """The exchange of statistics of synchronized batch normalization
+    (normalization/batch_norm_op.cc:29-43 and :168-170): ``stats`` holds this
+    rank's ``2C`` partial sums (float32) and is all-reduced in place.
+
+    With ``count_on_device=False`` the batch count goes through the blocking
+    host all-reduce, as in the reference, and the global count is returned.
+    With ``count_on_device=True`` ``stats`` holds ``2C + 1`` values, the last one
+    receives ``float(batch_size)`` and travels with the statistics: one device
+    kernel, nothing blocks, and the global count is ``stats[-1]``."""
+    group = _resolve(group)
+    args = group.arguments.copy()
+    args["comm"] = dist_backend.comm_argument(group)
+    if args["comm"] == 0:
+        args["group"] = 0  # not a member: the operator leaves the tensor alone
+    return op_lib.run_sync_bn_stats(stats, batch_size, count_on_device=count_on_device, **args)

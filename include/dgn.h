@@ -167,7 +167,7 @@ int dgn_comm_set_tuning(dgn_comm_t comm, int variant, int blocks, int threads,
 
 /* Named launch parameters beyond dgn_comm_set_tuning (0 restores the automatic
  * choice): "flow_chunk_bytes", "flow_switch_blocks", "flow_in_blocks",
- * "flow_out_blocks", "flow_groups", "flow_depth" shape the staged ring
+ * "flow_out_blocks", "flow_depth" shape the staged ring
  * all-reduce, "nvls_unroll" (4, 8 or 16) is the number of multimem loads a
  * thread keeps in flight; "nvls_min_bytes", "symm_min_bytes",
  * "nvls_bcast_min_bytes" and "bcast_scatter_min_bytes" move the size thresholds

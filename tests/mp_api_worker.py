@@ -78,11 +78,11 @@ def body(rank, world, dev, dist, distributed, tdist, oracle, H, np, torch):
 
     # SyncBatchNorm statistics the way the reference runs them: the batch count
     # through the blocking host all-reduce, 2C floats through the device kernel.
-    from dragon_b200 import op_lib
+    from dragon_b200.distributed import ops
     channels = 256
     parts = [np.random.default_rng(40 + r).normal(0, 8, 2 * channels).astype(np.float32) for r in range(world)]
     stats = torch.from_numpy(parts[rank].copy()).to(dev)
-    total = op_lib.run_sync_bn_stats(stats, 16 + rank, **group.arguments)
+    total = ops.sync_batch_norm_statistics(stats, 16 + rank, group)
     torch.cuda.synchronize()
     assert total == sum(16 + r for r in range(world))
     H.assert_bits_equal(H.to_numpy(stats, oracle.F32), oracle.allreduce(parts, oracle.F32, "SUM"))

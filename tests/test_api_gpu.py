@@ -194,6 +194,34 @@ def test_cached_operator_is_repointed(group):
         assert all(torch.equal(x, torch.full((100 + step,), want, device=DEV)) for x in xs)
 
 
+@pytest.mark.parametrize("channels", [64, 256, 2048])
+def test_sync_batch_norm_statistics_operator(group, channels):
+    """The statistics exchange of synchronized batch normalization
+    (normalization/batch_norm_op.cc:29-43) through the `SyncBNStats` operator,
+    with the batch count riding on the device message: 2C + 1 floats, one
+    low-latency all-reduce, no host round trip.  Bit-exact against the oracle."""
+    from dragon_b200 import _C, op_lib
+    from dragon_b200 import distributed
+    from dragon_b200.distributed import ops
+    rng = np.random.default_rng(channels)
+    host = [np.concatenate([rng.normal(0, 1, 2 * channels).astype(np.float32) * 32, np.zeros(1, np.float32)])
+            for _ in range(N)]
+    batch = [32, 31, 32, 17]
+    stats = [torch.from_numpy(h.copy()).to(DEV) for h in host]
+    before = _C.lib().dgn_launch_count()
+    per_rank(lambda r: ops.sync_batch_norm_statistics(stats[r], batch[r], group, count_on_device=True))
+    assert _C.lib().dgn_launch_count() == before + 1          # one kernel for the whole exchange
+    for r in range(N):
+        host[r][-1] = float(batch[r])
+    want = oracle.allreduce(host, oracle.F32, "SUM")
+    for r in range(N):
+        H.assert_bits_equal(H.to_numpy(stats[r], oracle.F32), want, "rank {}".format(r))
+    assert float(stats[0][-1].item()) == float(sum(batch))
+    with distributed.as_rank(0):
+        with pytest.raises(op_lib.OperatorError, match="2C"):   # host-count form takes 2C floats
+            ops.sync_batch_norm_statistics(stats[0], 32, group)
+
+
 def test_single_rank_group_is_a_no_op(dgn_lib):
     """comm_size <= 1: the operator returns at once and touches nothing (collective_op.cc:89)."""
     from dragon_b200 import _C, distributed
@@ -242,30 +270,3 @@ def test_optimizer_call_sites(dgn_lib):
     finally:
         torch.cuda.synchronize()
         distributed.finalize()
-
-
-@pytest.mark.parametrize("channels", [64, 256, 2048])
-def test_sync_batch_norm_statistics_operator(group, channels):
-    """The statistics exchange of synchronized batch normalization
-    (normalization/batch_norm_op.cc:29-43) through the `SyncBNStats` operator,
-    with the batch count riding on the device message: 2C + 1 floats, one
-    low-latency all-reduce, no host round trip.  Bit-exact against the oracle."""
-    from dragon_b200 import _C, op_lib
-    from dragon_b200 import distributed
-    rng = np.random.default_rng(channels)
-    host = [np.concatenate([rng.normal(0, 1, 2 * channels).astype(np.float32) * 32, np.zeros(1, np.float32)])
-            for _ in range(N)]
-    batch = [32, 31, 32, 17]
-    stats = [torch.from_numpy(h.copy()).to(DEV) for h in host]
-    before = _C.lib().dgn_launch_count()
-    per_rank(lambda r: op_lib.run_sync_bn_stats(stats[r], batch[r], count_on_device=True, **group.arguments))
-    assert _C.lib().dgn_launch_count() == before + 1          # one kernel for the whole exchange
-    for r in range(N):
-        host[r][-1] = float(batch[r])
-    want = oracle.allreduce(host, oracle.F32, "SUM")
-    for r in range(N):
-        H.assert_bits_equal(H.to_numpy(stats[r], oracle.F32), want, "rank {}".format(r))
-    assert float(stats[0][-1].item()) == float(sum(batch))
-    with distributed.as_rank(0):
-        with pytest.raises(op_lib.OperatorError, match="2C"):   # host-count form takes 2C floats
-            op_lib.run_sync_bn_stats(stats[0], 32, count_on_device=False, **group.arguments)

@@ -123,14 +123,14 @@ def test_allreduce_multi_round_small_chunks(teams, n):
 def test_allreduce_staged_ring_many_chunks(teams, n):
     """The staged dataflow kernel (copy-in, reducing and copy-out blocks around
     a ring of chunk buffers) with chunks so small that every ring slot is
-    reused several times, for one tensor and for a bucket, with one, two and
-    four groups of reducing blocks."""
+    reused many times, for one tensor and for a bucket, with rings of one, two,
+    four and eight slots and 4, 8 and 16 loads in flight per lane."""
     comms = teams(n)
     try:
-        for groups, depth, chunk in ((1, 2, 4096), (2, 4, 8192), (4, 8, 4096), (2, 0, 65536)):
+        for unroll, depth, chunk in ((4, 1, 4096), (8, 2, 4096), (16, 4, 8192), (8, 8, 4096), (8, 0, 65536)):
             for c in comms:
                 c.set_tuning(variant=7, chunk_bytes=chunk)
-                c.set_knob("flow_groups", groups)
+                c.set_knob("nvls_unroll", unroll)
                 c.set_knob("flow_depth", depth)
             for dtype, redop in ((oracle.F32, "MEAN"), (oracle.BF16, "SUM"), (oracle.I64, "SUM")):
                 check_allreduce(comms, 200011, dtype, redop, inplace=True)
@@ -150,7 +150,7 @@ def test_allreduce_staged_ring_many_chunks(teams, n):
     finally:
         for c in comms:
             c.set_tuning()
-            c.set_knob("flow_groups", 0)
+            c.set_knob("nvls_unroll", 0)
             c.set_knob("flow_depth", 0)
 
 

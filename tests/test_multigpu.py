@@ -82,14 +82,14 @@ def test_nvls_allreduce_across_gpus(comms):
     if not comms[0].has_nvls():
         pytest.skip("NVSwitch multicast is not available on this box")
     assert all(c.has_nvls() for c in comms)
-    cases = ((oracle.F32, "MEAN", 5, 0, 1), (oracle.F32, "SUM", (1 << 20) + 3, 0, 2),
-             (oracle.F16, "MEAN", 1 << 24, 1 << 20, 2), (oracle.BF16, "SUM", (1 << 22) + 1, 256 << 10, 4),
-             (oracle.F32, "MEAN", 1 << 22, 1 << 20, 1), (oracle.F32, "SUM", 1 << 24, 0, 2))
+    cases = ((oracle.F32, "MEAN", 5, 0, 8), (oracle.F32, "SUM", (1 << 20) + 3, 0, 4),
+             (oracle.F16, "MEAN", 1 << 24, 1 << 20, 8), (oracle.BF16, "SUM", (1 << 22) + 1, 256 << 10, 16),
+             (oracle.F32, "MEAN", 1 << 22, 1 << 20, 4), (oracle.F32, "SUM", 1 << 24, 0, 8))
     try:
-        for dtype, redop, count, chunk, groups in cases:
+        for dtype, redop, count, chunk, unroll in cases:
             for c in comms:
                 c.set_tuning(variant=3, chunk_bytes=chunk)
-                c.set_knob("flow_groups", groups)
+                c.set_knob("nvls_unroll", unroll)
             arrays = [H.make_input(r, count, dtype) for r in range(n)]
             xs = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
             outs = [torch.empty_like(x) for x in xs]
@@ -114,7 +114,7 @@ def test_nvls_allreduce_across_gpus(comms):
         # A bucket of ragged tensors as one message, several chunks.
         for c in comms:
             c.set_tuning(variant=3, chunk_bytes=1 << 20)
-            c.set_knob("flow_groups", 2)
+            c.set_knob("nvls_unroll", 8)
         sizes = [70001, 3, 1 << 19, 257, (1 << 20) + 1]
         host = [[H.make_input(r, k, oracle.F32, seed=77 + i) for i, k in enumerate(sizes)] for r in range(n)]
         dev = [[H.to_torch(a, oracle.F32, "cuda:{}".format(r)) for a in host[r]] for r in range(n)]
@@ -131,7 +131,7 @@ def test_nvls_allreduce_across_gpus(comms):
     finally:
         for c in comms:
             c.set_tuning()
-            c.set_knob("flow_groups", 0)
+            c.set_knob("nvls_unroll", 0)
 
 
 @needs_two
@@ -338,7 +338,7 @@ def test_multicast_broadcast_across_gpus(comms):
 @needs_two
 def test_two_processes_over_ipc_and_file_rendezvous():
     with tempfile.TemporaryDirectory() as rdv:
-        env = dict(os.environ, DGN_NVLS="0")  # workers may leave early: keep them off the multicast object
+        env = dict(os.environ, DGN_NVLS="0", PYTHONFAULTHANDLER="1")  # workers may leave early: keep them off the multicast object
         procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "mp_gpu_worker.py"), str(r), "2", rdv],
                                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env) for r in range(2)]
         # Every wait in a worker is bounded (rendezvous, device-side waits), so the

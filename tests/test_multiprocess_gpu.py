@@ -25,7 +25,7 @@ def test_python_api_one_process_per_gpu(dgn_lib):
     s.bind(("127.0.0.1", 0))
     port = str(s.getsockname()[1])
     s.close()
-    env = dict(os.environ, DGN_NVLS="0")  # workers may leave early: keep them off the multicast object
+    env = dict(os.environ, DGN_NVLS="0", PYTHONFAULTHANDLER="1")  # workers may leave early: keep them off the multicast object
     procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "mp_api_worker.py"), str(r), str(world), port],
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env) for r in range(world)]
     # Every wait in a worker is bounded, so the workers leave on their own.

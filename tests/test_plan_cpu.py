@@ -29,7 +29,7 @@ def plan(lib, n, op, nbytes, dtype=_C.F32, redop=_C.MEAN, nvls=True, symm=0, in_
 def clean_env(monkeypatch):
     for name in ("DGN_FORCE_VARIANT", "DGN_LL_MAX_BYTES", "DGN_LL2_MAX_BYTES", "DGN_ONESHOT_MAX_BYTES",
                  "DGN_NVLS_MIN_BYTES", "DGN_SYMM_MIN_BYTES", "DGN_NVLS_BCAST_MIN_BYTES", "DGN_FLOW_CHUNK_BYTES",
-                 "DGN_FLOW_SWITCH_BLOCKS", "DGN_FLOW_GROUPS", "DGN_FLOW_DEPTH", "DGN_NVLS_RING_BYTES", "DGN_RING_BYTES",
+                 "DGN_FLOW_SWITCH_BLOCKS", "DGN_FLOW_DEPTH", "DGN_NVLS_RING_BYTES", "DGN_RING_BYTES",
                  "DGN_MAX_BLOCKS", "DGN_SLOT_BYTES", "DGN_LL_ALLGATHER_MAX_BYTES", "DGN_BCAST_SCATTER_MIN_BYTES"):
         monkeypatch.delenv(name, raising=False)
 

@@ -304,9 +304,10 @@ def nvls_inplace(rk, c):
     rk.data(*[("peek", me, ("user", s), (c, "result")) for s in range(n)])
 
 
-def flow_roles(me, n, collectives, depth, groups):
-    """ar_flow_kernel: the copy-in blocks, each group of reducing blocks and the
-    copy-out blocks of one rank as processes of their own.  `collectives` lists
+def flow_roles(me, n, collectives, depth, groups=1):
+    """ar_flow_kernel: the copy-in blocks, the reducing blocks (as `groups`
+    processes that take chunks in turn: reducing warps work on different chunks
+    at the same time) and the copy-out blocks of one rank as processes of their own.  `collectives` lists
     the number of chunks of consecutive launches; a launch ends when all roles
     have finished (the kernel boundary), and the epoch base grows by its chunk
     count.  Counters in_done / sw_done / out_done are per ring slot and local;
