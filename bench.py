@@ -419,7 +419,8 @@ def bench_emulated(args):
     out = {}
     comms = Communicator.emulated(8, 0)
     try:
-        names = sorted(EMULATED_CASES) if args.emulated_case in ("default", "all") else [args.emulated_case]
+        names = sorted(EMULATED_CASES) if args.emulated_case in ("default", "all") else \
+            [n for n in (args.emulated_case,) if n in EMULATED_CASES]
         if args.emulated_case == "default" and not args.emulated_only:
             names = ["ll_oneshot_64KiB", "twoshot_64MiB", "ring_64MiB", "allgather_8MiB"]
         for name in names:
