@@ -307,7 +307,7 @@ struct dgn_comm {
   // buffer, chunk size, block split, ring slots, loads in flight (0: automatic).
   size_t flow_ring_off = 0, flow_ring_bytes = 0;
   long long flow_chunk_bytes = 0;
-  int flow_switch_blocks = 0, flow_in_blocks = 0, flow_out_blocks = 0, flow_depth = 0, unroll = 0;
+  int flow_switch_blocks = 0, flow_in_blocks = 0, flow_out_blocks = 0, flow_depth = 0, unroll = 0, pattern = 0;
   long long nvls_bcast_min_bytes = 0;  // smallest broadcast that goes through the switch
   bool plan_query = false, plan_query_in_symm = false;  // dgn_plan_query: no device, no real buffers
 };
@@ -685,6 +685,13 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
       if (b > nb) b = nb;
       if (b < 1) b = 1;
       long long cv = ceil_div(d.nvec, b);
+      if (c->tune_chunk < 16) {
+        // Several rounds per block, so that the peers copy round i out while the
+        // root stores round i + 1: a quarter of the block's share, 64 KiB at least.
+        long long part = ceil_div(cv, 4);
+        if (part < 4096) part = 4096;
+        if (cv > part) cv = part;
+      }
       if (cv > cap_v) cv = cap_v;
       p.variant = DGN_VARIANT_NVLS;
       p.blocks = (int)b;
@@ -832,6 +839,7 @@ void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p)
   P->redop = d.redop;
   P->root = d.root;
   P->unroll = p.unroll;
+  P->pattern = c->pattern;
   P->flow_cv = p.cv;
   P->flow_chunks = p.rounds;
   P->flow_depth = p.flow_depth;
@@ -1720,6 +1728,7 @@ int dgn_comm_set_knob(dgn_comm_t c, const char* name, int64_t value) {
   else if (k == "flow_out_blocks") c->flow_out_blocks = (int)value;
   else if (k == "flow_depth") c->flow_depth = (int)value;
   else if (k == "nvls_unroll") c->unroll = (int)value;
+  else if (k == "nvls_pattern") c->pattern = (int)value;
   else if (k == "nvls_min_bytes") c->nvls_min_bytes = value;
   else if (k == "symm_min_bytes") c->symm_min_bytes = value;
   else if (k == "nvls_bcast_min_bytes") c->nvls_bcast_min_bytes = value;

@@ -132,7 +132,8 @@ struct OpParams {
   int cv;                      // vectors per block per round (<= slot_bytes / 16)
   int redop;
   int root;
-  int unroll;                  // multicast kernels: loads in flight per thread (4, 8 or 16)
+  int unroll;                  // multicast kernels: loads in flight per thread (1, 2, 4, 8 or 16)
+  int pattern;                 // in-place multicast kernel: 0 contiguous batches per warp, 1 grid-strided
   // staged dataflow all-reduce (ar_flow_kernel)
   long long flow_cv;           // vectors per chunk
   int flow_chunks;             // chunks of the message
@@ -1184,8 +1185,12 @@ __device__ __forceinline__ void switch_reduce_dispatch(int unroll, char* mc, lon
                                                        long long step, bool mean, double scale) {
   if (unroll >= 16) switch_reduce_slice<T, 16>(mc, first, len, step, mean, scale);
   else if (unroll >= 8) switch_reduce_slice<T, 8>(mc, first, len, step, mean, scale);
-  else switch_reduce_slice<T, 4>(mc, first, len, step, mean, scale);
+  else if (unroll >= 4) switch_reduce_slice<T, 4>(mc, first, len, step, mean, scale);
+  else if (unroll >= 2) switch_reduce_slice<T, 2>(mc, first, len, step, mean, scale);
+  else switch_reduce_slice<T, 1>(mc, first, len, step, mean, scale);
 }
+
+__device__ __forceinline__ int clamp_unroll(int u) { return u >= 16 ? 16 : u >= 8 ? 8 : u >= 4 ? 4 : u >= 2 ? 2 : 1; }
 
 // ---------------------------------------------------------------------------
 // ALLREDUCE through NVSwitch multicast, in place on a buffer that itself lives
@@ -1214,9 +1219,25 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_nvls_inplace_kernel(const _
   const long long lo = (long long)r * vs;
   const long long len = clampll(P.nvec - lo, 0, vs);
   char* mc = pt.nvls_mc + (static_cast<char*>(ra.out) - pt.nvls_uc) + lo * 16;
-  const long long step = (long long)gridDim.x * blockDim.x;
-  switch_reduce_dispatch<T>(P.unroll, mc, (long long)b * blockDim.x + threadIdx.x, len, step, P.redop == kMean,
-                            P.scale);
+  if (P.pattern == 0) {
+    // Every warp owns whole batches of 32 x unroll consecutive vectors (unroll x 512
+    // contiguous bytes per warp and step), dealt round-robin to the warps of the grid.
+    const int U = clamp_unroll(P.unroll);
+    const long long per_batch = 32ll * U;
+    const long long W = (long long)gridDim.x * (blockDim.x >> 5);
+    const long long gw = (long long)b * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const long long nb = (len + per_batch - 1) / per_batch;
+    for (long long k = gw; k < nb; k += W) {
+      const long long hi = k * per_batch + per_batch < len ? k * per_batch + per_batch : len;
+      switch_reduce_dispatch<T>(U, mc, k * per_batch + lane, hi, 32, P.redop == kMean, P.scale);
+    }
+  } else {
+    // Grid-strided: consecutive loads of a thread lie one grid of vectors apart.
+    const long long step = (long long)gridDim.x * blockDim.x;
+    switch_reduce_dispatch<T>(P.unroll, mc, (long long)b * blockDim.x + threadIdx.x, len, step, P.redop == kMean,
+                              P.scale);
+  }
   end_collective(pt, b, turn, turn.base + 2);  // barrier, then the release store of "done"
   wait_peers(pt, b, kChanB, turn.base + 2, P.wait_ns);
 }
@@ -1393,7 +1414,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
     if (warp == 0 && lane < kFlowSlots) s_left[lane] = 0;
     if (threadIdx.x == 0) s_signalled = 0;
     __syncthreads();
-    const int U = P.unroll >= 16 ? 16 : (P.unroll >= 8 ? 8 : 4);
+    const int U = clamp_unroll(P.unroll);
     const long long per_batch = 32ll * U;
     const long long W = (long long)nsw * ndata;  // data warps of this rank
     const long long full_len = CV / n;           // this rank's shard of a full chunk (CV is a multiple of n)
@@ -1525,22 +1546,25 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
 }
 
 // ---------------------------------------------------------------------------
-// ALLGATHER (bytes), stores only.  Per round every rank stores its slice into
-// gather box [r] of every peer (and into its own block of the output), signals
-// (A), waits for all peers' slices, copies its gather boxes into the peers'
-// blocks of the output and signals (B) that the boxes are empty.  The push of
-// round i + 1 is issued before the local copy of round i, so the link keeps
-// working while boxes are emptied; box halves alternate per round, and a half
-// is refilled only after B of the round that used it came from every peer.
-// Peer traffic is remote stores exclusively (the fastest pattern on NVLink).
-// Epochs of round i: A = base+2i+1, B = base+2i+2; done = base+2*rounds+1 (B).
-// `count` is bytes per rank here.
+// ALLGATHER (bytes), stores only, two warp roles per block.
+//   pusher : [wait drained(i-2) on B]  store my slice of round i into gather box [r]
+//            of every peer and into my own block of the output   signal pushed(i)  on A
+//   drainer: wait pushed(j) on A from every peer; copy my gather boxes into the
+//            peers' blocks of my output                           signal drained(j) on B
+// The pusher feeds the link while the drainer moves data inside local HBM; box
+// halves alternate per round, and a half is refilled only after every peer has
+// drained the round that used it.  Peer traffic is remote stores exclusively
+// (the fastest pattern on NVLink).  Epoch of round j on both channels:
+// base + j + 1; done = base + rounds + 1 (B).  `count` is bytes per rank here.
+// Blocks of fewer than 64 threads run the two roles one after the other per round.
 
 template <int kUnused>
 __global__ void __launch_bounds__(kMaxThreads, 1) allgather_kernel(const __grid_constant__ OpParams P) {
+  __shared__ int s_abort;
   const PeerTable& pt = P.peers[blockIdx.y];
   const RankArgs& ra = P.ra[blockIdx.y];
   const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
+  if (threadIdx.x == 0) s_abort = 0;
   Turn turn;
   if (!begin_collective(pt, b, P, &turn)) return;
   const char* in = static_cast<const char*>(ra.in);
@@ -1550,44 +1574,62 @@ __global__ void __launch_bounds__(kMaxThreads, 1) allgather_kernel(const __grid_
   const bool mine_al = is_al16(mine);
   const long long cv = P.cv;
   const int R = P.rounds;
+  const u64 base = turn.base;
+  volatile int* abort_flag = &s_abort;
 
-  auto push = [&](int round) -> bool {
-    // Peers emptied this half two rounds ago.
-    if (round >= 2 && !wait_peers(pt, b, kChanB, turn.base + 2 * (u64)(round - 2) + 2, P.wait_ns)) return false;
-    const long long off = ((long long)round * gridDim.x + b) * cv;
+  const int nwarps = blockDim.x >> 5;
+  const bool split = nwarps >= 2;
+  const int w_push = split ? (nwarps + 1) / 2 : nwarps;
+  Role g;
+  int role;
+  if (!split) { role = -1; g.id = 1; g.t = threadIdx.x; g.n = blockDim.x; }
+  else if ((int)(threadIdx.x >> 5) < w_push) { role = 0; g.id = 1; g.t = threadIdx.x; g.n = w_push * 32; }
+  else { role = 1; g.id = 2; g.t = threadIdx.x - w_push * 32; g.n = (nwarps - w_push) * 32; }
+  bool alive = true;
+
+  auto push = [&](int i) -> bool {
+    if (i >= 2 && !role_wait(pt, g, b, kChanB, base + (u64)(i - 2) + 1, P.wait_ns, abort_flag)) return false;
+    const long long off = ((long long)i * gridDim.x + b) * cv;
     const long long len = clampll(P.nvec - off, 0, cv);
     char* dst[kMaxRanks];
 #pragma unroll
     for (int k = 1; k < kMaxRanks; ++k)
-      dst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, turn.parity, b, round & 1, n + r) : nullptr;
-    copy_vectors(len, [&](long long v) { return load_vec<1>(in, off + v, P.count, in_al); },
-                 [&](long long v, uint4 x) {
-                   if (mine != in) store_vec<1>(mine, off + v, P.count, mine_al, x);
+      dst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, turn.parity, b, i & 1, n + r) : nullptr;
+    role_copy(g, len, [&](long long v) { return load_vec<1>(in, off + v, P.count, in_al); },
+              [&](long long v, uint4 x) {
+                if (mine != in) store_vec<1>(mine, off + v, P.count, mine_al, x);
 #pragma unroll
-                   for (int k = 1; k < kMaxRanks; ++k)
-                     if (k < n) stv(dst[k] + v * 16, x);
-                 });
-    signal_peers(pt, b, kChanA, turn.base + 2 * (u64)round + 1);
+                for (int k = 1; k < kMaxRanks; ++k)
+                  if (k < n) stv(dst[k] + v * 16, x);
+              });
+    role_signal(pt, g, b, kChanA, base + (u64)i + 1);
     return true;
   };
-
-  if (!push(0)) return;
-  for (int round = 0; round < R; ++round) {
-    if (round + 1 < R && !push(round + 1)) return;
-    if (!wait_peers(pt, b, kChanA, turn.base + 2 * (u64)round + 1, P.wait_ns)) return;
-    const long long off = ((long long)round * gridDim.x + b) * cv;
+  auto drain = [&](int j) -> bool {
+    if (!role_wait(pt, g, b, kChanA, base + (u64)j + 1, P.wait_ns, abort_flag)) return false;
+    const long long off = ((long long)j * gridDim.x + b) * cv;
     const long long len = clampll(P.nvec - off, 0, cv);
     for (int k = 1; k < n; ++k) {
       const int peer = (r + k) % n;
-      const char* src = slot_ptr(pt, r, turn.parity, b, round & 1, n + peer);
+      const char* src = slot_ptr(pt, r, turn.parity, b, j & 1, n + peer);
       char* dst = out + (long long)peer * P.count;
       const bool dst_al = is_al16(dst);
-      copy_vectors(len, [&](long long v) { return ldv(src + v * 16); },
-                   [&](long long v, uint4 x) { store_vec<1>(dst, off + v, P.count, dst_al, x); });
+      role_copy(g, len, [&](long long v) { return ldv(src + v * 16); },
+                [&](long long v, uint4 x) { store_vec<1>(dst, off + v, P.count, dst_al, x); });
     }
-    signal_peers(pt, b, kChanB, turn.base + 2 * (u64)round + 2);
+    role_signal(pt, g, b, kChanB, base + (u64)j + 1);
+    return true;
+  };
+
+  if (role == 0) {
+    for (int i = 0; i < R && alive; ++i) alive = push(i);
+  } else if (role == 1) {
+    for (int j = 0; j < R && alive; ++j) alive = drain(j);
+  } else {
+    for (int i = 0; i < R && alive; ++i) alive = push(i) && drain(i);
   }
-  end_collective(pt, b, turn, turn.base + 2 * (u64)R + 1);
+  if (__syncthreads_or(!alive)) return;
+  end_collective(pt, b, turn, base + (u64)R + 1);
 }
 
 // ---------------------------------------------------------------------------
