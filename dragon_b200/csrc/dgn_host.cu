@@ -307,7 +307,7 @@ struct dgn_comm {
   // buffer, chunk size, block split, ring slots, loads in flight (0: automatic).
   size_t flow_ring_off = 0, flow_ring_bytes = 0;
   long long flow_chunk_bytes = 0;
-  int flow_switch_blocks = 0, flow_in_blocks = 0, flow_out_blocks = 0, flow_depth = 0, unroll = 0, pattern = 0;
+  int flow_switch_blocks = 0, flow_in_blocks = 0, flow_out_blocks = 0, flow_depth = 0, unroll = 0, pattern = 0, flow_debug = 0;
   long long nvls_bcast_min_bytes = 0;  // smallest broadcast that goes through the switch
   bool plan_query = false, plan_query_in_symm = false;  // dgn_plan_query: no device, no real buffers
 };
@@ -845,6 +845,7 @@ void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p)
   P->flow_depth = p.flow_depth;
   P->flow_nsw = p.flow_nsw;
   P->flow_nin = p.flow_nin;
+  P->flow_debug = c->flow_debug;
 }
 
 void fill_zero_params(ZeroParams* Z, const dgn_comm* c, const OpDesc& d, const Plan& p) {
@@ -1729,6 +1730,7 @@ int dgn_comm_set_knob(dgn_comm_t c, const char* name, int64_t value) {
   else if (k == "flow_depth") c->flow_depth = (int)value;
   else if (k == "nvls_unroll") c->unroll = (int)value;
   else if (k == "nvls_pattern") c->pattern = (int)value;
+  else if (k == "flow_debug") c->flow_debug = (int)value;
   else if (k == "nvls_min_bytes") c->nvls_min_bytes = value;
   else if (k == "symm_min_bytes") c->symm_min_bytes = value;
   else if (k == "nvls_bcast_min_bytes") c->nvls_bcast_min_bytes = value;

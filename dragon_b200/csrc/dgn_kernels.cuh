@@ -139,6 +139,7 @@ struct OpParams {
   int flow_chunks;             // chunks of the message
   int flow_depth;              // ring slots in use
   int flow_nsw, flow_nin;      // blocks [0, nsw) reduce, [nsw, nsw + nin) copy in, the rest copy out
+  int flow_debug;              // experiments only: bit 0 skips the copy-in loads/stores, bit 1 the copy-out ones
 };
 
 // ---------------------------------------------------------------------------
@@ -1276,9 +1277,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_nvls_inplace_kernel(const _
 // streams through its batches (unroll loads in flight per lane, as in the
 // in-place kernel) and, leaving chunk c, adds one to a counter in shared memory
 // without waiting.  The last warp of the block is its signal warp: when all data
-// warps have left chunk c it publishes their stores (one system-scope fence) and
-// counts the block into sw_done.  So the fence and the flag traffic stay off the
-// data path, and chunk borders cost the data warps nothing but a poll.
+// warps have left chunk c it publishes their stores (one system-scope fence for
+// all chunks they have left by then) and counts the block into sw_done.  So the
+// fence and the flag traffic stay off the data path, and chunk borders cost the
+// data warps nothing but a poll.
 // Flag values are base + c + 1 with base = chunks moved by all earlier launches
 // of this kernel (kept in FlowState, advanced by the last block to leave),
 // separate per ring slot so that they only ever grow.
@@ -1352,24 +1354,30 @@ __device__ __forceinline__ bool flow_wait_shared(volatile int* counter, int targ
 
 // Raises a flag word to `v` (never lowers it): flags of consecutive chunks of a
 // ring slot are sent by different threads, and a maximum cannot be overtaken.
-__device__ __forceinline__ void red_max_release_sys(u64* p, u64 v) {
-  asm volatile("red.release.sys.global.max.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+// Relaxed: the caller orders it behind its data with a system-scope fence.
+__device__ __forceinline__ void red_max_relaxed_sys(u64* p, u64 v) {
+  asm volatile("red.relaxed.sys.global.max.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
 // One thread, on behalf of a block whose other threads it has met at a barrier
 // (or whose data warps it has counted), adds one to `counter`; when that
 // completes `target` it tells every peer, on flag (kind, s), that epoch `val`
-// is reached.  The fences make everything the counted blocks have written
-// visible before the flag.
-__device__ __forceinline__ void flow_arrive(const PeerTable& pt, unsigned* counter, unsigned target, int kind, int s,
-                                            u64 val) {
-  __threadfence_system();
+// is reached.  The caller has issued a system-scope fence after the block's
+// writes; the fence here orders the flags behind the arrivals of the other
+// blocks that this thread has just observed through the counter.
+__device__ __forceinline__ void flow_count(const PeerTable& pt, unsigned* counter, unsigned target, int kind, int s,
+                                           u64 val) {
   const unsigned old = atomicAdd(counter, 1u);
   if (old + 1u == target) {
     __threadfence_system();
     for (int j = 0; j < pt.nranks; ++j)
-      if (j != pt.rank) red_max_release_sys(flow_flag(pt, j, kind, s, pt.rank), val);
+      if (j != pt.rank) red_max_relaxed_sys(flow_flag(pt, j, kind, s, pt.rank), val);
   }
+}
+__device__ __forceinline__ void flow_arrive(const PeerTable& pt, unsigned* counter, unsigned target, int kind, int s,
+                                            u64 val) {
+  __threadfence_system();
+  flow_count(pt, counter, target, kind, s, val);
 }
 
 // Reduce stage without the switch: vectors first, first + step, ... of the own
@@ -1456,23 +1464,37 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
         ok = __all_sync(0xffffffffu, ok);
       }
     } else {
-      for (int c = 0; c < K && ok; ++c) {
-        const int s = c % D;
-        const unsigned use = (unsigned)(c / D) + 1u;
+      // Signal warp.  A system-scope fence behind a stream of multicast stores
+      // takes many microseconds, so one fence serves every chunk that all data
+      // warps have left by then (and whose ring slot is free): the chain of
+      // fences never falls behind the data warps, however small the chunks are.
+      volatile int* left = s_left;
+      int c = 0;
+      while (c < K && ok) {
+        int hi = c;
         if (lane == 0) {
           ok = flow_wait_shared(&s_left[c % kFlowSlots], ndata, P.wait_ns, pt.status);
           // Data warps without a batch in a chunk pass it at once.  The block is
           // counted into sw_done[s] for chunk c only after chunk c - D has left
           // the slot (copied out), so that the counts of two chunks never mix.
-          if (ok && c >= D) ok = flow_wait_counter(&fs->out_done[s], (unsigned)nout * (use - 1u), P.wait_ns, pt.status);
+          if (ok && c >= D)
+            ok = flow_wait_counter(&fs->out_done[c % D], (unsigned)nout * (unsigned)(c / D), P.wait_ns, pt.status);
           if (ok) {
-            s_left[c % kFlowSlots] = 0;
-            flow_arrive(pt, &fs->sw_done[s], (unsigned)nsw * use, 1, s, base + (u64)c + 1);
+            while (hi + 1 < K && hi + 1 < c + kFlowSlots && left[(hi + 1) % kFlowSlots] >= ndata &&
+                   (hi + 1 < D ||
+                    ld_acquire_gpu_u32(&fs->out_done[(hi + 1) % D]) >= (unsigned)nout * (unsigned)((hi + 1) / D)))
+              ++hi;
+            __threadfence_system();
+            for (int j = c; j <= hi; ++j) {
+              left[j % kFlowSlots] = 0;
+              flow_count(pt, &fs->sw_done[j % D], (unsigned)nsw * ((unsigned)(j / D) + 1u), 1, j % D, base + (u64)j + 1);
+            }
             __threadfence_block();
-            s_signalled = c + 1;
+            s_signalled = hi + 1;
           }
         }
         ok = __all_sync(0xffffffffu, ok);
+        c = __shfl_sync(0xffffffffu, hi, 0) + 1;
       }
     }
   } else if (b < nsw + nin) {
@@ -1490,7 +1512,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
       const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
       const long long vbase = (long long)c * CV;
       char* dst = ring + (long long)s * CV * 16;
-      long long v = first;
+      long long v = (P.flow_debug & 1) ? clen : first;
       for (; v + 3 * step < clen; v += 4 * step) {
         const uint4 x0 = msg.load(vbase + v), x1 = msg.load(vbase + v + step), x2 = msg.load(vbase + v + 2 * step),
                     x3 = msg.load(vbase + v + 3 * step);
@@ -1517,7 +1539,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
       const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
       const long long vbase = (long long)c * CV;
       const char* src = ring + (long long)s * CV * 16;
-      long long v = first;
+      long long v = (P.flow_debug & 2) ? clen : first;
       for (; v + 3 * step < clen; v += 4 * step) {
         const uint4 x0 = ldv(src + v * 16), x1 = ldv(src + (v + step) * 16), x2 = ldv(src + (v + 2 * step) * 16),
                     x3 = ldv(src + (v + 3 * step) * 16);
