@@ -660,6 +660,7 @@ def parity_pass(comm, rank, world, dev, dist, headline):
     gather_case("allgather/low_latency", 4, "i64", 4099)
     gather_case("allgather/push_int64", 2, "i64", 65536)
     gather_case("allgather/push_bf16_many_rounds", 2, "bf16", (1 << 21) + 3, blocks=8, chunk_bytes=32 << 10)
+    gather_case("allgather/pull_bf16_many_rounds", 1, "bf16", (1 << 21) + 3, blocks=8, chunk_bytes=32 << 10)
     for root in sorted({0, world - 1}):
         broadcast_case("broadcast/pull_root{}".format(root), 1, "i64", 65536, root)
         if world > 2:

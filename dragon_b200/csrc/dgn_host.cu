@@ -45,6 +45,7 @@ const void* reduce_kernel_fn_5(int, bool);
 const void* reduce_kernel_fn_6(int, bool);
 const void* reduce_kernel_fn_7(int, bool);
 const void* allgather_kernel_fn();
+const void* allgather_pull_kernel_fn();
 const void* allgather_ll_kernel_fn();
 const void* broadcast_kernel_fn();
 const void* broadcast_scatter_kernel_fn();
@@ -276,6 +277,7 @@ struct dgn_comm {
   long long tune_chunk = 0;
   long long oneshot_max_bytes = -1, ll_max_bytes = -1, ll2_max_bytes = -1;
   long long bcast_scatter_min_bytes = 1ll << 20;
+  long long allgather_pull_min_bytes = 1ll << 62;  // per-rank block from which peers pull instead of being pushed to
   long long ll_allgather_max_bytes = 512ll << 10;  // per-rank block of the low-latency all-gather (set per rank count)
   bool fused_twoshot = false;  // DGN_TWOSHOT_FUSED=1: lock-step two-shot kernel instead of the warp-specialised one
   Team* team = nullptr;
@@ -340,6 +342,7 @@ int preload_kernels() {
     }
   }
   DGN_CUDA(cudaFuncGetAttributes(&attr, allgather_kernel_fn()));
+  DGN_CUDA(cudaFuncGetAttributes(&attr, allgather_pull_kernel_fn()));
   DGN_CUDA(cudaFuncGetAttributes(&attr, allgather_ll_kernel_fn()));
   DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_kernel_fn()));
   DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_scatter_kernel_fn()));
@@ -476,15 +479,16 @@ bool plan_flow(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring
   if (total > c->geo.max_blocks) total = c->geo.max_blocks;
   if (block_cap > 0 && block_cap < total) total = block_cap;
   if (total < 3 || ring_bytes < 2 * 4096) return false;
-  // Chunks: an eighth of the message, between 1 and 32 MiB.  Small chunks fill
-  // and drain the pipeline quickly; large ones keep more loads of one rank's
-  // shard (1/n of a chunk) in flight.
+  // Chunks: a quarter of the message, between 1 and 16 MiB.  Measured at 8 ranks
+  // (8 reducing blocks): 16 MiB chunks are best from 64 MiB to 1 GiB (192 / 332 /
+  // 615 / 2320 us at 64 / 128 / 256 / 1024 MiB); smaller chunks pay a few
+  // microseconds each for their flags, larger ones fill and drain longer.
   long long chunk = c->flow_chunk_bytes;
   if (c->tune_chunk >= 4096) chunk = c->tune_chunk;
   if (chunk <= 0) {
-    chunk = ceil_div(bytes, 8);
+    chunk = ceil_div(bytes, 4);
     if (chunk < (1ll << 20)) chunk = 1ll << 20;
-    if (chunk > (32ll << 20)) chunk = 32ll << 20;
+    if (chunk > (16ll << 20)) chunk = 16ll << 20;
   }
   if (chunk > ring_bytes / 2) chunk = ring_bytes / 2;
   long long cv = ceil_div(chunk, 16 * (long long)n) * n;  // whole vectors, equal shards
@@ -497,7 +501,11 @@ bool plan_flow(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring
   if (c->flow_depth > 0 && c->flow_depth < depth) depth = c->flow_depth;
   if (depth > K) depth = K;
   if (depth < 1) depth = 1;
-  int nsw = c->flow_switch_blocks > 0 ? c->flow_switch_blocks : (total >= 148 ? 64 : (total * 3) / 7);
+  // Few reducing blocks: the switch path saturates with about a quarter of a
+  // megabyte of loads in flight per rank, and every reducing block adds a fence
+  // per chunk.  Measured at 8 ranks, 256 MiB, 16 MiB chunks: 8 blocks 615 us,
+  // 16 blocks 690 us, 32 blocks 797 us.
+  int nsw = c->flow_switch_blocks > 0 ? c->flow_switch_blocks : (total >= 64 ? 8 : (total + 6) / 7);
   if (c->tune_blocks > 0) nsw = c->tune_blocks;
   if (nsw > total - 2) nsw = total - 2;
   if (nsw < 1) nsw = 1;
@@ -516,7 +524,7 @@ bool plan_flow(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring
   p.blocks = nsw + nin + nout;
   p.cv = (int)cv;
   p.rounds = (int)K;
-  p.unroll = c->unroll > 0 ? c->unroll : 8;
+  p.unroll = c->unroll > 0 ? c->unroll : 4;
   p.flow_nsw = nsw;
   p.flow_nin = nin;
   p.flow_depth = (int)depth;
@@ -550,11 +558,14 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
       bool symm = bytes >= c->symm_min_bytes && c->tune_variant == DGN_VARIANT_AUTO;
       if (c->tune_variant == DGN_VARIANT_SYMM) symm = true;
       if (symm) {
-        // No staging: the grid only has to keep enough multimem loads in flight.
+        // No staging: the grid only has to keep enough multimem loads in flight,
+        // and the switch path saturates early.  Measured at 8 ranks (64 / 256 MiB):
+        // 8 to 32 blocks x 128 or 256 threads with 8 loads per thread all give 163 /
+        // 576 us; 64 blocks x 512 threads 206 / 640 us, 148 x 512 up to 660 us.
         if (c->tune_threads <= 0) p.threads = 256;
         const long long vs = ceil_div(d.nvec, n);
         long long b = ceil_div(vs, p.threads);
-        int nb = 64;
+        int nb = 16;
         if (c->tune_blocks > 0) nb = c->tune_blocks < c->geo.max_blocks ? c->tune_blocks : c->geo.max_blocks;
         if (block_cap > 0 && nb > block_cap) nb = block_cap;
         if (b > nb) b = nb;
@@ -685,13 +696,6 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
       if (b > nb) b = nb;
       if (b < 1) b = 1;
       long long cv = ceil_div(d.nvec, b);
-      if (c->tune_chunk < 16) {
-        // Several rounds per block, so that the peers copy round i out while the
-        // root stores round i + 1: a quarter of the block's share, 64 KiB at least.
-        long long part = ceil_div(cv, 4);
-        if (part < 4096) part = 4096;
-        if (cv > part) cv = part;
-      }
       if (cv > cap_v) cv = cap_v;
       p.variant = DGN_VARIANT_NVLS;
       p.blocks = (int)b;
@@ -708,6 +712,12 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
   // begin and end inside a vector.
   if (is_zero_kind(d.kind)) per = ceil_div(ceil_div(d.count, n), 16 / (long long)kElemSize[d.dtype]) + 1;
   p.variant = DGN_VARIANT_TWOSHOT;
+  if (d.kind == kOpAllGather) {
+    // Stores only (peers are pushed to) up to the measured crossover, pulling above.
+    bool pull = d.nvec * 16 >= c->allgather_pull_min_bytes && c->tune_variant == DGN_VARIANT_AUTO;
+    if (c->tune_variant == DGN_VARIANT_ONESHOT) pull = true;
+    if (pull) p.variant = DGN_VARIANT_ONESHOT;
+  }
   if (d.kind == kOpBroadcast) {
     // Small messages: peers pull from the root (one flag exchange).  Large
     // ones: scatter + all-gather, so the root sends about 2 S instead of
@@ -750,6 +760,7 @@ void load_thresholds(dgn_comm* c) {
   // for pulling at 2 ranks and 512 KiB blocks, but no gain at 8 ranks there.
   c->ll_allgather_max_bytes =
       env_ll("DGN_LL_ALLGATHER_MAX_BYTES", nranks <= 2 ? (512ll << 10) : nranks <= 4 ? (256ll << 10) : (64ll << 10));
+  c->allgather_pull_min_bytes = env_ll("DGN_ALLGATHER_PULL_MIN_BYTES", 1ll << 62);
   c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
 }
 
@@ -783,9 +794,11 @@ void load_nvls_settings(dgn_comm* c, long long symm_request) {
   // In place on symmetric memory from this size on; never by default at two
   // ranks (measured there: 401 GB/s against 577 GB/s for two-shot at 256 MiB).
   c->symm_min_bytes = env_ll("DGN_SYMM_MIN_BYTES", nranks <= 2 ? (1ll << 62) : (4ll << 20));
-  // Opt-in until it has been measured beside the other broadcast kernels at
-  // every rank count.
-  c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", 1ll << 62);
+  // Through the switch the root sends S bytes whatever the rank count.  Measured
+  // at 8 ranks against pulling / scatter + all-gather: 20.6 against 22.1 us at
+  // 512 KiB, 29.5 against 37.9 us at 4 MiB, 188 against 197 us at 64 MiB; at 2
+  // ranks it loses from 64 MiB (148 against 121 us), so it is opt-in below 5 ranks.
+  c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", nranks >= 5 ? (256ll << 10) : (1ll << 62));
   c->flow_chunk_bytes = env_ll("DGN_FLOW_CHUNK_BYTES", 0);
   c->flow_switch_blocks = (int)env_ll("DGN_FLOW_SWITCH_BLOCKS", 0);
   c->flow_in_blocks = (int)env_ll("DGN_FLOW_IN_BLOCKS", 0);
@@ -808,7 +821,10 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
       k.smem = table ? table_smem_bytes(d.ntensors) : 0;
       break;
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
-    case kOpAllGather: k.fn = p.variant == DGN_VARIANT_LL ? allgather_ll_kernel_fn() : allgather_kernel_fn(); break;
+    case kOpAllGather:
+      k.fn = p.variant == DGN_VARIANT_LL ? allgather_ll_kernel_fn()
+             : p.variant == DGN_VARIANT_ONESHOT ? allgather_pull_kernel_fn() : allgather_kernel_fn();
+      break;
     case kOpBroadcast:
       k.fn = p.variant == DGN_VARIANT_NVLS      ? broadcast_nvls_kernel_fn()
              : p.variant == DGN_VARIANT_TWOSHOT ? broadcast_scatter_kernel_fn()
@@ -1735,6 +1751,7 @@ int dgn_comm_set_knob(dgn_comm_t c, const char* name, int64_t value) {
   else if (k == "symm_min_bytes") c->symm_min_bytes = value;
   else if (k == "nvls_bcast_min_bytes") c->nvls_bcast_min_bytes = value;
   else if (k == "bcast_scatter_min_bytes") c->bcast_scatter_min_bytes = value;
+  else if (k == "allgather_pull_min_bytes") c->allgather_pull_min_bytes = value;
   else return fail(DGN_ERR_ARG, "unknown knob '%s'", name);
   return DGN_OK;
 }

@@ -1568,25 +1568,22 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
 }
 
 // ---------------------------------------------------------------------------
-// ALLGATHER (bytes), stores only, two warp roles per block.
-//   pusher : [wait drained(i-2) on B]  store my slice of round i into gather box [r]
-//            of every peer and into my own block of the output   signal pushed(i)  on A
-//   drainer: wait pushed(j) on A from every peer; copy my gather boxes into the
-//            peers' blocks of my output                           signal drained(j) on B
-// The pusher feeds the link while the drainer moves data inside local HBM; box
-// halves alternate per round, and a half is refilled only after every peer has
-// drained the round that used it.  Peer traffic is remote stores exclusively
-// (the fastest pattern on NVLink).  Epoch of round j on both channels:
-// base + j + 1; done = base + rounds + 1 (B).  `count` is bytes per rank here.
-// Blocks of fewer than 64 threads run the two roles one after the other per round.
+// ALLGATHER (bytes), stores only.  Per round every rank stores its slice into
+// gather box [r] of every peer (and into its own block of the output), signals
+// (A), waits for all peers' slices, copies its gather boxes into the peers'
+// blocks of the output and signals (B) that the boxes are empty.  The push of
+// round i + 1 is issued before the local copy of round i, so the link keeps
+// working while boxes are emptied; box halves alternate per round, and a half
+// is refilled only after B of the round that used it came from every peer.
+// Peer traffic is remote stores exclusively (the fastest pattern on NVLink).
+// Epochs of round i: A = base+2i+1, B = base+2i+2; done = base+2*rounds+1 (B).
+// `count` is bytes per rank here.
 
 template <int kUnused>
 __global__ void __launch_bounds__(kMaxThreads, 1) allgather_kernel(const __grid_constant__ OpParams P) {
-  __shared__ int s_abort;
   const PeerTable& pt = P.peers[blockIdx.y];
   const RankArgs& ra = P.ra[blockIdx.y];
   const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
-  if (threadIdx.x == 0) s_abort = 0;
   Turn turn;
   if (!begin_collective(pt, b, P, &turn)) return;
   const char* in = static_cast<const char*>(ra.in);
@@ -1596,62 +1593,92 @@ __global__ void __launch_bounds__(kMaxThreads, 1) allgather_kernel(const __grid_
   const bool mine_al = is_al16(mine);
   const long long cv = P.cv;
   const int R = P.rounds;
-  const u64 base = turn.base;
-  volatile int* abort_flag = &s_abort;
 
-  const int nwarps = blockDim.x >> 5;
-  const bool split = nwarps >= 2;
-  const int w_push = split ? (nwarps + 1) / 2 : nwarps;
-  Role g;
-  int role;
-  if (!split) { role = -1; g.id = 1; g.t = threadIdx.x; g.n = blockDim.x; }
-  else if ((int)(threadIdx.x >> 5) < w_push) { role = 0; g.id = 1; g.t = threadIdx.x; g.n = w_push * 32; }
-  else { role = 1; g.id = 2; g.t = threadIdx.x - w_push * 32; g.n = (nwarps - w_push) * 32; }
-  bool alive = true;
-
-  auto push = [&](int i) -> bool {
-    if (i >= 2 && !role_wait(pt, g, b, kChanB, base + (u64)(i - 2) + 1, P.wait_ns, abort_flag)) return false;
-    const long long off = ((long long)i * gridDim.x + b) * cv;
+  auto push = [&](int round) -> bool {
+    // Peers emptied this half two rounds ago.
+    if (round >= 2 && !wait_peers(pt, b, kChanB, turn.base + 2 * (u64)(round - 2) + 2, P.wait_ns)) return false;
+    const long long off = ((long long)round * gridDim.x + b) * cv;
     const long long len = clampll(P.nvec - off, 0, cv);
     char* dst[kMaxRanks];
 #pragma unroll
     for (int k = 1; k < kMaxRanks; ++k)
-      dst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, turn.parity, b, i & 1, n + r) : nullptr;
-    role_copy(g, len, [&](long long v) { return load_vec<1>(in, off + v, P.count, in_al); },
-              [&](long long v, uint4 x) {
-                if (mine != in) store_vec<1>(mine, off + v, P.count, mine_al, x);
+      dst[k] = (k < n) ? slot_ptr(pt, (r + k) % n, turn.parity, b, round & 1, n + r) : nullptr;
+    copy_vectors(len, [&](long long v) { return load_vec<1>(in, off + v, P.count, in_al); },
+                 [&](long long v, uint4 x) {
+                   if (mine != in) store_vec<1>(mine, off + v, P.count, mine_al, x);
 #pragma unroll
-                for (int k = 1; k < kMaxRanks; ++k)
-                  if (k < n) stv(dst[k] + v * 16, x);
-              });
-    role_signal(pt, g, b, kChanA, base + (u64)i + 1);
-    return true;
-  };
-  auto drain = [&](int j) -> bool {
-    if (!role_wait(pt, g, b, kChanA, base + (u64)j + 1, P.wait_ns, abort_flag)) return false;
-    const long long off = ((long long)j * gridDim.x + b) * cv;
-    const long long len = clampll(P.nvec - off, 0, cv);
-    for (int k = 1; k < n; ++k) {
-      const int peer = (r + k) % n;
-      const char* src = slot_ptr(pt, r, turn.parity, b, j & 1, n + peer);
-      char* dst = out + (long long)peer * P.count;
-      const bool dst_al = is_al16(dst);
-      role_copy(g, len, [&](long long v) { return ldv(src + v * 16); },
-                [&](long long v, uint4 x) { store_vec<1>(dst, off + v, P.count, dst_al, x); });
-    }
-    role_signal(pt, g, b, kChanB, base + (u64)j + 1);
+                   for (int k = 1; k < kMaxRanks; ++k)
+                     if (k < n) stv(dst[k] + v * 16, x);
+                 });
+    signal_peers(pt, b, kChanA, turn.base + 2 * (u64)round + 1);
     return true;
   };
 
-  if (role == 0) {
-    for (int i = 0; i < R && alive; ++i) alive = push(i);
-  } else if (role == 1) {
-    for (int j = 0; j < R && alive; ++j) alive = drain(j);
-  } else {
-    for (int i = 0; i < R && alive; ++i) alive = push(i) && drain(i);
+  if (!push(0)) return;
+  for (int round = 0; round < R; ++round) {
+    if (round + 1 < R && !push(round + 1)) return;
+    if (!wait_peers(pt, b, kChanA, turn.base + 2 * (u64)round + 1, P.wait_ns)) return;
+    const long long off = ((long long)round * gridDim.x + b) * cv;
+    const long long len = clampll(P.nvec - off, 0, cv);
+    for (int k = 1; k < n; ++k) {
+      const int peer = (r + k) % n;
+      const char* src = slot_ptr(pt, r, turn.parity, b, round & 1, n + peer);
+      char* dst = out + (long long)peer * P.count;
+      const bool dst_al = is_al16(dst);
+      copy_vectors(len, [&](long long v) { return ldv(src + v * 16); },
+                   [&](long long v, uint4 x) { store_vec<1>(dst, off + v, P.count, dst_al, x); });
+    }
+    signal_peers(pt, b, kChanB, turn.base + 2 * (u64)round + 2);
   }
-  if (__syncthreads_or(!alive)) return;
-  end_collective(pt, b, turn, base + (u64)R + 1);
+  end_collective(pt, b, turn, turn.base + 2 * (u64)R + 1);
+}
+
+// ---------------------------------------------------------------------------
+// ALLGATHER (bytes), pulling version for large blocks.  Per round: copy my slice to my outbox and to my own
+// block of the output, signal (A), then pull every peer's outbox into its
+// block of my output and signal (B) that the outbox may be overwritten.
+// Outbox halves alternate per round, so the wait for B lags one round.
+// `count` is bytes per rank here.
+
+template <int kUnused>
+__global__ void __launch_bounds__(kMaxThreads, 1) allgather_pull_kernel(const __grid_constant__ OpParams P) {
+  const PeerTable& pt = P.peers[blockIdx.y];
+  const RankArgs& ra = P.ra[blockIdx.y];
+  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
+  Turn turn;
+  if (!begin_collective(pt, b, P, &turn)) return;
+  const char* in = static_cast<const char*>(ra.in);
+  char* out = static_cast<char*>(ra.out);
+  const bool in_al = is_al16(in);
+  char* mine = out + (long long)r * P.count;
+  const bool mine_al = is_al16(mine);
+  const long long cv = P.cv;
+
+  for (int round = 0; round < P.rounds; ++round) {
+    const long long off = ((long long)round * gridDim.x + b) * cv;
+    const long long len = clampll(P.nvec - off, 0, cv);
+    const u64 e_pub = turn.base + 2 * (u64)round + 1, e_got = e_pub + 1;
+    // The half written now was pulled by the peers two rounds ago.
+    if (round >= 2 && !wait_peers(pt, b, kChanB, turn.base + 2 * (u64)(round - 2) + 2, P.wait_ns)) return;
+    char* outbox = slot_ptr(pt, r, turn.parity, b, round & 1, n);
+    copy_vectors(len, [&](long long v) { return load_vec<1>(in, off + v, P.count, in_al); },
+                 [&](long long v, uint4 x) {
+                   stv(outbox + v * 16, x);
+                   if (mine != in) store_vec<1>(mine, off + v, P.count, mine_al, x);
+                 });
+    signal_peers(pt, b, kChanA, e_pub);
+    if (!wait_peers(pt, b, kChanA, e_pub, P.wait_ns)) return;
+    for (int k = 1; k < n; ++k) {
+      const int peer = (r + 1 + (k - 1 + b) % (n - 1)) % n;
+      const char* src = slot_ptr(pt, peer, turn.parity, b, round & 1, n);
+      char* dst = out + (long long)peer * P.count;
+      const bool dst_al = is_al16(dst);
+      copy_vectors(len, [&](long long v) { return ldv(src + v * 16); },
+                   [&](long long v, uint4 x) { store_vec<1>(dst, off + v, P.count, dst_al, x); });
+    }
+    signal_peers(pt, b, kChanB, e_got);
+  }
+  end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
 }
 
 // ---------------------------------------------------------------------------

@@ -71,6 +71,7 @@ const void* DGN_CAT(reduce_kernel_fn_, DGN_INST)(int kind, bool table) {
 }
 #else
 const void* allgather_kernel_fn() { return (const void*)allgather_kernel<0>; }
+const void* allgather_pull_kernel_fn() { return (const void*)allgather_pull_kernel<0>; }
 const void* allgather_ll_kernel_fn() { return (const void*)allgather_ll_kernel<0>; }
 const void* broadcast_kernel_fn() { return (const void*)broadcast_kernel<0>; }
 const void* broadcast_scatter_kernel_fn() { return (const void*)broadcast_scatter_kernel<0>; }

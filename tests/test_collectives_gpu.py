@@ -242,12 +242,15 @@ def test_allgather_bit_exact(teams, n):
     comms = teams(n)
     dev = "cuda:0"
     # variant 0: automatic (low-latency lines for small blocks, the pushing
-    # kernel above); variant 2: always the pushing kernel; the last shape
-    # forces many rounds of it, so that both halves of the gather boxes are reused.
+    # kernel above, the pulling one for the largest); variant 2: always the
+    # pushing kernel, variant 1: always the pulling one; the last shapes force
+    # many rounds of them, so that both halves of the boxes are reused.
     for variant, dtype, count, shape in (
             (0, oracle.I64, 65536, {}), (0, oracle.BF16, 70001, {}), (0, oracle.U8, 13, {}), (0, oracle.F64, 1, {}),
             (0, oracle.F32, (1 << 20) + 3, {}), (2, oracle.I64, 65536, {}), (2, oracle.BF16, 70001, {}),
             (2, oracle.U8, 13, {}), (4, oracle.F32, 100003, {}),
+            (1, oracle.I64, 65536, {}), (1, oracle.BF16, 70001, {}),
+            (1, oracle.F32, 50021, dict(blocks=3, threads=64, chunk_bytes=512)),
             (2, oracle.F32, 50021, dict(blocks=3, threads=64, chunk_bytes=512))):
         for c in comms:
             c.set_tuning(variant=variant, **shape)

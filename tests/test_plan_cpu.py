@@ -28,7 +28,7 @@ def plan(lib, n, op, nbytes, dtype=_C.F32, redop=_C.MEAN, nvls=True, symm=0, in_
 @pytest.fixture(autouse=True)
 def clean_env(monkeypatch):
     for name in ("DGN_FORCE_VARIANT", "DGN_LL_MAX_BYTES", "DGN_LL2_MAX_BYTES", "DGN_ONESHOT_MAX_BYTES",
-                 "DGN_NVLS_MIN_BYTES", "DGN_SYMM_MIN_BYTES", "DGN_NVLS_BCAST_MIN_BYTES", "DGN_FLOW_CHUNK_BYTES",
+                 "DGN_NVLS_MIN_BYTES", "DGN_SYMM_MIN_BYTES", "DGN_NVLS_BCAST_MIN_BYTES", "DGN_FLOW_CHUNK_BYTES", "DGN_ALLGATHER_PULL_MIN_BYTES",
                  "DGN_FLOW_SWITCH_BLOCKS", "DGN_FLOW_DEPTH", "DGN_NVLS_RING_BYTES", "DGN_RING_BYTES",
                  "DGN_MAX_BLOCKS", "DGN_SLOT_BYTES", "DGN_LL_ALLGATHER_MAX_BYTES", "DGN_BCAST_SCATTER_MIN_BYTES"):
         monkeypatch.delenv(name, raising=False)
@@ -65,8 +65,8 @@ def test_launch_shapes_stay_inside_the_workspace(dgn_lib):
         p = plan(dgn_lib, n, AR, 64 * KiB)
         assert p["rounds"] == 1 and p["blocks"] <= 64 and p["chunk_bytes"] * 2 <= 64 * KiB  # lines are half flags
     # The staged ring: all blocks resident (they wait for one another), chunks
-    # an eighth of the message between 1 and 32 MiB, the ring never overrun.
-    for nbytes, chunk, chunks in ((32 * MiB, 4 * MiB, 8), (512 * MiB, 32 * MiB, 16), (100 * MiB + 16, None, 8)):
+    # a quarter of the message between 1 and 16 MiB, the ring never overrun.
+    for nbytes, chunk, chunks in ((32 * MiB, 8 * MiB, 4), (512 * MiB, 16 * MiB, 32), (100 * MiB + 16, None, 7)):
         p = plan(dgn_lib, 8, AR, nbytes)
         assert p["variant"] == _C.VARIANT_NVLS and 3 <= p["blocks"] <= 148 and p["rounds"] == chunks, p
         assert chunk is None or p["chunk_bytes"] == chunk
@@ -91,9 +91,12 @@ def test_symmetric_memory_and_opt_in_variants(dgn_lib, monkeypatch):
     assert plan(dgn_lib, 8, AR, 64 * MiB + 4, symm=arena, in_symm=True)["variant"] == _C.VARIANT_NVLS  # ragged: staged
     assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=True, nvls=False)["variant"] == _C.VARIANT_TWOSHOT
     shape = plan(dgn_lib, 8, AR, 256 * MiB, symm=arena, in_symm=True)
-    assert shape["blocks"] <= 64 and shape["threads"] == 256 and shape["rounds"] == 1
-    # The broadcast through the switch is opt-in; chunk size and block split of the staged ring can be set.
-    assert plan(dgn_lib, 8, BC, 64 * MiB)["variant"] == _C.VARIANT_TWOSHOT
+    assert shape["blocks"] <= 16 and shape["threads"] == 256 and shape["rounds"] == 1
+    # The broadcast through the switch: from 256 KiB at 5 ranks and more, opt-in
+    # below; chunk size and block split of the staged ring can be set.
+    assert plan(dgn_lib, 8, BC, 64 * MiB)["variant"] == _C.VARIANT_NVLS
+    assert plan(dgn_lib, 8, BC, 64 * MiB, nvls=False)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 4, BC, 64 * MiB)["variant"] == _C.VARIANT_TWOSHOT
     monkeypatch.setenv("DGN_NVLS_BCAST_MIN_BYTES", str(1 * MiB))
     monkeypatch.setenv("DGN_FLOW_CHUNK_BYTES", str(2 * MiB))
     monkeypatch.setenv("DGN_FLOW_SWITCH_BLOCKS", "32")
@@ -108,8 +111,10 @@ def test_allgather_and_broadcast_variants(dgn_lib):
         assert plan(dgn_lib, n, AG, limit)["variant"] == _C.VARIANT_LL
         assert plan(dgn_lib, n, AG, limit * 2)["variant"] == _C.VARIANT_TWOSHOT
     assert plan(dgn_lib, 2, BC, 64 * MiB)["variant"] == _C.VARIANT_ONESHOT      # two ranks: peers pull
-    assert plan(dgn_lib, 8, BC, 512 * KiB)["variant"] == _C.VARIANT_ONESHOT
-    assert plan(dgn_lib, 8, BC, 1 * MiB)["variant"] == _C.VARIANT_TWOSHOT       # scatter + all-gather
+    assert plan(dgn_lib, 8, BC, 128 * KiB)["variant"] == _C.VARIANT_ONESHOT
+    assert plan(dgn_lib, 8, BC, 512 * KiB)["variant"] == _C.VARIANT_NVLS        # one multicast store
+    assert plan(dgn_lib, 8, BC, 1 * MiB, nvls=False)["variant"] == _C.VARIANT_TWOSHOT   # scatter + all-gather
+    assert plan(dgn_lib, 4, BC, 1 * MiB)["variant"] == _C.VARIANT_TWOSHOT
     assert plan(dgn_lib, 4, RS, 16 * MiB)["variant"] == _C.VARIANT_TWOSHOT
 
 

@@ -22,7 +22,8 @@ The programs restate, step for step, the waits, stores, loads and signals of
   ar_nvls_inplace_kernel   in place on symmetric memory, followed by the
                            caller's next write to the buffer
   ar_flow_kernel           staged ring: copy-in, reducing and copy-out blocks
-  allgather_kernel         stores only: pusher and drainer warps around gather boxes
+  allgather_kernel         stores only: push into the peers' gather boxes
+  allgather_pull_kernel    publish in the outbox, peers pull (large blocks)
 
 (dragon_b200/csrc/dgn_kernels.cuh, dgn_zero.cuh), including the bookkeeping
 that carries over from one collective to the next -- epoch, parity, last "done"
@@ -375,39 +376,41 @@ def ll_twoshot(rk, c):
 
 
 def allgather(rk, c, rounds):
-    """allgather_kernel with a single warp: push and drain of a round one after the other."""
+    """allgather_kernel: every rank stores its slice into gather box [me] of every
+    peer; the push of round i + 1 is issued before the boxes of round i are emptied."""
     n, me = rk.n, rk.me
     base, parity = rk.begin()
-    for i in range(rounds):
-        if i >= 2:
-            rk.wait(B, rk.peers, base + (i - 2) + 1)
-        rk.data(*[("write", p, (parity, i & 1, n + me), (c, i, me, "slice")) for p in rk.peers])
-        rk.signal(A, rk.peers, base + i + 1)
-        rk.wait(A, rk.peers, base + i + 1)
-        rk.data(*[("read", (parity, i & 1, n + p), (c, i, p, "slice")) for p in rk.peers])
-        rk.signal(B, rk.peers, base + i + 1)
-    rk.end(parity, base + rounds + 1)
+
+    def push(rnd):
+        if rnd >= 2:
+            rk.wait(B, rk.peers, base + 2 * (rnd - 2) + 2)
+        rk.data(*[("write", p, (parity, rnd & 1, n + me), (c, rnd, me, "slice")) for p in rk.peers])
+        rk.signal(A, rk.peers, base + 2 * rnd + 1)
+
+    push(0)
+    for rnd in range(rounds):
+        if rnd + 1 < rounds:
+            push(rnd + 1)
+        rk.wait(A, rk.peers, base + 2 * rnd + 1)
+        rk.data(*[("read", (parity, rnd & 1, n + p), (c, rnd, p, "slice")) for p in rk.peers])
+        rk.signal(B, rk.peers, base + 2 * rnd + 2)
+    rk.end(parity, base + 2 * rounds + 1)
 
 
-def allgather_roles(me, n, collectives):
-    """allgather_kernel: pusher and drainer warps of one block as two processes."""
-    roles = [Rank(me, n, role) for role in range(2)]
-    push, drain = roles
-    for c, rounds in enumerate(collectives):
-        base, parity = push.epoch, push.ops & 1
-        for rk in roles:
-            rk.wait(B, rk.peers, push.last_done[parity])
-        for i in range(rounds):
-            if i >= 2:
-                push.wait(B, push.peers, base + (i - 2) + 1)
-            push.data(*[("write", p, (parity, i & 1, n + me), (c, i, me, "slice")) for p in push.peers])
-            push.signal(A, push.peers, base + i + 1)
-        for j in range(rounds):
-            drain.wait(A, drain.peers, base + j + 1)
-            drain.data(*[("read", (parity, j & 1, n + p), (c, j, p, "slice")) for p in drain.peers])
-            drain.signal(B, drain.peers, base + j + 1)
-        _join_and_end(roles, c, parity, base + rounds + 1)
-    return roles
+def allgather_pull(rk, c, rounds):
+    """allgather_pull_kernel: publish in the outbox, peers pull."""
+    n = rk.n
+    base, parity = rk.begin()
+    for rnd in range(rounds):
+        e_pub, e_got = base + 2 * rnd + 1, base + 2 * rnd + 2
+        if rnd >= 2:
+            rk.wait(B, rk.peers, base + 2 * (rnd - 2) + 2)
+        rk.data(("store", rk.me, (parity, rnd & 1, n), (c, rnd, rk.me, "outbox")))
+        rk.signal(A, rk.peers, e_pub)
+        rk.wait(A, rk.peers, e_pub)
+        rk.data(*[("peek", p, (parity, rnd & 1, n), (c, rnd, p, "outbox")) for p in rk.peers])
+        rk.signal(B, rk.peers, e_got)
+    rk.end(parity, base + 2 * rounds + 1)
 
 
 def broadcast_pull(rk, c, rounds, root):
@@ -592,18 +595,14 @@ def test_allgather_and_the_three_broadcasts(n, rounds):
         broadcast_pull(rk, 1, rounds, root=n - 1)
         if n > 2:
             broadcast_scatter(rk, 2, rounds, root=1)
-        allgather(rk, 3, 1)
-        broadcast_pull(rk, 4, 1, root=0)
+        allgather_pull(rk, 3, rounds)
+        allgather(rk, 4, 1)
+        broadcast_pull(rk, 5, 1, root=0)
     assert run(n, build) > 0
 
 
 def test_broadcast_scatter_four_ranks():
     assert run(4, lambda rk: broadcast_scatter(rk, 0, 3, root=2)) > 0
-
-
-@pytest.mark.parametrize("n,collectives", [(2, (5, 1, 3)), (3, (4, 2)), (4, (3,))])
-def test_allgather_pusher_and_drainer(n, collectives):
-    assert run_roles(n, lambda me, n_: allgather_roles(me, n_, collectives)) > 0
 
 
 @pytest.mark.parametrize("n,collectives", [(2, (5, 1, 3)), (3, (4, 3)), (4, (3,))])
