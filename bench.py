@@ -661,8 +661,14 @@ def parity_pass(comm, rank, world, dev, dist, headline):
     gather_case("allgather/push_int64", 2, "i64", 65536)
     gather_case("allgather/push_bf16_many_rounds", 2, "bf16", (1 << 21) + 3, blocks=8, chunk_bytes=32 << 10)
     gather_case("allgather/pull_bf16_many_rounds", 1, "bf16", (1 << 21) + 3, blocks=8, chunk_bytes=32 << 10)
+    gather_case("allgather/staged_peer_stores", 7, "f16", (1 << 20) + 5, blocks=2, chunk_bytes=16 << 10)
+    if nvls:
+        gather_case("allgather/staged_multicast", 3, "bf16", (1 << 21) + 3, chunk_bytes=32 << 10)
+        gather_case("allgather/staged_multicast_default_shape", 3, "i64", (1 << 20) + 1)
     for root in sorted({0, world - 1}):
         broadcast_case("broadcast/pull_root{}".format(root), 1, "i64", 65536, root)
+        broadcast_case("broadcast/staged_peer_stores_root{}".format(root), 7, "bf16", (1 << 20) + 3, root,
+                       chunk_bytes=16 << 10)
         if world > 2:
             broadcast_case("broadcast/scatter_root{}".format(root), 2, "bf16", (1 << 22) + 3, root)
         if nvls:

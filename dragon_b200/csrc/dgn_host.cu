@@ -49,7 +49,7 @@ const void* allgather_pull_kernel_fn();
 const void* allgather_ll_kernel_fn();
 const void* broadcast_kernel_fn();
 const void* broadcast_scatter_kernel_fn();
-const void* broadcast_nvls_kernel_fn();
+const void* gather_flow_kernel_fn(bool through_switch);
 const void* local_copy_kernel_fn(int es, bool table);
 const void* zero_kernel_fn(int dtype, int which);  // dgn_zero_inst.cu
 const void* update_kernel_fn(int kind);             // dgn_update_inst.cu
@@ -161,8 +161,9 @@ Geometry make_geometry(int nranks) {
   g.blk_off = g.flags_bytes;
   size_t head = g.blk_off + (size_t)g.max_blocks * sizeof(BlockState);
   g.flow_state_off = (head + 255) & ~(size_t)255;
-  g.flow_flags_off = g.flow_state_off + ((sizeof(FlowState) + 255) & ~(size_t)255);
-  head = g.flow_flags_off + 2 * (size_t)kFlowSlots * kMaxRanks * sizeof(u64);
+  // Two states (staged all-reduce, staged gather) and four kinds of flag words.
+  g.flow_flags_off = g.flow_state_off + ((2 * sizeof(FlowState) + 255) & ~(size_t)255);
+  head = g.flow_flags_off + 4 * (size_t)kFlowSlots * kMaxRanks * sizeof(u64);
   g.stage_off = (head + 4095) & ~(size_t)4095;
   g.ll_off = g.stage_off + 2 * (size_t)g.max_blocks * 2 * (size_t)(2 * nranks) * (size_t)g.slot_bytes;
   g.ll2_off = g.ll_off + 2 * (size_t)g.ll_max_blocks * (size_t)nranks * (size_t)g.ll_slot_bytes;
@@ -298,8 +299,12 @@ struct dgn_comm {
   NvlsBuffer* nvls = nullptr;
   bool nvls_capable = false;
   char nvls_sock[64] = {};
-  int nvls_max_blocks = 0;
-  long long nvls_slot_bytes = 0, nvls_min_bytes = 0;
+  long long nvls_min_bytes = 0;
+  // Staged gather (gather_flow_kernel): ring at the start of the multicast-bound
+  // buffer, chunk size per source, pushing blocks (0: automatic), thresholds.
+  size_t gather_ring_bytes = 0;
+  long long gather_chunk_bytes = 0, nvls_allgather_min_bytes = 0;
+  int gather_push_blocks = 0;
   size_t nvls_bytes = 0;
   // Symmetric arena: the tail of the multicast-bound buffer, handed out by
   // dgn_comm_symm_alloc; buffers in it can be reduced in place by the switch.
@@ -309,7 +314,7 @@ struct dgn_comm {
   // buffer, chunk size, block split, ring slots, loads in flight (0: automatic).
   size_t flow_ring_off = 0, flow_ring_bytes = 0;
   long long flow_chunk_bytes = 0;
-  int flow_switch_blocks = 0, flow_in_blocks = 0, flow_out_blocks = 0, flow_depth = 0, unroll = 0, pattern = 0, flow_debug = 0;
+  int flow_switch_blocks = 0, flow_in_blocks = 0, flow_out_blocks = 0, flow_depth = 0, unroll = 0, pattern = 0;
   long long nvls_bcast_min_bytes = 0;  // smallest broadcast that goes through the switch
   bool plan_query = false, plan_query_in_symm = false;  // dgn_plan_query: no device, no real buffers
 };
@@ -346,7 +351,8 @@ int preload_kernels() {
   DGN_CUDA(cudaFuncGetAttributes(&attr, allgather_ll_kernel_fn()));
   DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_kernel_fn()));
   DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_scatter_kernel_fn()));
-  DGN_CUDA(cudaFuncGetAttributes(&attr, broadcast_nvls_kernel_fn()));
+  DGN_CUDA(cudaFuncGetAttributes(&attr, gather_flow_kernel_fn(true)));
+  DGN_CUDA(cudaFuncGetAttributes(&attr, gather_flow_kernel_fn(false)));
   const int sizes[4] = {1, 2, 4, 8};
   for (int es : sizes)
     for (int table = 0; table < 2; ++table)
@@ -406,8 +412,7 @@ void fill_peer_table(const dgn_comm* c, PeerTable* t) {
   t->ll_slot_bytes = c->geo.ll_slot_bytes;
   t->nvls_uc = t->nvls_mc = nullptr;
   if (c->nvls) nvls_pointers(c->nvls, &t->nvls_uc, &t->nvls_mc);
-  t->nvls_slot_bytes = c->nvls_slot_bytes;
-  t->nvls_max_blocks = c->nvls_max_blocks;
+  t->ring_gather_off = (long long)(c->geo.ring_off + c->geo.ring_bytes / 2);
   t->flow_state_off = (long long)c->geo.flow_state_off;
   t->flow_flags_off = (long long)c->geo.flow_flags_off;
   t->ring_off = (long long)c->geo.ring_off;
@@ -479,14 +484,16 @@ bool plan_flow(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring
   if (total > c->geo.max_blocks) total = c->geo.max_blocks;
   if (block_cap > 0 && block_cap < total) total = block_cap;
   if (total < 3 || ring_bytes < 2 * 4096) return false;
-  // Chunks: a quarter of the message, between 1 and 16 MiB.  Measured at 8 ranks
-  // (8 reducing blocks): 16 MiB chunks are best from 64 MiB to 1 GiB (192 / 332 /
-  // 615 / 2320 us at 64 / 128 / 256 / 1024 MiB); smaller chunks pay a few
-  // microseconds each for their flags, larger ones fill and drain longer.
+  // Chunks: half of the message, between 1 and 16 MiB.  Measured at 8 ranks (8
+  // reducing blocks): 16 MiB chunks are best from 32 MiB to 1 GiB (115 / 189 /
+  // 330 / 611 / 2311 us at 32 / 64 / 128 / 256 / 1024 MiB); two chunks are best
+  // at 8 and 16 MiB (56 and 77 us, against 64 and 89 us with four); smaller
+  // chunks pay a few microseconds each for their flags, larger ones fill and
+  // drain longer.
   long long chunk = c->flow_chunk_bytes;
   if (c->tune_chunk >= 4096) chunk = c->tune_chunk;
   if (chunk <= 0) {
-    chunk = ceil_div(bytes, 4);
+    chunk = ceil_div(bytes, 2);
     if (chunk < (1ll << 20)) chunk = 1ll << 20;
     if (chunk > (16ll << 20)) chunk = 16ll << 20;
   }
@@ -527,6 +534,67 @@ bool plan_flow(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring
   p.unroll = c->unroll > 0 ? c->unroll : 4;
   p.flow_nsw = nsw;
   p.flow_nin = nin;
+  p.flow_depth = (int)depth;
+  *out = p;
+  return true;
+}
+
+// Launch shape of the staged gather (gather_flow_kernel: all-gather and
+// broadcast) over a ring of `ring_bytes`; false if ring or grid are too small.
+bool plan_gather(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring_bytes, int variant, Plan* out) {
+  const int n = c->nranks;
+  const int nsrc = d.kind == kOpAllGather ? n : 1;
+  const long long bytes = d.nvec * 16;  // per source
+  int total = c->num_sms;
+  if (total > c->geo.max_blocks) total = c->geo.max_blocks;
+  if (block_cap > 0 && block_cap < total) total = block_cap;
+  if (total < 2 || ring_bytes < 2ll * nsrc * 4096) return false;
+  // Chunk per source: an eighth of the block, between 256 KiB and 4 MiB (8 MiB
+  // for the single source of a broadcast).
+  long long chunk = c->gather_chunk_bytes;
+  if (c->tune_chunk >= 4096) chunk = c->tune_chunk;
+  if (chunk <= 0) {
+    chunk = ceil_div(bytes, 8);
+    const long long hi = nsrc == 1 ? (8ll << 20) : (4ll << 20);
+    if (chunk < (256ll << 10)) chunk = 256ll << 10;
+    if (chunk > hi) chunk = hi;
+  }
+  long long cv = ceil_div(chunk, 16);
+  const long long cv_max = ring_bytes / (2ll * nsrc * 16);  // at least two slots
+  if (cv > cv_max) cv = cv_max;
+  if (cv > d.nvec) cv = d.nvec;
+  if (cv < 1 || cv > 0x7fffffff) return false;
+  const long long K = ceil_div(d.nvec, cv);
+  if (K > 0x7fffffff) return false;
+  long long depth = ring_bytes / (nsrc * cv * 16);
+  if (depth > kFlowSlots) depth = kFlowSlots;
+  if (c->flow_depth > 0 && c->flow_depth < depth) depth = c->flow_depth;
+  if (depth > K) depth = K;
+  if (depth < 1) depth = 1;
+  Plan p;
+  p.variant = variant;
+  p.threads = c->tune_threads > 0 ? c->tune_threads : 512;
+  if (p.threads > kMaxThreads) p.threads = kMaxThreads;
+  p.threads = p.threads / 32 * 32;
+  if (p.threads < 64) p.threads = 64;  // a pushing block needs a data warp and its signal warp
+  // Pushing blocks: a source of an all-gather sends only S while 7 S arrive, so a
+  // few blocks keep up; the single source of a broadcast feeds everybody.
+  int npush = c->gather_push_blocks > 0 ? c->gather_push_blocks : (nsrc == 1 ? 16 : 4);
+  if (c->tune_blocks > 0) npush = c->tune_blocks;
+  const long long per_push = (long long)(p.threads - 32) * 4;  // vectors one block pushes per pass
+  if (npush > ceil_div(cv, per_push)) npush = (int)ceil_div(cv, per_push);
+  if (npush > total - 1) npush = total - 1;
+  if (npush < 1) npush = 1;
+  // Copying blocks: enough for the n blocks of a chunk, no more than the SMs left.
+  long long nout = ceil_div((long long)nsrc * cv, (long long)p.threads * 4);
+  if (nout > total - npush) nout = total - npush;
+  if (nout < 1) nout = 1;
+  p.blocks = npush + (int)nout;
+  p.cv = (int)cv;
+  p.rounds = (int)K;
+  p.unroll = c->unroll > 0 ? (c->unroll > 8 ? 8 : c->unroll) : 4;
+  p.flow_nsw = npush;
+  p.flow_nin = 0;
   p.flow_depth = (int)depth;
   *out = p;
   return true;
@@ -583,7 +651,7 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
     if (nvls && plan_flow(c, d, block_cap, (long long)c->flow_ring_bytes, DGN_VARIANT_NVLS, &p)) return p;
   }
   if (d.kind == kOpAllReduce && c->tune_variant == DGN_VARIANT_RING &&
-      plan_flow(c, d, block_cap, (long long)c->geo.ring_bytes, DGN_VARIANT_RING, &p))
+      plan_flow(c, d, block_cap, (long long)c->geo.ring_bytes / 2, DGN_VARIANT_RING, &p))
     return p;
   if (d.kind == kOpAllReduce) {
     const long long bytes = d.nvec * 16;
@@ -681,28 +749,19 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
       return p;
     }
   }
-  if (d.kind == kOpBroadcast && c->nvls && !c->team) {
-    // Through the switch: the root stores the message once and the switch
-    // replicates it into every rank's staging memory.
-    const long long bytes = d.nvec * 16;
-    bool nvls = bytes >= c->nvls_bcast_min_bytes && c->tune_variant == DGN_VARIANT_AUTO;
-    if (c->tune_variant == DGN_VARIANT_NVLS) nvls = true;
-    if (nvls) {
-      long long cap_v = 2 * (long long)n * c->nvls_slot_bytes / 16;  // both areas of one staging half
-      if (c->tune_chunk >= 16 && c->tune_chunk / 16 < cap_v) cap_v = c->tune_chunk / 16;
-      long long nb = c->tune_blocks > 0 ? c->tune_blocks : 64;
-      if (nb > c->nvls_max_blocks) nb = c->nvls_max_blocks;
-      long long b = ceil_div(d.nvec, 512);
-      if (b > nb) b = nb;
-      if (b < 1) b = 1;
-      long long cv = ceil_div(d.nvec, b);
-      if (cv > cap_v) cv = cap_v;
-      p.variant = DGN_VARIANT_NVLS;
-      p.blocks = (int)b;
-      p.cv = (int)cv;
-      p.rounds = (int)ceil_div(d.nvec, b * cv);
-      return p;
+  if (d.kind == kOpAllGather || d.kind == kOpBroadcast) {
+    // Staged through the switch: a source stores its block once and the switch
+    // replicates it into every rank's ring.
+    if (c->nvls && !c->team) {
+      const long long thr = d.kind == kOpAllGather ? c->nvls_allgather_min_bytes : c->nvls_bcast_min_bytes;
+      bool nvls = d.nvec * 16 >= thr && c->tune_variant == DGN_VARIANT_AUTO;
+      if (c->tune_variant == DGN_VARIANT_NVLS) nvls = true;
+      if (nvls && plan_gather(c, d, block_cap, (long long)c->gather_ring_bytes, DGN_VARIANT_NVLS, &p)) return p;
     }
+    // The same protocol with remote stores (never chosen automatically).
+    if (c->tune_variant == DGN_VARIANT_RING &&
+        plan_gather(c, d, block_cap, (long long)c->geo.ring_bytes / 2, DGN_VARIANT_RING, &p))
+      return p;
   }
   // Multi-round kernels: two-shot all-reduce, reduce-scatter, all-gather,
   // broadcast.  `per` = vectors each block column has to cover.
@@ -760,7 +819,9 @@ void load_thresholds(dgn_comm* c) {
   // for pulling at 2 ranks and 512 KiB blocks, but no gain at 8 ranks there.
   c->ll_allgather_max_bytes =
       env_ll("DGN_LL_ALLGATHER_MAX_BYTES", nranks <= 2 ? (512ll << 10) : nranks <= 4 ? (256ll << 10) : (64ll << 10));
-  c->allgather_pull_min_bytes = env_ll("DGN_ALLGATHER_PULL_MIN_BYTES", 1ll << 62);
+  // Pushing wins up to 4 MiB blocks (85 against 100 us at 8 ranks), pulling from
+  // 16 MiB (222 against 246 us; 803 against 838 us at 64 MiB).
+  c->allgather_pull_min_bytes = env_ll("DGN_ALLGATHER_PULL_MIN_BYTES", nranks >= 5 ? (8ll << 20) : (1ll << 62));
   c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
 }
 
@@ -768,14 +829,13 @@ void load_thresholds(dgn_comm* c) {
 // size of the symmetric arena asked for.  No device is touched.
 void load_nvls_settings(dgn_comm* c, long long symm_request) {
   const int nranks = c->nranks;
-  // Layout of the multicast-bound buffer: [staging of the broadcast through the
-  // switch][ring of the staged dataflow all-reduce][symmetric arena].
-  c->nvls_max_blocks = c->geo.max_blocks < 64 ? c->geo.max_blocks : 64;
-  c->nvls_slot_bytes = env_ll("DGN_NVLS_SLOT_BYTES", 64 * 1024);
-  if (c->nvls_slot_bytes < 4096) c->nvls_slot_bytes = 4096;
-  c->nvls_slot_bytes = (c->nvls_slot_bytes + 4095) & ~4095ll;
+  // Layout of the multicast-bound buffer: [ring of the staged gather (all-gather
+  // and broadcast)][ring of the staged all-reduce][symmetric arena].
   const size_t gran = (size_t)2 << 20;
-  c->nvls_bytes = 2 * (size_t)c->nvls_max_blocks * 2 * 2 * (size_t)nranks * (size_t)c->nvls_slot_bytes;
+  long long gring = env_ll("DGN_NVLS_GATHER_RING_BYTES", (long long)nranks * (32ll << 20));
+  if (gring < 0) gring = 0;
+  c->gather_ring_bytes = ((size_t)gring + gran - 1) / gran * gran;
+  c->nvls_bytes = c->gather_ring_bytes;
   c->flow_ring_off = (c->nvls_bytes + gran - 1) / gran * gran;
   long long ring = env_ll("DGN_NVLS_RING_BYTES", 256ll << 20);
   if (ring < 0) ring = 0;
@@ -789,8 +849,10 @@ void load_nvls_settings(dgn_comm* c, long long symm_request) {
   }
   // Staged through the switch from this size on (any tensors, buckets included).
   // With two ranks the switch saves nothing (1.5 S per direction against 1.0 S
-  // for the store-only two-shot kernel), so it is opt-in there.
-  c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", nranks >= 8 ? (32ll << 20) : (1ll << 62));
+  // for the store-only two-shot kernel), so it is opt-in there.  Measured at 8
+  // ranks against the two-shot kernel: 77 against 84 us at 16 MiB, 115 against 129
+  // at 32 MiB, 189 against 227 at 64 MiB; level at 8 MiB (57 against 59).
+  c->nvls_min_bytes = env_ll("DGN_NVLS_MIN_BYTES", nranks >= 8 ? (16ll << 20) : (1ll << 62));
   // In place on symmetric memory from this size on; never by default at two
   // ranks (measured there: 401 GB/s against 577 GB/s for two-shot at 256 MiB).
   c->symm_min_bytes = env_ll("DGN_SYMM_MIN_BYTES", nranks <= 2 ? (1ll << 62) : (4ll << 20));
@@ -799,6 +861,9 @@ void load_nvls_settings(dgn_comm* c, long long symm_request) {
   // 512 KiB, 29.5 against 37.9 us at 4 MiB, 188 against 197 us at 64 MiB; at 2
   // ranks it loses from 64 MiB (148 against 121 us), so it is opt-in below 5 ranks.
   c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", nranks >= 5 ? (256ll << 10) : (1ll << 62));
+  c->nvls_allgather_min_bytes = env_ll("DGN_NVLS_ALLGATHER_MIN_BYTES", 1ll << 62);
+  c->gather_chunk_bytes = env_ll("DGN_GATHER_CHUNK_BYTES", 0);
+  c->gather_push_blocks = (int)env_ll("DGN_GATHER_PUSH_BLOCKS", 0);
   c->flow_chunk_bytes = env_ll("DGN_FLOW_CHUNK_BYTES", 0);
   c->flow_switch_blocks = (int)env_ll("DGN_FLOW_SWITCH_BLOCKS", 0);
   c->flow_in_blocks = (int)env_ll("DGN_FLOW_IN_BLOCKS", 0);
@@ -822,11 +887,15 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
       break;
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
     case kOpAllGather:
-      k.fn = p.variant == DGN_VARIANT_LL ? allgather_ll_kernel_fn()
-             : p.variant == DGN_VARIANT_ONESHOT ? allgather_pull_kernel_fn() : allgather_kernel_fn();
+      k.fn = p.variant == DGN_VARIANT_NVLS      ? gather_flow_kernel_fn(true)
+             : p.variant == DGN_VARIANT_RING    ? gather_flow_kernel_fn(false)
+             : p.variant == DGN_VARIANT_LL      ? allgather_ll_kernel_fn()
+             : p.variant == DGN_VARIANT_ONESHOT ? allgather_pull_kernel_fn()
+                                                : allgather_kernel_fn();
       break;
     case kOpBroadcast:
-      k.fn = p.variant == DGN_VARIANT_NVLS      ? broadcast_nvls_kernel_fn()
+      k.fn = p.variant == DGN_VARIANT_NVLS      ? gather_flow_kernel_fn(true)
+             : p.variant == DGN_VARIANT_RING    ? gather_flow_kernel_fn(false)
              : p.variant == DGN_VARIANT_TWOSHOT ? broadcast_scatter_kernel_fn()
                                                 : broadcast_kernel_fn();
       break;
@@ -853,7 +922,7 @@ void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p)
   P->rounds = p.rounds;
   P->cv = p.cv;
   P->redop = d.redop;
-  P->root = d.root;
+  P->root = d.kind == kOpAllGather ? -1 : d.root;  // staged gather: every rank is a source
   P->unroll = p.unroll;
   P->pattern = c->pattern;
   P->flow_cv = p.cv;
@@ -861,7 +930,6 @@ void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p)
   P->flow_depth = p.flow_depth;
   P->flow_nsw = p.flow_nsw;
   P->flow_nin = p.flow_nin;
-  P->flow_debug = c->flow_debug;
 }
 
 void fill_zero_params(ZeroParams* Z, const dgn_comm* c, const OpDesc& d, const Plan& p) {
@@ -929,8 +997,9 @@ int issue(dgn_comm* c, const OpDesc& d) {
     KernelChoice k = choose_kernel(c, d, p);
     if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
     int rc;
-    if (d.kind == kOpAllReduce && (p.variant == DGN_VARIANT_NVLS || p.variant == DGN_VARIANT_RING)) {
-      // The blocks of the dataflow kernel wait for one another: cooperative launch.
+    if ((d.kind == kOpAllReduce || d.kind == kOpAllGather || d.kind == kOpBroadcast) &&
+        (p.variant == DGN_VARIANT_NVLS || p.variant == DGN_VARIANT_RING)) {
+      // The blocks of the dataflow kernels wait for one another: cooperative launch.
       OpParams P;
       fill_params(&P, c, d, p);
       P.peers[0] = c->table;
@@ -1746,12 +1815,14 @@ int dgn_comm_set_knob(dgn_comm_t c, const char* name, int64_t value) {
   else if (k == "flow_depth") c->flow_depth = (int)value;
   else if (k == "nvls_unroll") c->unroll = (int)value;
   else if (k == "nvls_pattern") c->pattern = (int)value;
-  else if (k == "flow_debug") c->flow_debug = (int)value;
   else if (k == "nvls_min_bytes") c->nvls_min_bytes = value;
   else if (k == "symm_min_bytes") c->symm_min_bytes = value;
   else if (k == "nvls_bcast_min_bytes") c->nvls_bcast_min_bytes = value;
   else if (k == "bcast_scatter_min_bytes") c->bcast_scatter_min_bytes = value;
   else if (k == "allgather_pull_min_bytes") c->allgather_pull_min_bytes = value;
+  else if (k == "nvls_allgather_min_bytes") c->nvls_allgather_min_bytes = value;
+  else if (k == "gather_chunk_bytes") c->gather_chunk_bytes = value;
+  else if (k == "gather_push_blocks") c->gather_push_blocks = (int)value;
   else return fail(DGN_ERR_ARG, "unknown knob '%s'", name);
   return DGN_OK;
 }

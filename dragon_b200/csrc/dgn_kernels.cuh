@@ -96,8 +96,7 @@ struct PeerTable {
   // multicast mapping, which addresses all ranks' buffers at once.
   char* nvls_uc;
   char* nvls_mc;
-  long long nvls_slot_bytes;
-  int nvls_max_blocks, reserved2;
+  long long ring_gather_off;  // gather ring (gather_flow_kernel) in ordinary memory, from the workspace base
   // Staged ring of the dataflow all-reduce (ar_flow_kernel).  Offsets from a
   // rank's workspace base (= flags[j]): its FlowState, the flag words peers
   // write, and the ring in ordinary (peer-mapped) memory; the ring of the
@@ -139,7 +138,6 @@ struct OpParams {
   int flow_chunks;             // chunks of the message
   int flow_depth;              // ring slots in use
   int flow_nsw, flow_nin;      // blocks [0, nsw) reduce, [nsw, nsw + nin) copy in, the rest copy out
-  int flow_debug;              // experiments only: bit 0 skips the copy-in loads/stores, bit 1 the copy-out ones
 };
 
 // ---------------------------------------------------------------------------
@@ -1150,13 +1148,6 @@ template <> struct Multimem<__nv_bfloat16> {
                  :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
   }
 };
-// Byte offset of slot `slot` of area `area` (0 in, 1 out) of (parity, block, half)
-// in the multicast-bound staging memory (used by the broadcast through the switch).
-__device__ __forceinline__ long long nvls_offset(const PeerTable& pt, int parity, int b, int half, int area, int slot) {
-  const long long idx = ((((long long)parity * pt.nvls_max_blocks + b) * 2 + half) * 2 + area) * pt.nranks + slot;
-  return idx * pt.nvls_slot_bytes;
-}
-
 // multimem.ld_reduce + multimem.st over vectors first, first + step, ... of a
 // slice, U loads in flight per thread (a multimem.ld_reduce is a round trip
 // through the switch).  Whole batches of U first, then the remainder in batches
@@ -1306,7 +1297,7 @@ __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
 __device__ __forceinline__ FlowState* flow_state(const PeerTable& pt) {
   return reinterpret_cast<FlowState*>(reinterpret_cast<char*>(pt.flags[pt.rank]) + pt.flow_state_off);
 }
-// Flag word of kind (0 ready, 1 done), ring slot s, written by rank `src`, in rank `owner`'s workspace.
+// Flag word of kind (0 ready, 1 done: staged all-reduce; 2 pushed, 3 freed: staged gather), ring slot s, written by rank `src`, in rank `owner`'s workspace.
 __device__ __forceinline__ u64* flow_flag(const PeerTable& pt, int owner, int kind, int s, int src) {
   return reinterpret_cast<u64*>(reinterpret_cast<char*>(pt.flags[owner]) + pt.flow_flags_off) +
          ((size_t)kind * kFlowSlots + s) * kMaxRanks + src;
@@ -1512,7 +1503,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
       const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
       const long long vbase = (long long)c * CV;
       char* dst = ring + (long long)s * CV * 16;
-      long long v = (P.flow_debug & 1) ? clen : first;
+      long long v = first;
       for (; v + 3 * step < clen; v += 4 * step) {
         const uint4 x0 = msg.load(vbase + v), x1 = msg.load(vbase + v + step), x2 = msg.load(vbase + v + 2 * step),
                     x3 = msg.load(vbase + v + 3 * step);
@@ -1539,7 +1530,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) ar_flow_kernel(const __grid_co
       const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
       const long long vbase = (long long)c * CV;
       const char* src = ring + (long long)s * CV * 16;
-      long long v = (P.flow_debug & 2) ? clen : first;
+      long long v = first;
       for (; v + 3 * step < clen; v += 4 * step) {
         const uint4 x0 = ldv(src + v * 16), x1 = ldv(src + (v + step) * 16), x2 = ldv(src + (v + 2 * step) * 16),
                     x3 = ldv(src + (v + 3 * step) * 16);
@@ -1854,47 +1845,183 @@ __global__ void __launch_bounds__(kMaxThreads, 1) broadcast_scatter_kernel(const
 }
 
 // ---------------------------------------------------------------------------
-// BROADCAST in place through NVSwitch multicast: the root stores every slice
-// once, with multimem.st, into the staging memory of ALL ranks (the switch
-// replicates it), so it sends S bytes instead of (n-1) S when the peers pull or
-// about 2 S (n-1)/n with scatter + all-gather; the peers copy the slices from
-// their own staging memory into their buffers.  Per round and block the 2n
-// slots of one staging half form one buffer.  Epochs as in broadcast_kernel:
-// published(i) = base+2i+1 on channel A (root -> peers), emptied(i) = base+2i+2
-// on channel B (peers -> root); a half is refilled after every peer has
-// emptied it.
+// ALLGATHER and BROADCAST (bytes) as a staged dataflow kernel.  The sources
+// (every rank for the all-gather, the root for the broadcast) store their block
+// chunk by chunk into the gather ring of ALL ranks: with one multimem.st per
+// vector through the switch (SWITCH: a source sends S bytes whatever the rank
+// count, the switch replicates them) or with one remote store per rank (the same
+// protocol on any communicator, virtual ranks included).  The other blocks copy
+// each chunk from the local ring into the output as soon as every source has
+// pushed it.  Roles: blocks [0, P.flow_nsw) of a source push (data warps take
+// batches of 32 x unroll vectors round-robin, the last warp publishes what they
+// have left with ONE system fence for all finished chunks), all other blocks
+// copy out.  Flags (one word per rank and kind, raised with a maximum):
+//   pushed[j] = base + c + 1   rank j's chunks 0..c are in every ring
+//   freed[j]  = base + c + 1   rank j has copied chunks 0..c out of its ring
+// A source writes chunk c into ring slot c % D once freed[j] >= base + c - D + 1
+// came from every rank j (itself included); for c < D that is `base`: every
+// chunk of the launches before is out of the ring, whatever shape they had.
+// `count` is bytes per source block; P.root < 0 means every rank is a source.
 
-template <int kUnused>
-__global__ void __launch_bounds__(kMaxThreads, 1) broadcast_nvls_kernel(const __grid_constant__ OpParams P) {
+__device__ __forceinline__ void gather_count(const PeerTable& pt, unsigned* counter, unsigned target, int kind, u64 val) {
+  const unsigned old = atomicAdd(counter, 1u);
+  if (old + 1u == target) {
+    __threadfence_system();
+    for (int j = 0; j < pt.nranks; ++j) red_max_relaxed_sys(flow_flag(pt, j, kind, 0, pt.rank), val);
+  }
+}
+
+template <bool SWITCH>
+__global__ void __launch_bounds__(kMaxThreads, 1) gather_flow_kernel(const __grid_constant__ OpParams P) {
   const PeerTable& pt = P.peers[blockIdx.y];
   const RankArgs& ra = P.ra[blockIdx.y];
-  const int r = pt.rank, b = blockIdx.x, root = P.root;
-  Turn turn;
-  if (!begin_collective(pt, b, P, &turn)) return;
-  char* buf = static_cast<char*>(ra.out);
-  const bool al = is_al16(buf);
-  const long long cv = P.cv;
+  const int r = pt.rank, n = pt.nranks, b = blockIdx.x;
+  FlowState* fs = flow_state(pt) + 1;
+  const u64 base = fs->base;
+  __shared__ int s_left[kFlowSlots];
+  __shared__ volatile int s_signalled;
+  const int K = P.flow_chunks, D = P.flow_depth, root = P.root;
+  const int nsrc = root < 0 ? n : 1;
+  const bool source = root < 0 || r == root;
+  const int my = root < 0 ? r : 0;  // my region inside a ring slot
+  const int npush = source ? P.flow_nsw : 0, nout = (int)gridDim.x - npush;
+  const long long CV = P.flow_cv;
+  const long long ring_off = SWITCH ? 0 : pt.ring_gather_off;
+  char* const ring = SWITCH ? pt.nvls_uc : reinterpret_cast<char*>(pt.flags[r]) + ring_off;
+  const char* in = static_cast<const char*>(root < 0 ? ra.in : ra.out);
+  char* out = static_cast<char*>(ra.out);
+  const int nwarps = blockDim.x >> 5;
+  bool ok = true;
 
-  for (int round = 0; round < P.rounds; ++round) {
-    const long long off = ((long long)round * gridDim.x + b) * cv;
-    const long long len = clampll(P.nvec - off, 0, cv);
-    const u64 e_pub = turn.base + 2 * (u64)round + 1, e_got = e_pub + 1;
-    const long long so = nvls_offset(pt, turn.parity, b, round & 1, 0, 0);
-    if (r == root) {
-      if (round >= 2 && !wait_peers(pt, b, kChanB, turn.base + 2 * (u64)(round - 2) + 2, P.wait_ns)) return;
-      char* dst = pt.nvls_mc + so;
-      copy_vectors(len, [&](long long v) { return load_vec<1>(buf, off + v, P.count, al); },
-                   [&](long long v, uint4 x) { Multimem<float>::st(dst + v * 16, x); });
-      signal_peers(pt, b, kChanA, e_pub);
+  if (b < npush) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ndata = nwarps - 1;
+    if (warp == 0 && lane < kFlowSlots) s_left[lane] = 0;
+    if (threadIdx.x == 0) s_signalled = 0;
+    __syncthreads();
+    const int U = clamp_unroll(P.unroll) > 8 ? 8 : clamp_unroll(P.unroll);
+    const long long per_batch = 32ll * U;
+    const long long W = (long long)npush * ndata;
+    const long long nb_full = (CV + per_batch - 1) / per_batch;
+    const bool in_al = is_al16(in);
+    if (warp < ndata) {
+      const long long gw = (long long)b * ndata + warp;
+      for (int c = 0; c < K && ok; ++c) {
+        const int s = c % D;
+        const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
+        const long long nb = (clen + per_batch - 1) / per_batch;
+        long long k = (gw - ((long long)c * nb_full) % W + W) % W;
+        if (k < nb) {
+          const u64 need = base + (u64)(c >= D ? c - D + 1 : 0);
+          if (lane < n) ok = flow_wait_flag(flow_flag(pt, r, 3, 0, lane), need, P.wait_ns, pt.status);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          const long long off = ring_off + (((long long)s * nsrc + my) * CV) * 16;
+          const long long vbase = (long long)c * CV;
+          for (; k < nb; k += W) {
+            const long long lo = k * per_batch + lane;
+            const long long hi = k * per_batch + per_batch < clen ? k * per_batch + per_batch : clen;
+            uint4 x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (u < U && lo + 32 * u < hi) x[u] = load_vec<1>(in, vbase + lo + 32 * u, P.count, in_al);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (u < U && lo + 32 * u < hi) {
+                const long long o = off + (lo + 32 * u) * 16;
+                if constexpr (SWITCH) {
+                  Multimem<float>::st(pt.nvls_mc + o, x[u]);
+                } else {
+                  for (int j = 0; j < n; ++j) stv(reinterpret_cast<char*>(pt.flags[j]) + o, x[u]);
+                }
+              }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          if (c >= kFlowSlots) ok = flow_wait_shared(&s_signalled, c - kFlowSlots + 1, P.wait_ns, pt.status);
+          __threadfence_block();
+          atomicAdd(&s_left[c % kFlowSlots], 1);
+        }
+        ok = __all_sync(0xffffffffu, ok);
+      }
     } else {
-      if (!wait_peers(pt, b, kChanA, e_pub, P.wait_ns, root)) return;
-      const char* src = pt.nvls_uc + so;
-      copy_vectors(len, [&](long long v) { return ldv(src + v * 16); },
-                   [&](long long v, uint4 x) { store_vec<1>(buf, off + v, P.count, al, x); });
-      signal_peers(pt, b, kChanB, e_got, root);
+      // Signal warp: one system fence serves every chunk all data warps have left.
+      // The block is counted into sw_done[s] for chunk c only after this rank has
+      // copied chunk c - D out (which needs every block's count for c - D), so the
+      // counts of two chunks of one slot never mix.
+      volatile int* left = s_left;
+      const u64* self_freed = flow_flag(pt, r, 3, 0, r);
+      int c = 0;
+      while (c < K && ok) {
+        int hi = c;
+        if (lane == 0) {
+          ok = flow_wait_shared(&s_left[c % kFlowSlots], ndata, P.wait_ns, pt.status);
+          if (ok && c >= D) ok = flow_wait_flag(self_freed, base + (u64)(c - D + 1), P.wait_ns, pt.status);
+          if (ok) {
+            while (hi + 1 < K && hi + 1 < c + kFlowSlots && left[(hi + 1) % kFlowSlots] >= ndata &&
+                   (hi + 1 < D || ld_acquire_sys(self_freed) >= base + (u64)(hi + 1 - D + 1)))
+              ++hi;
+            __threadfence_system();
+            for (int j = c; j <= hi; ++j) {
+              left[j % kFlowSlots] = 0;
+              gather_count(pt, &fs->sw_done[j % D], (unsigned)npush * ((unsigned)(j / D) + 1u), 2, base + (u64)j + 1);
+            }
+            __threadfence_block();
+            s_signalled = hi + 1;
+          }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        c = __shfl_sync(0xffffffffu, hi, 0) + 1;
+      }
+    }
+  } else {
+    const long long first = (long long)(b - npush) * blockDim.x + threadIdx.x;
+    const long long step = (long long)nout * blockDim.x;
+    for (int c = 0; c < K; ++c) {
+      const int s = c % D;
+      const unsigned use = (unsigned)(c / D) + 1u;
+      const int t = threadIdx.x;
+      if (t < nsrc) ok = flow_wait_flag(flow_flag(pt, r, 2, 0, root < 0 ? t : root), base + (u64)c + 1, P.wait_ns, pt.status);
+      ok = __syncthreads_and(ok) != 0;
+      if (!ok) break;
+      const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
+      const long long vbase = (long long)c * CV;
+      for (int i = 0; i < nsrc; ++i) {
+        const int j = root < 0 ? (i + r) % n : root;  // ranks start at different sources
+        const int region = root < 0 ? j : 0;
+        char* dst = root < 0 ? out + (long long)j * P.count : out;
+        if (j == r && dst == in) continue;  // the own block is in place already
+        const bool dst_al = is_al16(dst);
+        const char* src = ring + (((long long)s * nsrc + region) * CV) * 16;
+        long long v = first;
+        for (; v + 3 * step < clen; v += 4 * step) {
+          const uint4 x0 = ldv(src + v * 16), x1 = ldv(src + (v + step) * 16), x2 = ldv(src + (v + 2 * step) * 16),
+                      x3 = ldv(src + (v + 3 * step) * 16);
+          store_vec<1>(dst, vbase + v, P.count, dst_al, x0);
+          store_vec<1>(dst, vbase + v + step, P.count, dst_al, x1);
+          store_vec<1>(dst, vbase + v + 2 * step, P.count, dst_al, x2);
+          store_vec<1>(dst, vbase + v + 3 * step, P.count, dst_al, x3);
+        }
+        for (; v < clen; v += step) store_vec<1>(dst, vbase + v, P.count, dst_al, ldv(src + v * 16));
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        gather_count(pt, &fs->out_done[s], (unsigned)nout * use, 3, base + (u64)c + 1);
+      }
     }
   }
-  end_collective(pt, b, turn, turn.base + 2 * (u64)P.rounds + 1);
+  if (!__syncthreads_and(ok)) return;  // a wait ran out: the communicator is unusable from here on
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&fs->exit_count, 1u) + 1u == gridDim.x) {
+      for (int s = 0; s < kFlowSlots; ++s) { fs->sw_done[s] = 0u; fs->out_done[s] = 0u; }
+      fs->exit_count = 0u;
+      fs->base = base + (u64)K;
+      __threadfence();
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------

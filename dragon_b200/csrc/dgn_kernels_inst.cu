@@ -75,7 +75,9 @@ const void* allgather_pull_kernel_fn() { return (const void*)allgather_pull_kern
 const void* allgather_ll_kernel_fn() { return (const void*)allgather_ll_kernel<0>; }
 const void* broadcast_kernel_fn() { return (const void*)broadcast_kernel<0>; }
 const void* broadcast_scatter_kernel_fn() { return (const void*)broadcast_scatter_kernel<0>; }
-const void* broadcast_nvls_kernel_fn() { return (const void*)broadcast_nvls_kernel<0>; }
+const void* gather_flow_kernel_fn(bool through_switch) {
+  return through_switch ? (const void*)gather_flow_kernel<true> : (const void*)gather_flow_kernel<false>;
+}
 const void* local_copy_kernel_fn(int es, bool table) {
   switch (es) {
     case 1: return table ? (const void*)local_copy_kernel<1, true> : (const void*)local_copy_kernel<1, false>;

@@ -167,11 +167,14 @@ int dgn_comm_set_tuning(dgn_comm_t comm, int variant, int blocks, int threads,
 
 /* Named launch parameters beyond dgn_comm_set_tuning (0 restores the automatic
  * choice): "flow_chunk_bytes", "flow_switch_blocks", "flow_in_blocks",
- * "flow_out_blocks", "flow_depth" shape the staged ring
- * all-reduce, "nvls_unroll" (4, 8 or 16) is the number of multimem loads a
- * thread keeps in flight; "nvls_min_bytes", "symm_min_bytes",
- * "nvls_bcast_min_bytes" and "bcast_scatter_min_bytes" move the size thresholds
- * of the corresponding variants.  Every rank must set the same values. */
+ * "flow_out_blocks", "flow_depth" shape the staged ring all-reduce;
+ * "nvls_unroll" (1, 2, 4, 8 or 16) is the number of multimem loads a thread
+ * keeps in flight and "nvls_pattern" (0 contiguous batches per warp, 1
+ * grid-strided) how the in-place kernel deals its vectors; "nvls_min_bytes",
+ * "symm_min_bytes", "nvls_bcast_min_bytes", "bcast_scatter_min_bytes" and
+ * "allgather_pull_min_bytes" move the size thresholds of the corresponding
+ * variants.  Every rank must set the same values.  An unknown name or a
+ * negative value returns DGN_ERR_ARG. */
 int dgn_comm_set_knob(dgn_comm_t comm, const char* name, int64_t value);
 
 /* 1 if the NVSwitch-multicast variant was set up for this communicator. */

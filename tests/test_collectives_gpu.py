@@ -251,7 +251,11 @@ def test_allgather_bit_exact(teams, n):
             (2, oracle.U8, 13, {}), (4, oracle.F32, 100003, {}),
             (1, oracle.I64, 65536, {}), (1, oracle.BF16, 70001, {}),
             (1, oracle.F32, 50021, dict(blocks=3, threads=64, chunk_bytes=512)),
-            (2, oracle.F32, 50021, dict(blocks=3, threads=64, chunk_bytes=512))):
+            (2, oracle.F32, 50021, dict(blocks=3, threads=64, chunk_bytes=512)),
+            # variant 7: the staged gather (pushing and copying blocks around a ring) with remote stores
+            (7, oracle.I64, 65536, {}), (7, oracle.BF16, 70001, {}), (7, oracle.U8, 13, {}),
+            (7, oracle.F32, 50021, dict(blocks=2, threads=64, chunk_bytes=4096)),
+            (7, oracle.F32, (1 << 20) + 3, dict(blocks=3, threads=96, chunk_bytes=65536))):
         for c in comms:
             c.set_tuning(variant=variant, **shape)
         arrays = [H.make_input(r, count, dtype) for r in range(n)]
@@ -277,7 +281,9 @@ def test_broadcast_bit_exact(teams, n):
     dev = "cuda:0"
     # variant 1: peers pull from the root; variant 2: scatter + all-gather
     # (large messages); the third shape forces many rounds of the latter.
-    shapes = [dict(variant=1), dict(variant=2), dict(variant=2, blocks=3, threads=64, chunk_bytes=512)]
+    # variant 7: the staged gather with the root as its only source.
+    shapes = [dict(variant=1), dict(variant=2), dict(variant=2, blocks=3, threads=64, chunk_bytes=512),
+              dict(variant=7), dict(variant=7, blocks=2, threads=64, chunk_bytes=4096)]
     most_rounds = 0
     try:
         for shape in shapes:
@@ -297,6 +303,54 @@ def test_broadcast_bit_exact(teams, n):
                         H.assert_bits_equal(H.to_numpy(bufs[r], dtype), want[r],
                                             "broadcast {} root {} rank {}".format(shape, root, r))
         assert most_rounds > 4
+    finally:
+        for c in comms:
+            c.set_tuning()
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_staged_gather_launches_back_to_back(teams, n):
+    """All-gathers (one of them in place) and broadcasts from changing roots,
+    with changing chunk sizes, share one ring: a launch must not overwrite what
+    a slower rank has not copied out of the launch before."""
+    comms = teams(n)
+    dev = "cuda:0"
+    try:
+        plan = [("gather", oracle.F32, 30011, 4096), ("bcast", oracle.BF16, 100003, 8192), ("gather", oracle.U8, 77777, 4096),
+                ("bcast", oracle.I64, 9000, 4096), ("gather", oracle.F16, 4099, 0), ("bcast", oracle.F32, 50021, 16384)]
+        for rep in range(2):
+            for i, (op, dtype, count, chunk) in enumerate(plan):
+                for c in comms:
+                    c.set_tuning(variant=7, chunk_bytes=chunk, threads=128 if i % 2 else 64, blocks=1 + i % 3)
+                arrays = [H.make_input(10 * i + r, count, dtype) for r in range(n)]
+                if op == "gather":
+                    in_place = i == 2
+                    outs = [torch.empty(n * count, dtype=H.to_torch(arrays[0], dtype, dev).dtype, device=dev)
+                            for _ in range(n)]
+                    ins = []
+                    for r in range(n):
+                        t = H.to_torch(arrays[r], dtype, dev)
+                        if in_place:
+                            outs[r][r * count:(r + 1) * count].copy_(t)
+                            t = outs[r][r * count:(r + 1) * count]
+                        ins.append(t)
+                    for r in range(n):
+                        comms[r].all_gather(ins[r], outs[r])
+                    torch.cuda.synchronize()
+                    want = oracle.allgather(arrays, dtype)
+                    for r in range(n):
+                        H.assert_bits_equal(H.to_numpy(outs[r], dtype), want, "staged gather {} rank {}".format(i, r))
+                else:
+                    root = (i + rep) % n
+                    bufs = [H.to_torch(a, dtype, dev) for a in arrays]
+                    for r in range(n):
+                        comms[r].broadcast(bufs[r], root)
+                    torch.cuda.synchronize()
+                    want = oracle.broadcast(arrays, dtype, root)
+                    for r in range(n):
+                        H.assert_bits_equal(H.to_numpy(bufs[r], dtype), want[r], "staged broadcast {} rank {}".format(i, r))
+                assert all(c.status() == 0 for c in comms)
+                assert comms[0].last_launch()["variant"] == 7
     finally:
         for c in comms:
             c.set_tuning()

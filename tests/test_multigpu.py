@@ -336,6 +336,44 @@ def test_multicast_broadcast_across_gpus(comms):
 
 
 @needs_two
+def test_multicast_allgather_across_gpus(comms):
+    """ALLGATHER through the switch (every rank stores its block once, the switch
+    replicates it): byte-exact, ragged sizes, more chunks than ring slots, in
+    place and out of place, alternating with broadcasts on the same ring."""
+    n = len(comms)
+    if not comms[0].has_nvls():
+        pytest.skip("NVSwitch multicast is not available on this box")
+    try:
+        for i, (dtype, count, chunk) in enumerate(((oracle.I64, 65536, 0), (oracle.U8, 13, 0), (oracle.BF16, (1 << 20) + 5, 65536),
+                                                   (oracle.F32, (3 << 20) + 1, 256 << 10), (oracle.F16, 70001, 4096))):
+            for c in comms:
+                c.set_tuning(variant=3, chunk_bytes=chunk, blocks=1 + i % 4)
+            arrays = [H.make_input(r, count, dtype, seed=700 + i) for r in range(n)]
+            want = oracle.allgather(arrays, dtype)
+            ins = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
+            outs = [torch.empty(n * count, dtype=ins[r].dtype, device="cuda:{}".format(r)) for r in range(n)]
+            if i == 3:  # in place: the own block already sits in the output
+                for r in range(n):
+                    outs[r][r * count:(r + 1) * count].copy_(ins[r])
+                    ins[r] = outs[r][r * count:(r + 1) * count]
+            bs = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
+            for rep in range(2):
+                for r in range(n):
+                    with torch.cuda.device(r):
+                        comms[r].all_gather(ins[r], outs[r])
+                        comms[r].broadcast(bs[r], (i + rep) % n)
+            sync_all(n)
+            assert comms[0].last_launch()["variant"] == 3
+            for r in range(n):
+                assert comms[r].status() == 0
+                H.assert_bits_equal(H.to_numpy(outs[r], dtype), want, "multicast all-gather case {} rank {}".format(i, r))
+                H.assert_bits_equal(H.to_numpy(bs[r], dtype), arrays[i % n], "broadcast between gathers, rank {}".format(r))
+    finally:
+        for c in comms:
+            c.set_tuning()
+
+
+@needs_two
 def test_two_processes_over_ipc_and_file_rendezvous():
     with tempfile.TemporaryDirectory() as rdv:
         env = dict(os.environ, DGN_NVLS="0", PYTHONFAULTHANDLER="1")  # workers may leave early: keep them off the multicast object

@@ -2,7 +2,7 @@
 without a GPU (dgn_plan_query).  The expectations are the measured crossovers
 the library documents: low-latency one-shot up to 1 MiB / 512 KiB / 128 KiB at
 2 / 4 / 8 ranks, low-latency two-shot up to 2 MiB from 3 ranks, the store-only
-two-shot kernel above, the staged ring through NVSwitch multicast from 32 MiB at
+two-shot kernel above, the staged ring through NVSwitch multicast from 16 MiB at
 8 ranks, in place on symmetric memory from 4 MiB (never by default at 2 ranks)."""
 
 import ctypes
@@ -41,8 +41,8 @@ def test_allreduce_variant_by_size_and_rank_count(dgn_lib):
         4: [(64 * KiB, _C.VARIANT_LL), (512 * KiB, _C.VARIANT_LL), (1 * MiB, _C.VARIANT_LL2),
             (2 * MiB, _C.VARIANT_LL2), (4 * MiB, _C.VARIANT_TWOSHOT), (1024 * MiB, _C.VARIANT_TWOSHOT)],
         8: [(1 * KiB, _C.VARIANT_LL), (128 * KiB, _C.VARIANT_LL), (256 * KiB, _C.VARIANT_LL2),
-            (2 * MiB, _C.VARIANT_LL2), (4 * MiB, _C.VARIANT_TWOSHOT), (16 * MiB, _C.VARIANT_TWOSHOT),
-            (32 * MiB, _C.VARIANT_NVLS), (256 * MiB, _C.VARIANT_NVLS), (1024 * MiB, _C.VARIANT_NVLS)],
+            (2 * MiB, _C.VARIANT_LL2), (4 * MiB, _C.VARIANT_TWOSHOT), (8 * MiB, _C.VARIANT_TWOSHOT),
+            (16 * MiB, _C.VARIANT_NVLS), (32 * MiB, _C.VARIANT_NVLS), (256 * MiB, _C.VARIANT_NVLS), (1024 * MiB, _C.VARIANT_NVLS)],
     }
     for n, rows in expect.items():
         for nbytes, variant in rows:
@@ -65,8 +65,9 @@ def test_launch_shapes_stay_inside_the_workspace(dgn_lib):
         p = plan(dgn_lib, n, AR, 64 * KiB)
         assert p["rounds"] == 1 and p["blocks"] <= 64 and p["chunk_bytes"] * 2 <= 64 * KiB  # lines are half flags
     # The staged ring: all blocks resident (they wait for one another), chunks
-    # a quarter of the message between 1 and 16 MiB, the ring never overrun.
-    for nbytes, chunk, chunks in ((32 * MiB, 8 * MiB, 4), (512 * MiB, 16 * MiB, 32), (100 * MiB + 16, None, 7)):
+    # half of the message between 1 and 16 MiB, the ring never overrun.
+    for nbytes, chunk, chunks in ((16 * MiB, 8 * MiB, 2), (32 * MiB, 16 * MiB, 2), (512 * MiB, 16 * MiB, 32),
+                                  (100 * MiB + 16, None, 7)):
         p = plan(dgn_lib, 8, AR, nbytes)
         assert p["variant"] == _C.VARIANT_NVLS and 3 <= p["blocks"] <= 148 and p["rounds"] == chunks, p
         assert chunk is None or p["chunk_bytes"] == chunk
@@ -86,7 +87,7 @@ def test_symmetric_memory_and_opt_in_variants(dgn_lib, monkeypatch):
     monkeypatch.delenv("DGN_SYMM_MIN_BYTES")
     small = plan(dgn_lib, 8, AR, 1 * MiB, symm=arena, in_symm=True)
     assert small["variant"] == _C.VARIANT_LL2                       # below 4 MiB the low-latency kernels win
-    assert plan(dgn_lib, 8, AR, 16 * MiB, symm=arena, in_symm=False)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 8, AR, 8 * MiB, symm=arena, in_symm=False)["variant"] == _C.VARIANT_TWOSHOT
     assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=False)["variant"] == _C.VARIANT_NVLS   # staged
     assert plan(dgn_lib, 8, AR, 64 * MiB + 4, symm=arena, in_symm=True)["variant"] == _C.VARIANT_NVLS  # ragged: staged
     assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=True, nvls=False)["variant"] == _C.VARIANT_TWOSHOT

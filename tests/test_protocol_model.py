@@ -18,7 +18,7 @@ The programs restate, step for step, the waits, stores, loads and signals of
   ar_twoshot_kernel        lock-step two-shot all-reduce
   zero_reduce_kernel       reduce-scatter of the sharded optimizer step
   zero_update_kernel       verdict exchange, update, all-gather
-  broadcast_nvls_kernel    the root stores through the switch, peers copy out
+  gather_flow_kernel       staged all-gather / broadcast: pushing and copying blocks
   ar_nvls_inplace_kernel   in place on symmetric memory, followed by the
                            caller's next write to the buffer
   ar_flow_kernel           staged ring: copy-in, reducing and copy-out blocks
@@ -271,23 +271,40 @@ def zero_update(rk, c, rounds, check=True, overflow=False):
     rk.end(parity, base + 2 * rounds + 1)
 
 
-def broadcast_nvls(rk, c, rounds, root):
-    """broadcast_nvls_kernel: the root's multimem.st lands in every rank's staging half."""
-    me = rk.me
-    base, parity = rk.begin()
-    for rnd in range(rounds):
-        e_pub, e_got = base + 2 * rnd + 1, base + 2 * rnd + 2
-        key = ("nvls", parity, rnd & 1)
-        if me == root:
-            if rnd >= 2:
-                rk.wait(B, rk.peers, base + 2 * (rnd - 2) + 2)
-            rk.data(*[("write", p, key, (c, rnd, "slice")) for p in rk.peers])  # its own copy is never read
-            rk.signal(A, rk.peers, e_pub)
-        else:
-            rk.wait(A, [root], e_pub)
-            rk.data(("read", key, (c, rnd, "slice")))
-            rk.signal(B, [root], e_got)
-    rk.end(parity, base + 2 * rounds + 1)
+def gather_roles(me, n, launches, depth):
+    """gather_flow_kernel (staged all-gather and broadcast): the pushing blocks and
+    the copying blocks of one rank as two processes.  `launches` lists (chunks,
+    root) of consecutive launches, root < 0 meaning that every rank is a source.
+    One "pushed" and one "freed" word per rank, raised to base + chunk + 1; a
+    source writes chunk k into slot k % D of EVERY rank's ring (its own
+    included) once every rank has freed chunk k - D -- or, for the first D
+    chunks, everything the launches before have pushed.  Every rank is modelled
+    as reading every region (the kernel skips the copy of a block that is in
+    place already, which only removes reads)."""
+    push, out = Rank(me, n, 0), Rank(me, n, 1)
+    roles = [push, out]
+    everyone = list(range(n))
+    base = 0
+    for c, (K, root) in enumerate(launches):
+        D = min(depth, K)
+        sources = everyone if root < 0 else [root]
+        if me in sources:
+            region = me if root < 0 else 0
+            for k in range(K):
+                push.wait("freed", everyone, base + max(0, k - D + 1))
+                push.data(*[("write", t, ("gring", k % D, region), (c, k, me)) for t in everyone])
+                push.signal("pushed", everyone, base + k + 1)
+        for k in range(K):
+            out.wait("pushed", sources, base + k + 1)
+            out.data(*[("read", ("gring", k % D, j if root < 0 else 0), (c, k, j)) for j in sources])
+            out.signal("freed", everyone, base + k + 1)
+        for rk in roles:  # kernel boundary
+            rk.local_set(("gleft", c, rk.role), 1)
+        for rk in roles:
+            for other in roles:
+                rk.local_wait(("gleft", c, other.role), 1)
+        base += K
+    return roles
 
 
 def nvls_inplace(rk, c):
@@ -549,18 +566,17 @@ def test_sharded_step_between_other_collectives():
         twoshot_allreduce(rk, 0, 2)
         zero_reduce(rk, 1, 3)
         zero_update(rk, 2, 3, check=False)
-        broadcast_nvls(rk, 3, 3, root=1)
+        broadcast_scatter(rk, 3, 3, root=1)
         twoshot_allreduce(rk, 4, 1)
     assert run(2, build) > 0
 
 
-@pytest.mark.parametrize("n,rounds,root", [(2, 5, 0), (3, 4, 2), (4, 4, 1)])
-def test_broadcast_through_the_switch(n, rounds, root):
-    def build(rk):
-        broadcast_nvls(rk, 0, rounds, root)
-        broadcast_nvls(rk, 1, rounds, (root + 1) % n)
-        broadcast_nvls(rk, 2, 1, root)
-    assert run(n, build) > 0
+@pytest.mark.parametrize("n,launches,depth", [(2, ((5, -1), (1, 0), (3, 1)), 2), (2, ((4, 1), (4, -1)), 3),
+                                              (3, ((4, -1), (3, 2)), 2), (3, ((3, 0), (2, -1), (2, 1)), 2),
+                                              (4, ((3, 1), (2, -1)), 2)])
+def test_staged_gather_and_broadcast(n, launches, depth):
+    """More chunks than ring slots; all-gathers and broadcasts from different roots back to back."""
+    assert run_roles(n, lambda me, n_: gather_roles(me, n_, launches, depth)) > 0
 
 
 @pytest.mark.parametrize("n", [2, 3, 4])
@@ -616,7 +632,8 @@ def test_eight_ranks():
     assert run_roles(4, lambda me, n: flow_roles(me, n, (3,), 2, 1)) > 0
     assert run(8, lambda rk: [twoshot_allreduce(rk, c, 2) for c in range(2)]) > 0
     assert run(8, lambda rk: [(zero_reduce(rk, 2 * c, 3), zero_update(rk, 2 * c + 1, 3)) for c in range(2)]) > 0
-    assert run(8, lambda rk: broadcast_nvls(rk, 0, 3, root=5)) > 0
+    assert run_roles(8, lambda me, n: gather_roles(me, n, ((3, 5),), 2)) > 0
+    assert run_roles(4, lambda me, n: gather_roles(me, n, ((2, -1),), 1)) > 0
     assert run(8, lambda rk: broadcast_scatter(rk, 0, 3, root=5)) > 0
     assert run(5, lambda rk: allgather(rk, 0, 2)) > 0   # the pushing kernel branches more: five ranks
 
