@@ -551,9 +551,9 @@ def parity_pass(comm, rank, world, dev, dist, headline):
                          "ok": all_ranks(ok)}
 
     def tune(variant=0, **kw):
-        knobs = {k: kw.pop(k) for k in list(kw) if k in ("flow_depth", "nvls_unroll")}
+        knobs = {k: kw.pop(k) for k in list(kw) if k in ("flow_depth", "nvls_unroll", "gather_mode")}
         comm.set_tuning(variant=variant, **kw)
-        for k in ("flow_depth", "nvls_unroll"):
+        for k in ("flow_depth", "nvls_unroll", "gather_mode"):
             comm.set_knob(k, knobs.get(k, 0))
 
     def allreduce_case(name, variant, kind, count, redop, ordered=True, symm=False, shift=0, want_rounds=0, **shape):
@@ -662,18 +662,25 @@ def parity_pass(comm, rank, world, dev, dist, headline):
     gather_case("allgather/push_bf16_many_rounds", 2, "bf16", (1 << 21) + 3, blocks=8, chunk_bytes=32 << 10)
     gather_case("allgather/pull_bf16_many_rounds", 1, "bf16", (1 << 21) + 3, blocks=8, chunk_bytes=32 << 10)
     gather_case("allgather/staged_peer_stores", 7, "f16", (1 << 20) + 5, blocks=2, chunk_bytes=16 << 10)
+    gather_case("allgather/staged_peer_loads", 8, "bf16", (1 << 21) + 3, chunk_bytes=64 << 10)
+    gather_case("allgather/planner_choice_large", 0, "f32", (1 << 22) + 1)
     if nvls:
         gather_case("allgather/staged_multicast", 3, "bf16", (1 << 21) + 3, chunk_bytes=32 << 10)
         gather_case("allgather/staged_multicast_default_shape", 3, "i64", (1 << 20) + 1)
     for root in sorted({0, world - 1}):
         broadcast_case("broadcast/pull_root{}".format(root), 1, "i64", 65536, root)
         broadcast_case("broadcast/staged_peer_stores_root{}".format(root), 7, "bf16", (1 << 20) + 3, root,
-                       chunk_bytes=16 << 10)
+                       chunk_bytes=16 << 10, gather_mode=1)
+        broadcast_case("broadcast/staged_shards_peer_stores_root{}".format(root), 7, "bf16", (1 << 20) + 3, root,
+                       chunk_bytes=64 << 10, gather_mode=2)
         if world > 2:
             broadcast_case("broadcast/scatter_root{}".format(root), 2, "bf16", (1 << 22) + 3, root)
         if nvls:
             broadcast_case("broadcast/multicast_root{}".format(root), 3, "bf16", (1 << 22) + 3, root,
-                           chunk_bytes=128 << 10)
+                           chunk_bytes=128 << 10, gather_mode=1)
+            broadcast_case("broadcast/multicast_shards_root{}".format(root), 3, "bf16", (1 << 22) + 3, root,
+                           chunk_bytes=512 << 10, gather_mode=2)
+            broadcast_case("broadcast/planner_choice_large_root{}".format(root), 0, "f32", (1 << 22) + 1, root)
     reducescatter_case("reducescatter/f32_mean", "f32", 300001, "MEAN")
     reducescatter_case("reducescatter/int64_sum", "i64", 4099, "SUM")
     tune(0)

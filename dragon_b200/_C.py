@@ -18,7 +18,7 @@ OK, ERR_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_PEER, ERR_STATE, ERR_UNSUPPORTED = range
 U8, I8, I32, I64, F16, BF16, F32, F64 = range(8)
 SUM, MEAN, PROD, MIN, MAX = range(5)
 (VARIANT_AUTO, VARIANT_ONESHOT, VARIANT_TWOSHOT, VARIANT_NVLS, VARIANT_LL, VARIANT_LL2, VARIANT_SYMM,
- VARIANT_RING) = range(8)
+ VARIANT_RING, VARIANT_RING_PULL) = range(9)
 
 REDOPS = {"SUM": SUM, "MEAN": MEAN, "PROD": PROD, "MIN": MIN, "MAX": MAX}
 

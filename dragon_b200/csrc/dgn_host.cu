@@ -196,6 +196,9 @@ struct Plan {
   int unroll = 8;  // multicast kernels: loads in flight per thread
   // staged dataflow all-reduce: reducing / copy-in blocks (the rest copy out), ring slots
   int flow_nsw = 0, flow_nin = 0, flow_depth = 0;
+  // staged gather: mode bits and the inbox of the scattering broadcast (bytes from the workspace base)
+  int flow_mode = 0;
+  long long inbox_off = 0;
 };
 
 enum OpKind { kOpAllReduce = 0, kOpReduceScatter, kOpAllGather, kOpBroadcast, kOpZeroReduce, kOpZeroUpdate,
@@ -303,8 +306,9 @@ struct dgn_comm {
   // Staged gather (gather_flow_kernel): ring at the start of the multicast-bound
   // buffer, chunk size per source, pushing blocks (0: automatic), thresholds.
   size_t gather_ring_bytes = 0;
-  long long gather_chunk_bytes = 0, nvls_allgather_min_bytes = 0;
-  int gather_push_blocks = 0;
+  long long gather_chunk_bytes = 0, nvls_allgather_min_bytes = 0, allgather_ring_min_bytes = 0;
+  long long bcast_shard_min_bytes = 0;  // smallest staged broadcast whose root scatters shards
+  int gather_push_blocks = 0, gather_forward_blocks = 0, gather_mode = 0;
   size_t nvls_bytes = 0;
   // Symmetric arena: the tail of the multicast-bound buffer, handed out by
   // dgn_comm_symm_alloc; buffers in it can be reduced in place by the switch.
@@ -540,33 +544,52 @@ bool plan_flow(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring
 }
 
 // Launch shape of the staged gather (gather_flow_kernel: all-gather and
-// broadcast) over a ring of `ring_bytes`; false if ring or grid are too small.
-bool plan_gather(const dgn_comm* c, const OpDesc& d, int block_cap, long long ring_bytes, int variant, Plan* out) {
+// broadcast); false if ring, inbox or grid are too small.  Variant NVLS keeps the
+// ring in the multicast-bound buffer and the inbox of the scattering broadcast
+// in the gather half of the workspace ring; RING / RING_PULL keep both in that
+// half (ring first, inbox behind it).
+bool plan_gather(const dgn_comm* c, const OpDesc& d, int block_cap, int variant, Plan* out) {
   const int n = c->nranks;
-  const int nsrc = d.kind == kOpAllGather ? n : 1;
-  const long long bytes = d.nvec * 16;  // per source
+  const bool gather = d.kind == kOpAllGather;
+  const bool pull = variant == DGN_VARIANT_RING_PULL;
+  if (pull && !gather) return false;
+  const long long bytes = d.nvec * 16;  // per block (all-gather) / of the message (broadcast)
+  // Broadcast: from three ranks on the root scatters shards and every rank
+  // multicasts its own (no rank has to feed the switch alone).
+  bool scatter = !gather && n >= 3 && bytes >= c->bcast_shard_min_bytes;
+  if (c->gather_mode == 1) scatter = false;
+  if (c->gather_mode == 2 && !gather && n >= 2) scatter = true;
+  const int nsrc = (gather || scatter) ? n : 1;
+  const int nreg = pull ? 1 : nsrc;
+  const long long half = (long long)c->geo.ring_bytes / 2;
+  const long long ring_bytes = variant == DGN_VARIANT_NVLS ? (long long)c->gather_ring_bytes : half;
   int total = c->num_sms;
   if (total > c->geo.max_blocks) total = c->geo.max_blocks;
   if (block_cap > 0 && block_cap < total) total = block_cap;
-  if (total < 2 || ring_bytes < 2ll * nsrc * 4096) return false;
-  // Chunk per source: an eighth of the block, between 256 KiB and 4 MiB (8 MiB
-  // for the single source of a broadcast).
+  if (total < 2 || ring_bytes < 2ll * (nreg + 1) * 4096) return false;
+  // Bytes per chunk and source: an eighth of a block, 256 KiB to 4 MiB
+  // (all-gather); of the message: an eighth, 256 KiB to 8 MiB (broadcast).
   long long chunk = c->gather_chunk_bytes;
   if (c->tune_chunk >= 4096) chunk = c->tune_chunk;
   if (chunk <= 0) {
     chunk = ceil_div(bytes, 8);
-    const long long hi = nsrc == 1 ? (8ll << 20) : (4ll << 20);
+    const long long hi = gather ? (4ll << 20) : (8ll << 20);
     if (chunk < (256ll << 10)) chunk = 256ll << 10;
     if (chunk > hi) chunk = hi;
   }
-  long long cv = ceil_div(chunk, 16);
-  const long long cv_max = ring_bytes / (2ll * nsrc * 16);  // at least two slots
+  long long cv = ceil_div(chunk, 16 * (long long)(gather ? 1 : nsrc));  // per source
+  // At least two slots of ring (and of inbox, where the two share the half).
+  const bool shared = variant != DGN_VARIANT_NVLS;
+  long long cv_max = ring_bytes / (2ll * (nreg + (shared && scatter ? 1 : 0)) * 16);
+  if (scatter && !shared && cv_max > half / (2 * 16)) cv_max = half / (2 * 16);
   if (cv > cv_max) cv = cv_max;
-  if (cv > d.nvec) cv = d.nvec;
+  const long long per_src = gather ? d.nvec : ceil_div(d.nvec, nsrc);
+  if (cv > per_src) cv = per_src;
   if (cv < 1 || cv > 0x7fffffff) return false;
-  const long long K = ceil_div(d.nvec, cv);
+  const long long K = ceil_div(d.nvec, gather ? cv : cv * nsrc);
   if (K > 0x7fffffff) return false;
-  long long depth = ring_bytes / (nsrc * cv * 16);
+  long long depth = ring_bytes / ((nreg + (shared && scatter ? 1 : 0)) * cv * 16);
+  if (scatter && !shared && depth > half / (cv * 16)) depth = half / (cv * 16);
   if (depth > kFlowSlots) depth = kFlowSlots;
   if (c->flow_depth > 0 && c->flow_depth < depth) depth = c->flow_depth;
   if (depth > K) depth = K;
@@ -577,25 +600,37 @@ bool plan_gather(const dgn_comm* c, const OpDesc& d, int block_cap, long long ri
   if (p.threads > kMaxThreads) p.threads = kMaxThreads;
   p.threads = p.threads / 32 * 32;
   if (p.threads < 64) p.threads = 64;  // a pushing block needs a data warp and its signal warp
-  // Pushing blocks: a source of an all-gather sends only S while 7 S arrive, so a
-  // few blocks keep up; the single source of a broadcast feeds everybody.
-  int npush = c->gather_push_blocks > 0 ? c->gather_push_blocks : (nsrc == 1 ? 16 : 4);
+  // Pushing blocks.  All-gather: a source sends S while (n - 1) S arrive, and
+  // few pushing blocks congest the switch least (2 blocks: 835 us, 8 blocks: 930
+  // us at 8 ranks and 64 MiB).  Broadcast: the root feeds everybody.
+  int npush = c->gather_push_blocks > 0 ? c->gather_push_blocks : (gather ? 2 : 16);
   if (c->tune_blocks > 0) npush = c->tune_blocks;
   const long long per_push = (long long)(p.threads - 32) * 4;  // vectors one block pushes per pass
-  if (npush > ceil_div(cv, per_push)) npush = (int)ceil_div(cv, per_push);
+  const long long root_cv = scatter ? cv * nsrc : cv;
+  if (npush > ceil_div(root_cv, per_push)) npush = (int)ceil_div(root_cv, per_push);
   if (npush > total - 1) npush = total - 1;
   if (npush < 1) npush = 1;
-  // Copying blocks: enough for the n blocks of a chunk, no more than the SMs left.
+  int nfwd = 0;
+  if (scatter) {
+    nfwd = c->gather_forward_blocks > 0 ? c->gather_forward_blocks : 2;
+    if (nfwd > ceil_div(cv, per_push)) nfwd = (int)ceil_div(cv, per_push);
+    if (nfwd > total - 1) nfwd = total - 1;
+    if (nfwd < 1) nfwd = 1;
+  }
+  // Copying blocks: enough for the parts of a chunk, no more than the SMs left.
+  const int most = npush > nfwd ? npush : nfwd;
   long long nout = ceil_div((long long)nsrc * cv, (long long)p.threads * 4);
-  if (nout > total - npush) nout = total - npush;
+  if (nout > total - most) nout = total - most;
   if (nout < 1) nout = 1;
-  p.blocks = npush + (int)nout;
+  p.blocks = most + (int)nout;
   p.cv = (int)cv;
   p.rounds = (int)K;
   p.unroll = c->unroll > 0 ? (c->unroll > 8 ? 8 : c->unroll) : 4;
   p.flow_nsw = npush;
-  p.flow_nin = 0;
+  p.flow_nin = nfwd;
   p.flow_depth = (int)depth;
+  p.flow_mode = (scatter ? kGatherScatter : 0) | (pull ? kGatherPull : 0);
+  p.inbox_off = (long long)c->geo.ring_off + half + (shared ? depth * nreg * cv * 16 : 0);
   *out = p;
   return true;
 }
@@ -756,11 +791,14 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
       const long long thr = d.kind == kOpAllGather ? c->nvls_allgather_min_bytes : c->nvls_bcast_min_bytes;
       bool nvls = d.nvec * 16 >= thr && c->tune_variant == DGN_VARIANT_AUTO;
       if (c->tune_variant == DGN_VARIANT_NVLS) nvls = true;
-      if (nvls && plan_gather(c, d, block_cap, (long long)c->gather_ring_bytes, DGN_VARIANT_NVLS, &p)) return p;
+      if (nvls && plan_gather(c, d, block_cap, DGN_VARIANT_NVLS, &p)) return p;
     }
-    // The same protocol with remote stores (never chosen automatically).
-    if (c->tune_variant == DGN_VARIANT_RING &&
-        plan_gather(c, d, block_cap, (long long)c->geo.ring_bytes / 2, DGN_VARIANT_RING, &p))
+    // The same protocol with remote stores, or with remote loads (all-gather).
+    if ((c->tune_variant == DGN_VARIANT_RING || c->tune_variant == DGN_VARIANT_RING_PULL) &&
+        plan_gather(c, d, block_cap, c->tune_variant, &p))
+      return p;
+    if (d.kind == kOpAllGather && c->tune_variant == DGN_VARIANT_AUTO && d.nvec * 16 >= c->allgather_ring_min_bytes &&
+        plan_gather(c, d, block_cap, DGN_VARIANT_RING_PULL, &p))
       return p;
   }
   // Multi-round kernels: two-shot all-reduce, reduce-scatter, all-gather,
@@ -822,6 +860,19 @@ void load_thresholds(dgn_comm* c) {
   // Pushing wins up to 4 MiB blocks (85 against 100 us at 8 ranks), pulling from
   // 16 MiB (222 against 246 us; 803 against 838 us at 64 MiB).
   c->allgather_pull_min_bytes = env_ll("DGN_ALLGATHER_PULL_MIN_BYTES", nranks >= 5 ? (8ll << 20) : (1ll << 62));
+  c->allgather_ring_min_bytes = env_ll("DGN_ALLGATHER_RING_MIN_BYTES", 1ll << 62);
+  // Shapes of the staged kernels (0: automatic).
+  c->gather_chunk_bytes = env_ll("DGN_GATHER_CHUNK_BYTES", 0);
+  c->gather_push_blocks = (int)env_ll("DGN_GATHER_PUSH_BLOCKS", 0);
+  c->gather_forward_blocks = (int)env_ll("DGN_GATHER_FORWARD_BLOCKS", 0);
+  c->gather_mode = (int)env_ll("DGN_GATHER_MODE", 0);
+  c->bcast_shard_min_bytes = env_ll("DGN_BCAST_SHARD_MIN_BYTES", 2ll << 20);
+  c->flow_chunk_bytes = env_ll("DGN_FLOW_CHUNK_BYTES", 0);
+  c->flow_switch_blocks = (int)env_ll("DGN_FLOW_SWITCH_BLOCKS", 0);
+  c->flow_in_blocks = (int)env_ll("DGN_FLOW_IN_BLOCKS", 0);
+  c->flow_out_blocks = (int)env_ll("DGN_FLOW_OUT_BLOCKS", 0);
+  c->flow_depth = (int)env_ll("DGN_FLOW_DEPTH", 0);
+  c->unroll = (int)env_ll("DGN_NVLS_UNROLL", 0);
   c->tune_variant = (int)env_ll("DGN_FORCE_VARIANT", 0);
 }
 
@@ -862,14 +913,6 @@ void load_nvls_settings(dgn_comm* c, long long symm_request) {
   // ranks it loses from 64 MiB (148 against 121 us), so it is opt-in below 5 ranks.
   c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", nranks >= 5 ? (256ll << 10) : (1ll << 62));
   c->nvls_allgather_min_bytes = env_ll("DGN_NVLS_ALLGATHER_MIN_BYTES", 1ll << 62);
-  c->gather_chunk_bytes = env_ll("DGN_GATHER_CHUNK_BYTES", 0);
-  c->gather_push_blocks = (int)env_ll("DGN_GATHER_PUSH_BLOCKS", 0);
-  c->flow_chunk_bytes = env_ll("DGN_FLOW_CHUNK_BYTES", 0);
-  c->flow_switch_blocks = (int)env_ll("DGN_FLOW_SWITCH_BLOCKS", 0);
-  c->flow_in_blocks = (int)env_ll("DGN_FLOW_IN_BLOCKS", 0);
-  c->flow_out_blocks = (int)env_ll("DGN_FLOW_OUT_BLOCKS", 0);
-  c->flow_depth = (int)env_ll("DGN_FLOW_DEPTH", 0);
-  c->unroll = (int)env_ll("DGN_NVLS_UNROLL", 0);
 }
 
 struct KernelChoice {
@@ -888,7 +931,7 @@ KernelChoice choose_kernel(const dgn_comm* c, const OpDesc& d, const Plan& p) {
     case kOpReduceScatter: k.fn = reduce_fn(d.dtype, 2, false); break;
     case kOpAllGather:
       k.fn = p.variant == DGN_VARIANT_NVLS      ? gather_flow_kernel_fn(true)
-             : p.variant == DGN_VARIANT_RING    ? gather_flow_kernel_fn(false)
+             : p.variant == DGN_VARIANT_RING || p.variant == DGN_VARIANT_RING_PULL ? gather_flow_kernel_fn(false)
              : p.variant == DGN_VARIANT_LL      ? allgather_ll_kernel_fn()
              : p.variant == DGN_VARIANT_ONESHOT ? allgather_pull_kernel_fn()
                                                 : allgather_kernel_fn();
@@ -930,6 +973,8 @@ void fill_params(OpParams* P, const dgn_comm* c, const OpDesc& d, const Plan& p)
   P->flow_depth = p.flow_depth;
   P->flow_nsw = p.flow_nsw;
   P->flow_nin = p.flow_nin;
+  P->flow_mode = p.flow_mode;
+  P->inbox_off = p.inbox_off;
 }
 
 void fill_zero_params(ZeroParams* Z, const dgn_comm* c, const OpDesc& d, const Plan& p) {
@@ -998,7 +1043,7 @@ int issue(dgn_comm* c, const OpDesc& d) {
     if (!k.fn) return fail(DGN_ERR_UNSUPPORTED, "no kernel for dtype %d", d.dtype);
     int rc;
     if ((d.kind == kOpAllReduce || d.kind == kOpAllGather || d.kind == kOpBroadcast) &&
-        (p.variant == DGN_VARIANT_NVLS || p.variant == DGN_VARIANT_RING)) {
+        (p.variant == DGN_VARIANT_NVLS || p.variant == DGN_VARIANT_RING || p.variant == DGN_VARIANT_RING_PULL)) {
       // The blocks of the dataflow kernels wait for one another: cooperative launch.
       OpParams P;
       fill_params(&P, c, d, p);
@@ -1793,7 +1838,7 @@ int dgn_comm_set_wait_limit_ms(dgn_comm_t c, int ms) {
 
 int dgn_comm_set_tuning(dgn_comm_t c, int variant, int blocks, int threads, int64_t chunk_bytes) {
   if (!c) return fail(DGN_ERR_ARG, "null communicator");
-  if (variant < 0 || variant > DGN_VARIANT_RING || blocks < 0 || threads < 0 || chunk_bytes < 0)
+  if (variant < 0 || variant > DGN_VARIANT_RING_PULL || blocks < 0 || threads < 0 || chunk_bytes < 0)
     return fail(DGN_ERR_ARG, "bad tuning value");
   if ((variant == DGN_VARIANT_NVLS || variant == DGN_VARIANT_SYMM) && !c->nvls)
     return fail(DGN_ERR_UNSUPPORTED, "the NVLS variants are not set up on this communicator");
@@ -1823,6 +1868,10 @@ int dgn_comm_set_knob(dgn_comm_t c, const char* name, int64_t value) {
   else if (k == "nvls_allgather_min_bytes") c->nvls_allgather_min_bytes = value;
   else if (k == "gather_chunk_bytes") c->gather_chunk_bytes = value;
   else if (k == "gather_push_blocks") c->gather_push_blocks = (int)value;
+  else if (k == "gather_forward_blocks") c->gather_forward_blocks = (int)value;
+  else if (k == "gather_mode") c->gather_mode = (int)value;
+  else if (k == "bcast_shard_min_bytes") c->bcast_shard_min_bytes = value;
+  else if (k == "allgather_ring_min_bytes") c->allgather_ring_min_bytes = value;
   else return fail(DGN_ERR_ARG, "unknown knob '%s'", name);
   return DGN_OK;
 }

@@ -138,6 +138,10 @@ struct OpParams {
   int flow_chunks;             // chunks of the message
   int flow_depth;              // ring slots in use
   int flow_nsw, flow_nin;      // blocks [0, nsw) reduce, [nsw, nsw + nin) copy in, the rest copy out
+  // staged gather (gather_flow_kernel): flow_cv vectors per source and chunk; flow_nsw pushing blocks
+  // (flow_nin on the ranks that forward from their inbox)
+  int flow_mode;               // kGatherScatter, kGatherPull
+  long long inbox_off;         // inbox of the scattering broadcast, bytes from the workspace base
 };
 
 // ---------------------------------------------------------------------------
@@ -1846,22 +1850,37 @@ __global__ void __launch_bounds__(kMaxThreads, 1) broadcast_scatter_kernel(const
 
 // ---------------------------------------------------------------------------
 // ALLGATHER and BROADCAST (bytes) as a staged dataflow kernel.  The sources
-// (every rank for the all-gather, the root for the broadcast) store their block
-// chunk by chunk into the gather ring of ALL ranks: with one multimem.st per
-// vector through the switch (SWITCH: a source sends S bytes whatever the rank
-// count, the switch replicates them) or with one remote store per rank (the same
-// protocol on any communicator, virtual ranks included).  The other blocks copy
-// each chunk from the local ring into the output as soon as every source has
-// pushed it.  Roles: blocks [0, P.flow_nsw) of a source push (data warps take
-// batches of 32 x unroll vectors round-robin, the last warp publishes what they
-// have left with ONE system fence for all finished chunks), all other blocks
-// copy out.  Flags (one word per rank and kind, raised with a maximum):
-//   pushed[j] = base + c + 1   rank j's chunks 0..c are in every ring
+// store their data chunk by chunk into the gather ring of ALL ranks: with one
+// multimem.st per vector through the switch (SWITCH: a source sends its bytes
+// once whatever the rank count, the switch replicates them) or with one remote
+// store per rank (the same protocol on any communicator, virtual ranks
+// included).  The other blocks copy each chunk from the local ring into the
+// output as soon as every source has pushed it.  Who is a source:
+//   all-gather (P.root < 0)       every rank, of its own block
+//   broadcast, kGatherScatter     every rank, of shard r of every chunk: the root
+//                                 forwards shard j to rank j's inbox with plain
+//                                 remote stores and pushes only its own shard,
+//                                 so no rank multicasts more than S / n (one
+//                                 source alone cannot feed the switch fast
+//                                 enough: 350 GB/s measured at 8 ranks)
+//   broadcast otherwise           the root alone
+// kGatherPull (all-gather without the switch): a source stores into its OWN ring
+// only and the copying blocks load from the sources' rings (remote loads).
+// Roles: the first blocks of a source push (data warps take batches of 32 x
+// unroll vectors round-robin, the last warp publishes what they have left with
+// ONE system fence for all finished chunks), all other blocks copy out.  Flags
+// (one word per rank and kind, raised with a maximum):
+//   pushed[j] = base + c + 1   rank j's part of chunks 0..c is in every ring
+//                              (the root's: and in every inbox)
 //   freed[j]  = base + c + 1   rank j has copied chunks 0..c out of its ring
 // A source writes chunk c into ring slot c % D once freed[j] >= base + c - D + 1
 // came from every rank j (itself included); for c < D that is `base`: every
-// chunk of the launches before is out of the ring, whatever shape they had.
-// `count` is bytes per source block; P.root < 0 means every rank is a source.
+// chunk of the launches before is out of the ring, whatever shape they had.  A
+// rank that forwards from its inbox waits for pushed[root] instead, which the
+// root raises after that same wait.  `count` is bytes per block (all-gather) or
+// of the message (broadcast).
+
+constexpr int kGatherScatter = 1, kGatherPull = 2;
 
 __device__ __forceinline__ void gather_count(const PeerTable& pt, unsigned* counter, unsigned target, int kind, u64 val) {
   const unsigned old = atomicAdd(counter, 1u);
@@ -1881,15 +1900,21 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gather_flow_kernel(const __gri
   __shared__ int s_left[kFlowSlots];
   __shared__ volatile int s_signalled;
   const int K = P.flow_chunks, D = P.flow_depth, root = P.root;
-  const int nsrc = root < 0 ? n : 1;
-  const bool source = root < 0 || r == root;
-  const int my = root < 0 ? r : 0;  // my region inside a ring slot
-  const int npush = source ? P.flow_nsw : 0, nout = (int)gridDim.x - npush;
-  const long long CV = P.flow_cv;
+  const bool scatter = root >= 0 && (P.flow_mode & kGatherScatter) != 0;
+  const bool pull = !SWITCH && root < 0 && (P.flow_mode & kGatherPull) != 0;
+  const int nsrc = (root < 0 || scatter) ? n : 1;       // sources of a chunk
+  const bool source = nsrc == n || r == root;
+  const int my = nsrc == n ? r : 0;                      // my part of a chunk
+  const int nreg = pull ? 1 : nsrc;                      // regions of a ring slot
+  const int npush = !source ? 0 : (scatter && r != root) ? P.flow_nin : P.flow_nsw;
+  const int nout = (int)gridDim.x - npush;
+  const long long CV = P.flow_cv;                        // vectors per source and chunk
   const long long ring_off = SWITCH ? 0 : pt.ring_gather_off;
-  char* const ring = SWITCH ? pt.nvls_uc : reinterpret_cast<char*>(pt.flags[r]) + ring_off;
-  const char* in = static_cast<const char*>(root < 0 ? ra.in : ra.out);
+  char* const wbase = reinterpret_cast<char*>(pt.flags[r]);
+  char* const ring = SWITCH ? pt.nvls_uc : wbase + ring_off;
   char* out = static_cast<char*>(ra.out);
+  // Part j of chunk c: first vector in its buffer, and the buffer.
+  auto part_begin = [&](int c, int j) -> long long { return root < 0 ? (long long)c * CV : ((long long)c * nsrc + j) * CV; };
   const int nwarps = blockDim.x >> 5;
   bool ok = true;
 
@@ -1903,43 +1928,63 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gather_flow_kernel(const __gri
     const long long per_batch = 32ll * U;
     const long long W = (long long)npush * ndata;
     const long long nb_full = (CV + per_batch - 1) / per_batch;
+    const bool forward = scatter && r != root;  // my input is what the root left in my inbox
+    const char* in = static_cast<const char*>(root < 0 ? ra.in : ra.out);
     const bool in_al = is_al16(in);
+    const int nparts = (scatter && r == root) ? n : 1;  // the root handles every shard of a chunk
     if (warp < ndata) {
       const long long gw = (long long)b * ndata + warp;
       for (int c = 0; c < K && ok; ++c) {
         const int s = c % D;
-        const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
-        const long long nb = (clen + per_batch - 1) / per_batch;
-        long long k = (gw - ((long long)c * nb_full) % W + W) % W;
-        if (k < nb) {
-          const u64 need = base + (u64)(c >= D ? c - D + 1 : 0);
-          if (lane < n) ok = flow_wait_flag(flow_flag(pt, r, 3, 0, lane), need, P.wait_ns, pt.status);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          const long long off = ring_off + (((long long)s * nsrc + my) * CV) * 16;
-          const long long vbase = (long long)c * CV;
+        bool waited = false;
+        for (int q = 0; q < nparts && ok; ++q) {
+          const int j = nparts == 1 ? my : q;
+          const long long pb = part_begin(c, j);
+          const long long clen = clampll(P.nvec - pb, 0, CV);
+          const long long nb = (clen + per_batch - 1) / per_batch;
+          long long k = (gw - (((long long)c * nparts + q) * nb_full) % W + W) % W;
+          if (k >= nb) continue;
+          if (!waited) {
+            if (forward) {
+              if (lane == 0) ok = flow_wait_flag(flow_flag(pt, r, 2, 0, root), base + (u64)c + 1, P.wait_ns, pt.status);
+            } else {
+              const u64 need = base + (u64)(c >= D ? c - D + 1 : 0);
+              if (lane < n) ok = flow_wait_flag(flow_flag(pt, r, 3, 0, lane), need, P.wait_ns, pt.status);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            waited = true;
+            if (!ok) break;
+          }
+          const bool mine = j == my || nparts == 1;  // goes into the rings; otherwise into rank j's inbox
+          const long long roff = ring_off + (((long long)s * nreg + (pull ? 0 : j)) * CV) * 16;
+          const long long ioff = P.inbox_off + (long long)s * CV * 16;
           for (; k < nb; k += W) {
             const long long lo = k * per_batch + lane;
             const long long hi = k * per_batch + per_batch < clen ? k * per_batch + per_batch : clen;
             uint4 x[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u)
-              if (u < U && lo + 32 * u < hi) x[u] = load_vec<1>(in, vbase + lo + 32 * u, P.count, in_al);
+              if (u < U && lo + 32 * u < hi)
+                x[u] = forward ? ldv(wbase + ioff + (lo + 32 * u) * 16) : load_vec<1>(in, pb + lo + 32 * u, P.count, in_al);
 #pragma unroll
             for (int u = 0; u < 8; ++u)
               if (u < U && lo + 32 * u < hi) {
-                const long long o = off + (lo + 32 * u) * 16;
-                if constexpr (SWITCH) {
-                  Multimem<float>::st(pt.nvls_mc + o, x[u]);
+                const long long v16 = (lo + 32 * u) * 16;
+                if (!mine) {
+                  stv(reinterpret_cast<char*>(pt.flags[j]) + ioff + v16, x[u]);
+                } else if constexpr (SWITCH) {
+                  Multimem<float>::st(pt.nvls_mc + roff + v16, x[u]);
+                } else if (pull) {
+                  stv(wbase + roff + v16, x[u]);
                 } else {
-                  for (int j = 0; j < n; ++j) stv(reinterpret_cast<char*>(pt.flags[j]) + o, x[u]);
+                  for (int t = 0; t < n; ++t) stv(reinterpret_cast<char*>(pt.flags[t]) + roff + v16, x[u]);
                 }
               }
           }
         }
         __syncwarp();
         if (lane == 0) {
-          if (c >= kFlowSlots) ok = flow_wait_shared(&s_signalled, c - kFlowSlots + 1, P.wait_ns, pt.status);
+          if (c >= kFlowSlots) ok = ok && flow_wait_shared(&s_signalled, c - kFlowSlots + 1, P.wait_ns, pt.status);
           __threadfence_block();
           atomicAdd(&s_left[c % kFlowSlots], 1);
         }
@@ -1978,32 +2023,35 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gather_flow_kernel(const __gri
   } else {
     const long long first = (long long)(b - npush) * blockDim.x + threadIdx.x;
     const long long step = (long long)nout * blockDim.x;
+    const char* in = static_cast<const char*>(root < 0 ? ra.in : ra.out);
+    const bool idle = root >= 0 && r == root;  // the root of a broadcast has its data already
     for (int c = 0; c < K; ++c) {
       const int s = c % D;
       const unsigned use = (unsigned)(c / D) + 1u;
       const int t = threadIdx.x;
-      if (t < nsrc) ok = flow_wait_flag(flow_flag(pt, r, 2, 0, root < 0 ? t : root), base + (u64)c + 1, P.wait_ns, pt.status);
+      if (t < nsrc) ok = flow_wait_flag(flow_flag(pt, r, 2, 0, nsrc == n ? t : root), base + (u64)c + 1, P.wait_ns, pt.status);
       ok = __syncthreads_and(ok) != 0;
       if (!ok) break;
-      const long long clen = clampll(P.nvec - (long long)c * CV, 0, CV);
-      const long long vbase = (long long)c * CV;
-      for (int i = 0; i < nsrc; ++i) {
-        const int j = root < 0 ? (i + r) % n : root;  // ranks start at different sources
-        const int region = root < 0 ? j : 0;
+      for (int i = 0; i < nsrc && !idle; ++i) {
+        const int j = nsrc == n ? (i + r) % n : root;  // ranks start at different sources
+        const int region = nsrc == n ? j : 0;
         char* dst = root < 0 ? out + (long long)j * P.count : out;
         if (j == r && dst == in) continue;  // the own block is in place already
         const bool dst_al = is_al16(dst);
-        const char* src = ring + (((long long)s * nsrc + region) * CV) * 16;
+        const long long pb = part_begin(c, region);
+        const long long clen = clampll(P.nvec - pb, 0, CV);
+        const char* src = pull ? reinterpret_cast<char*>(pt.flags[j]) + ring_off + ((long long)s * CV) * 16
+                               : ring + (((long long)s * nreg + region) * CV) * 16;
         long long v = first;
         for (; v + 3 * step < clen; v += 4 * step) {
           const uint4 x0 = ldv(src + v * 16), x1 = ldv(src + (v + step) * 16), x2 = ldv(src + (v + 2 * step) * 16),
                       x3 = ldv(src + (v + 3 * step) * 16);
-          store_vec<1>(dst, vbase + v, P.count, dst_al, x0);
-          store_vec<1>(dst, vbase + v + step, P.count, dst_al, x1);
-          store_vec<1>(dst, vbase + v + 2 * step, P.count, dst_al, x2);
-          store_vec<1>(dst, vbase + v + 3 * step, P.count, dst_al, x3);
+          store_vec<1>(dst, pb + v, P.count, dst_al, x0);
+          store_vec<1>(dst, pb + v + step, P.count, dst_al, x1);
+          store_vec<1>(dst, pb + v + 2 * step, P.count, dst_al, x2);
+          store_vec<1>(dst, pb + v + 3 * step, P.count, dst_al, x3);
         }
-        for (; v < clen; v += step) store_vec<1>(dst, vbase + v, P.count, dst_al, ldv(src + v * 16));
+        for (; v < clen; v += step) store_vec<1>(dst, pb + v, P.count, dst_al, ldv(src + v * 16));
       }
       __syncthreads();
       if (threadIdx.x == 0) {

@@ -73,11 +73,12 @@ typedef enum {
   DGN_VARIANT_AUTO = 0,
   DGN_VARIANT_ONESHOT = 1, /* every rank pushes its whole message to every peer */
   DGN_VARIANT_TWOSHOT = 2, /* reduce-scatter by peer stores + all-gather by peer loads */
-  DGN_VARIANT_NVLS = 3,    /* staged ring reduced through NVSwitch multicast (multimem), any tensors */
+  DGN_VARIANT_NVLS = 3,    /* staged through NVSwitch multicast (multimem): all-reduce ring, all-gather, broadcast */
   DGN_VARIANT_LL = 4,      /* one-shot with flag-in-data lines, no barrier (small messages) */
   DGN_VARIANT_LL2 = 5,     /* two-shot with flag-in-data lines (medium messages) */
   DGN_VARIANT_SYMM = 6,    /* NVSwitch multicast in place, on a buffer from dgn_comm_symm_alloc */
-  DGN_VARIANT_RING = 7     /* the same staged ring reduced with peer loads and stores (no switch needed; never chosen automatically) */
+  DGN_VARIANT_RING = 7,    /* the same staged kernels with peer loads and stores (no switch needed; never chosen automatically) */
+  DGN_VARIANT_RING_PULL = 8 /* all-gather only: staged, every rank loads the chunks from the sources' rings */
 } dgn_variant;
 
 /* ---- library ----------------------------------------------------------- */
@@ -172,8 +173,11 @@ int dgn_comm_set_tuning(dgn_comm_t comm, int variant, int blocks, int threads,
  * keeps in flight and "nvls_pattern" (0 contiguous batches per warp, 1
  * grid-strided) how the in-place kernel deals its vectors; "nvls_min_bytes",
  * "symm_min_bytes", "nvls_bcast_min_bytes", "bcast_scatter_min_bytes" and
- * "allgather_pull_min_bytes" move the size thresholds of the corresponding
- * variants.  Every rank must set the same values.  An unknown name or a
+ * "allgather_pull_min_bytes", "nvls_allgather_min_bytes" move the size
+ * thresholds of the corresponding variants; "gather_chunk_bytes",
+ * "gather_push_blocks", "gather_forward_blocks" and "gather_mode" (1 the root
+ * multicasts alone, 2 the root scatters and every rank multicasts its shard)
+ * shape the staged all-gather / broadcast.  Every rank must set the same values.  An unknown name or a
  * negative value returns DGN_ERR_ARG. */
 int dgn_comm_set_knob(dgn_comm_t comm, const char* name, int64_t value);
 

@@ -255,7 +255,11 @@ def test_allgather_bit_exact(teams, n):
             # variant 7: the staged gather (pushing and copying blocks around a ring) with remote stores
             (7, oracle.I64, 65536, {}), (7, oracle.BF16, 70001, {}), (7, oracle.U8, 13, {}),
             (7, oracle.F32, 50021, dict(blocks=2, threads=64, chunk_bytes=4096)),
-            (7, oracle.F32, (1 << 20) + 3, dict(blocks=3, threads=96, chunk_bytes=65536))):
+            (7, oracle.F32, (1 << 20) + 3, dict(blocks=3, threads=96, chunk_bytes=65536)),
+            # variant 8: staged too, but the ranks load the chunks from the sources' rings
+            (8, oracle.I64, 65536, {}), (8, oracle.U8, 13, {}),
+            (8, oracle.BF16, 70001, dict(blocks=2, threads=64, chunk_bytes=4096)),
+            (8, oracle.F32, (1 << 20) + 3, dict(blocks=3, threads=96, chunk_bytes=65536))):
         for c in comms:
             c.set_tuning(variant=variant, **shape)
         arrays = [H.make_input(r, count, dtype) for r in range(n)]
@@ -282,13 +286,18 @@ def test_broadcast_bit_exact(teams, n):
     # variant 1: peers pull from the root; variant 2: scatter + all-gather
     # (large messages); the third shape forces many rounds of the latter.
     # variant 7: the staged gather with the root as its only source.
+    # The last two: the root scatters shards to the ranks' inboxes and every rank pushes its own.
     shapes = [dict(variant=1), dict(variant=2), dict(variant=2, blocks=3, threads=64, chunk_bytes=512),
-              dict(variant=7), dict(variant=7, blocks=2, threads=64, chunk_bytes=4096)]
+              dict(variant=7), dict(variant=7, blocks=2, threads=64, chunk_bytes=4096),
+              dict(variant=7, gather_mode=2), dict(variant=7, blocks=2, threads=64, chunk_bytes=4096, gather_mode=2)]
     most_rounds = 0
     try:
         for shape in shapes:
+            shape = dict(shape)
+            mode = shape.pop("gather_mode", 1)
             for c in comms:
                 c.set_tuning(**shape)
+                c.set_knob("gather_mode", mode)
             for root in (0, n - 1):
                 for dtype, count in ((oracle.I64, 65536), (oracle.BF16, 100003), (oracle.U8, 1), (oracle.F32, 7)):
                     arrays = [H.make_input(r, count, dtype) for r in range(n)]
@@ -306,6 +315,7 @@ def test_broadcast_bit_exact(teams, n):
     finally:
         for c in comms:
             c.set_tuning()
+            c.set_knob("gather_mode", 0)
 
 
 @pytest.mark.parametrize("n", [2, 4, 8])
@@ -320,8 +330,11 @@ def test_staged_gather_launches_back_to_back(teams, n):
                 ("bcast", oracle.I64, 9000, 4096), ("gather", oracle.F16, 4099, 0), ("bcast", oracle.F32, 50021, 16384)]
         for rep in range(2):
             for i, (op, dtype, count, chunk) in enumerate(plan):
+                variant = 8 if op == "gather" and i == 4 else 7   # one all-gather pulls
                 for c in comms:
-                    c.set_tuning(variant=7, chunk_bytes=chunk, threads=128 if i % 2 else 64, blocks=1 + i % 3)
+                    c.set_tuning(variant=variant, chunk_bytes=chunk, threads=128 if i % 2 else 64, blocks=1 + i % 3)
+                    c.set_knob("gather_mode", 2 if i in (1, 5) else 1)   # two broadcasts scatter shards
+                    c.set_knob("gather_forward_blocks", 1 + rep)
                 arrays = [H.make_input(10 * i + r, count, dtype) for r in range(n)]
                 if op == "gather":
                     in_place = i == 2
@@ -350,10 +363,12 @@ def test_staged_gather_launches_back_to_back(teams, n):
                     for r in range(n):
                         H.assert_bits_equal(H.to_numpy(bufs[r], dtype), want[r], "staged broadcast {} rank {}".format(i, r))
                 assert all(c.status() == 0 for c in comms)
-                assert comms[0].last_launch()["variant"] == 7
+                assert comms[0].last_launch()["variant"] == variant
     finally:
         for c in comms:
             c.set_tuning()
+            c.set_knob("gather_mode", 0)
+            c.set_knob("gather_forward_blocks", 0)
 
 
 @pytest.mark.parametrize("n", [2, 4, 8])

@@ -303,7 +303,7 @@ def test_sharded_adamw_step_across_gpus(comms):
 
 @needs_two
 def test_multicast_broadcast_across_gpus(comms):
-    """BROADCAST through the switch (the root stores once, every rank receives):
+    """BROADCAST through the switch (the root alone, or every rank its shard):
     byte-exact for every root, ragged sizes, several rounds, back to back."""
     n = len(comms)
     if not comms[0].has_nvls():
@@ -314,7 +314,10 @@ def test_multicast_broadcast_across_gpus(comms):
             # The large case in 128 KiB pieces, so that it takes several rounds at any rank count.
             for c in comms:
                 c.set_tuning(variant=3, chunk_bytes=(128 << 10) if count > (4 << 20) else 0)
-            for root in sorted({0, n - 1}):
+            # mode 1: the root multicasts alone; mode 2: it scatters shards and every rank multicasts its own
+            for root, mode in ((0, 1), (n - 1, 2), (0, 2), (n - 1, 1)):
+                for c in comms:
+                    c.set_knob("gather_mode", mode)
                 arrays = [H.make_input(r, count, dtype, seed=500 + root) for r in range(n)]
                 if dtype == oracle.BF16:
                     arrays[root][:4] = [0x7FC1, 0xFFFF, 0x8000, 0x0001]  # NaN payloads, -0, a subnormal
@@ -333,6 +336,7 @@ def test_multicast_broadcast_across_gpus(comms):
     finally:
         for c in comms:
             c.set_tuning()
+            c.set_knob("gather_mode", 0)
 
 
 @needs_two
@@ -348,6 +352,7 @@ def test_multicast_allgather_across_gpus(comms):
                                                    (oracle.F32, (3 << 20) + 1, 256 << 10), (oracle.F16, 70001, 4096))):
             for c in comms:
                 c.set_tuning(variant=3, chunk_bytes=chunk, blocks=1 + i % 4)
+                c.set_knob("gather_mode", 2 if i % 2 else 1)  # the broadcasts in between: scattering / root alone
             arrays = [H.make_input(r, count, dtype, seed=700 + i) for r in range(n)]
             want = oracle.allgather(arrays, dtype)
             ins = [H.to_torch(a, dtype, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
@@ -368,9 +373,26 @@ def test_multicast_allgather_across_gpus(comms):
                 assert comms[r].status() == 0
                 H.assert_bits_equal(H.to_numpy(outs[r], dtype), want, "multicast all-gather case {} rank {}".format(i, r))
                 H.assert_bits_equal(H.to_numpy(bs[r], dtype), arrays[i % n], "broadcast between gathers, rank {}".format(r))
+        # All-gather where every rank loads from the sources' rings (no switch involved).
+        for c in comms:
+            c.set_tuning(variant=8, chunk_bytes=64 << 10)
+        arrays = [H.make_input(r, (1 << 20) + 7, oracle.BF16, seed=900) for r in range(n)]
+        ins = [H.to_torch(a, oracle.BF16, "cuda:{}".format(r)) for r, a in enumerate(arrays)]
+        outs = [torch.empty(n * ins[r].numel(), dtype=ins[r].dtype, device="cuda:{}".format(r)) for r in range(n)]
+        for rep in range(2):
+            for r in range(n):
+                with torch.cuda.device(r):
+                    comms[r].all_gather(ins[r], outs[r])
+        sync_all(n)
+        assert comms[0].last_launch()["variant"] == 8 and comms[0].last_launch()["rounds"] > 8
+        want = oracle.allgather(arrays, oracle.BF16)
+        for r in range(n):
+            assert comms[r].status() == 0
+            H.assert_bits_equal(H.to_numpy(outs[r], oracle.BF16), want, "pulling staged all-gather rank {}".format(r))
     finally:
         for c in comms:
             c.set_tuning()
+            c.set_knob("gather_mode", 0)
 
 
 @needs_two

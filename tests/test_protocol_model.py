@@ -274,29 +274,48 @@ def zero_update(rk, c, rounds, check=True, overflow=False):
 def gather_roles(me, n, launches, depth):
     """gather_flow_kernel (staged all-gather and broadcast): the pushing blocks and
     the copying blocks of one rank as two processes.  `launches` lists (chunks,
-    root) of consecutive launches, root < 0 meaning that every rank is a source.
-    One "pushed" and one "freed" word per rank, raised to base + chunk + 1; a
-    source writes chunk k into slot k % D of EVERY rank's ring (its own
-    included) once every rank has freed chunk k - D -- or, for the first D
-    chunks, everything the launches before have pushed.  Every rank is modelled
-    as reading every region (the kernel skips the copy of a block that is in
-    place already, which only removes reads)."""
+    root, mode) of consecutive launches; root < 0: all-gather, every rank is a
+    source; mode "scatter": broadcast whose root forwards shard j of every chunk
+    to rank j's inbox, every rank then pushing its shard; mode "pull": all-gather
+    whose sources store into their own ring only, the copying blocks loading
+    from the sources' rings.  One "pushed" and one "freed" word per rank, raised
+    to base + chunk + 1; a source writes chunk k into slot k % D of the rings
+    once every rank has freed chunk k - D -- or, for the first D chunks,
+    everything the launches before have pushed; a forwarding rank waits for the
+    root's "pushed" instead.  Every rank is modelled as reading every region
+    (the kernel skips the copy of a block that is in place already, which only
+    removes reads)."""
     push, out = Rank(me, n, 0), Rank(me, n, 1)
     roles = [push, out]
     everyone = list(range(n))
     base = 0
-    for c, (K, root) in enumerate(launches):
+    for c, (K, root, mode) in enumerate(launches):
         D = min(depth, K)
-        sources = everyone if root < 0 else [root]
+        scatter, pull = mode == "scatter", mode == "pull"
+        sources = everyone if root < 0 or scatter else [root]
         if me in sources:
-            region = me if root < 0 else 0
+            region = me if len(sources) == n else 0
             for k in range(K):
-                push.wait("freed", everyone, base + max(0, k - D + 1))
-                push.data(*[("write", t, ("gring", k % D, region), (c, k, me)) for t in everyone])
+                s = k % D
+                if scatter and me != root:
+                    push.wait("pushed", [root], base + k + 1)
+                    push.data(("read", ("inbox", s), (c, k, "shard", me)))
+                else:
+                    push.wait("freed", everyone, base + max(0, k - D + 1))
+                    if scatter:
+                        push.data(*[("write", t, ("inbox", s), (c, k, "shard", t)) for t in everyone if t != root])
+                targets = [me] if pull else everyone
+                push.data(*[("write", t, ("gring", s, region), (c, k, me)) for t in targets])
                 push.signal("pushed", everyone, base + k + 1)
         for k in range(K):
             out.wait("pushed", sources, base + k + 1)
-            out.data(*[("read", ("gring", k % D, j if root < 0 else 0), (c, k, j)) for j in sources])
+            if pull:
+                # every rank loads the source's one copy; the model marks a buffer as read
+                # by its owner only, so the owner reads and the others peek
+                out.data(*[("read" if j == me else "peek",) + ((("gring", k % D, j), (c, k, j)) if j == me else
+                                                              (j, ("gring", k % D, j), (c, k, j))) for j in sources])
+            else:
+                out.data(*[("read", ("gring", k % D, j if len(sources) == n else 0), (c, k, j)) for j in sources])
             out.signal("freed", everyone, base + k + 1)
         for rk in roles:  # kernel boundary
             rk.local_set(("gleft", c, rk.role), 1)
@@ -571,9 +590,11 @@ def test_sharded_step_between_other_collectives():
     assert run(2, build) > 0
 
 
-@pytest.mark.parametrize("n,launches,depth", [(2, ((5, -1), (1, 0), (3, 1)), 2), (2, ((4, 1), (4, -1)), 3),
-                                              (3, ((4, -1), (3, 2)), 2), (3, ((3, 0), (2, -1), (2, 1)), 2),
-                                              (4, ((3, 1), (2, -1)), 2)])
+@pytest.mark.parametrize("n,launches,depth", [
+    (2, ((5, -1, ""), (1, 0, ""), (3, 1, "")), 2), (2, ((4, 1, "scatter"), (4, -1, "")), 3),
+    (3, ((4, -1, ""), (3, 2, "scatter")), 2), (3, ((3, 0, "scatter"), (2, -1, ""), (2, 1, "")), 2),
+    (3, ((3, -1, "pull"), (3, 1, "scatter"), (2, -1, "pull")), 2), (4, ((3, 1, "scatter"), (2, -1, "")), 2),
+    (4, ((3, -1, "pull"),), 2)])
 def test_staged_gather_and_broadcast(n, launches, depth):
     """More chunks than ring slots; all-gathers and broadcasts from different roots back to back."""
     assert run_roles(n, lambda me, n_: gather_roles(me, n_, launches, depth)) > 0
@@ -632,8 +653,8 @@ def test_eight_ranks():
     assert run_roles(4, lambda me, n: flow_roles(me, n, (3,), 2, 1)) > 0
     assert run(8, lambda rk: [twoshot_allreduce(rk, c, 2) for c in range(2)]) > 0
     assert run(8, lambda rk: [(zero_reduce(rk, 2 * c, 3), zero_update(rk, 2 * c + 1, 3)) for c in range(2)]) > 0
-    assert run_roles(8, lambda me, n: gather_roles(me, n, ((3, 5),), 2)) > 0
-    assert run_roles(4, lambda me, n: gather_roles(me, n, ((2, -1),), 1)) > 0
+    assert run_roles(4, lambda me, n: gather_roles(me, n, ((2, 3, "scatter"),), 1)) > 0
+    assert run_roles(4, lambda me, n: gather_roles(me, n, ((2, -1, ""),), 1)) > 0
     assert run(8, lambda rk: broadcast_scatter(rk, 0, 3, root=5)) > 0
     assert run(5, lambda rk: allgather(rk, 0, 2)) > 0   # the pushing kernel branches more: five ranks
 
