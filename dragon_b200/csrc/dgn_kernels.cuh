@@ -2036,7 +2036,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gather_flow_kernel(const __gri
         const int j = nsrc == n ? (i + r) % n : root;  // ranks start at different sources
         const int region = nsrc == n ? j : 0;
         char* dst = root < 0 ? out + (long long)j * P.count : out;
-        if (j == r && dst == in) continue;  // the own block is in place already
+        if (root < 0 && j == r && dst == in) continue;  // all-gather in place: the own block is there already
         const bool dst_al = is_al16(dst);
         const long long pb = part_begin(c, region);
         const long long clen = clampll(P.nvec - pb, 0, CV);

@@ -310,7 +310,7 @@ def test_broadcast_bit_exact(teams, n):
                     want = oracle.broadcast(arrays, dtype, root)
                     for r in range(n):
                         H.assert_bits_equal(H.to_numpy(bufs[r], dtype), want[r],
-                                            "broadcast {} root {} rank {}".format(shape, root, r))
+                                            "broadcast {} mode {} root {} rank {}".format(shape, mode, root, r))
         assert most_rounds > 4
     finally:
         for c in comms:
