@@ -567,14 +567,25 @@ bool plan_gather(const dgn_comm* c, const OpDesc& d, int block_cap, int variant,
   if (total > c->geo.max_blocks) total = c->geo.max_blocks;
   if (block_cap > 0 && block_cap < total) total = block_cap;
   if (total < 2 || ring_bytes < 2ll * (nreg + 1) * 4096) return false;
-  // Bytes per chunk and source: an eighth of a block, 256 KiB to 4 MiB
-  // (all-gather); of the message: an eighth, 256 KiB to 8 MiB (broadcast).
+  // Chunk sizes from the sweeps at 8 ranks.  All-gather through the switch: half
+  // a block up to 2 MiB (78 us at 4 MiB blocks, 835 us at 64 MiB); pulling: a
+  // quarter up to 4 MiB.  Broadcast with the root alone: half the message up to
+  // 8 MiB (34 / 66 / 196 us at 4 / 16 / 64 MiB); scattered: an eighth, 1 to 8 MiB
+  // (181 us at 64 MiB with 8 MiB chunks, 212 us with 4 MiB, 192 us with 16 MiB).
   long long chunk = c->gather_chunk_bytes;
   if (c->tune_chunk >= 4096) chunk = c->tune_chunk;
   if (chunk <= 0) {
-    chunk = ceil_div(bytes, 8);
-    const long long hi = gather ? (4ll << 20) : (8ll << 20);
-    if (chunk < (256ll << 10)) chunk = 256ll << 10;
+    long long lo = 256ll << 10, hi = 8ll << 20;
+    if (gather) {
+      chunk = ceil_div(bytes, pull ? 4 : 2);
+      hi = pull ? (4ll << 20) : (2ll << 20);
+    } else if (scatter) {
+      chunk = ceil_div(bytes, 8);
+      lo = 1ll << 20;
+    } else {
+      chunk = ceil_div(bytes, 2);
+    }
+    if (chunk < lo) chunk = lo;
     if (chunk > hi) chunk = hi;
   }
   long long cv = ceil_div(chunk, 16 * (long long)(gather ? 1 : nsrc));  // per source
@@ -602,8 +613,10 @@ bool plan_gather(const dgn_comm* c, const OpDesc& d, int block_cap, int variant,
   if (p.threads < 64) p.threads = 64;  // a pushing block needs a data warp and its signal warp
   // Pushing blocks.  All-gather: a source sends S while (n - 1) S arrive, and
   // few pushing blocks congest the switch least (2 blocks: 835 us, 8 blocks: 930
-  // us at 8 ranks and 64 MiB).  Broadcast: the root feeds everybody.
-  int npush = c->gather_push_blocks > 0 ? c->gather_push_blocks : (gather ? 2 : 16);
+  // us at 8 ranks and 64 MiB); when pulling they only copy into the own ring (32
+  // blocks: 898 us, 8 blocks: 1128 us).  Broadcast: the root feeds everybody (16
+  // blocks alone, 32 when it scatters: 181 us against 197 / 214 us with 16 / 64).
+  int npush = c->gather_push_blocks > 0 ? c->gather_push_blocks : gather ? (pull ? 32 : 2) : (scatter ? 32 : 16);
   if (c->tune_blocks > 0) npush = c->tune_blocks;
   const long long per_push = (long long)(p.threads - 32) * 4;  // vectors one block pushes per pass
   const long long root_cv = scatter ? cv * nsrc : cv;
@@ -625,7 +638,7 @@ bool plan_gather(const dgn_comm* c, const OpDesc& d, int block_cap, int variant,
   p.blocks = most + (int)nout;
   p.cv = (int)cv;
   p.rounds = (int)K;
-  p.unroll = c->unroll > 0 ? (c->unroll > 8 ? 8 : c->unroll) : 4;
+  p.unroll = c->unroll > 0 ? (c->unroll > 8 ? 8 : c->unroll) : (gather ? 8 : 4);
   p.flow_nsw = npush;
   p.flow_nin = nfwd;
   p.flow_depth = (int)depth;
@@ -852,7 +865,7 @@ void load_thresholds(dgn_comm* c) {
   c->ll_max_bytes = env_ll("DGN_LL_MAX_BYTES", -1);
   c->ll2_max_bytes = env_ll("DGN_LL2_MAX_BYTES", -1);
   c->fused_twoshot = env_ll("DGN_TWOSHOT_FUSED", 0) != 0;
-  c->bcast_scatter_min_bytes = env_ll("DGN_BCAST_SCATTER_MIN_BYTES", 1ll << 20);
+  c->bcast_scatter_min_bytes = env_ll("DGN_BCAST_SCATTER_MIN_BYTES", nranks >= 5 ? (2ll << 20) : (1ll << 20));  // 8 ranks, 1 MiB: pulling 25 us, scatter 34 us
   // Every rank receives (n - 1) * 2 * S bytes of lines: 15.7 us against 26.2 us
   // for pulling at 2 ranks and 512 KiB blocks, but no gain at 8 ranks there.
   c->ll_allgather_max_bytes =
@@ -866,7 +879,7 @@ void load_thresholds(dgn_comm* c) {
   c->gather_push_blocks = (int)env_ll("DGN_GATHER_PUSH_BLOCKS", 0);
   c->gather_forward_blocks = (int)env_ll("DGN_GATHER_FORWARD_BLOCKS", 0);
   c->gather_mode = (int)env_ll("DGN_GATHER_MODE", 0);
-  c->bcast_shard_min_bytes = env_ll("DGN_BCAST_SHARD_MIN_BYTES", 2ll << 20);
+  c->bcast_shard_min_bytes = env_ll("DGN_BCAST_SHARD_MIN_BYTES", 32ll << 20);
   c->flow_chunk_bytes = env_ll("DGN_FLOW_CHUNK_BYTES", 0);
   c->flow_switch_blocks = (int)env_ll("DGN_FLOW_SWITCH_BLOCKS", 0);
   c->flow_in_blocks = (int)env_ll("DGN_FLOW_IN_BLOCKS", 0);
@@ -908,10 +921,11 @@ void load_nvls_settings(dgn_comm* c, long long symm_request) {
   // ranks (measured there: 401 GB/s against 577 GB/s for two-shot at 256 MiB).
   c->symm_min_bytes = env_ll("DGN_SYMM_MIN_BYTES", nranks <= 2 ? (1ll << 62) : (4ll << 20));
   // Through the switch the root sends S bytes whatever the rank count.  Measured
-  // at 8 ranks against pulling / scatter + all-gather: 20.6 against 22.1 us at
-  // 512 KiB, 29.5 against 37.9 us at 4 MiB, 188 against 197 us at 64 MiB; at 2
-  // ranks it loses from 64 MiB (148 against 121 us), so it is opt-in below 5 ranks.
-  c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", nranks >= 5 ? (256ll << 10) : (1ll << 62));
+  // at 8 ranks: peers pulling from the root is level up to 1 MiB (22 to 25 us) and
+  // falls behind above (56 us at 4 MiB against 34 us staged through the switch and
+  // 38 us for scatter + all-gather by remote stores; 66 / 73 us at 16 MiB; 181 /
+  // 201 us at 64 MiB).  At 2 ranks the switch loses, so it is opt-in below 5 ranks.
+  c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", nranks >= 5 ? (2ll << 20) : (1ll << 62));
   c->nvls_allgather_min_bytes = env_ll("DGN_NVLS_ALLGATHER_MIN_BYTES", 1ll << 62);
 }
 

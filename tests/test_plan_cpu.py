@@ -30,7 +30,10 @@ def clean_env(monkeypatch):
     for name in ("DGN_FORCE_VARIANT", "DGN_LL_MAX_BYTES", "DGN_LL2_MAX_BYTES", "DGN_ONESHOT_MAX_BYTES",
                  "DGN_NVLS_MIN_BYTES", "DGN_SYMM_MIN_BYTES", "DGN_NVLS_BCAST_MIN_BYTES", "DGN_FLOW_CHUNK_BYTES", "DGN_ALLGATHER_PULL_MIN_BYTES",
                  "DGN_FLOW_SWITCH_BLOCKS", "DGN_FLOW_DEPTH", "DGN_NVLS_RING_BYTES", "DGN_RING_BYTES",
-                 "DGN_MAX_BLOCKS", "DGN_SLOT_BYTES", "DGN_LL_ALLGATHER_MAX_BYTES", "DGN_BCAST_SCATTER_MIN_BYTES"):
+                 "DGN_MAX_BLOCKS", "DGN_SLOT_BYTES", "DGN_LL_ALLGATHER_MAX_BYTES", "DGN_BCAST_SCATTER_MIN_BYTES",
+                 "DGN_NVLS_ALLGATHER_MIN_BYTES", "DGN_ALLGATHER_RING_MIN_BYTES", "DGN_GATHER_CHUNK_BYTES",
+                 "DGN_GATHER_PUSH_BLOCKS", "DGN_GATHER_FORWARD_BLOCKS", "DGN_GATHER_MODE", "DGN_BCAST_SHARD_MIN_BYTES",
+                 "DGN_NVLS_GATHER_RING_BYTES"):
         monkeypatch.delenv(name, raising=False)
 
 
@@ -93,7 +96,7 @@ def test_symmetric_memory_and_opt_in_variants(dgn_lib, monkeypatch):
     assert plan(dgn_lib, 8, AR, 64 * MiB, symm=arena, in_symm=True, nvls=False)["variant"] == _C.VARIANT_TWOSHOT
     shape = plan(dgn_lib, 8, AR, 256 * MiB, symm=arena, in_symm=True)
     assert shape["blocks"] <= 16 and shape["threads"] == 256 and shape["rounds"] == 1
-    # The broadcast through the switch: from 256 KiB at 5 ranks and more, opt-in
+    # The broadcast through the switch: from 2 MiB at 5 ranks and more, opt-in
     # below; chunk size and block split of the staged ring can be set.
     assert plan(dgn_lib, 8, BC, 64 * MiB)["variant"] == _C.VARIANT_NVLS
     assert plan(dgn_lib, 8, BC, 64 * MiB, nvls=False)["variant"] == _C.VARIANT_TWOSHOT
@@ -113,8 +116,15 @@ def test_allgather_and_broadcast_variants(dgn_lib):
         assert plan(dgn_lib, n, AG, limit * 2)["variant"] == _C.VARIANT_TWOSHOT
     assert plan(dgn_lib, 2, BC, 64 * MiB)["variant"] == _C.VARIANT_ONESHOT      # two ranks: peers pull
     assert plan(dgn_lib, 8, BC, 128 * KiB)["variant"] == _C.VARIANT_ONESHOT
-    assert plan(dgn_lib, 8, BC, 512 * KiB)["variant"] == _C.VARIANT_NVLS        # one multicast store
-    assert plan(dgn_lib, 8, BC, 1 * MiB, nvls=False)["variant"] == _C.VARIANT_TWOSHOT   # scatter + all-gather
+    assert plan(dgn_lib, 8, BC, 1 * MiB)["variant"] == _C.VARIANT_ONESHOT
+    assert plan(dgn_lib, 8, BC, 2 * MiB)["variant"] == _C.VARIANT_NVLS          # staged through the switch
+    root_alone, shards = plan(dgn_lib, 8, BC, 16 * MiB), plan(dgn_lib, 8, BC, 64 * MiB)
+    assert root_alone["rounds"] == 2 and root_alone["chunk_bytes"] == 8 * MiB   # the root multicasts halves
+    assert shards["rounds"] == 8 and shards["chunk_bytes"] == 1 * MiB           # 8 MiB chunks, a shard per rank
+    assert plan(dgn_lib, 8, BC, 2 * MiB, nvls=False)["variant"] == _C.VARIANT_TWOSHOT   # scatter + all-gather
+    assert plan(dgn_lib, 8, AG, 4 * MiB)["variant"] == _C.VARIANT_TWOSHOT       # push
+    assert plan(dgn_lib, 8, AG, 16 * MiB)["variant"] == _C.VARIANT_ONESHOT      # pull
+    assert plan(dgn_lib, 4, AG, 64 * MiB)["variant"] == _C.VARIANT_TWOSHOT
     assert plan(dgn_lib, 4, BC, 1 * MiB)["variant"] == _C.VARIANT_TWOSHOT
     assert plan(dgn_lib, 4, RS, 16 * MiB)["variant"] == _C.VARIANT_TWOSHOT
 
