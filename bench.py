@@ -378,7 +378,7 @@ EMULATED_CASES = {
     "allgather_pull_8MiB": ("allgather", 1, 8 << 20, {}),
     "allgather_staged_loads_8MiB": ("allgather", 8, 8 << 20, {}),
     "allgather_staged_stores_8MiB": ("allgather", 7, 8 << 20, {}),
-    "broadcast_staged_shards_16MiB": ("broadcast", 7, 16 << 20, {}),
+    "broadcast_staged_16MiB": ("broadcast", 7, 16 << 20, {}),
     "broadcast_pull_512KiB": ("broadcast", 1, 512 << 10, {}),
     "broadcast_scatter_64MiB": ("broadcast", 2, 64 << 20, {}),
     "reducescatter_8MiB": ("reducescatter", 2, 8 << 20, {}),
