@@ -1,6 +1,6 @@
 """Which kernel serves which message: the thresholds of the planner, queried
 without a GPU (dgn_plan_query).  The expectations are the measured crossovers
-the library documents: low-latency one-shot up to 1 MiB / 512 KiB / 128 KiB at
+the library documents: low-latency one-shot up to 2 MiB / 512 KiB / 128 KiB at
 2 / 4 / 8 ranks, low-latency two-shot up to 2 MiB from 3 ranks, the store-only
 two-shot kernel above, the staged ring through NVSwitch multicast from 16 MiB at
 8 ranks, in place on symmetric memory from 4 MiB (never by default at 2 ranks)."""
@@ -39,7 +39,7 @@ def clean_env(monkeypatch):
 
 def test_allreduce_variant_by_size_and_rank_count(dgn_lib):
     expect = {
-        2: [(1 * KiB, _C.VARIANT_LL), (1 * MiB, _C.VARIANT_LL), (2 * MiB, _C.VARIANT_TWOSHOT),
+        2: [(1 * KiB, _C.VARIANT_LL), (1 * MiB, _C.VARIANT_LL), (2 * MiB, _C.VARIANT_LL), (3 * MiB, _C.VARIANT_TWOSHOT),
             (1024 * MiB, _C.VARIANT_TWOSHOT)],
         4: [(64 * KiB, _C.VARIANT_LL), (512 * KiB, _C.VARIANT_LL), (1 * MiB, _C.VARIANT_LL2),
             (2 * MiB, _C.VARIANT_LL2), (4 * MiB, _C.VARIANT_TWOSHOT), (1024 * MiB, _C.VARIANT_TWOSHOT)],
