@@ -557,7 +557,7 @@ bool plan_gather(const dgn_comm* c, const OpDesc& d, int block_cap, int variant,
   const long long bytes = d.nvec * 16;  // per block (all-gather) / of the message (broadcast)
   // Broadcast: from three ranks on the root scatters shards and every rank
   // multicasts its own (no rank has to feed the switch alone).
-  bool scatter = !gather && n >= 3 && bytes >= c->bcast_shard_min_bytes;
+  bool scatter = !gather && n >= 5 && bytes >= c->bcast_shard_min_bytes;  // 4 ranks: 303 us scattered, 181 us alone at 64 MiB
   if (c->gather_mode == 1) scatter = false;
   if (c->gather_mode == 2 && !gather && n >= 2) scatter = true;
   const int nsrc = (gather || scatter) ? n : 1;
@@ -804,6 +804,9 @@ Plan make_plan(const dgn_comm* c, const OpDesc& d, int block_cap) {
     if (c->nvls && !c->team) {
       const long long thr = d.kind == kOpAllGather ? c->nvls_allgather_min_bytes : c->nvls_bcast_min_bytes;
       bool nvls = d.nvec * 16 >= thr && c->tune_variant == DGN_VARIANT_AUTO;
+      // Below 5 ranks the root alone through the switch wins only in the middle (4
+      // ranks: 31 / 53 us against 33 / 64 us at 4 / 16 MiB, 181 against 171 us at 64 MiB).
+      if (d.kind == kOpBroadcast && n < 5 && d.nvec * 16 >= c->bcast_shard_min_bytes) nvls = false;
       if (c->tune_variant == DGN_VARIANT_NVLS) nvls = true;
       if (nvls && plan_gather(c, d, block_cap, DGN_VARIANT_NVLS, &p)) return p;
     }
@@ -925,8 +928,9 @@ void load_nvls_settings(dgn_comm* c, long long symm_request) {
   // at 8 ranks: peers pulling from the root is level up to 1 MiB (22 to 25 us) and
   // falls behind above (56 us at 4 MiB against 34 us staged through the switch and
   // 38 us for scatter + all-gather by remote stores; 66 / 73 us at 16 MiB; 181 /
-  // 201 us at 64 MiB).  At 2 ranks the switch loses, so it is opt-in below 5 ranks.
-  c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", nranks >= 5 ? (2ll << 20) : (1ll << 62));
+  // 201 us at 64 MiB).  At 3 and 4 ranks it is used from 4 MiB to below 32 MiB; at 2
+  // ranks the switch loses (178 against 118 us at 64 MiB), so it is opt-in there.
+  c->nvls_bcast_min_bytes = env_ll("DGN_NVLS_BCAST_MIN_BYTES", nranks >= 5 ? (2ll << 20) : nranks >= 3 ? (4ll << 20) : (1ll << 62));
   c->nvls_allgather_min_bytes = env_ll("DGN_NVLS_ALLGATHER_MIN_BYTES", 1ll << 62);
 }
 

@@ -100,7 +100,11 @@ def test_symmetric_memory_and_opt_in_variants(dgn_lib, monkeypatch):
     # below; chunk size and block split of the staged ring can be set.
     assert plan(dgn_lib, 8, BC, 64 * MiB)["variant"] == _C.VARIANT_NVLS
     assert plan(dgn_lib, 8, BC, 64 * MiB, nvls=False)["variant"] == _C.VARIANT_TWOSHOT
-    assert plan(dgn_lib, 4, BC, 64 * MiB)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 4, BC, 64 * MiB)["variant"] == _C.VARIANT_TWOSHOT      # scatter + all-gather by stores
+    assert plan(dgn_lib, 4, BC, 16 * MiB)["variant"] == _C.VARIANT_NVLS         # 4 ranks: the middle sizes only
+    assert plan(dgn_lib, 4, BC, 16 * MiB)["rounds"] == 2
+    assert plan(dgn_lib, 4, BC, 2 * MiB)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 2, BC, 16 * MiB)["variant"] == _C.VARIANT_ONESHOT
     monkeypatch.setenv("DGN_NVLS_BCAST_MIN_BYTES", str(1 * MiB))
     monkeypatch.setenv("DGN_FLOW_CHUNK_BYTES", str(2 * MiB))
     monkeypatch.setenv("DGN_FLOW_SWITCH_BLOCKS", "32")
