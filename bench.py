@@ -60,7 +60,8 @@ def parse_args():
     ap.add_argument("--emulated-only", action="store_true",
                     help="N=1: run only multi-rank kernels on 8 virtual ranks of one GPU (profiling target)")
     ap.add_argument("--emulated-case", default="default",
-                    help="with --emulated-only: one of " + ", ".join(sorted(EMULATED_CASES)) + ", or 'default'")
+                    help="with --emulated-only: one of " + ", ".join(sorted(EMULATED_CASES)) +
+                    ", fused_adam_64MiB, zero_adamw_64MiB_fp16, 'all' or 'default'")
     args = ap.parse_args()
     if args.size_mib is None:
         multi = args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1
@@ -429,6 +430,19 @@ def bench_emulated(args):
             names = ["ll_oneshot_64KiB", "twoshot_64MiB", "ring_64MiB", "allgather_8MiB"]
         for name in names:
             out[name] = run_emulated_case(comms, name)
+        if args.emulated_case in ("all", "fused_adam_64MiB"):
+            # All-reduce fused with the Adam update: eight fp32 tensors of 2 Mi elements per rank (64 MiB of gradients).
+            from dragon_b200.fused_optim import FusedAdam
+            fopts = []
+            for r, c in enumerate(comms):
+                g = torch.Generator(device="cuda:0").manual_seed(2000 + r)
+                params = [torch.randn(2 << 20, generator=g, device="cuda:0") for _ in range(8)]
+                for p in params:
+                    p.grad = torch.randn(2 << 20, generator=g, device="cuda:0") * 1e-2
+                fopts.append(FusedAdam(params, lr=1e-4, comm=c))
+            _, total = time_steps(lambda: [o.step() for o in fopts], 10, 3)
+            out["fused_adam_64MiB"] = {"ms": total / 10, "bytes_per_rank": 64 << 20, "launch": comms[0].last_launch()}
+            del fopts
         if args.emulated_case in ("default", "all", "zero_adamw_64MiB_fp16"):
             # The sharded AdamW step: eight fp16 tensors of 4 Mi elements per rank (64 MiB), overflow check on.
             from dragon_b200.zero import ZeroAdamW
