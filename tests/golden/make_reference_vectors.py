@@ -1,7 +1,7 @@
 """Writes tests/golden/reference_vectors.npz: outputs of REFERENCE code.
 
-Run where the Dragon source tree is present (default /root/reference, or
-DRAGON_REFERENCE): `make -C oracle ref` compiles dragon/utils/conversions.h and
+Run where the Dragon source tree is present (its location: the environment
+variable DRAGON_REFERENCE, else the recipe's default): `make -C oracle ref` compiles dragon/utils/conversions.h and
 dragon/kernels/training/cpu/{adam,sgd}_kernel.cc where they lie, and this script
 runs them on seeded inputs.  The committed file lets a machine without the
 reference tree still check the oracle against the reference's own arithmetic
