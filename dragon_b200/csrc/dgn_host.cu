@@ -622,13 +622,13 @@ bool plan_gather(const dgn_comm* c, const OpDesc& d, int block_cap, int variant,
   const long long per_push = (long long)(p.threads - 32) * 4;  // vectors one block pushes per pass
   const long long root_cv = scatter ? cv * nsrc : cv;
   if (npush > ceil_div(root_cv, per_push)) npush = (int)ceil_div(root_cv, per_push);
-  if (npush > total - 1) npush = total - 1;
+  if (npush > total / 2) npush = total / 2;  // small grids (virtual ranks): leave half the blocks to the copies
   if (npush < 1) npush = 1;
   int nfwd = 0;
   if (scatter) {
     nfwd = c->gather_forward_blocks > 0 ? c->gather_forward_blocks : 2;
     if (nfwd > ceil_div(cv, per_push)) nfwd = (int)ceil_div(cv, per_push);
-    if (nfwd > total - 1) nfwd = total - 1;
+    if (nfwd > total / 2) nfwd = total / 2;
     if (nfwd < 1) nfwd = 1;
   }
   // Copying blocks: enough for the parts of a chunk, no more than the SMs left.
