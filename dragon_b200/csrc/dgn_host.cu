@@ -560,9 +560,10 @@ bool plan_gather(const dgn_comm* c, const OpDesc& d, int block_cap, int variant,
   bool scatter = !gather && n >= 5 && bytes >= c->bcast_shard_min_bytes;  // 4 ranks: 303 us scattered, 181 us alone at 64 MiB
   if (c->gather_mode == 1) scatter = false;
   if (c->gather_mode == 2 && !gather && n >= 2) scatter = true;
+  const long long half = (long long)c->geo.ring_bytes / 2;
+  if (scatter && half < 2 * 4096) scatter = false;  // no room for the inboxes: the root multicasts alone
   const int nsrc = (gather || scatter) ? n : 1;
   const int nreg = pull ? 1 : nsrc;
-  const long long half = (long long)c->geo.ring_bytes / 2;
   const long long ring_bytes = variant == DGN_VARIANT_NVLS ? (long long)c->gather_ring_bytes : half;
   int total = c->num_sms;
   if (total > c->geo.max_blocks) total = c->geo.max_blocks;

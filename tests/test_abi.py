@@ -48,6 +48,9 @@ def test_entry_points_without_a_device(dgn_lib):
     assert dgn_lib.dgn_allreduce(None, None, None, None, 0, 0, 0, None) == _C.ERR_ARG
     assert dgn_lib.dgn_comm_status(None) == _C.ERR_ARG
     assert dgn_lib.dgn_comm_rank(None) == -1 and dgn_lib.dgn_comm_size(None) == 0
+    assert dgn_lib.dgn_comm_set_knob(None, b"gather_mode", 1) == _C.ERR_ARG
+    assert dgn_lib.dgn_comm_set_tuning(None, 0, 0, 0, 0) == _C.ERR_ARG
+    assert dgn_lib.dgn_comm_has_nvls(None) == 0
 
 
 def test_missing_library_is_an_error(monkeypatch):

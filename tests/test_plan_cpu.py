@@ -133,6 +133,36 @@ def test_allgather_and_broadcast_variants(dgn_lib):
     assert plan(dgn_lib, 4, RS, 16 * MiB)["variant"] == _C.VARIANT_TWOSHOT
 
 
+def test_staged_gather_shapes_cover_the_message(dgn_lib, monkeypatch):
+    """All-gather and broadcast as staged kernels (through the switch, with remote
+    stores, pulling): the chunks cover every source's bytes, the grid fits the
+    device, and a ring that is too small makes the planner fall back."""
+    for forced, nvls in ((3, True), (7, False), (8, False)):
+        monkeypatch.setenv("DGN_FORCE_VARIANT", str(forced))
+        for n in (2, 3, 4, 8):
+            for nbytes in (16, 1 * KiB, 100 * KiB + 16, 4 * MiB, 64 * MiB + 48, 1024 * MiB):
+                ag = plan(dgn_lib, n, AG, nbytes, dtype=_C.U8, redop=_C.SUM, nvls=nvls)
+                assert ag["variant"] == forced and 2 <= ag["blocks"] <= 148, (forced, n, nbytes, ag)
+                assert ag["chunk_bytes"] * ag["rounds"] >= nbytes and ag["chunk_bytes"] <= 4 * MiB
+                bc = plan(dgn_lib, n, BC, nbytes, dtype=_C.U8, redop=_C.SUM, nvls=nvls)
+                if forced == 8:
+                    assert bc["variant"] in (_C.VARIANT_ONESHOT, _C.VARIANT_TWOSHOT)   # pulling is an all-gather mode
+                    continue
+                assert bc["variant"] == forced and 2 <= bc["blocks"] <= 148, (forced, n, nbytes, bc)
+                # chunk_bytes is per source: the root alone, or one shard per rank
+                sources = n if (n >= 5 and nbytes >= 32 * MiB) else 1
+                assert bc["chunk_bytes"] * sources * bc["rounds"] >= nbytes, (forced, n, nbytes, bc)
+    # Without the ring in the workspace the remote-store form is not offered.
+    monkeypatch.setenv("DGN_RING_BYTES", "0")
+    monkeypatch.setenv("DGN_FORCE_VARIANT", "7")
+    assert plan(dgn_lib, 8, AG, 4 * MiB, nvls=False)["variant"] == _C.VARIANT_TWOSHOT
+    assert plan(dgn_lib, 8, BC, 4 * MiB, nvls=False)["variant"] in (_C.VARIANT_ONESHOT, _C.VARIANT_TWOSHOT)
+    # ... and the broadcast through the switch goes back to the root alone (the inboxes of the scattered form lie there).
+    monkeypatch.delenv("DGN_FORCE_VARIANT")
+    alone = plan(dgn_lib, 8, BC, 64 * MiB)
+    assert alone["variant"] == _C.VARIANT_NVLS and alone["chunk_bytes"] == 8 * MiB and alone["rounds"] == 8
+
+
 def test_environment_overrides(dgn_lib, monkeypatch):
     monkeypatch.setenv("DGN_FORCE_VARIANT", "2")
     assert plan(dgn_lib, 8, AR, 1 * KiB)["variant"] == _C.VARIANT_TWOSHOT
