@@ -43,10 +43,12 @@ class _Stack(threading.local):
 
 
 class Backend(object):
-    """An enum-like class of available backends: MPI and NCCL.
-
-    The strings are kept for compatibility; on a CUDA tensor every backend
-    runs the same peer-memory kernels of this library."""
+    """Names of the collective backends a group can ask for (MPI, NCCL, CNCL,
+    or AUTO for "whichever is there").  `Backend(name)` returns the canonical
+    upper-case string, as `dragon.distributed.Backend` does
+    (dragon/python/core/distributed/backend.py); the strings are kept for
+    compatibility only: on a CUDA tensor every backend runs the same
+    peer-memory kernels of this library."""
 
     UNDEFINED = "UNDEFINED"
     AUTO = "AUTO"
@@ -54,70 +56,48 @@ class Backend(object):
     NCCL = "NCCL"
     CNCL = "CNCL"
 
+    # backends that exist only where their library is present: name -> probe
+    _NEEDS = {"NCCL": lambda: is_nccl_available(), "CNCL": lambda: is_cncl_available()}
+
     def __new__(cls, name):
         if not isinstance(name, str):
             raise ValueError("Backend name must be a string, but got: {}".format(name))
-        value = getattr(Backend, name.upper(), Backend.UNDEFINED)
-        if value == "AUTO":
-            if is_nccl_available():
-                return Backend.NCCL
-            elif is_cncl_available():
-                return Backend.CNCL
-            return Backend.MPI
-        elif value == "NCCL":
-            if not is_nccl_available():
-                raise ValueError("NCCL backend is not available.")
-        elif value == "CNCL":
-            if not is_cncl_available():
-                raise ValueError("CNCL backend is not available.")
-        elif value == Backend.UNDEFINED:
+        canonical = getattr(cls, name.upper(), cls.UNDEFINED)
+        if canonical == cls.UNDEFINED or canonical not in (cls.AUTO, cls.MPI, cls.NCCL, cls.CNCL):
             raise ValueError("Invalid backend: " + name)
-        return value
+        if canonical == cls.AUTO:
+            present = [b for b, probe in cls._NEEDS.items() if probe()]
+            return present[0] if present else cls.MPI
+        probe = cls._NEEDS.get(canonical)
+        if probe is not None and not probe():
+            raise ValueError("{} backend is not available.".format(canonical))
+        return canonical
 
 
 class ProcessGroup(object):
-    """A group that stores a set of ranks."""
+    """A set of ranks that run collectives together.  `arguments` is what the
+    collective operators receive (communicator, group handle, backend, ranks),
+    under the keys the reference's operators read."""
 
     def __init__(self, ranks, comm, handle, backend):
-        self._handle = handle
-        self._ranks, self._comm = ranks, comm
-        if backend is None:
-            self._backend = Backend("AUTO")
-        else:
-            self._backend = Backend(backend)
-        # Stored for executing the collective ops.
-        self._arguments = {
-            "comm": self._comm,
-            "group": self._handle,
-            "backend": self._backend,
-            "ranks": self._ranks,
-        }
+        self._ranks, self._comm, self._handle = ranks, comm, handle
+        self._backend = Backend("AUTO" if backend is None else backend)
+        self._arguments = dict(comm=comm, group=handle, backend=self._backend, ranks=ranks)
 
-    @property
-    def arguments(self):
-        """Return the arguments of this group."""
-        return self._arguments
-
-    @property
-    def backend(self):
-        """Return the backend of this group."""
-        return self._backend
-
-    @property
-    def ranks(self):
-        """Return the ranks of this group."""
-        return self._ranks
+    arguments = property(lambda self: self._arguments, doc="Operator arguments of this group.")
+    backend = property(lambda self: self._backend, doc="Backend of this group.")
+    ranks = property(lambda self: self._ranks, doc="Ranks of this group (None: not a member).")
 
     @property
     def size(self):
-        """Return the size of this group."""
-        return len(self._ranks) if self._ranks is not None else 0
+        """Number of ranks; 0 for a group this process is not part of."""
+        return 0 if self._ranks is None else len(self._ranks)
 
     def as_default(self):
-        """Switch ``self`` as the default process group (use with ``with``)."""
-        if self._ranks is None:
-            return _GLOBAL_PROCESS_GROUP_STACK.get_controller(None)
-        return _GLOBAL_PROCESS_GROUP_STACK.get_controller(self)
+        """Context manager that makes this group the default one (a group this
+        process is not part of clears the default instead)."""
+        target = None if self._ranks is None else self
+        return _GLOBAL_PROCESS_GROUP_STACK.get_controller(target)
 
     def __repr__(self):
         return "{}:{}".format(self._backend, self._handle)
