@@ -83,6 +83,17 @@ class UpdateArgs(ctypes.Structure):
 
 UPDATE_MOMENTUM_SGD, UPDATE_NESTEROV_SGD, UPDATE_ADAM, UPDATE_ADAMW = range(4)
 
+
+class StagedPlan(ctypes.Structure):
+    """dgn_staged_plan of include/dgn.h."""
+    _fields_ = [("variant", ctypes.c_int), ("blocks", ctypes.c_int), ("threads", ctypes.c_int), ("chunks", ctypes.c_int),
+                ("chunk_vectors", ctypes.c_int64), ("staged", ctypes.c_int), ("depth", ctypes.c_int),
+                ("first_role_blocks", ctypes.c_int), ("second_role_blocks", ctypes.c_int), ("mode", ctypes.c_int),
+                ("ring_bytes_needed", ctypes.c_int64), ("ring_bytes_available", ctypes.c_int64),
+                ("inbox_bytes_needed", ctypes.c_int64), ("inbox_bytes_available", ctypes.c_int64),
+                ("inbox_offset_in_half", ctypes.c_int64)]
+
+
 SIGNATURES.update({
     "dgn_allreduce_update": (ctypes.c_int, [ctypes.c_void_p, _c_void_pp, _c_void_pp, _c_void_pp, _c_void_pp, _c_i64_p,
                                             ctypes.c_int, ctypes.c_int, ctypes.POINTER(UpdateArgs), ctypes.c_void_p]),
@@ -93,6 +104,8 @@ SIGNATURES.update({
     "dgn_plan_query": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int,
                                       ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int,
                                       _c_int_p, _c_int_p, _c_int_p, _c_i64_p, _c_int_p]),
+    "dgn_plan_query_staged": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64,
+                                             ctypes.POINTER(StagedPlan)]),
     "dgn_zero_shard_count": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64]),
     "dgn_zero_state_count": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int]),
     "dgn_zero_state_offset": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int]),

@@ -2261,6 +2261,64 @@ int dgn_plan_query(int nranks, int num_sms, int has_nvls, int64_t symm_bytes, in
   return DGN_OK;
 }
 
+int dgn_plan_query_staged(int nranks, int num_sms, int has_nvls, int op, int64_t bytes, dgn_staged_plan* out) {
+  if (!out) return fail(DGN_ERR_ARG, "null argument");
+  if (nranks < 2 || nranks > DGN_MAX_RANKS) return fail(DGN_ERR_ARG, "nranks %d outside 2..%d", nranks, DGN_MAX_RANKS);
+  if (bytes <= 0 || num_sms < 1 || (op != kOpAllReduce && op != kOpAllGather && op != kOpBroadcast))
+    return fail(DGN_ERR_ARG, "bad plan query");
+  dgn_comm q;
+  q.nranks = nranks;
+  q.num_sms = num_sms;
+  load_thresholds(&q);
+  if (has_nvls) {
+    load_nvls_settings(&q, 0);
+    q.nvls = reinterpret_cast<NvlsBuffer*>(&q);  // only its presence is looked at
+  }
+  q.plan_query = true;
+  OpDesc d;
+  d.kind = op;
+  d.dtype = op == kOpAllReduce ? (int)DGN_F32 : (int)DGN_U8;
+  d.redop = DGN_SUM;
+  d.ntensors = 1;
+  d.count = op == kOpAllReduce ? bytes / 4 : bytes;
+  d.nvec = ceil_div(bytes, 16);
+  d.in = d.out = reinterpret_cast<void*>(16);
+  const Plan p = make_plan(&q, d, 0);
+  q.nvls = nullptr;
+  memset(out, 0, sizeof(*out));
+  out->variant = p.variant;
+  out->blocks = p.blocks;
+  out->threads = p.threads;
+  out->chunks = p.rounds;
+  out->chunk_vectors = p.cv;
+  const bool staged = p.variant == DGN_VARIANT_NVLS || p.variant == DGN_VARIANT_RING || p.variant == DGN_VARIANT_RING_PULL;
+  if (!staged) return DGN_OK;
+  out->staged = 1;
+  out->depth = p.flow_depth;
+  out->first_role_blocks = p.flow_nsw;
+  out->second_role_blocks = p.flow_nin;
+  const long long half = (long long)q.geo.ring_bytes / 2;
+  const bool through_switch = p.variant == DGN_VARIANT_NVLS;
+  if (op == kOpAllReduce) {
+    out->ring_bytes_needed = (int64_t)p.flow_depth * p.cv * 16;
+    out->ring_bytes_available = through_switch ? (int64_t)q.flow_ring_bytes : half;
+  } else {
+    const bool scatter = (p.flow_mode & kGatherScatter) != 0, pull = (p.flow_mode & kGatherPull) != 0;
+    const int regions = pull ? 1 : (op == kOpAllGather || scatter) ? nranks : 1;
+    out->mode = p.flow_mode;
+    out->ring_bytes_needed = (int64_t)p.flow_depth * regions * p.cv * 16;
+    out->ring_bytes_available = through_switch ? (int64_t)q.gather_ring_bytes : half;
+    if (scatter) {
+      out->inbox_bytes_needed = (int64_t)p.flow_depth * p.cv * 16;
+      // Through the switch the inboxes have the gather half of the workspace ring to
+      // themselves; otherwise they lie behind the ring inside that half.
+      out->inbox_offset_in_half = p.inbox_off - ((int64_t)q.geo.ring_off + half);
+      out->inbox_bytes_available = half - out->inbox_offset_in_half;
+    }
+  }
+  return DGN_OK;
+}
+
 int64_t dgn_launch_count(void) { return g_launches.load(); }
 
 int dgn_comm_last_launch(dgn_comm_t c, int* variant, int* blocks, int* threads, int64_t* chunk_bytes,

@@ -367,6 +367,27 @@ int dgn_plan_query(int nranks, int num_sms, int has_nvls, int64_t symm_bytes, in
                    int dtype, int redop, int64_t count, int ntensors, int* variant, int* blocks,
                    int* threads, int64_t* chunk_bytes, int* rounds);
 
+/* The same for the staged kernels (ar_flow_kernel, gather_flow_kernel), with
+ * what the plan needs of the rings: op 0 ALLREDUCE (fp32 SUM), 2 ALLGATHER
+ * (bytes per rank), 3 BROADCAST, one tensor of `bytes`.  `staged` is 0 when
+ * another kernel serves the message (the other fields past chunk_vectors are
+ * zero then).  A plan is memory-safe when ring_bytes_needed <=
+ * ring_bytes_available, inbox_bytes_needed <= inbox_bytes_available, and at
+ * least one block is left for every other role.  Touches no device. */
+typedef struct dgn_staged_plan {
+  int variant, blocks, threads, chunks;
+  int64_t chunk_vectors;          /* 16-byte vectors per chunk (all-reduce) or per chunk and source */
+  int staged;
+  int depth;                      /* ring slots in use */
+  int first_role_blocks;          /* reducing blocks (all-reduce), pushing blocks of a source (gather) */
+  int second_role_blocks;         /* copy-in blocks (all-reduce), forwarding blocks (scattered broadcast) */
+  int mode;                       /* gather: 1 scattered shards, 2 pulling */
+  int64_t ring_bytes_needed, ring_bytes_available;
+  int64_t inbox_bytes_needed, inbox_bytes_available, inbox_offset_in_half;
+} dgn_staged_plan;
+int dgn_plan_query_staged(int nranks, int num_sms, int has_nvls, int op, int64_t bytes,
+                          dgn_staged_plan* out);
+
 /* Number of kernels this library has launched from the calling process. */
 int64_t dgn_launch_count(void);
 /* Variant / grid the last collective of `comm` used (any pointer may be NULL). */

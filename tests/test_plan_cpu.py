@@ -163,6 +163,61 @@ def test_staged_gather_shapes_cover_the_message(dgn_lib, monkeypatch):
     assert alone["variant"] == _C.VARIANT_NVLS and alone["chunk_bytes"] == 8 * MiB and alone["rounds"] == 8
 
 
+def staged(lib, n, op, nbytes, nvls=True, sms=148):
+    out = _C.StagedPlan()
+    assert lib.dgn_plan_query_staged(n, sms, int(nvls), op, nbytes, ctypes.byref(out)) == _C.OK, lib.dgn_last_error_string()
+    return out
+
+
+@pytest.mark.parametrize("ring_bytes", [None, 64 * MiB, 1 * MiB, 64 * KiB])
+def test_staged_plans_stay_inside_their_rings(dgn_lib, monkeypatch, ring_bytes):
+    """Memory safety of the staged kernels' plans, for every staged variant,
+    rank count, grid size and ring size: the ring slots in use fit the ring,
+    the inboxes of the scattered broadcast fit what is left for them, every
+    role keeps at least one block, the chunks cover the message."""
+    if ring_bytes is not None:
+        monkeypatch.setenv("DGN_RING_BYTES", str(ring_bytes))
+        monkeypatch.setenv("DGN_NVLS_RING_BYTES", str(4 * ring_bytes))
+        monkeypatch.setenv("DGN_NVLS_GATHER_RING_BYTES", str(2 * ring_bytes))
+    seen = set()
+    for forced, nvls in ((0, True), (3, True), (7, False), (8, False)):
+        monkeypatch.setenv("DGN_FORCE_VARIANT", str(forced))
+        for mode in (0, 1, 2):
+            monkeypatch.setenv("DGN_GATHER_MODE", str(mode))
+            for n in (2, 3, 4, 5, 8):
+                for sms in (148, 18, 4):
+                    for op in (AR, AG, BC):
+                        for nbytes in (16, 48, 4 * KiB, 100 * KiB + 16, 3 * MiB, 16 * MiB, 64 * MiB + 48, 1024 * MiB):
+                            p = staged(dgn_lib, n, op, nbytes, nvls=nvls, sms=sms)
+                            if not p.staged:
+                                continue
+                            what = (forced, mode, n, sms, op, nbytes, p.variant, p.mode, p.depth, p.chunk_vectors, p.chunks)
+                            seen.add((op, p.variant, p.mode))
+                            assert p.variant in (_C.VARIANT_NVLS, _C.VARIANT_RING, _C.VARIANT_RING_PULL), what
+                            assert 1 <= p.depth <= 8 and p.chunk_vectors >= 1 and p.chunks >= 1, what
+                            assert p.ring_bytes_needed <= p.ring_bytes_available, what
+                            assert p.inbox_bytes_needed <= p.inbox_bytes_available, what
+                            assert p.blocks <= min(sms, 160), what
+                            vectors = -(-nbytes // 16)
+                            if op == AR:
+                                assert p.chunk_vectors % n == 0, what                       # equal shards
+                                assert p.first_role_blocks >= 1 and p.second_role_blocks >= 1, what
+                                assert p.blocks - p.first_role_blocks - p.second_role_blocks >= 1, what
+                                assert p.chunk_vectors * p.chunks >= vectors, what
+                            else:
+                                sources = n if (op == AG or p.mode & 1) else 1
+                                assert p.first_role_blocks >= 1 and p.blocks - p.first_role_blocks >= 1, what
+                                if p.mode & 1:
+                                    assert p.second_role_blocks >= 1 and p.blocks - p.second_role_blocks >= 1, what
+                                    assert p.inbox_bytes_needed == p.depth * p.chunk_vectors * 16, what
+                                per_chunk = p.chunk_vectors * (1 if op == AG else sources)
+                                assert per_chunk * p.chunks >= vectors, what
+                                assert p.threads >= 64, what
+    if ring_bytes is None:
+        # every staged form was met: all-reduce ring (switch, peer), gather (switch, stores, loads), broadcast alone and scattered
+        assert {(AR, 3, 0), (AR, 7, 0), (AG, 3, 0), (AG, 7, 0), (AG, 8, 2), (BC, 3, 0), (BC, 3, 1), (BC, 7, 0), (BC, 7, 1)} <= seen, seen
+
+
 def test_environment_overrides(dgn_lib, monkeypatch):
     monkeypatch.setenv("DGN_FORCE_VARIANT", "2")
     assert plan(dgn_lib, 8, AR, 1 * KiB)["variant"] == _C.VARIANT_TWOSHOT
