@@ -820,8 +820,7 @@ def bench_multi(args):
         bad = sorted(k for k, v in parity.items() if not v["ok"])
         if bad:
             if rank == 0:
-                print(json.dumps({"metric": METRIC, "n_gpus": world, "parity_failed": bad,
-                                  "parity": parity}), flush=True)
+                emit_result({"metric": METRIC, "n_gpus": world, "parity_failed": bad, "parity": parity})
             barrier()
             torch.cuda.synchronize()
             if nccl is not None:
@@ -1277,8 +1276,32 @@ def bench_reference(args):
     }
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """Libraries write to file descriptor 1 on their own (NCCL prints its version
+    there when the comparison arm creates its communicator); the one JSON line
+    must be alone on standard output, so everything else goes to standard error."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit_result(obj):
+    data = (json.dumps(obj) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
     args = parse_args()
+    keep_stdout_for_the_result()
     if args.impl == "reference":
         line = bench_reference(args)
     elif args.emulated_only:
@@ -1288,7 +1311,7 @@ def main():
     else:
         line = bench_multi(args)
     if line is not None:
-        print(json.dumps(line), flush=True)
+        emit_result(line)
 
 
 if __name__ == "__main__":

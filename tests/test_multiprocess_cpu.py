@@ -45,10 +45,23 @@ def test_bench_reference_arm(gpus):
                           "--steps", "2", "--warmup", "1", "--size-mib", "4"],
                          stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=300, cwd=ROOT)
     assert out.returncode == 0, out.stderr[-2000:]
+    assert len(out.stdout.strip().splitlines()) == 1, out.stdout[-500:]   # the JSON line is alone on standard output
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["unit"] == "GB/s" and line["value"] > 0
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] == gpus
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["gpu_launches"] == 0
+
+
+def test_bench_keeps_library_chatter_off_standard_output():
+    """What a library writes to file descriptor 1 behind Python's back (NCCL prints
+    its version there) must not land beside the JSON line."""
+    code = ("import os, sys; sys.path.insert(0, {!r}); import bench; bench.keep_stdout_for_the_result(); "
+            "os.write(1, b'NCCL version x.y\\n'); print('python chatter'); bench.emit_result({{'value': 1}})").format(ROOT)
+    out = subprocess.run([sys.executable, "-c", code], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                         timeout=120, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout == '{"value": 1}\n', out.stdout
+    assert "NCCL version x.y" in out.stderr and "python chatter" in out.stderr
 
 
 def test_bench_reference_arm_other_ranks_do_nothing():
